@@ -1,0 +1,133 @@
+// Strict-f32 contraction on the CUDA cores: the GB_MATH_F32 path.  One kernel covers the dense matmul
+// family in every layout and the three convolution passes, because both operands are read through the
+// same (line, inner) element accessors the tensor-core kernel's gather warps use.  Every product is an
+// f32 FMA into an f32 accumulator, K ascending within a split -- the arithmetic of grad's `Gemm`
+// (src/gpu/device.zig:122-201) and `f32Compute` (:1665-1684).
+#include "gemm_sm100.cuh"
+#include "sm100_ptx.cuh"
+
+namespace gb {
+
+namespace {
+
+constexpr uint32_t kTM = 64, kTN = 64, kTK = 16;
+
+__device__ __forceinline__ int64_t f32_gather_index(const GatherDesc& d, const ConvGeo& g, uint32_t line, uint32_t inner) {
+  if (line >= d.lines_total || inner >= d.inner_total) return -1;
+  switch (d.source) {
+    case kSrcDense:
+      return (int64_t)line * d.ld + inner;
+    case kSrcPatch: {
+      const uint32_t tap = inner / g.c, ci = inner - tap * g.c;
+      const uint32_t ky = tap / g.k, kx = tap - ky * g.k;
+      const uint32_t per_image = g.out_h * g.out_w;
+      const uint32_t n = line / per_image, rem = line - n * per_image;
+      const uint32_t oy = rem / g.out_w, ox = rem - oy * g.out_w;
+      const uint32_t py = oy * g.stride + ky * g.dilation, px = ox * g.stride + kx * g.dilation;
+      if (py < g.pad || px < g.pad || py - g.pad >= g.h || px - g.pad >= g.w) return -1;
+      return ((int64_t)(n * g.h + py - g.pad) * g.w + px - g.pad) * g.c_step + ci;
+    }
+    case kSrcPatchT: {
+      const uint32_t tap = inner / g.c_out, co = inner - tap * g.c_out;
+      const uint32_t ky = tap / g.k, kx = tap - ky * g.k;
+      const uint32_t per_image = g.h * g.w;
+      const uint32_t n = line / per_image, rem = line - n * per_image;
+      const uint32_t y = rem / g.w, x = rem - y * g.w;
+      const int32_t ty = (int32_t)(y + g.pad) - (int32_t)(ky * g.dilation);
+      const int32_t tx = (int32_t)(x + g.pad) - (int32_t)(kx * g.dilation);
+      if (ty < 0 || tx < 0) return -1;
+      const uint32_t oy = (uint32_t)ty / g.stride, ox = (uint32_t)tx / g.stride;
+      if (oy * g.stride != (uint32_t)ty || ox * g.stride != (uint32_t)tx || oy >= g.out_h || ox >= g.out_w) return -1;
+      return ((int64_t)(n * g.out_h + oy) * g.out_w + ox) * g.c_out + co;
+    }
+    default: {
+      const uint32_t tap = inner / g.c_out, co = inner - tap * g.c_out;
+      return ((int64_t)tap * g.c + line) * g.c_out + co;
+    }
+  }
+}
+
+__device__ __forceinline__ float f32_operand(const GatherDesc& d, const ConvGeo& g, uint64_t batch_off, uint32_t mn, uint32_t kk) {
+  const int64_t idx = d.mn_major ? f32_gather_index(d, g, kk, mn) : f32_gather_index(d, g, mn, kk);
+  if (idx < 0) return 0.0f;
+  return d.src_is_bf16 ? bf16_to_f32(((const uint16_t*)d.base)[batch_off + idx]) : ((const float*)d.base)[batch_off + idx];
+}
+
+// grid: (tiles_n, tiles_m, batch * splits); 256 threads, each a 4 x 4 block of the 64 x 64 tile.
+__global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmParams p) {
+  __shared__ float As[kTK][kTM + 4];
+  __shared__ float Bs[kTK][kTN + 4];
+  const uint32_t tid = threadIdx.x;
+  const uint32_t split = blockIdx.z % p.splits, batch = blockIdx.z / p.splits;
+  const uint32_t m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
+  const uint32_t k_begin = split * p.k_blocks_per_split * kTK;
+  const uint32_t k_end = min(p.k, k_begin + p.k_blocks_per_split * kTK);
+  const uint64_t a_off = (uint64_t)batch * p.ga.batch_stride, b_off = (uint64_t)batch * p.gbsrc.batch_stride;
+  const uint32_t tr = tid / 16, tc = tid % 16;
+  float acc[4][4] = {};
+  for (uint32_t k0 = k_begin; k0 < k_end; k0 += kTK) {
+    // A tile: 64 rows x 16 k.  K-major sources are contiguous along k, MN-major ones along m.
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+      const uint32_t e = tid + i * 256;
+      uint32_t r, kk;
+      if (p.ga.mn_major) { r = e % kTM; kk = e / kTM; } else { kk = e % kTK; r = e / kTK; }
+      As[kk][r] = (k0 + kk < k_end) ? f32_operand(p.ga, p.geo, a_off, m0 + r, k0 + kk) : 0.0f;
+    }
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+      const uint32_t e = tid + i * 256;
+      uint32_t c, kk;
+      if (p.gbsrc.mn_major) { c = e % kTN; kk = e / kTN; } else { kk = e % kTK; c = e / kTK; }
+      Bs[kk][c] = (k0 + kk < k_end) ? f32_operand(p.gbsrc, p.geo, b_off, n0 + c, k0 + kk) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (uint32_t kk = 0; kk < kTK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (uint32_t i = 0; i < 4; ++i) a[i] = As[kk][tr * 4 + i];
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) b[j] = Bs[kk][tc * 4 + j];
+#pragma unroll
+      for (uint32_t i = 0; i < 4; ++i)
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (uint32_t i = 0; i < 4; ++i) {
+    const uint32_t row = m0 + tr * 4 + i;
+    if (row >= p.m) continue;
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) {
+      const uint32_t col = n0 + tc * 4 + j;
+      if (col >= p.n) continue;
+      float x = acc[i][j];
+      if (p.splits > 1) {
+        p.partial[(((uint64_t)split * p.batch + batch) * p.m + row) * p.n + col] = x;
+        continue;
+      }
+      const uint64_t idx = (uint64_t)batch * p.stride_c + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
+      if (p.accumulate) x += p.c_is_bf16 ? bf16_to_f32(((const uint16_t*)p.c)[idx]) : ((const float*)p.c)[idx];
+      if (p.bias) x += p.bias[col];
+      if (p.residual) x += p.c_is_bf16 ? bf16_to_f32(((const uint16_t*)p.residual)[idx]) : ((const float*)p.residual)[idx];
+      if (p.relu) x = fmaxf(x, 0.0f);
+      if (p.c_is_bf16) ((uint16_t*)p.c)[idx] = (uint16_t)bf16_bits(x);
+      else ((float*)p.c)[idx] = x;
+    }
+  }
+}
+
+}  // namespace
+
+// p.k_blocks_per_split counts blocks of 16 K values here; p.tiles_* are 64-wide.
+cudaError_t launch_gemm_f32(const GemmParams& p, cudaStream_t stream) {
+  if (p.m == 0 || p.n == 0 || p.batch == 0) return cudaSuccess;
+  const dim3 grid((p.n + kTN - 1) / kTN, (p.m + kTM - 1) / kTM, p.batch * p.splits);
+  gemm_f32_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace gb

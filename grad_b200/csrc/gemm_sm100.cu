@@ -1,0 +1,570 @@
+// The tcgen05 contraction kernel: one persistent, warp-specialised CTA per SM computes 128 x BN output
+// tiles of C = A * B with f32 accumulators in tensor memory.
+//
+//   warp 0      TMA producer: one elected thread streams 128-byte-swizzled operand tiles into a ring of
+//               shared-memory stages and signals each stage's "full" mbarrier with the byte count.
+//   warp 1      MMA issuer: owns the TMEM allocation; one thread issues four tcgen05.mma per stage
+//               (K = 16 bf16 or 8 tf32 each) and commits the stage's "empty" barrier; after the last
+//               K block of a tile it commits the accumulator's "full" barrier.
+//   warps 2-5   epilogue: each warp owns one 32-lane quarter of TMEM, reads the accumulator with
+//               tcgen05.ld, applies (+C) (+bias) (+residual) (ReLU), rounds to the output type and
+//               stores.  Two accumulator buffers let the epilogue of tile i overlap the mainloop of i+1.
+//   warps 6-9   (only when an operand cannot be fetched by TMA) gather warps fill the stage with plain
+//               loads: any pitch, f32 -> bf16 conversion on the fly, implicit im2col of NHWC activations
+//               for any stride / dilation / padding / channel count.
+//
+// The same kernel serves the dense matmul family (NN / NT / TN through K-major or MN-major shared-memory
+// descriptors, no packed or transposed copies) and the implicit-GEMM convolutions (forward, input
+// gradient, weight gradient) whose activation operand is fetched as 4-D TMA boxes of the NHWC tensor.
+// Replaces grad's `tileGemm` (src/gpu/device.zig:1162-1708) and `Gemm` (:122-201) tensor paths.
+#include "gemm_sm100.cuh"
+#include "sm100_ptx.cuh"
+
+namespace gb {
+
+namespace {
+
+constexpr uint32_t kBM = 128;            // tile rows = TMEM lanes
+constexpr uint32_t kLineBytes = 128;     // one swizzled line
+constexpr uint32_t kATileBytes = kBM * kLineBytes;
+constexpr uint32_t kMaxStages = 8;
+constexpr uint32_t kHeaderBytes = 1024;  // barriers + TMEM base + abort flag, ahead of the 1024-aligned tiles
+
+struct SmemHeader {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+struct Work {
+  uint32_t batch, m_tile, n_tile, split, kb_begin, kb_end;
+};
+
+__device__ __forceinline__ Work decode_work(const GemmParams& p, uint32_t w) {
+  Work out;
+  out.split = w % p.splits;
+  uint32_t t = w / p.splits;
+  const uint32_t per_batch = p.tiles_m * p.tiles_n;
+  out.batch = t / per_batch;
+  t -= out.batch * per_batch;
+  const uint32_t band_size = p.group_m * p.tiles_n;
+  const uint32_t band = t / band_size;
+  const uint32_t within = t - band * band_size;
+  const uint32_t rows_in_band = min(p.group_m, p.tiles_m - band * p.group_m);
+  out.m_tile = band * p.group_m + within % rows_in_band;
+  out.n_tile = within / rows_in_band;
+  out.kb_begin = out.split * p.k_blocks_per_split;
+  out.kb_end = min(out.kb_begin + p.k_blocks_per_split, p.k_blocks_total);
+  return out;
+}
+
+// ---- gather sources ---------------------------------------------------------------------------------
+// Element index (in elements from desc.base) of (line_major, inner), or -1 for an implicit zero.
+__device__ __forceinline__ int64_t gather_index(const GatherDesc& d, const ConvGeo& g, uint32_t line, uint32_t inner) {
+  if (line >= d.lines_total || inner >= d.inner_total) return -1;
+  switch (d.source) {
+    case kSrcDense:
+      return (int64_t)line * d.ld + inner;
+    case kSrcPatch: {   // src/gpu/math/conv.zig:47-65 `patchOf` + `patchSource`
+      const uint32_t tap = inner / g.c, ci = inner - tap * g.c;
+      const uint32_t ky = tap / g.k, kx = tap - ky * g.k;
+      const uint32_t per_image = g.out_h * g.out_w;
+      const uint32_t n = line / per_image, rem = line - n * per_image;
+      const uint32_t oy = rem / g.out_w, ox = rem - oy * g.out_w;
+      const uint32_t py = oy * g.stride + ky * g.dilation, px = ox * g.stride + kx * g.dilation;
+      if (py < g.pad || px < g.pad || py - g.pad >= g.h || px - g.pad >= g.w) return -1;
+      return ((int64_t)(n * g.h + py - g.pad) * g.w + px - g.pad) * g.c_step + ci;
+    }
+    case kSrcPatchT: {  // the adjoint gather: which dy element input pixel `line` sees through tap `inner / c_out`
+      const uint32_t tap = inner / g.c_out, co = inner - tap * g.c_out;
+      const uint32_t ky = tap / g.k, kx = tap - ky * g.k;
+      const uint32_t per_image = g.h * g.w;
+      const uint32_t n = line / per_image, rem = line - n * per_image;
+      const uint32_t y = rem / g.w, x = rem - y * g.w;
+      const int32_t ty = (int32_t)(y + g.pad) - (int32_t)(ky * g.dilation);
+      const int32_t tx = (int32_t)(x + g.pad) - (int32_t)(kx * g.dilation);
+      if (ty < 0 || tx < 0) return -1;
+      const uint32_t oy = (uint32_t)ty / g.stride, ox = (uint32_t)tx / g.stride;
+      if (oy * g.stride != (uint32_t)ty || ox * g.stride != (uint32_t)tx || oy >= g.out_h || ox >= g.out_w) return -1;
+      return ((int64_t)(n * g.out_h + oy) * g.out_w + ox) * g.c_out + co;
+    }
+    default: {          // kSrcWeightT: w[(tap, ci), co] read as [ci][(tap, co)]
+      const uint32_t tap = inner / g.c_out, co = inner - tap * g.c_out;
+      return ((int64_t)tap * g.c + line) * g.c_out + co;
+    }
+  }
+}
+
+__device__ __forceinline__ float load_as_f32(const GatherDesc& d, int64_t idx) {
+  if (idx < 0) return 0.0f;
+  return d.src_is_bf16 ? bf16_to_f32(((const uint16_t*)d.base)[idx]) : ((const float*)d.base)[idx];
+}
+
+// Fills one 128-byte line of an operand tile.  `l` is the line's index within the tile (its low three
+// bits select the swizzle), `line_major`/`inner0` locate it in the source.
+__device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDesc& d, uint8_t* tile, uint32_t l,
+                                            uint32_t line_major, uint32_t inner0, uint64_t batch_off) {
+  uint8_t* line = tile + l * kLineBytes;
+  const uint32_t epc = p.tf32 ? 4u : 8u;   // elements per 16-byte chunk
+  GatherDesc src = d;
+  src.base = (const uint8_t*)d.base + batch_off * (d.src_is_bf16 ? 2 : 4);
+#pragma unroll 1
+  for (uint32_t chunk = 0; chunk < 8; ++chunk) {
+    const uint32_t inner = inner0 + chunk * epc;
+    float v[8];
+    // Fast path: the chunk is one contiguous, fully valid, 16-byte-aligned run in the source.
+    const int64_t first = gather_index(src, p.geo, line_major, inner);
+    const int64_t last = gather_index(src, p.geo, line_major, inner + epc - 1);
+    bool vec = first >= 0 && last == first + (int64_t)epc - 1;
+    uint4 out;
+    if (vec && !p.tf32 && src.src_is_bf16) {
+      const uint16_t* ptr = (const uint16_t*)src.base + first;
+      if (((uintptr_t)ptr & 15) == 0) {
+        out = *(const uint4*)ptr;
+        *(uint4*)(line + ((chunk ^ (l & 7)) << 4)) = out;
+        continue;
+      }
+    } else if (vec && !src.src_is_bf16) {
+      const float* ptr = (const float*)src.base + first;
+      if (((uintptr_t)ptr & 15) == 0) {
+        const float4 lo = *(const float4*)ptr;
+        if (p.tf32) {
+          *(float4*)(line + ((chunk ^ (l & 7)) << 4)) = lo;
+          continue;
+        }
+        const float4 hi = *(const float4*)(ptr + 4);
+        out.x = pack_bf16x2(lo.x, lo.y);
+        out.y = pack_bf16x2(lo.z, lo.w);
+        out.z = pack_bf16x2(hi.x, hi.y);
+        out.w = pack_bf16x2(hi.z, hi.w);
+        *(uint4*)(line + ((chunk ^ (l & 7)) << 4)) = out;
+        continue;
+      }
+    }
+    for (uint32_t e = 0; e < epc; ++e) v[e] = load_as_f32(src, gather_index(src, p.geo, line_major, inner + e));
+    if (p.tf32) {
+      out.x = __float_as_uint(v[0]);
+      out.y = __float_as_uint(v[1]);
+      out.z = __float_as_uint(v[2]);
+      out.w = __float_as_uint(v[3]);
+    } else {
+      out.x = pack_bf16x2(v[0], v[1]);
+      out.y = pack_bf16x2(v[2], v[3]);
+      out.z = pack_bf16x2(v[4], v[5]);
+      out.w = pack_bf16x2(v[6], v[7]);
+    }
+    *(uint4*)(line + ((chunk ^ (l & 7)) << 4)) = out;
+  }
+}
+
+// Fills operand tile `tile` (lines_in_tile lines) for the K block starting at element k0.
+__device__ __forceinline__ void gather_tile(const GemmParams& p, const GatherDesc& d, uint8_t* tile, uint32_t lines_in_tile,
+                                            uint32_t mn0, uint32_t k0, uint32_t batch, uint32_t tid) {
+  const uint32_t epl = p.tf32 ? 32u : 64u;
+  const uint64_t batch_off = (uint64_t)batch * d.batch_stride;
+  for (uint32_t l = tid; l < lines_in_tile; l += 128) {
+    if (d.mn_major) {
+      const uint32_t block = l / epl, kline = l - block * epl;
+      gather_line(p, d, tile, l, k0 + kline, mn0 + block * epl, batch_off);
+    } else {
+      gather_line(p, d, tile, l, mn0 + l, k0, batch_off);
+    }
+  }
+}
+
+// ---- TMA issue ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void patch_coords(const GemmParams& p, uint32_t p0, uint32_t tap, int32_t& w0, int32_t& h0, int32_t& n0) {
+  // Grid the positions of this pass run over: the output grid (forward, weight gradient) or the input grid
+  // (input gradient, whose patches are taken from dy).
+  const uint32_t grid_h = p.dgrad ? p.geo.h : p.geo.out_h;
+  const uint32_t grid_w = p.dgrad ? p.geo.w : p.geo.out_w;
+  const uint32_t per_image = grid_h * grid_w;
+  const uint32_t ky = tap / p.geo.k, kx = tap - ky * p.geo.k;
+  n0 = (int32_t)(p0 / per_image);
+  const uint32_t row0 = p.box_n > 1 ? 0u : (p0 - (uint32_t)n0 * per_image) / grid_w;
+  if (p.dgrad) {
+    w0 = (int32_t)p.geo.pad - (int32_t)(kx * p.geo.dilation);
+    h0 = (int32_t)row0 + (int32_t)p.geo.pad - (int32_t)(ky * p.geo.dilation);
+  } else {
+    w0 = (int32_t)(kx * p.geo.dilation) - (int32_t)p.geo.pad;
+    h0 = (int32_t)row0 + (int32_t)(ky * p.geo.dilation) - (int32_t)p.geo.pad;
+  }
+}
+
+__device__ __forceinline__ void issue_a(const GemmParams& p, const CUtensorMap* tmap, uint8_t* tile, uint64_t* bar,
+                                        const Work& w, uint32_t kb) {
+  const uint32_t epl = p.tf32 ? 32u : 64u;
+  const uint32_t m0 = w.m_tile * kBM;
+  switch (p.a_kind) {
+    case kDenseK:
+      tma_load_3d(tile, tmap, bar, (int32_t)(kb * epl), (int32_t)m0, (int32_t)w.batch);
+      break;
+    case kDenseMN:
+      for (uint32_t j = 0; j < kBM / epl; ++j)
+        tma_load_3d(tile + j * epl * kLineBytes, tmap, bar, (int32_t)(m0 + j * epl), (int32_t)(kb * epl), (int32_t)w.batch);
+      break;
+    case kPatchK: {
+      // K runs over (tap, channel block); the box is 128 positions x 128 bytes of channels.
+      const uint32_t channels = p.dgrad ? p.geo.c_out : p.geo.c;
+      const uint32_t cblocks = channels / epl;
+      const uint32_t tap = kb / cblocks, cb = kb - tap * cblocks;
+      int32_t w0, h0, n0;
+      patch_coords(p, m0, tap, w0, h0, n0);
+      tma_load_4d(tile, tmap, bar, (int32_t)(cb * epl), w0, h0, n0);
+      break;
+    }
+    case kPatchMN: {
+      // Weight gradient: M runs over (tap, channel), K over positions; each box is `epl` positions deep.
+      const uint32_t taps = p.geo.k * p.geo.k;
+      for (uint32_t j = 0; j < kBM / epl; ++j) {
+        const uint32_t kk0 = m0 + j * epl;
+        const uint32_t tap = min(kk0 / p.geo.c, taps - 1);   // rows past the last tap are never stored
+        const uint32_t c0 = kk0 >= taps * p.geo.c ? 0u : kk0 - tap * p.geo.c;
+        int32_t w0, h0, n0;
+        patch_coords(p, kb * epl, tap, w0, h0, n0);
+        tma_load_4d(tile + j * epl * kLineBytes, tmap, bar, (int32_t)c0, w0, h0, n0);
+      }
+      break;
+    }
+    default:
+      break;
+  }
+}
+
+__device__ __forceinline__ void issue_b(const GemmParams& p, const CUtensorMap* tmap, uint8_t* tile, uint64_t* bar,
+                                        const Work& w, uint32_t kb) {
+  const uint32_t epl = p.tf32 ? 32u : 64u;
+  const uint32_t n0 = w.n_tile * p.bn;
+  switch (p.b_kind) {
+    case kDenseK:
+      tma_load_3d(tile, tmap, bar, (int32_t)(kb * epl), (int32_t)n0, (int32_t)w.batch);
+      break;
+    case kDenseMN:
+      for (uint32_t j = 0; j < p.bn / epl; ++j)
+        tma_load_3d(tile + j * epl * kLineBytes, tmap, bar, (int32_t)(n0 + j * epl), (int32_t)(kb * epl), (int32_t)w.batch);
+      break;
+    case kWeightK: {
+      const uint32_t cblocks = p.geo.c_out / epl;
+      const uint32_t tap = kb / cblocks, cb = kb - tap * cblocks;
+      tma_load_3d(tile, tmap, bar, (int32_t)(cb * epl), (int32_t)n0, (int32_t)tap);
+      break;
+    }
+    default:
+      break;
+  }
+}
+
+// ---- epilogue -----------------------------------------------------------------------------------------
+__device__ __forceinline__ float load_out(const void* base, uint32_t is_bf16, uint64_t idx) {
+  return is_bf16 ? bf16_to_f32(((const uint16_t*)base)[idx]) : ((const float*)base)[idx];
+}
+__device__ __forceinline__ void store_out(void* base, uint32_t is_bf16, uint64_t idx, float v) {
+  if (is_bf16) ((uint16_t*)base)[idx] = (uint16_t)bf16_bits(v);
+  else ((float*)base)[idx] = v;
+}
+
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&acc)[32], uint32_t batch, uint32_t split,
+                                               uint32_t row, uint32_t col0) {
+  if (row >= p.m || col0 >= p.n) return;
+  const uint32_t cols = min(32u, p.n - col0);
+  if (p.splits > 1) {
+    float* dst = p.partial + (((uint64_t)split * p.batch + batch) * p.m + row) * p.n + col0;
+    if (cols == 32 && (p.n & 3) == 0) {
+#pragma unroll
+      for (uint32_t i = 0; i < 32; i += 4) *(uint4*)(dst + i) = make_uint4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+    } else {
+      for (uint32_t i = 0; i < cols; ++i) dst[i] = __uint_as_float(acc[i]);
+    }
+    return;
+  }
+  const uint64_t cbase = (uint64_t)batch * p.stride_c;
+  float v[32];
+#pragma unroll
+  for (uint32_t i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
+  const bool vec = p.vec_store && !p.transpose_out && cols == 32;
+  if (vec) {
+    const uint64_t off = cbase + (uint64_t)row * p.ldc + col0;
+    if (p.accumulate) {
+      if (p.c_is_bf16) {
+#pragma unroll
+        for (uint32_t i = 0; i < 32; i += 8) {
+          const uint4 q = *(const uint4*)((const uint16_t*)p.c + off + i);
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            v[i + 2 * j] += __uint_as_float(w[j] << 16);
+            v[i + 2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+          }
+        }
+      } else {
+#pragma unroll
+        for (uint32_t i = 0; i < 32; i += 4) {
+          const float4 q = *(const float4*)((const float*)p.c + off + i);
+          v[i] += q.x; v[i + 1] += q.y; v[i + 2] += q.z; v[i + 3] += q.w;
+        }
+      }
+    }
+    if (p.bias) {
+#pragma unroll
+      for (uint32_t i = 0; i < 32; i += 4) {
+        const float4 q = *(const float4*)(p.bias + col0 + i);
+        v[i] += q.x; v[i + 1] += q.y; v[i + 2] += q.z; v[i + 3] += q.w;
+      }
+    }
+    if (p.residual) {
+      if (p.c_is_bf16) {
+#pragma unroll
+        for (uint32_t i = 0; i < 32; i += 8) {
+          const uint4 q = *(const uint4*)((const uint16_t*)p.residual + off + i);
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            v[i + 2 * j] += __uint_as_float(w[j] << 16);
+            v[i + 2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+          }
+        }
+      } else {
+#pragma unroll
+        for (uint32_t i = 0; i < 32; i += 4) {
+          const float4 q = *(const float4*)((const float*)p.residual + off + i);
+          v[i] += q.x; v[i + 1] += q.y; v[i + 2] += q.z; v[i + 3] += q.w;
+        }
+      }
+    }
+    if (p.relu) {
+#pragma unroll
+      for (uint32_t i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
+    }
+    if (p.c_is_bf16) {
+#pragma unroll
+      for (uint32_t i = 0; i < 32; i += 8)
+        *(uint4*)((uint16_t*)p.c + off + i) = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
+                                                         pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
+    } else {
+#pragma unroll
+      for (uint32_t i = 0; i < 32; i += 4) *(float4*)((float*)p.c + off + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    }
+    return;
+  }
+#pragma unroll
+  for (uint32_t i = 0; i < 32; ++i) {
+    if (i < cols) {
+      const uint32_t col = col0 + i;
+      const uint64_t idx = cbase + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
+      float x = v[i];
+      if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx);
+      if (p.bias) x += p.bias[col];
+      if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
+      if (p.relu) x = fmaxf(x, 0.0f);
+      store_out(p.c, p.c_is_bf16, idx, x);
+    }
+  }
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(320, 1)
+gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
+                  const __grid_constant__ CUtensorMap tmap_b) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  SmemHeader* hdr = (SmemHeader*)smem;
+  uint8_t* tiles = smem + kHeaderBytes;
+  const uint32_t b_tile_bytes = p.bn * kLineBytes;
+  const uint32_t stage_bytes = kATileBytes + b_tile_bytes;
+  volatile uint32_t* abort_flag = &hdr->abort_flag;
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool has_gather = blockDim.x > 192;
+  const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
+  const uint32_t tmem_cols = p.bn * 2 <= 32 ? 32u : (p.bn * 2 <= 64 ? 64u : (p.bn * 2 <= 128 ? 128u : (p.bn * 2 <= 256 ? 256u : 512u)));
+
+  if (threadIdx.x == 0) {
+    const uint32_t full_count = 1 + (has_gather ? 4 : 0);
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_init(&hdr->full[s], full_count);
+      mbar_init(&hdr->empty[s], 1);
+    }
+    for (uint32_t b = 0; b < 2; ++b) {
+      mbar_init(&hdr->acc_full[b], 1);
+      mbar_init(&hdr->acc_empty[b], 4);
+    }
+    hdr->abort_flag = 0;
+    fence_barrier_init();
+    if (p.a_kind != kGather) prefetch_tmap(&tmap_a);
+    if (p.b_kind != kGather) prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&hdr->tmem_base, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = hdr->tmem_base;
+  const uint32_t epl = p.tf32 ? 32u : 64u;
+
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      const uint32_t tx_bytes = (p.a_kind != kGather ? kATileBytes : 0u) + (p.b_kind != kGather ? b_tile_bytes : 0u);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const Work work = decode_work(p, w);
+        for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
+          if (!(ok = mbar_wait(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
+          uint8_t* a_tile = tiles + stage * stage_bytes;
+          mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
+          issue_a(p, &tmap_a, a_tile, &hdr->full[stage], work, kb);
+          issue_b(p, &tmap_b, a_tile + kATileBytes, &hdr->full[stage], work, kb);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer =====
+    if (lane == 0) {
+      const uint32_t idesc = make_instr_desc(p.tf32 ? 2u : 1u, p.a_mn_major, p.b_mn_major, kBM, p.bn);
+      // K-major: the four K slices of a stage sit 32 bytes apart inside each line.  MN-major: a slice
+      // is 16 (bf16) or 8 (tf32) whole lines, and 64-/32-wide MN blocks follow each other every epl lines.
+      const uint32_t slice_lines = p.tf32 ? 8u : 16u;
+      const uint32_t a_lbo = p.a_mn_major ? epl * kLineBytes : 16u, a_step = p.a_mn_major ? slice_lines * kLineBytes : 32u;
+      const uint32_t b_lbo = p.b_mn_major ? epl * kLineBytes : 16u, b_step = p.b_mn_major ? slice_lines * kLineBytes : 32u;
+      uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
+      bool ok = true;
+      for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+        const Work work = decode_work(p, w);
+        if (!(ok = mbar_wait(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + buf * p.bn;
+        for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
+          if (!(ok = mbar_wait(&hdr->full[stage], phase, abort_flag, kStatusMmaTimeout))) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(tiles + stage * stage_bytes);
+          const uint32_t b_addr = a_addr + kATileBytes;
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            const uint64_t da = make_smem_desc_sw128(a_addr + j * a_step, a_lbo, 1024);
+            const uint64_t db = make_smem_desc_sw128(b_addr + j * b_step, b_lbo, 1024);
+            const uint32_t acc = (kb > work.kb_begin || j > 0) ? 1u : 0u;
+            if (p.tf32) mma_tf32_ss(tmem_d, da, db, idesc, acc);
+            else mma_bf16_ss(tmem_d, da, db, idesc, acc);
+          }
+          mma_commit(&hdr->empty[stage]);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&hdr->acc_full[buf]);
+        if ((buf ^= 1) == 0) buf_phase ^= 1;
+      }
+    }
+  } else if (warp < 6) {
+    // ===== epilogue =====
+    const uint32_t quarter = warp & 3;
+    uint32_t buf = 0, buf_phase = 0;
+    bool ok = true;
+    for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      const Work work = decode_work(p, w);
+      ok = mbar_wait(&hdr->acc_full[buf], buf_phase, abort_flag, kStatusEpilogueTimeout);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t row = work.m_tile * kBM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
+      for (uint32_t c = 0; c < p.bn; c += 32) {
+        uint32_t acc[32];
+        tmem_ld_32x32(taddr + c, acc);
+        tmem_ld_wait();
+        epilogue_chunk(p, acc, work.batch, work.split, row, work.n_tile * p.bn + c);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hdr->acc_empty[buf]);
+      if ((buf ^= 1) == 0) buf_phase ^= 1;
+    }
+  } else {
+    // ===== gather warps =====
+    const uint32_t tid = threadIdx.x - 192;
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      const Work work = decode_work(p, w);
+      for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
+        ok = mbar_wait(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        uint8_t* a_tile = tiles + stage * stage_bytes;
+        if (p.a_kind == kGather) gather_tile(p, p.ga, a_tile, kBM, work.m_tile * kBM, kb * epl, work.batch, tid);
+        if (p.b_kind == kGather) gather_tile(p, p.gbsrc, a_tile + kATileBytes, p.bn, work.n_tile * p.bn, kb * epl, work.batch, tid);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&hdr->full[stage]);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  }
+
+  // ===== teardown =====
+  __syncwarp();
+  if (*abort_flag != 0) {
+    // A wait gave up: let copies and MMAs already in flight land before shared and tensor memory go away.
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (threadIdx.x == 0 && hdr->abort_flag != 0 && p.status != nullptr) atomicCAS(p.status, 0u, hdr->abort_flag);
+  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// Ordered combine of split-K partials followed by the epilogue; one thread per output element.
+// Takes the place of grad's `splitCombine` (src/gpu/device.zig:664-670), which only deterministic runs use.
+__global__ void splitk_reduce_kernel(const GemmParams p) {
+  const uint64_t per_batch = (uint64_t)p.m * p.n;
+  const uint64_t total = per_batch * p.batch;
+  for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t batch = (uint32_t)(t / per_batch);
+    const uint64_t r = t - (uint64_t)batch * per_batch;
+    const uint32_t row = (uint32_t)(r / p.n), col = (uint32_t)(r - (uint64_t)row * p.n);
+    float x = 0.0f;
+    for (uint32_t s = 0; s < p.splits; ++s) x += p.partial[(uint64_t)s * total + t];
+    const uint64_t idx = (uint64_t)batch * p.stride_c + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
+    if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx);
+    if (p.bias) x += p.bias[col];
+    if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
+    if (p.relu) x = fmaxf(x, 0.0f);
+    store_out(p.c, p.c_is_bf16, idx, x);
+  }
+}
+
+}  // namespace
+
+size_t gemm_smem_bytes(const GemmParams& p) {
+  return 1024 /* alignment slack */ + kHeaderBytes + (size_t)p.stages * (kATileBytes + (size_t)p.bn * kLineBytes);
+}
+
+cudaError_t gemm_sm100_configure() {
+  return cudaFuncSetAttribute(gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+}
+
+cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, int sm_count, cudaStream_t stream) {
+  const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
+  if (total_work == 0) return cudaSuccess;
+  const bool gather = p.a_kind == kGather || p.b_kind == kGather;
+  const uint32_t grid = total_work < (uint32_t)sm_count ? total_work : (uint32_t)sm_count;
+  gemm_sm100_kernel<<<grid, gather ? 320 : 192, gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream) {
+  const uint64_t total = (uint64_t)p.m * p.n * p.batch;
+  if (total == 0) return cudaSuccess;
+  const uint32_t blocks = (uint32_t)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace gb

@@ -1,0 +1,75 @@
+// Parameter block shared by the host dispatcher and the tcgen05 contraction kernel.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gb {
+
+// How one operand's tile reaches shared memory.
+enum OperandKind : uint32_t {
+  kDenseK = 0,      // TMA, K contiguous in memory: lines = MN index, 128 B of K per line
+  kDenseMN = 1,     // TMA, MN contiguous in memory: blocks of `epl` MN values, one line per K index
+  kPatchK = 2,      // TMA over NHWC activations, lines = output positions, 128 B of channels per line (conv A, K-major)
+  kPatchMN = 3,     // same boxes read as MN-major A: lines = positions (K), 128 B of (tap, channel) per line (wgrad)
+  kWeightK = 4,     // TMA over weights viewed (c_out, c_in, taps): lines = c_in (N), 128 B of c_out (K) (dgrad B)
+  kGather = 5,      // filled by the gather warps with plain loads (any stride, dtype or geometry)
+};
+
+// What the gather warps read when an operand is kGather.
+enum GatherSource : uint32_t {
+  kSrcDense = 0,    // element(line_major, inner) = base[line_major * ld + inner]
+  kSrcPatch = 1,    // lines = positions, inner = (tap, channel): the implicit im2col matrix of x
+  kSrcPatchT = 2,   // zero-insertion gather of dy for the input gradient of a strided convolution
+  kSrcWeightT = 3,  // lines = c_in, inner = (flipped tap, c_out): w read transposed for the input gradient
+};
+
+struct ConvGeo {
+  uint32_t n, h, w, c, k, stride, pad, dilation, out_h, out_w, c_out, c_step;
+};
+
+struct GatherDesc {
+  const void* base;
+  uint64_t batch_stride;   // elements
+  uint32_t source;         // GatherSource
+  uint32_t src_is_bf16;    // storage type in global memory
+  uint32_t ld;             // dense: row pitch in elements
+  uint32_t lines_total;    // bound on the line-major index (rows that exist)
+  uint32_t inner_total;    // bound on the inner index
+  uint32_t mn_major;       // 1: lines are K indices and inner is MN; 0: lines are MN and inner is K
+};
+
+struct GemmParams {
+  // problem
+  uint32_t m, n, k, batch;
+  uint32_t tiles_m, tiles_n, splits, k_blocks_per_split, k_blocks_total;
+  uint32_t bn;              // tile columns (multiple of 32, <= 256)
+  uint32_t stages;
+  uint32_t tf32;            // 1: kind::tf32 on f32 tiles (32 elements per line), 0: kind::f16 on bf16 tiles (64 per line)
+  uint32_t a_kind, b_kind;  // OperandKind
+  uint32_t a_mn_major, b_mn_major;
+  uint32_t group_m;         // tile rasterisation band height
+  // TMA patch boxes (conv): positions per box and its decomposition
+  uint32_t box_w, box_h, box_n;
+  ConvGeo geo;
+  uint32_t dgrad;           // 1: patches are taken from dy with flipped taps (stride-1 input gradient)
+  // gather sources
+  GatherDesc ga, gbsrc;
+  // output
+  void* c;
+  const float* bias;
+  const void* residual;
+  float* partial;           // split-K partials: [split][batch][m][n] f32, dense
+  uint64_t stride_c;        // batch stride of C in elements
+  uint32_t ldc;
+  uint32_t c_is_bf16, transpose_out, accumulate, relu, vec_store;
+  uint32_t* status;
+};
+
+size_t gemm_smem_bytes(const GemmParams& p);
+cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, int sm_count, cudaStream_t stream);
+cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream);
+cudaError_t gemm_sm100_configure();
+
+}  // namespace gb

@@ -1,0 +1,551 @@
+// Host side of libgradb200.so: argument validation, tile / split-K selection, tensor-map encoding and
+// dispatch for the entry points declared in include/gradb200.h.  This is the counterpart of the
+// wrappers in grad's src/gpu/gpu.zig (`matmul` :642-679, `matmulPacked` :1036-1064, `forwardPlan`
+// :890-913, `convImplicitWeightGrad` :983-1022, `convF32Forward` :789-826): it decides how a product is
+// cut into tiles and K parts; the kernels it launches live in gemm_sm100.cu and gemm_f32.cu.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/gradb200.h"
+#include "gemm_sm100.cuh"
+
+namespace gb {
+cudaError_t launch_gemm_f32(const GemmParams& p, cudaStream_t stream);
+}
+
+struct gb_handle {
+  int device = 0;
+  int sm_count = 0;
+  int last_cuda = 0;
+  uint32_t* status = nullptr;   // device word the kernels report bounded-wait failures into
+};
+
+namespace {
+
+using gb::GemmParams;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return (EncodeTiledFn) nullptr;
+    return (EncodeTiledFn)ptr;
+  }();
+  return fn;
+}
+
+int cuda_fail(gb_handle* h, cudaError_t e) {
+  if (h) h->last_cuda = (int)e;
+  return GB_ERR_CUDA;
+}
+
+uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+uint32_t elem_size(uint32_t dtype) { return dtype == GB_BF16 ? 2u : 4u; }
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+// Encodes a tiled map with 128-byte swizzle.  dims/strides/box follow the driver's convention: dims[0] is
+// the contiguous one, strides (bytes) start at dims[1].
+bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                const uint32_t* box) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[5], estr[5];
+  for (uint32_t i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estr[i] = 1;
+    if (i + 1 < rank) gstrides[i] = strides_bytes[i];
+  }
+  const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<void*>(base),
+                        gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct Plan {
+  GemmParams p;
+  CUtensorMap tmap_a, tmap_b;
+  bool tensor = false;      // tcgen05 path, else strict-f32
+  size_t workspace = 0;     // bytes of split-K partials
+};
+
+// Dense operand stored as `lines` rows of `inner` contiguous elements with pitch ld.
+struct DenseOperand {
+  const void* base;
+  uint32_t dtype, lines, inner, ld;
+  uint64_t batch_stride;
+  bool mn_major;            // the contiguous (inner) index is the MN index
+};
+
+void fill_dense_gather(gb::GatherDesc& g, const DenseOperand& o) {
+  g.base = o.base;
+  g.batch_stride = o.batch_stride;
+  g.source = gb::kSrcDense;
+  g.src_is_bf16 = o.dtype == GB_BF16;
+  g.ld = o.ld;
+  g.lines_total = o.lines;
+  g.inner_total = o.inner;
+  g.mn_major = o.mn_major;
+}
+
+// Tries to describe a dense operand by a 3-D TMA map {inner, lines, batch}; false means "gather it".
+bool dense_tma(CUtensorMap* map, const DenseOperand& o, bool smem_bf16, uint32_t batch, uint32_t tile_mn, uint32_t epl) {
+  const uint32_t es = smem_bf16 ? 2 : 4;
+  if ((o.dtype == GB_BF16) != smem_bf16) return false;
+  if (!aligned16(o.base) || ((uint64_t)o.ld * es) % 16 != 0) return false;
+  if (batch > 1 && (o.batch_stride == 0 || (o.batch_stride * es) % 16 != 0)) return false;
+  const uint64_t dims[3] = {o.inner, o.lines, batch};
+  const uint64_t batch_bytes = batch > 1 ? o.batch_stride * es : (uint64_t)o.ld * es * std::max<uint64_t>(o.lines, 1);
+  const uint64_t strides[2] = {(uint64_t)o.ld * es, batch_bytes};
+  // K-major: box = 128 bytes of K x tile_mn lines.  MN-major: box = 128 bytes of MN x epl K lines.
+  const uint32_t box[3] = {epl, o.mn_major ? epl : tile_mn, 1};
+  if (box[1] > 256) return false;
+  return encode_map(map, smem_bf16, o.base, 3, dims, strides, box);
+}
+
+uint32_t pick_stages(uint32_t bn) {
+  const uint32_t stage = 128 * 128 + bn * 128;
+  return std::min<uint32_t>(8, (227 * 1024 - 2048) / stage);
+}
+
+// Tile width and K split for an m x n x k_blocks product on `sms` multiprocessors: the widest tile that
+// still gives every SM a tile; when no width does, a 128-wide (or narrower, for a narrow n) tile with K
+// split so that about one work item per SM exists, each at least four K blocks long (the role of
+// `splits` in src/gpu/gpu.zig:664, 1000, 1041).
+void pick_tiling(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint32_t min_bn, uint32_t sms, bool allow_split,
+                 uint32_t& bn, uint32_t& splits, uint32_t& kbps) {
+  const uint32_t tiles_m = ceil_div(m, 128) * batch;
+  const uint32_t n_cap = std::max(min_bn, ceil_div(n, min_bn) * min_bn);   // n rounded up to the narrowest tile
+  bn = 0;
+  for (uint32_t cand : {256u, 128u, 64u, 32u}) {
+    if (cand < min_bn || cand > n_cap) continue;
+    if (tiles_m * ceil_div(n, cand) >= sms) { bn = cand; break; }
+  }
+  if (bn == 0) {
+    bn = std::min(n_cap, 128u);
+    while (bn > min_bn && (bn & (bn - 1)) != 0) bn &= bn - 1;   // round down to a power of two
+    bn = std::max(bn, min_bn);
+  }
+  const uint32_t tiles = tiles_m * ceil_div(n, bn);
+  splits = 1;
+  if (allow_split && tiles < sms && k_blocks >= 8) splits = std::max(1u, std::min(ceil_div(sms, tiles), k_blocks / 4));
+  kbps = ceil_div(k_blocks, splits);
+  splits = ceil_div(k_blocks, kbps);
+}
+
+int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_bn, const gb_epilogue* ep) {
+  GemmParams& p = plan.p;
+  p.bias = ep ? ep->bias : nullptr;
+  p.residual = ep ? ep->residual : nullptr;
+  p.relu = ep && ep->activation == GB_ACT_RELU;
+  p.status = h->status;
+  p.group_m = 8;
+  if (plan.tensor) {
+    const uint32_t epl = p.tf32 ? 32 : 64;
+    p.k_blocks_total = ceil_div(p.k, epl);
+    uint32_t bn, splits, kbps;
+    pick_tiling(p.m, p.n, p.batch, p.k_blocks_total, min_bn, (uint32_t)h->sm_count, allow_split, bn, splits, kbps);
+    p.bn = bn;
+    p.splits = splits;
+    p.k_blocks_per_split = kbps;
+    p.tiles_m = ceil_div(p.m, 128);
+    p.tiles_n = ceil_div(p.n, bn);
+    p.stages = pick_stages(bn);
+  } else {
+    p.k_blocks_total = ceil_div(p.k, 16);
+    const uint32_t tiles = ceil_div(p.m, 64) * ceil_div(p.n, 64) * p.batch;
+    uint32_t splits = 1;
+    if (allow_split && tiles < 2u * h->sm_count && p.k_blocks_total >= 32)
+      splits = std::max(1u, std::min(ceil_div(2u * h->sm_count, tiles), p.k_blocks_total / 16));
+    p.k_blocks_per_split = ceil_div(p.k_blocks_total, splits);
+    p.splits = ceil_div(p.k_blocks_total, p.k_blocks_per_split);
+    p.tiles_m = ceil_div(p.m, 64);
+    p.tiles_n = ceil_div(p.n, 64);
+    p.bn = 64;
+    p.stages = 1;
+  }
+  plan.workspace = p.splits > 1 ? (size_t)p.splits * p.batch * p.m * p.n * sizeof(float) : 0;
+  return GB_OK;
+}
+
+void set_output(GemmParams& p, void* c, uint32_t dtype_c, uint32_t ldc, uint64_t stride_c, bool transpose_out, bool accumulate,
+                const gb_epilogue* ep) {
+  p.c = c;
+  p.c_is_bf16 = dtype_c == GB_BF16;
+  p.ldc = ldc;
+  p.stride_c = stride_c;
+  p.transpose_out = transpose_out;
+  p.accumulate = accumulate;
+  const uint32_t es = elem_size(dtype_c);
+  bool vec = aligned16(c) && ((uint64_t)ldc * es) % 16 == 0 && (stride_c * es) % 16 == 0 && !transpose_out;
+  if (ep && ep->bias && !aligned16(ep->bias)) vec = false;
+  if (ep && ep->residual && !aligned16(ep->residual)) vec = false;
+  p.vec_store = vec;
+}
+
+int validate_gemm(const gb_gemm_desc* d) {
+  if (!d) return GB_ERR_INVALID;
+  if (d->trans_a && d->trans_b) return GB_ERR_INVALID;   // src/gpu/gpu.zig:643
+  if (d->dtype_a > GB_BF16 || d->dtype_b > GB_BF16 || d->dtype_c > GB_BF16 || d->math > GB_MATH_BF16) return GB_ERR_INVALID;
+  return GB_OK;
+}
+
+int plan_gemm(const gb_handle* h, const gb_gemm_desc* d, const void* a, const void* b, void* c, const gb_epilogue* ep, Plan& plan) {
+  std::memset(&plan.p, 0, sizeof(plan.p));
+  GemmParams& p = plan.p;
+  const uint32_t batch = std::max<uint32_t>(d->batch, 1);
+  p.m = d->m; p.n = d->n; p.k = d->k; p.batch = batch;
+  // The bf16 path is taken whenever an operand or the result is bf16, like `Gpu.matmul` (gpu.zig:644-647).
+  uint32_t math = d->math;
+  if (math == GB_MATH_F32 && (d->dtype_a == GB_BF16 || d->dtype_b == GB_BF16)) math = GB_MATH_BF16;
+  plan.tensor = math != GB_MATH_F32;
+  p.tf32 = math == GB_MATH_TF32;
+  const bool smem_bf16 = math == GB_MATH_BF16;
+  const uint32_t epl = p.tf32 ? 32 : 64;
+
+  DenseOperand oa, ob;
+  oa.base = a; oa.dtype = d->dtype_a; oa.batch_stride = batch > 1 ? d->stride_a : 0;
+  oa.mn_major = d->trans_a;
+  oa.lines = d->trans_a ? d->k : d->m;
+  oa.inner = d->trans_a ? d->m : d->k;
+  oa.ld = d->lda ? d->lda : oa.inner;
+  ob.base = b; ob.dtype = d->dtype_b; ob.batch_stride = batch > 1 ? d->stride_b : 0;
+  ob.mn_major = !d->trans_b;
+  ob.lines = d->trans_b ? d->n : d->k;
+  ob.inner = d->trans_b ? d->k : d->n;
+  ob.ld = d->ldb ? d->ldb : ob.inner;
+  if (oa.ld < oa.inner || ob.ld < ob.inner) return GB_ERR_INVALID;
+  fill_dense_gather(p.ga, oa);
+  fill_dense_gather(p.gbsrc, ob);
+  p.a_mn_major = oa.mn_major;
+  p.b_mn_major = ob.mn_major;
+
+  const uint32_t out_inner = d->transpose_out ? d->m : d->n;
+  const uint32_t ldc = d->ldc ? d->ldc : out_inner;
+  if (ldc < out_inner) return GB_ERR_INVALID;
+  set_output(p, c, d->dtype_c, ldc, batch > 1 ? d->stride_c : 0, d->transpose_out, d->accumulate, ep);
+
+  const uint32_t min_bn = (plan.tensor && ob.mn_major) ? epl : 32;
+  int rc = finish_plan(h, plan, true, min_bn, ep);
+  if (rc != GB_OK) return rc;
+  if (plan.tensor) {
+    p.a_kind = dense_tma(&plan.tmap_a, oa, smem_bf16, batch, 128, epl) ? (oa.mn_major ? gb::kDenseMN : gb::kDenseK) : gb::kGather;
+    p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, batch, p.bn, epl) ? (ob.mn_major ? gb::kDenseMN : gb::kDenseK) : gb::kGather;
+  }
+  return GB_OK;
+}
+
+int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, size_t workspace_bytes) {
+  GemmParams& p = plan.p;
+  if (p.m == 0 || p.n == 0 || p.batch == 0) return GB_OK;   // an empty grid is a no-op (src/gpu/gpu.zig:612)
+  if (p.splits > 1) {
+    if (workspace == nullptr || workspace_bytes < plan.workspace || !aligned16(workspace)) {
+      // Without room for partials the product runs unsplit rather than failing.
+      p.splits = 1;
+      p.k_blocks_per_split = p.k_blocks_total;
+    } else {
+      p.partial = (float*)workspace;
+    }
+  }
+  cudaError_t e;
+  if (p.k == 0) {
+    // An empty contraction is a zero product: only the epilogue runs (through the reduce kernel, zero parts).
+    p.splits = 0;
+    p.partial = nullptr;
+    e = gb::launch_splitk_reduce(p, stream);
+    return e == cudaSuccess ? GB_OK : cuda_fail(h, e);
+  }
+  e = plan.tensor ? gb::launch_gemm_sm100(p, plan.tmap_a, plan.tmap_b, h->sm_count, stream) : gb::launch_gemm_f32(p, stream);
+  if (e != cudaSuccess) return cuda_fail(h, e);
+  if (p.splits > 1) {
+    e = gb::launch_splitk_reduce(p, stream);
+    if (e != cudaSuccess) return cuda_fail(h, e);
+  }
+  return GB_OK;
+}
+
+// ---- convolution planning ---------------------------------------------------------------------------
+int validate_conv(const gb_conv_desc* d) {
+  if (!d) return GB_ERR_INVALID;
+  const gb_conv_geometry& g = d->geo;
+  if (g.n == 0 || g.h == 0 || g.w == 0 || g.c == 0 || g.k == 0 || g.stride == 0 || g.c_out == 0) return GB_ERR_INVALID;
+  const uint32_t dil = g.dilation ? g.dilation : 1;
+  if (dil * (g.k - 1) + 1 > g.h + 2 * g.pad || dil * (g.k - 1) + 1 > g.w + 2 * g.pad) return GB_ERR_INVALID;
+  const uint32_t oh = (g.h + 2 * g.pad - dil * (g.k - 1) - 1) / g.stride + 1;   // src/gpu/math/conv.zig:24-30
+  const uint32_t ow = (g.w + 2 * g.pad - dil * (g.k - 1) - 1) / g.stride + 1;
+  if (g.out_h != oh || g.out_w != ow) return GB_ERR_INVALID;
+  if ((uint64_t)g.positions != (uint64_t)g.n * oh * ow) return GB_ERR_INVALID;
+  if (g.c_step != 0 && g.c_step < g.c) return GB_ERR_INVALID;
+  if (d->dtype_x > GB_BF16 || d->dtype_w > GB_BF16 || d->dtype_y > GB_BF16 || d->math > GB_MATH_BF16) return GB_ERR_INVALID;
+  return GB_OK;
+}
+
+gb::ConvGeo to_geo(const gb_conv_geometry& g) {
+  gb::ConvGeo o;
+  o.n = g.n; o.h = g.h; o.w = g.w; o.c = g.c; o.k = g.k; o.stride = g.stride; o.pad = g.pad;
+  o.dilation = g.dilation ? g.dilation : 1;
+  o.out_h = g.out_h; o.out_w = g.out_w; o.c_out = g.c_out;
+  o.c_step = g.c_step ? g.c_step : g.c;
+  return o;
+}
+
+// Splits `count` consecutive positions of a (grid_h x grid_w) grid into a box of whole rows (and whole
+// images when count spans several).  False when the positions do not form such a box.
+bool patch_box(uint32_t count, uint32_t grid_h, uint32_t grid_w, uint32_t& bw, uint32_t& bh, uint32_t& bn) {
+  if (grid_w == 0 || count % grid_w != 0) return false;
+  const uint32_t per_image = grid_h * grid_w;
+  if (per_image % count == 0) {
+    bw = grid_w; bh = count / grid_w; bn = 1;
+  } else if (count % per_image == 0) {
+    bw = grid_w; bh = grid_h; bn = count / per_image;
+  } else {
+    return false;
+  }
+  return bw <= 256 && bh <= 256 && bn <= 256;
+}
+
+// 4-D map over an NHWC tensor {channels, width, height, images} with a box of `epl` channels x (bw, bh, bn).
+bool nhwc_tma(CUtensorMap* map, const void* base, bool smem_bf16, uint32_t dtype, uint32_t channels, uint32_t c_step, uint32_t width,
+              uint32_t height, uint32_t images, uint32_t epl, uint32_t bw, uint32_t bh, uint32_t bn) {
+  const uint32_t es = smem_bf16 ? 2 : 4;
+  if ((dtype == GB_BF16) != smem_bf16) return false;
+  if (channels % epl != 0 || !aligned16(base) || ((uint64_t)c_step * es) % 16 != 0) return false;
+  const uint64_t dims[4] = {channels, width, height, images};
+  const uint64_t strides[3] = {(uint64_t)c_step * es, (uint64_t)c_step * es * width, (uint64_t)c_step * es * width * height};
+  const uint32_t box[4] = {epl, bw, bh, bn};
+  return encode_map(map, smem_bf16, base, 4, dims, strides, box);
+}
+
+int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* act, const void* other, void* out,
+              const gb_epilogue* ep, Plan& plan) {
+  std::memset(&plan.p, 0, sizeof(plan.p));
+  GemmParams& p = plan.p;
+  const gb::ConvGeo g = to_geo(d->geo);
+  p.geo = g;
+  p.batch = 1;
+  uint32_t math = d->math;
+  if (math == GB_MATH_F32 && (d->dtype_x == GB_BF16 || d->dtype_y == GB_BF16)) math = GB_MATH_BF16;
+  plan.tensor = math != GB_MATH_F32;
+  p.tf32 = math == GB_MATH_TF32;
+  const bool smem_bf16 = math == GB_MATH_BF16;
+  const uint32_t epl = p.tf32 ? 32 : 64;
+  const uint32_t taps = g.k * g.k;
+  const uint32_t positions = d->geo.positions;
+  const uint32_t pixels = g.n * g.h * g.w;
+  uint32_t min_bn = 32;
+
+  if (pass == 0) {
+    // y[positions, c_out] = patches(x)[positions, taps*c] * w[taps*c, c_out]
+    p.m = positions; p.n = g.c_out; p.k = taps * g.c;
+    p.ga.base = act; p.ga.source = gb::kSrcPatch; p.ga.src_is_bf16 = d->dtype_x == GB_BF16;
+    p.ga.lines_total = positions; p.ga.inner_total = p.k; p.ga.mn_major = 0;
+    DenseOperand ob{other, d->dtype_w, p.k, g.c_out, g.c_out, 0, true};
+    fill_dense_gather(p.gbsrc, ob);
+    p.a_mn_major = 0; p.b_mn_major = 1;
+    min_bn = plan.tensor ? epl : 32;
+    set_output(p, out, d->dtype_y, g.c_out, 0, false, d->accumulate, ep);
+    int rc = finish_plan(h, plan, true, min_bn, ep);
+    if (rc != GB_OK) return rc;
+    if (plan.tensor) {
+      p.a_kind = gb::kGather;
+      if (g.stride == 1 && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+          nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n))
+        p.a_kind = gb::kPatchK;
+      p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
+    }
+  } else if (pass == 1) {
+    // dx[pixels, c] = patchesT(dy)[pixels, taps*c_out] * wT[taps*c_out, c]
+    p.m = pixels; p.n = g.c; p.k = taps * g.c_out;
+    p.dgrad = 1;
+    p.ga.base = act; p.ga.source = gb::kSrcPatchT; p.ga.src_is_bf16 = d->dtype_y == GB_BF16;
+    p.ga.lines_total = pixels; p.ga.inner_total = p.k; p.ga.mn_major = 0;
+    p.gbsrc.base = other; p.gbsrc.source = gb::kSrcWeightT; p.gbsrc.src_is_bf16 = d->dtype_w == GB_BF16;
+    p.gbsrc.lines_total = g.c; p.gbsrc.inner_total = p.k; p.gbsrc.mn_major = 0;
+    p.a_mn_major = 0; p.b_mn_major = 0;
+    set_output(p, out, d->dtype_x, g.c_step, 0, false, d->accumulate, nullptr);
+    int rc = finish_plan(h, plan, true, 32, nullptr);
+    if (rc != GB_OK) return rc;
+    if (plan.tensor) {
+      p.a_kind = gb::kGather;
+      if (g.stride == 1 && patch_box(128, g.h, g.w, p.box_w, p.box_h, p.box_n) &&
+          nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_y, g.c_out, g.c_out, g.out_w, g.out_h, g.n, epl, p.box_w, p.box_h, p.box_n))
+        p.a_kind = gb::kPatchK;
+      p.b_kind = gb::kGather;
+      const uint32_t es = smem_bf16 ? 2 : 4;
+      if ((d->dtype_w == GB_BF16) == smem_bf16 && g.c_out % epl == 0 && aligned16(other) && p.bn <= 256) {
+        const uint64_t dims[3] = {g.c_out, g.c, taps};
+        const uint64_t strides[2] = {(uint64_t)g.c_out * es, (uint64_t)g.c_out * es * g.c};
+        const uint32_t box[3] = {epl, p.bn, 1};
+        if (encode_map(&plan.tmap_b, smem_bf16, other, 3, dims, strides, box)) p.b_kind = gb::kWeightK;
+      }
+    }
+  } else {
+    // dw[taps*c, c_out] += patches(x)^T[taps*c, positions] * dy[positions, c_out]
+    p.m = taps * g.c; p.n = g.c_out; p.k = positions;
+    p.ga.base = other; p.ga.source = gb::kSrcPatch; p.ga.src_is_bf16 = d->dtype_x == GB_BF16;
+    p.ga.lines_total = positions; p.ga.inner_total = p.m; p.ga.mn_major = 1;
+    DenseOperand ob{act, d->dtype_y, positions, g.c_out, g.c_out, 0, true};
+    fill_dense_gather(p.gbsrc, ob);
+    p.a_mn_major = 1; p.b_mn_major = 1;
+    min_bn = plan.tensor ? epl : 32;
+    set_output(p, out, d->dtype_w, g.c_out, 0, false, d->accumulate, nullptr);
+    int rc = finish_plan(h, plan, true, min_bn, nullptr);
+    if (rc != GB_OK) return rc;
+    if (plan.tensor) {
+      p.a_kind = gb::kGather;
+      if (g.stride == 1 && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+          nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n))
+        p.a_kind = gb::kPatchMN;
+      p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
+    }
+  }
+  return GB_OK;
+}
+
+}  // namespace
+
+// =====================================================================================================
+extern "C" {
+
+int gb_abi_version(void) { return GB_ABI_VERSION; }
+
+const char* gb_error_string(int status) {
+  switch (status) {
+    case GB_OK: return "success";
+    case GB_ERR_INVALID: return "invalid argument";
+    case GB_ERR_CUDA: return "a CUDA call failed";
+    case GB_ERR_WORKSPACE: return "workspace missing or too small";
+    case GB_ERR_UNSUPPORTED: return "shape or dtype combination not supported";
+    case GB_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+    case GB_ERR_NCCL: return "NCCL unavailable or a collective failed";
+    case GB_ERR_NO_DEVICE: return "no sm_100 CUDA device";
+    default: return "unknown status";
+  }
+}
+
+int gb_create(int device_ordinal, gb_handle** out) {
+  if (!out) return GB_ERR_INVALID;
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device_ordinal < 0 || device_ordinal >= count) return GB_ERR_NO_DEVICE;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess) return GB_ERR_NO_DEVICE;
+  if (prop.major != 10) return GB_ERR_NO_DEVICE;   // the kernels are sm_100a only; there is no fallback
+  if (cudaSetDevice(device_ordinal) != cudaSuccess) return GB_ERR_CUDA;
+  gb_handle* h = new gb_handle();
+  h->device = device_ordinal;
+  h->sm_count = prop.multiProcessorCount;
+  cudaError_t e = cudaMalloc(&h->status, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(h->status, 0, sizeof(uint32_t));
+  if (e == cudaSuccess) e = gb::gemm_sm100_configure();
+  if (e != cudaSuccess || encode_tiled_fn() == nullptr) {
+    if (h->status) cudaFree(h->status);
+    delete h;
+    return GB_ERR_CUDA;
+  }
+  *out = h;
+  return GB_OK;
+}
+
+void gb_destroy(gb_handle* h) {
+  if (!h) return;
+  cudaSetDevice(h->device);
+  if (h->status) cudaFree(h->status);
+  delete h;
+}
+
+int gb_last_cuda_error(const gb_handle* h) { return h ? h->last_cuda : 0; }
+int gb_sm_count(const gb_handle* h) { return h ? h->sm_count : 0; }
+
+int gb_last_status(gb_handle* h, void* stream, uint32_t* device_status) {
+  if (!h) return GB_ERR_INVALID;
+  uint32_t word = 0;
+  cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaMemcpy(&word, h->status, sizeof(word), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && word != 0) e = cudaMemset(h->status, 0, sizeof(word));
+  if (e != cudaSuccess) return cuda_fail(h, e);
+  if (device_status) *device_status = word;
+  return word == 0 ? GB_OK : GB_ERR_TIMEOUT;
+}
+
+int gb_gemm_workspace(const gb_handle* h, const gb_gemm_desc* desc, size_t* bytes) {
+  if (!h || !bytes) return GB_ERR_INVALID;
+  int rc = validate_gemm(desc);
+  if (rc != GB_OK) return rc;
+  Plan plan;
+  rc = plan_gemm(h, desc, nullptr, nullptr, nullptr, nullptr, plan);
+  if (rc != GB_OK) return rc;
+  *bytes = plan.workspace;
+  return GB_OK;
+}
+
+int gb_gemm(gb_handle* h, void* stream, const gb_gemm_desc* desc, const void* a, const void* b, void* c,
+            const gb_epilogue* epilogue, void* workspace, size_t workspace_bytes) {
+  if (!h) return GB_ERR_INVALID;
+  int rc = validate_gemm(desc);
+  if (rc != GB_OK) return rc;
+  if (desc->m != 0 && desc->n != 0 && (!c || (desc->k != 0 && (!a || !b)))) return GB_ERR_INVALID;
+  Plan plan;
+  rc = plan_gemm(h, desc, a, b, c, epilogue, plan);
+  if (rc != GB_OK) return rc;
+  return run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+}
+
+int gb_conv_workspace(const gb_handle* h, int pass, const gb_conv_desc* desc, size_t* bytes) {
+  if (!h || !bytes || pass < 0 || pass > 2) return GB_ERR_INVALID;
+  int rc = validate_conv(desc);
+  if (rc != GB_OK) return rc;
+  Plan plan;
+  rc = plan_conv(h, pass, desc, nullptr, nullptr, nullptr, nullptr, plan);
+  if (rc != GB_OK) return rc;
+  *bytes = plan.workspace;
+  return GB_OK;
+}
+
+int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* x, const void* w, void* y,
+                  const gb_epilogue* epilogue, void* workspace, size_t workspace_bytes) {
+  if (!h || !x || !w || !y) return GB_ERR_INVALID;
+  int rc = validate_conv(desc);
+  if (rc != GB_OK) return rc;
+  Plan plan;
+  rc = plan_conv(h, 0, desc, x, w, y, epilogue, plan);
+  if (rc != GB_OK) return rc;
+  return run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+}
+
+int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* w, void* dx,
+                  void* workspace, size_t workspace_bytes) {
+  if (!h || !dy || !w || !dx) return GB_ERR_INVALID;
+  int rc = validate_conv(desc);
+  if (rc != GB_OK) return rc;
+  Plan plan;
+  rc = plan_conv(h, 1, desc, dy, w, dx, nullptr, plan);
+  if (rc != GB_OK) return rc;
+  return run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+}
+
+int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* x, void* dw,
+                  void* workspace, size_t workspace_bytes) {
+  if (!h || !dy || !x || !dw) return GB_ERR_INVALID;
+  int rc = validate_conv(desc);
+  if (rc != GB_OK) return rc;
+  if (desc->dtype_w != GB_F32) return GB_ERR_UNSUPPORTED;   // weight gradients accumulate in f32 (gpu.zig:983)
+  Plan plan;
+  rc = plan_conv(h, 2, desc, dy, x, dw, nullptr, plan);
+  if (rc != GB_OK) return rc;
+  return run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+}
+
+}  // extern "C"

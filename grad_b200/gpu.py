@@ -1,0 +1,235 @@
+"""Host-side mirror of grad's ``Gpu`` contraction wrappers (src/gpu/gpu.zig) on top of the C ABI.
+
+Method names and argument meaning follow the reference (`matmul`, `convImplicitForward`,
+`convF32Forward`, `convImplicitWeightGrad`, `convF32WeightGrad`) so the parity tests read like
+tests/parity.zig and tests/autograd.zig.  Tensors are torch CUDA tensors used purely as device
+buffers: the kernels receive their raw addresses, bf16 is 16-bit storage.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import abi
+from .abi import ACT_NONE, ACT_RELU, BF16, F32, MATH_BF16, MATH_F32, MATH_TF32
+
+
+@dataclass
+class MatmulOpts:
+    """src/gpu/gpu.zig:22 `MatmulOpts`."""
+
+    trans_a: bool = False
+    trans_b: bool = False
+    accumulate: bool = False
+
+
+@dataclass
+class MatmulShape:
+    """src/gpu/gpu.zig:29 `MatmulShape`."""
+
+    m: int
+    n: int
+    k: int
+    batch: int = 1
+
+
+@dataclass
+class Epilogue:
+    bias: Optional[torch.Tensor] = None        # f32[n]
+    residual: Optional[torch.Tensor] = None    # same shape / dtype as the output
+    relu: bool = False
+
+
+@dataclass
+class ConvGeometry:
+    """src/gpu/args.zig:78 `ConvGeometry` (forward geometry of the layer)."""
+
+    n: int
+    h: int
+    w: int
+    c: int
+    k: int
+    stride: int
+    pad: int
+    out_h: int
+    out_w: int
+    positions: int
+    c_out: int
+    dilation: int = 1
+    c_step: int = 0
+    subsample: int = 1
+
+    def c_struct(self) -> abi.ConvGeometryC:
+        return abi.ConvGeometryC(self.n, self.h, self.w, self.c, self.k, self.stride, self.pad, self.out_h, self.out_w,
+                                 self.positions, self.c_out, self.dilation, self.c_step, self.subsample)
+
+
+def conv_geometry(n, h, w, c, k, c_out, stride=1, pad=0, dilation=1) -> ConvGeometry:
+    """src/autograd/autograd.zig:99-141 `convGeometry` (forward case) with conv.zig's output-size formula."""
+    oh = (h + 2 * pad - dilation * (k - 1) - 1) // stride + 1
+    ow = (w + 2 * pad - dilation * (k - 1) - 1) // stride + 1
+    return ConvGeometry(n, h, w, c, k, stride, pad, oh, ow, n * oh * ow, c_out, dilation)
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype in (torch.bfloat16, torch.uint16, torch.int16):
+        return BF16
+    raise TypeError(f"unsupported dtype {t.dtype}: the path stores f32 or bf16")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+class Gpu:
+    """One per device and host thread, like the reference's `Gpu` (src/gpu/gpu.zig:247-477).
+
+    `tensor_cores`, `tf32` and `deterministic` are the reference's `Gpu.Config` (gpu.zig:291-298);
+    `tensor_core_min_work` is its threshold for routing an f32 product to the bf16 kernels (:251, 703-705).
+    """
+
+    tensor_core_min_work = 1 << 22
+
+    def __init__(self, device: int = 0, tensor_cores: bool = False, tf32: bool = False, deterministic: bool = False):
+        if not torch.cuda.is_available():
+            raise RuntimeError("grad_b200 needs a CUDA device: there is no CPU fallback")
+        self.lib = abi.library()
+        self.device = torch.device("cuda", device)
+        self.tensor_cores = tensor_cores
+        self.tf32 = tf32
+        self.deterministic = deterministic
+        torch.cuda.set_device(self.device)
+        handle = C.c_void_p()
+        abi.check(self.lib.gb_create(device, C.byref(handle)), "gb_create")
+        self.handle = handle
+        self.multiprocessors = int(self.lib.gb_sm_count(handle))
+        self._scratch: Optional[torch.Tensor] = None
+        self.launches = 0   # calls into compute entry points (each is one or two kernel launches)
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.gb_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- arena ------------------------------------------------------------------------------------
+    def scratch(self, nbytes: int) -> Optional[torch.Tensor]:
+        """Grow-only workspace, the role of `Gpu.scratch` (gpu.zig:403-410); allocated outside the timed step."""
+        if nbytes == 0:
+            return None
+        if self._scratch is None or self._scratch.numel() < nbytes:
+            self._scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        return self._scratch
+
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def check_status(self) -> int:
+        """Synchronises and raises GB_ERR_TIMEOUT if a bounded device wait gave up."""
+        word = C.c_uint32(0)
+        rc = self.lib.gb_last_status(self.handle, self._stream(), C.byref(word))
+        abi.check(rc, f"gb_last_status (device status {word.value})")
+        return word.value
+
+    def _epilogue(self, ep: Optional[Epilogue]):
+        if ep is None:
+            return None
+        e = abi.Epilogue(_ptr(ep.bias), _ptr(ep.residual), ACT_RELU if ep.relu else ACT_NONE, 0)
+        return C.byref(e)
+
+    # ---- matmul family ----------------------------------------------------------------------------
+    def tensorWorthwhile(self, m: int, n: int, k: int) -> bool:
+        return self.tensor_cores and m * n * k >= self.tensor_core_min_work
+
+    def _gemm_math(self, a, b, out, shape: MatmulShape, math: Optional[int]) -> int:
+        if math is not None:
+            return math
+        wide = all(_dtype_code(t) == F32 for t in (a, b, out))
+        if not wide or self.tensorWorthwhile(shape.m, shape.n, shape.k):
+            return MATH_BF16
+        return MATH_F32
+
+    def matmul(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, shape: MatmulShape, opts: MatmulOpts = MatmulOpts(),
+               epilogue: Optional[Epilogue] = None, math: Optional[int] = None, transpose_out: bool = False,
+               lda: int = 0, ldb: int = 0, ldc: int = 0):
+        """`Gpu.matmul` (src/gpu/gpu.zig:642-679): out (+)= op(a) * op(b), row-major; any operand may be bf16."""
+        assert not (opts.trans_a and opts.trans_b)
+        d = abi.GemmDesc()
+        d.m, d.n, d.k, d.batch = shape.m, shape.n, shape.k, shape.batch
+        d.stride_a, d.stride_b, d.stride_c = shape.m * shape.k, shape.k * shape.n, shape.m * shape.n
+        d.lda, d.ldb, d.ldc = lda, ldb, ldc
+        d.trans_a, d.trans_b, d.accumulate, d.transpose_out = opts.trans_a, opts.trans_b, opts.accumulate, transpose_out
+        d.dtype_a, d.dtype_b, d.dtype_c = _dtype_code(a), _dtype_code(b), _dtype_code(out)
+        d.math = self._gemm_math(a, b, out, shape, math)
+        d.deterministic = self.deterministic
+        need = C.c_size_t(0)
+        abi.check(self.lib.gb_gemm_workspace(self.handle, C.byref(d), C.byref(need)), "gb_gemm_workspace")
+        ws = self.scratch(need.value)
+        rc = self.lib.gb_gemm(self.handle, self._stream(), C.byref(d), _ptr(a), _ptr(b), _ptr(out), self._epilogue(epilogue),
+                              _ptr(ws), need.value)
+        abi.check(rc, "gb_gemm")
+        self.launches += 1
+
+    # ---- convolution ------------------------------------------------------------------------------
+    def _conv_desc(self, geo: ConvGeometry, x_like, w_like, y_like, math: Optional[int], accumulate: bool) -> abi.ConvDesc:
+        d = abi.ConvDesc()
+        d.geo = geo.c_struct()
+        d.dtype_x, d.dtype_w, d.dtype_y = _dtype_code(x_like), _dtype_code(w_like), _dtype_code(y_like)
+        if math is None:
+            half = d.dtype_x == BF16 or d.dtype_y == BF16
+            math = MATH_BF16 if (half or self.tensor_cores) else (MATH_TF32 if self.tf32 else MATH_F32)
+        d.math = math
+        d.accumulate = accumulate
+        d.deterministic = self.deterministic
+        return d
+
+    def _conv_ws(self, which: int, d: abi.ConvDesc):
+        need = C.c_size_t(0)
+        abi.check(self.lib.gb_conv_workspace(self.handle, which, C.byref(d), C.byref(need)), "gb_conv_workspace")
+        return self.scratch(need.value), need.value
+
+    def convForward(self, x, w, out, geo: ConvGeometry, accumulate: bool = False, epilogue: Optional[Epilogue] = None,
+                    math: Optional[int] = None):
+        """Forward implicit GEMM: `convImplicitForward` (gpu.zig:926-929) for bf16 data, `convF32Forward` (:789-826)
+        for f32 data; x is NHWC, w is (k*k*c, c_out)."""
+        d = self._conv_desc(geo, x, w, out, math, accumulate)
+        ws, n = self._conv_ws(abi.PASS_FPROP, d)
+        rc = self.lib.gb_conv_fprop(self.handle, self._stream(), C.byref(d), _ptr(x), _ptr(w), _ptr(out), self._epilogue(epilogue),
+                                    _ptr(ws), n)
+        abi.check(rc, "gb_conv_fprop")
+        self.launches += 1
+
+    convImplicitForward = convForward
+    convF32Forward = convForward
+
+    def convInputGrad(self, dy, w, dx, geo: ConvGeometry, accumulate: bool = True, math: Optional[int] = None):
+        """dx (+)= adjoint of the forward gather applied to dy * w^T.  The reference runs its forward kernel on the
+        reversed geometry with rotated weights (autograd.zig:1052-1100, gpu.zig:856-866); here `geo` stays the
+        forward geometry and `w` the unrotated weights."""
+        d = self._conv_desc(geo, dx, w, dy, math, accumulate)
+        ws, n = self._conv_ws(abi.PASS_DGRAD, d)
+        rc = self.lib.gb_conv_dgrad(self.handle, self._stream(), C.byref(d), _ptr(dy), _ptr(w), _ptr(dx), _ptr(ws), n)
+        abi.check(rc, "gb_conv_dgrad")
+        self.launches += 1
+
+    def convWeightGrad(self, dy, x, out, geo: ConvGeometry, math: Optional[int] = None, accumulate: bool = True):
+        """`convImplicitWeightGrad` (gpu.zig:983-1022) / `convF32WeightGrad` (:828-866): out (taps, c_out) f32 += ...;
+        dy is read as stored (positions, c_out), no transposed copy."""
+        d = self._conv_desc(geo, x, out, dy, math, accumulate)
+        ws, n = self._conv_ws(abi.PASS_WGRAD, d)
+        rc = self.lib.gb_conv_wgrad(self.handle, self._stream(), C.byref(d), _ptr(dy), _ptr(x), _ptr(out), _ptr(ws), n)
+        abi.check(rc, "gb_conv_wgrad")
+        self.launches += 1
+
+    convImplicitWeightGrad = convWeightGrad
+    convF32WeightGrad = convWeightGrad

@@ -1,0 +1,155 @@
+/*
+ * gradb200.h -- C ABI of libgradb200.so: the dense-contraction path of hyunjun3952/grad
+ * (matmul family + implicit-GEMM conv2d + gradient allreduce) as hand-written sm_100a kernels.
+ *
+ * The library is loaded the way grad loads libcuda and cuDNN: dlopen + one dlsym per entry point
+ * into a struct of C function pointers (src/gpu/dynlib.zig:20-61, src/gpu/cudnn.zig:22-86,120-127).
+ * Conventions, taken from the callers in src/gpu/gpu.zig:
+ *   - every pointer argument is a raw device address from cuMemAlloc (gpu.zig:395-410); the library
+ *     never frees, retains or allocates tensors.  bf16 is uint16_t storage (src/gpu/math/bf16.zig).
+ *   - temporaries come from a caller-owned workspace (like cudnn_workspace, gpu.zig:485-501); the
+ *     size is asked with the *_workspace query.  No entry point allocates device memory after
+ *     gb_create, none synchronises, none reads back: all are safe under stream capture
+ *     (src/gpu/cuda.zig:151-159).
+ *   - `stream` is the CUstream the caller launches on (NULL = legacy default stream, cuda.zig:210-212).
+ *   - return value: 0 on success, a gb_status otherwise (cuda.zig:118-124); never aborts or throws.
+ *   - there is no CPU fallback: without a CUDA device every compute entry point fails.
+ */
+#ifndef GRADB200_H
+#define GRADB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GB_ABI_VERSION 1
+
+typedef struct gb_handle gb_handle;   /* per-device state; one per host thread, like one `Gpu` per thread */
+typedef struct gb_comm gb_comm;       /* one rank of a gradient-averaging group */
+
+typedef enum {
+  GB_OK = 0,
+  GB_ERR_INVALID = 1,       /* bad argument (null pointer, zero stride, trans_a and trans_b both set, ...) */
+  GB_ERR_CUDA = 2,          /* a CUDA call failed; gb_last_cuda_error() has the code (maps to error.CudaFailed) */
+  GB_ERR_WORKSPACE = 3,     /* workspace pointer null or too small (maps to error.OutOfMemory) */
+  GB_ERR_UNSUPPORTED = 4,   /* shape / dtype combination outside what the kernels cover (error.NoAlgorithm) */
+  GB_ERR_TIMEOUT = 5,       /* a bounded device-side wait gave up; see gb_last_status */
+  GB_ERR_NCCL = 6,          /* NCCL missing or a collective failed */
+  GB_ERR_NO_DEVICE = 7      /* no CUDA device / not an sm_100 part (error.NoSuchDevice) */
+} gb_status;
+
+typedef enum { GB_F32 = 0, GB_BF16 = 1 } gb_dtype;
+
+/* Arithmetic of the contraction.  Accumulation is always f32.
+ *   GB_MATH_F32  strict f32 FMA on the CUDA cores (device.zig `f32Compute` :1665-1684, `Gemm` :122-201)
+ *   GB_MATH_TF32 operands read as TF32 by the tensor core (`tf32Compute` :1888-1913)
+ *   GB_MATH_BF16 operands rounded to bf16 (RNE) when not already bf16 (`bf16Compute` :997-1045) */
+typedef enum { GB_MATH_F32 = 0, GB_MATH_TF32 = 1, GB_MATH_BF16 = 2 } gb_math;
+
+typedef enum { GB_ACT_NONE = 0, GB_ACT_RELU = 1 } gb_activation;
+
+/* Fused epilogue.  grad has no fused bias today: `Tape.linear` adds the bias with a second launch
+ * (src/autograd/autograd.zig:449-468) and the ONNX executor adds bias and applies Relu with two more
+ * (src/onnx/gpu.zig:518-519, 372-377).  The fused result is defined as that unfused sequence in f32:
+ *   v = acc (+ old C when accumulate) ; v += bias[col] ; v += residual[row][col] ; v = act(v) ; store. */
+typedef struct {
+  const float* bias;        /* f32[n] (per output column / output channel) or NULL */
+  const void* residual;     /* same shape, pitch and dtype as the output, or NULL (ONNX Add before Relu) */
+  int32_t activation;       /* gb_activation */
+  int32_t reserved;
+} gb_epilogue;
+
+/* One product C[m,n] (+)= op(A) * op(B), row-major.  Replaces `MatmulShape` + `MatmulOpts`
+ * (src/gpu/gpu.zig:22,29), `GemmShape` (src/gpu/args.zig:2-12) and the fields of `TensorShape`
+ * (args.zig:72) that `Gpu.matmulPacked` sets (gpu.zig:1036-1064).
+ *   trans_a: A is stored (k, m);  trans_b: B is stored (n, k);  never both (gpu.zig:643).
+ *   lda/ldb/ldc: row pitch in elements of the STORED matrices; 0 = dense (the stored row length).
+ *   batch > 1: that many consecutive products, operands stride_* elements apart (args.zig:1-12);
+ *              a stride of 0 broadcasts that operand.
+ *   transpose_out: C is written as (n, m) with pitch ldc (args.zig `transpose_out`).
+ *   deterministic: split-K partials are combined in a fixed order (gpu.zig:1024-1034); this
+ *              library's split-K is always ordered, so the flag only documents the caller's intent. */
+typedef struct {
+  uint32_t m, n, k, batch;
+  uint64_t stride_a, stride_b, stride_c;
+  uint32_t lda, ldb, ldc;
+  uint8_t trans_a, trans_b, accumulate, transpose_out;
+  uint8_t dtype_a, dtype_b, dtype_c, math;   /* gb_dtype x3, gb_math */
+  uint8_t deterministic, reserved[3];
+} gb_gemm_desc;
+
+/* Field-for-field copy of `ConvGeometry` (src/gpu/args.zig:78) so a Zig `extern struct` passes by
+ * pointer.  Always the FORWARD geometry of the layer: x is (n,h,w,c) NHWC, y is (n,out_h,out_w,c_out),
+ * w is (k*k*c, c_out) with row (ky*k+kx)*c+ci (src/autograd/autograd.zig:91,1150).  positions =
+ * n*out_h*out_w.  c_step = channel stride of x in memory (0 = c).  subsample is ignored: the input
+ * gradient entry point derives the reverse gather itself instead of taking a reversed geometry and
+ * rotated weights (autograd.zig:101-125, gpu.zig:856-866). */
+typedef struct {
+  uint32_t n, h, w, c, k, stride, pad, out_h, out_w, positions, c_out, dilation, c_step, subsample;
+} gb_conv_geometry;
+
+typedef struct {
+  gb_conv_geometry geo;
+  uint8_t dtype_x, dtype_w, dtype_y, math;   /* dtype of x (or dx), of w (or dw), of y (or dy); gb_math */
+  uint8_t accumulate, deterministic, reserved[2];
+} gb_conv_desc;
+
+/* ---- lifetime --------------------------------------------------------------------------------- */
+/* Uses the primary context of `device_ordinal` like `Cuda.init` (src/gpu/cuda.zig:67-83); created in
+ * `Gpu.init`, destroyed in `Gpu.deinit` (src/gpu/gpu.zig:362-392).  Allocates one status word. */
+int gb_create(int device_ordinal, gb_handle** out);
+void gb_destroy(gb_handle* h);
+int gb_abi_version(void);
+const char* gb_error_string(int status);
+/* Last cudaError_t seen by this handle (0 if none). */
+int gb_last_cuda_error(const gb_handle* h);
+/* Reads (and clears) the device-side status word: 0 = every bounded wait completed.  Synchronises the
+ * stream, so call it outside capture -- the analogue of `Gpu.sync` + error check. */
+int gb_last_status(gb_handle* h, void* stream, uint32_t* device_status);
+/* Multiprocessor count the tile/split heuristics use (src/gpu/gpu.zig `multiprocessors`). */
+int gb_sm_count(const gb_handle* h);
+
+/* ---- matmul family ---------------------------------------------------------------------------- */
+/* Replaces `Gpu.matmul` (src/gpu/gpu.zig:642-679), `Gpu.matmulTensor` / `packMatrix` / `matmulPacked`
+ * (:1066-1073, :711-722, :1036-1064) and the kernels `sgemm*` / `sgemmTensor`
+ * (src/gpu/device.zig:122-250, 1710-1712).  Operands are consumed in place: no packed copies. */
+int gb_gemm_workspace(const gb_handle* h, const gb_gemm_desc* desc, size_t* bytes);
+int gb_gemm(gb_handle* h, void* stream, const gb_gemm_desc* desc, const void* a, const void* b, void* c,
+            const gb_epilogue* epilogue, void* workspace, size_t workspace_bytes);
+
+/* ---- implicit-GEMM convolution ---------------------------------------------------------------- */
+/* Forward: replaces `Gpu.convImplicitForward` (src/gpu/gpu.zig:926-929), `Gpu.convF32Forward`
+ * (:789-826), the im2col+GEMM paths `chooseConvPath` picks for strided or narrow layers
+ * (src/autograd/autograd.zig:143-163) and `Executor.convNhwc` (src/onnx/gpu.zig:576-610).
+ * y[n,oy,ox,co] (+)= sum x[n, oy*s+ky*d-p, ox*s+kx*d-p, ci] * w[(ky*k+kx)*c+ci, co], then the epilogue. */
+int gb_conv_workspace(const gb_handle* h, int pass /*0 fprop, 1 dgrad, 2 wgrad*/, const gb_conv_desc* desc, size_t* bytes);
+int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* x, const void* w, void* y,
+                  const gb_epilogue* epilogue, void* workspace, size_t workspace_bytes);
+/* Input gradient: dx (+)= conv_transpose(dy, w).  Replaces `convImplicitForward` / `convF32Forward` on
+ * the reversed geometry with `packRotatedWeights` / `rotateWeightsF32` (gpu.zig:754-772, 856-866) and
+ * the `*Subsampled` kernels for strided layers (device.zig:1921-1925). */
+int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* w, void* dx,
+                  void* workspace, size_t workspace_bytes);
+/* Weight gradient: dw[(tap,ci),co] (+)= sum_positions patch(x)[pos,(tap,ci)] * dy[pos,co], f32 output.
+ * Replaces `Gpu.convImplicitWeightGrad` (gpu.zig:983-1022) and `convF32WeightGrad` + `transposeF32`
+ * (:775-787, :828-866).  Partials of the split over positions are combined in order. */
+int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* x, void* dw,
+                  void* workspace, size_t workspace_bytes);
+
+/* ---- data-parallel gradient mean -------------------------------------------------------------- */
+/* Replaces `Replicas.averageGrads` (src/nn/replicas.zig:57-91): the mean over replicas of one flat
+ * f32 gradient vector, in place, identical bits on every rank -- over NCCL (NVLink) instead of host
+ * memory.  unique_id is 128 bytes from gb_comm_unique_id on rank 0, shared by the caller. */
+int gb_comm_unique_id(void* out128);
+int gb_comm_create(int nranks, int rank, const void* unique_id128, int device_ordinal, gb_comm** out);
+int gb_allreduce_mean(gb_comm* comm, void* stream, float* grads, size_t count);
+int gb_comm_abort(gb_comm* comm);     /* the analogue of `Replicas.stop` (replicas.zig:36-38) */
+void gb_comm_destroy(gb_comm* comm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRADB200_H */
