@@ -108,6 +108,8 @@ __device__ __forceinline__ float load_as_f32(const GatherDesc& d, int64_t idx) {
 __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDesc& d, uint8_t* tile, uint32_t l,
                                             uint32_t line_major, uint32_t inner0, uint64_t batch_off) {
   uint8_t* line = tile + l * kLineBytes;
+  // 16-byte chunk j of line l lands at chunk j ^ (l % 8); MN-major tf32 tiles swizzle 32-byte chunks by l % 4.
+  const uint32_t sw = (p.tf32 && d.mn_major) ? ((l & 3) << 1) : (l & 7);
   const uint32_t epc = p.tf32 ? 4u : 8u;   // elements per 16-byte chunk
   GatherDesc src = d;
   src.base = (const uint8_t*)d.base + batch_off * (d.src_is_bf16 ? 2 : 4);
@@ -124,7 +126,7 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
       const uint16_t* ptr = (const uint16_t*)src.base + first;
       if (((uintptr_t)ptr & 15) == 0) {
         out = *(const uint4*)ptr;
-        *(uint4*)(line + ((chunk ^ (l & 7)) << 4)) = out;
+        *(uint4*)(line + ((chunk ^ sw) << 4)) = out;
         continue;
       }
     } else if (vec && !src.src_is_bf16) {
@@ -132,7 +134,7 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
       if (((uintptr_t)ptr & 15) == 0) {
         const float4 lo = *(const float4*)ptr;
         if (p.tf32) {
-          *(float4*)(line + ((chunk ^ (l & 7)) << 4)) = lo;
+          *(float4*)(line + ((chunk ^ sw) << 4)) = lo;
           continue;
         }
         const float4 hi = *(const float4*)(ptr + 4);
@@ -140,7 +142,7 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
         out.y = pack_bf16x2(lo.z, lo.w);
         out.z = pack_bf16x2(hi.x, hi.y);
         out.w = pack_bf16x2(hi.z, hi.w);
-        *(uint4*)(line + ((chunk ^ (l & 7)) << 4)) = out;
+        *(uint4*)(line + ((chunk ^ sw) << 4)) = out;
         continue;
       }
     }
@@ -156,7 +158,7 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
       out.z = pack_bf16x2(v[4], v[5]);
       out.w = pack_bf16x2(v[6], v[7]);
     }
-    *(uint4*)(line + ((chunk ^ (l & 7)) << 4)) = out;
+    *(uint4*)(line + ((chunk ^ sw) << 4)) = out;
   }
 }
 
@@ -433,6 +435,9 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       const uint32_t slice_lines = p.tf32 ? 8u : 16u;
       const uint32_t a_lbo = p.a_mn_major ? epl * kLineBytes : 16u, a_step = p.a_mn_major ? slice_lines * kLineBytes : 32u;
       const uint32_t b_lbo = p.b_mn_major ? epl * kLineBytes : 16u, b_step = p.b_mn_major ? slice_lines * kLineBytes : 32u;
+      // MN-major tf32 tiles use the 32-byte-chunk swizzle whose atom is four lines (512 bytes).
+      const uint32_t a_mode = (p.tf32 && p.a_mn_major) ? kSwizzle128Base32 : kSwizzle128, a_sbo = (p.tf32 && p.a_mn_major) ? 512u : 1024u;
+      const uint32_t b_mode = (p.tf32 && p.b_mn_major) ? kSwizzle128Base32 : kSwizzle128, b_sbo = (p.tf32 && p.b_mn_major) ? 512u : 1024u;
       uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
@@ -447,8 +452,8 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           const uint32_t b_addr = a_addr + kATileBytes;
 #pragma unroll
           for (uint32_t j = 0; j < 4; ++j) {
-            const uint64_t da = make_smem_desc_sw128(a_addr + j * a_step, a_lbo, 1024);
-            const uint64_t db = make_smem_desc_sw128(b_addr + j * b_step, b_lbo, 1024);
+            const uint64_t da = make_smem_desc(a_addr + j * a_step, a_lbo, a_sbo, a_mode);
+            const uint64_t db = make_smem_desc(b_addr + j * b_step, b_lbo, b_sbo, b_mode);
             const uint32_t acc = (kb > work.kb_begin || j > 0) ? 1u : 0u;
             if (p.tf32) mma_tf32_ss(tmem_d, da, db, idesc, acc);
             else mma_bf16_ss(tmem_d, da, db, idesc, acc);

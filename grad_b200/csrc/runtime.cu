@@ -56,7 +56,7 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 // Encodes a tiled map with 128-byte swizzle.  dims/strides/box follow the driver's convention: dims[0] is
 // the contiguous one, strides (bytes) start at dims[1].
 bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                const uint32_t* box) {
+                const uint32_t* box, bool swizzle_32b_chunks = false) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t gdims[5];
@@ -69,7 +69,8 @@ bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, co
     if (i + 1 < rank) gstrides[i] = strides_bytes[i];
   }
   const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<void*>(base),
-                        gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle_32b_chunks ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -112,7 +113,8 @@ bool dense_tma(CUtensorMap* map, const DenseOperand& o, bool smem_bf16, uint32_t
   // K-major: box = 128 bytes of K x tile_mn lines.  MN-major: box = 128 bytes of MN x epl K lines.
   const uint32_t box[3] = {epl, o.mn_major ? epl : tile_mn, 1};
   if (box[1] > 256) return false;
-  return encode_map(map, smem_bf16, o.base, 3, dims, strides, box);
+  // MN-major 32-bit tiles must use the 32-byte-chunk flavour of the 128-byte swizzle.
+  return encode_map(map, smem_bf16, o.base, 3, dims, strides, box, !smem_bf16 && o.mn_major);
 }
 
 uint32_t pick_stages(uint32_t bn) {
@@ -140,9 +142,9 @@ void pick_tiling(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint
   }
   const uint32_t tiles = tiles_m * ceil_div(n, bn);
   splits = 1;
-  if (allow_split && tiles < sms && k_blocks >= 8) splits = std::max(1u, std::min(ceil_div(sms, tiles), k_blocks / 4));
-  kbps = ceil_div(k_blocks, splits);
-  splits = ceil_div(k_blocks, kbps);
+  if (allow_split && tiles > 0 && tiles < sms && k_blocks >= 8) splits = std::max(1u, std::min(ceil_div(sms, tiles), k_blocks / 4));
+  kbps = std::max(1u, ceil_div(k_blocks, splits));
+  splits = std::max(1u, ceil_div(k_blocks, kbps));
 }
 
 int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_bn, const gb_epilogue* ep) {
@@ -167,10 +169,10 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
     p.k_blocks_total = ceil_div(p.k, 16);
     const uint32_t tiles = ceil_div(p.m, 64) * ceil_div(p.n, 64) * p.batch;
     uint32_t splits = 1;
-    if (allow_split && tiles < 2u * h->sm_count && p.k_blocks_total >= 32)
+    if (allow_split && tiles > 0 && tiles < 2u * h->sm_count && p.k_blocks_total >= 32)
       splits = std::max(1u, std::min(ceil_div(2u * h->sm_count, tiles), p.k_blocks_total / 16));
-    p.k_blocks_per_split = ceil_div(p.k_blocks_total, splits);
-    p.splits = ceil_div(p.k_blocks_total, p.k_blocks_per_split);
+    p.k_blocks_per_split = std::max(1u, ceil_div(p.k_blocks_total, splits));
+    p.splits = std::max(1u, ceil_div(p.k_blocks_total, p.k_blocks_per_split));
     p.tiles_m = ceil_div(p.m, 64);
     p.tiles_n = ceil_div(p.n, 64);
     p.bn = 64;
@@ -318,14 +320,14 @@ bool patch_box(uint32_t count, uint32_t grid_h, uint32_t grid_w, uint32_t& bw, u
 
 // 4-D map over an NHWC tensor {channels, width, height, images} with a box of `epl` channels x (bw, bh, bn).
 bool nhwc_tma(CUtensorMap* map, const void* base, bool smem_bf16, uint32_t dtype, uint32_t channels, uint32_t c_step, uint32_t width,
-              uint32_t height, uint32_t images, uint32_t epl, uint32_t bw, uint32_t bh, uint32_t bn) {
+              uint32_t height, uint32_t images, uint32_t epl, uint32_t bw, uint32_t bh, uint32_t bn, bool mn_major = false) {
   const uint32_t es = smem_bf16 ? 2 : 4;
   if ((dtype == GB_BF16) != smem_bf16) return false;
   if (channels % epl != 0 || !aligned16(base) || ((uint64_t)c_step * es) % 16 != 0) return false;
   const uint64_t dims[4] = {channels, width, height, images};
   const uint64_t strides[3] = {(uint64_t)c_step * es, (uint64_t)c_step * es * width, (uint64_t)c_step * es * width * height};
   const uint32_t box[4] = {epl, bw, bh, bn};
-  return encode_map(map, smem_bf16, base, 4, dims, strides, box);
+  return encode_map(map, smem_bf16, base, 4, dims, strides, box, !smem_bf16 && mn_major);
 }
 
 int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* act, const void* other, void* out,
@@ -406,7 +408,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     if (plan.tensor) {
       p.a_kind = gb::kGather;
       if (g.stride == 1 && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
-          nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n))
+          nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, true))
         p.a_kind = gb::kPatchMN;
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
     }

@@ -112,17 +112,20 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t columns) {
 }
 
 // ---- tcgen05.mma ----------------------------------------------------------------------------------
-// Shared-memory matrix descriptor for a 128-byte-swizzled operand tile: lines of 128 bytes, eight
-// lines per 1024-byte swizzle atom.  Field layout (PTX ISA, tcgen05 shared memory descriptor):
-//   [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
-//   [46,48) version = 1 on sm_100, [61,64) swizzle mode (2 = 128 B).
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+// Shared-memory matrix descriptor for an operand tile made of 128-byte lines.  Field layout (PTX ISA,
+// tcgen05 shared memory descriptor): [0,14) start address >> 4, [16,30) leading byte offset >> 4,
+// [32,46) stride byte offset >> 4, [46,48) version = 1 on sm_100, [61,64) swizzle mode.
+//   mode 2: 128-byte swizzle of 16-byte chunks, eight lines per 1024-byte atom (every bf16 tile, K-major tf32)
+//   mode 1: 128-byte swizzle of 32-byte chunks, four lines per 512-byte atom -- the only layout the
+//           tensor core accepts for MN-major 32-bit (tf32) operands
+constexpr uint32_t kSwizzle128 = 2, kSwizzle128Base32 = 1;
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes, uint32_t mode) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
   d |= (uint64_t)((leading_bytes >> 4) & 0x3FFFu) << 16;
   d |= (uint64_t)((stride_bytes >> 4) & 0x3FFFu) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)mode << 61;
   return d;
 }
 

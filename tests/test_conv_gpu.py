@@ -1,0 +1,218 @@
+"""GPU parity of the implicit-GEMM convolution (forward, input gradient, weight gradient) against the CPU
+oracle, through the C ABI.
+
+Geometries follow the reference's conv tests (tests/autograd.zig:2002-2072: 2x5x5 inputs, k in {1,2,3},
+stride {1,2,3}, pad {0,1,2}, dilation 2, channels 2..128) plus the ResNet-14 layer shapes of the benchmark
+configuration at a reduced batch.  Tolerances: relative Frobenius error <= 1e-5 (strict f32), 5e-3 (TF32),
+2e-2 (bf16) against the f32 oracle on the same seeded inputs.
+"""
+import numpy as np
+import pytest
+
+from tests.util import TOL_BF16, TOL_F32, TOL_TF32, rel_fro, seeded, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+# (n, h, w, c, k, c_out, stride, pad, dilation)
+SMALL = [
+    (2, 5, 5, 2, 3, 3, 1, 0, 1), (2, 5, 5, 4, 3, 8, 1, 1, 1), (2, 5, 5, 8, 3, 4, 2, 1, 1), (2, 5, 5, 2, 3, 3, 2, 0, 1),
+    (2, 5, 5, 3, 3, 4, 1, 2, 2), (2, 5, 5, 2, 2, 4, 1, 0, 2), (2, 5, 5, 3, 1, 4, 1, 1, 1), (2, 5, 5, 64, 3, 32, 1, 1, 1),
+    (2, 5, 5, 64, 3, 64, 1, 0, 1), (2, 5, 5, 128, 3, 64, 1, 1, 1), (2, 5, 5, 64, 1, 128, 1, 0, 1), (2, 7, 6, 5, 3, 7, 3, 1, 1),
+    (1, 9, 8, 4, 5, 6, 2, 2, 1),
+]
+# ResNet-14 layer shapes (examples/cifar/main.zig:15-34) at batch 4, plus the strided transition variants.
+RESNET = [
+    (4, 32, 32, 3, 3, 64, 1, 1, 1),      # stem: K = 27
+    (4, 32, 32, 64, 3, 64, 1, 1, 1),
+    (4, 16, 16, 64, 3, 128, 1, 1, 1),
+    (4, 16, 16, 128, 3, 128, 1, 1, 1),
+    (4, 16, 16, 64, 1, 128, 1, 0, 1),    # 1x1 shortcut
+    (4, 8, 8, 128, 3, 256, 1, 1, 1),
+    (4, 8, 8, 256, 3, 256, 1, 1, 1),
+    (4, 32, 32, 64, 3, 128, 2, 1, 1),    # strided transition
+    (4, 32, 32, 64, 1, 128, 2, 0, 1),    # strided shortcut
+    (3, 16, 16, 128, 3, 256, 2, 1, 1),
+]
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    import grad_b200
+
+    g = grad_b200.Gpu(0)
+    yield g
+    g.check_status()
+    g.close()
+
+
+def _dims(case):
+    from oracle.binding import ConvDims
+
+    n, h, w, c, k, c_out, s, p, d = case
+    return ConvDims(n=n, h=h, w=w, c=c, k=k, stride=s, pad=p, dilation=d, c_out=c_out)
+
+
+def _geo(case):
+    from grad_b200 import conv_geometry
+
+    n, h, w, c, k, c_out, s, p, d = case
+    return conv_geometry(n, h, w, c, k, c_out, s, p, d)
+
+
+def _inputs(case, seed):
+    d = _dims(case)
+    x = seeded(seed, d.n, d.h, d.w, d.c)
+    w = (seeded(seed + 1, d.taps, d.c_out) * np.float32(np.sqrt(2.0 / d.taps))).astype(np.float32)   # He-normal
+    dy = seeded(seed + 2, d.n, d.out_h, d.out_w, d.c_out)
+    return d, x, w, dy
+
+
+def _run_all(gpu, case, math, tol, bf16_storage=False, seed=100):
+    import torch
+    from oracle import binding as orc
+
+    d, x, w, dy = _inputs(case, seed)
+    geo = _geo(case)
+    threads = orc.host_threads()
+    want_y = orc.conv_forward(x, w, d, threads)
+    want_dx = orc.conv_input_grad(dy, w, d, threads)
+    want_dw = orc.conv_weight_grad(x, dy, d, threads)
+    act = torch.bfloat16 if bf16_storage else torch.float32
+    dx_, dw_ = to_dev(x, bf16_storage), to_dev(w)   # weights stay f32 masters (src/autograd/autograd.zig:955)
+    ddy = to_dev(dy, bf16_storage)
+    y = torch.full((d.n, d.out_h, d.out_w, d.c_out), 5.0, dtype=act, device="cuda")
+    gpu.convForward(dx_, dw_, y, geo, math=math)
+    gx = torch.zeros((d.n, d.h, d.w, d.c), dtype=act, device="cuda")
+    gpu.convInputGrad(ddy, dw_, gx, geo, accumulate=True, math=math)
+    gw = torch.zeros((d.taps, d.c_out), dtype=torch.float32, device="cuda")
+    gpu.convWeightGrad(ddy, dx_, gw, geo, math=math)
+    torch.cuda.synchronize()
+    errs = (rel_fro(to_host(y), want_y), rel_fro(to_host(gx), want_dx), rel_fro(to_host(gw), want_dw))
+    assert max(errs) <= tol, (case, math, bf16_storage, errs)
+    return errs
+
+
+@pytest.mark.parametrize("case", SMALL)
+def test_small_geometries_strict_f32(gpu, case):
+    _run_all(gpu, case, 0, TOL_F32)
+
+
+@pytest.mark.parametrize("case", SMALL)
+def test_small_geometries_tf32(gpu, case):
+    _run_all(gpu, case, 1, TOL_TF32)
+
+
+@pytest.mark.parametrize("case", SMALL)
+def test_small_geometries_bf16_math_on_f32_storage(gpu, case):
+    _run_all(gpu, case, 2, TOL_BF16)
+
+
+@pytest.mark.parametrize("case", SMALL)
+def test_small_geometries_bf16_storage(gpu, case):
+    _run_all(gpu, case, 2, TOL_BF16, bf16_storage=True)
+
+
+@pytest.mark.parametrize("case", RESNET)
+@pytest.mark.parametrize("math,tol,half", [(0, TOL_F32, False), (1, TOL_TF32, False), (2, TOL_BF16, False), (2, TOL_BF16, True)])
+def test_resnet_layer_shapes(gpu, case, math, tol, half):
+    _run_all(gpu, case, math, tol, bf16_storage=half, seed=200)
+
+
+def test_bf16_conv_agrees_with_f32_conv_within_reference_bounds(gpu):
+    """tests/autograd.zig:1309-1359: 2x8x8x64 -> 32, pad 1; y, dX, dW element-wise bounds."""
+    import torch
+    from oracle import binding as orc
+
+    case = (2, 8, 8, 64, 3, 32, 1, 1, 1)
+    d = _dims(case)
+    geo = _geo(case)
+    x, w, g = seeded(37, 2, 8, 8, 64), seeded(38, 576, 32) * np.float32(0.05), seeded(39, 2, 8, 8, 32)
+    wide_y = orc.conv_forward(x, w, d)
+    wide_dx = orc.conv_input_grad(g, w, d)
+    wide_dw = orc.conv_weight_grad(x, g, d)
+    hx, hg, dw_ = to_dev(x, True), to_dev(g, True), to_dev(w)
+    y = torch.empty((2, 8, 8, 32), dtype=torch.bfloat16, device="cuda")
+    gx = torch.zeros((2, 8, 8, 64), dtype=torch.bfloat16, device="cuda")
+    gw = torch.zeros((576, 32), dtype=torch.float32, device="cuda")
+    gpu.convForward(hx, dw_, y, geo)
+    gpu.convInputGrad(hg, dw_, gx, geo)
+    gpu.convWeightGrad(hg, hx, gw, geo)
+    torch.cuda.synchronize()
+    assert np.all(np.abs(wide_y - to_host(y)) <= 0.08 + 0.02 * np.abs(wide_y))
+    assert np.all(np.abs(wide_dx - to_host(gx)) <= 0.25 + 0.03 * np.abs(wide_dx))
+    assert np.all(np.abs(wide_dw - to_host(gw)) <= 0.6 + 0.03 * np.abs(wide_dw))
+
+
+@pytest.mark.parametrize("math,tol,half", [(0, TOL_F32, False), (1, TOL_TF32, False), (2, TOL_BF16, True)])
+def test_fused_bias_residual_relu_epilogue(gpu, math, tol, half):
+    """Conv + bias -> Add(residual) -> Relu in one launch == the executor's separate nodes (src/onnx/gpu.zig:608, 372-377)."""
+    import torch
+    from oracle import binding as orc
+
+    case = (3, 16, 16, 64, 3, 128, 1, 1, 1)
+    d, x, w, _ = _inputs(case, 300)
+    geo = _geo(case)
+    bias = seeded(303, d.c_out) * np.float32(0.1)
+    res = seeded(304, d.n, d.out_h, d.out_w, d.c_out)
+    if half:
+        res = orc.bf16_round(res)
+    want = orc.conv_forward(x, w, d, orc.host_threads())
+    want = orc.relu(orc.bias_act(want, bias, False) + res)
+    act = torch.bfloat16 if half else torch.float32
+    y = torch.empty((d.n, d.out_h, d.out_w, d.c_out), dtype=act, device="cuda")
+    from grad_b200 import Epilogue
+
+    gpu.convForward(to_dev(x, half), to_dev(w, half), y, geo, epilogue=Epilogue(to_dev(bias), to_dev(res, half), True), math=math)
+    torch.cuda.synchronize()
+    got = to_host(y)
+    assert rel_fro(got, want) <= tol
+    assert (got >= 0).all()
+
+
+def test_accumulate_semantics(gpu):
+    """Gradients are `+=` into caller-zeroed buffers (autograd.zig:49-50): two calls add up; forward stores."""
+    import torch
+
+    case = (2, 8, 8, 64, 3, 64, 1, 1, 1)
+    d, x, w, dy = _inputs(case, 400)
+    geo = _geo(case)
+    for math in (0, 2):
+        gw = torch.zeros((d.taps, d.c_out), device="cuda")
+        gpu.convWeightGrad(to_dev(dy), to_dev(x), gw, geo, math=math)
+        once = to_host(gw).copy()
+        gpu.convWeightGrad(to_dev(dy), to_dev(x), gw, geo, math=math)
+        torch.cuda.synchronize()
+        assert rel_fro(to_host(gw), 2 * once) <= 1e-6
+        gx = torch.zeros((d.n, d.h, d.w, d.c), device="cuda")
+        gpu.convInputGrad(to_dev(dy), to_dev(w), gx, geo, accumulate=True, math=math)
+        first = to_host(gx).copy()
+        gpu.convInputGrad(to_dev(dy), to_dev(w), gx, geo, accumulate=False, math=math)
+        torch.cuda.synchronize()
+        assert rel_fro(to_host(gx), first) <= 1e-6
+
+
+@pytest.mark.parametrize("case", [(128, 32, 32, 64, 3, 64, 1, 1, 1), (128, 16, 16, 128, 3, 128, 1, 1, 1), (128, 8, 8, 256, 3, 256, 1, 1, 1),
+                                  (128, 32, 32, 64, 3, 128, 2, 1, 1), (128, 32, 32, 3, 3, 64, 1, 1, 1)])
+def test_full_size_adjoint_identity(gpu, case):
+    """At the benchmark's batch 128 the oracle is too slow, but the three passes are adjoints of one another:
+    <conv(x, w), dy> == <x, dgrad(dy, w)> == <w, wgrad(x, dy)>.  Checked in bf16 with f32 sums on the device."""
+    import torch
+
+    n, h, w_, c, k, c_out, s, p, dil = case
+    geo = _geo(case)
+    gen = torch.Generator(device="cuda").manual_seed(1234)
+    x = torch.randn((n, h, w_, c), generator=gen, device="cuda").bfloat16()
+    w = (torch.randn((k * k * c, c_out), generator=gen, device="cuda") * (2.0 / (k * k * c)) ** 0.5).bfloat16()
+    dy = torch.randn((n, geo.out_h, geo.out_w, c_out), generator=gen, device="cuda").bfloat16()
+    y = torch.empty_like(dy, dtype=torch.float32)
+    gx = torch.zeros(x.shape, dtype=torch.float32, device="cuda")
+    gw = torch.zeros(w.shape, dtype=torch.float32, device="cuda")
+    gpu.convForward(x, w, y, geo)
+    gpu.convInputGrad(dy, w, gx, geo)
+    gpu.convWeightGrad(dy, x, gw, geo)
+    torch.cuda.synchronize()
+    a = (y.double() * dy.double()).sum().item()
+    b = (gx.double() * x.double()).sum().item()
+    c_ = (gw.double() * w.double()).sum().item()
+    scale = (y.double().norm() * dy.double().norm()).item()
+    assert abs(a - b) <= 1e-4 * scale and abs(a - c_) <= 1e-4 * scale, (a, b, c_, scale)
