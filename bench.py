@@ -1,0 +1,292 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-contraction path: bf16 GEMM TFLOP/s at M = N = K = 8192 (fused bias + ReLU).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--size S] [--layout NN|NT|TN]
+
+One step is one pass of the hot path over one batch of synthetic input: one 8192 x 8192 x 8192 product
+with N(0,1) bf16 operands, f32 accumulation, y = relu(A*B + bias) stored as bf16.  With --gpus N every rank
+runs an independent replica on its own GPU (the GEMM sweep does not shard; no collective on the data
+path), the timed region is bracketed by a barrier and a device synchronise, and the time is the maximum over
+ranks.  Rank 0 prints ONE JSON line.
+
+  value     whole-job TFLOP/s with operands resident in HBM (CUDA events around exactly K steps)
+  e2e       the same metric through the public `Gpu.upload` / `Gpu.matmul` / `Gpu.download` calls with
+            pinned HOST buffers: both operands go host->device and the result device->host every step
+  roofline  tensor bound: 2*M*N*K per launch / mean launch time, against the measured cuBLAS bf16 peak
+  cpu_baseline  the CPU oracle (restatement of grad's `matmulTiled`) on a bounded row slice, rank 0, N = 1
+  --impl reference  times that CPU path alone (the reference is Zig and cannot be built here)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "bf16 GEMM TFLOP/s (M=N=K=8192, fused bias+ReLU)"
+UNIT = "TFLOP/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", type=int, default=8192)
+    ap.add_argument("--layout", default="NN", choices=["NN", "NT", "TN"])
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.dev = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.dev, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nvml = None
+
+    def _run(self):
+        n = self.nvml
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "hw_power_brake_slowdown": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(n.nvmlDeviceGetClockInfo(self.dev, n.NVML_CLOCK_SM))
+                try:
+                    mask = n.nvmlDeviceGetCurrentClocksEventReasons(self.dev)
+                except Exception:
+                    mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.dev)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        if self.nvml is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def cpu_sample(size: int, rows: int, reps: int):
+    """Times the CPU oracle on `rows` rows of the size^3 product (same N, K, same fused epilogue); TFLOP/s."""
+    import numpy as np
+    from oracle import binding as orc
+
+    rng = np.random.default_rng(1235)
+    a = orc.bf16_round(rng.standard_normal((rows, size), dtype=np.float32))
+    b = orc.bf16_round(rng.standard_normal((size, size), dtype=np.float32))
+    bias = rng.standard_normal(size, dtype=np.float32)
+    threads = orc.host_threads()
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        out = orc.matmul_tiled(a, b, rows, size, size, threads=threads)
+        out = orc.bias_act(out, bias, True)
+        best = min(best, time.perf_counter() - t0)
+    flops = 2.0 * rows * size * size
+    return flops / best / 1e12, min(threads, 16), best
+
+
+def run_reference(args):
+    """The reference arm: grad's own CPU implementation of the path (its Zig cannot be built here, so the C++
+    restatement in oracle/ stands in), every host thread it can use, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    size = args.size
+    rows = 512 if size >= 4096 else min(size, 1024)
+    steps = max(1, min(args.steps, 5))
+    warmup = max(1, min(args.warmup, 1))
+    cpu_sample(size, rows, warmup)
+    t0 = time.perf_counter()
+    value, cores, _ = cpu_sample(size, rows, steps)
+    total = time.perf_counter() - t0
+    sample = f"{rows} of {size} rows of A per step (N=K={size}), best of {steps} steps; oracle port of grad's matmulTiled"
+    line = {"impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": warmup, "ms_per_step": round(total / steps * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 (bf16-rounded operands)", "data": "synthetic",
+            "config": {"workload": f"GEMM sweep M=N=K={size} NN + bias + ReLU, CPU tiled matmul", "sample": sample},
+            "cpu_baseline": {"value": round(value, 4), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": round(value, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    import grad_b200
+    from grad_b200 import Epilogue, MatmulOpts, MatmulShape
+
+    gpu = grad_b200.Gpu(local)
+    size = args.size
+    m = n = k = size
+    ta, tb = args.layout == "TN", args.layout == "NT"
+    gen = torch.Generator(device="cuda").manual_seed(1234 + 1 + rank)   # seed = 1234 + config index (+ rank)
+    a = torch.randn((k, m) if ta else (m, k), generator=gen, device="cuda").bfloat16()
+    b = torch.randn((n, k) if tb else (k, n), generator=gen, device="cuda").bfloat16()
+    bias = torch.randn(n, generator=gen, device="cuda")
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    shape, opts, ep = MatmulShape(m, n, k), MatmulOpts(ta, tb), Epilogue(bias, None, True)
+
+    def step():
+        gpu.matmul(a, b, out, shape, opts, epilogue=ep)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    plan = gpu.last_plan()
+
+    sampler = ClockSampler(local)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches0 = gpu.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if world > 1:
+        dist.barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = gpu.launches - launches0
+    gpu.check_status()
+    if world > 1:
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    flops = 2.0 * m * n * k
+    value = world * flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end: pinned host operands in, host result out, every step ----
+    ha, hb = a.cpu().pin_memory(), b.cpu().pin_memory()
+    hout = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+    da, db = torch.empty_like(a), torch.empty_like(b)
+
+    def e2e_step():
+        gpu.upload(da, ha)
+        gpu.upload(db, hb)
+        gpu.matmul(da, db, out, shape, opts, epilogue=ep)
+        gpu.download(hout, out)
+
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * flops / (e2e_ms / args.e2e_steps * 1e-3) / 1e12
+    h2d = ha.numel() * 2 + hb.numel() * 2
+    d2h = hout.numel() * 2
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    timed_s = ms_total * 1e-3
+    sustained = timed_s > 1.0
+    peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+    achieved = flops / (ms_step * 1e-3) / 1e12   # per launch on one GPU (max over ranks)
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            traffic = json.load(f).get(f"gemm_bf16_{size}_{args.layout}")
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"GEMM sweep M=N=K={size} {args.layout}, N(0,1) bf16 operands, f32 accumulate, fused bias+ReLU, bf16 out",
+                   "parallelism": f"replicas x{world} (no collective on the data path)",
+                   "l2": "operands + result = %d MB per step, larger than the 126 MB L2" % ((a.numel() + b.numel() + out.numel()) * 2 // 2**20),
+                   "tile": f"{plan['tile_m']}x{plan['tile_n']}", "stages": plan["stages"], "splits": plan["splits"]},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": round(e2e_ms / args.e2e_steps, 3)},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peak, "unit": UNIT, "frac": round(achieved / peak, 4),
+                     "traffic": traffic, "peak_source": f"{peak_kind} cuBLAS bf16 {'sustained' if sustained else 'burst'}",
+                     "frac_of_nominal_2250": round(achieved / 2250.0, 4)},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        rows = 4096 if size >= 4096 else size
+        cpu_value, cores, secs = cpu_sample(size, rows, 2)
+        line["cpu_baseline"] = {"value": round(cpu_value, 4), "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"{rows} of {size} rows of A (N=K={size}), best of 2, {secs:.1f} s each; "
+                                          "C++ restatement of grad's matmulTiled + bias + ReLU"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -53,6 +53,11 @@ class ConvDesc(C.Structure):
                 ("accumulate", C.c_uint8), ("deterministic", C.c_uint8), ("reserved", C.c_uint8 * 2)]
 
 
+class PlanInfo(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("tensor_path", "a_kind", "b_kind", "tile_m", "tile_n", "stages", "splits", "k_blocks",
+                                          "work_items", "kernel_launches")]
+
+
 # name -> (argtypes, restype): exactly the declarations of include/gradb200.h
 SIGNATURES = {
     "gb_create": ([C.c_int, C.POINTER(C.c_void_p)], C.c_int),
@@ -62,6 +67,7 @@ SIGNATURES = {
     "gb_last_cuda_error": ([C.c_void_p], C.c_int),
     "gb_last_status": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)], C.c_int),
     "gb_sm_count": ([C.c_void_p], C.c_int),
+    "gb_last_plan": ([C.c_void_p, C.POINTER(PlanInfo)], C.c_int),
     "gb_gemm_workspace": ([C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_size_t)], C.c_int),
     "gb_gemm": ([C.c_void_p, C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Epilogue), C.c_void_p,
                  C.c_size_t], C.c_int),

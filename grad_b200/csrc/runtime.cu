@@ -23,6 +23,7 @@ struct gb_handle {
   int sm_count = 0;
   int last_cuda = 0;
   uint32_t* status = nullptr;   // device word the kernels report bounded-wait failures into
+  gb_plan_info last_plan = {};
 };
 
 namespace {
@@ -261,6 +262,17 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
       p.partial = (float*)workspace;
     }
   }
+  gb_plan_info& info = h->last_plan;
+  info.tensor_path = plan.tensor;
+  info.a_kind = plan.tensor ? p.a_kind : (uint32_t)gb::kGather;
+  info.b_kind = plan.tensor ? p.b_kind : (uint32_t)gb::kGather;
+  info.tile_m = plan.tensor ? 128 : 64;
+  info.tile_n = p.bn;
+  info.stages = p.stages;
+  info.splits = p.splits;
+  info.k_blocks = p.k_blocks_total;
+  info.work_items = p.tiles_m * p.tiles_n * p.batch * p.splits;
+  info.kernel_launches = p.k == 0 ? 1 : (p.splits > 1 ? 2 : 1);
   cudaError_t e;
   if (p.k == 0) {
     // An empty contraction is a zero product: only the epilogue runs (through the reduce kernel, zero parts).
@@ -480,6 +492,12 @@ int gb_last_status(gb_handle* h, void* stream, uint32_t* device_status) {
   if (e != cudaSuccess) return cuda_fail(h, e);
   if (device_status) *device_status = word;
   return word == 0 ? GB_OK : GB_ERR_TIMEOUT;
+}
+
+int gb_last_plan(const gb_handle* h, gb_plan_info* out) {
+  if (!h || !out) return GB_ERR_INVALID;
+  *out = h->last_plan;
+  return GB_OK;
 }
 
 int gb_gemm_workspace(const gb_handle* h, const gb_gemm_desc* desc, size_t* bytes) {

@@ -141,6 +141,24 @@ class Gpu:
         abi.check(rc, f"gb_last_status (device status {word.value})")
         return word.value
 
+    def _count(self) -> int:
+        info = abi.PlanInfo()
+        self.lib.gb_last_plan(self.handle, C.byref(info))
+        return int(info.kernel_launches)
+
+    def last_plan(self) -> dict:
+        """Tile width, stages, K split and operand paths of the last compute call (gb_last_plan)."""
+        info = abi.PlanInfo()
+        abi.check(self.lib.gb_last_plan(self.handle, C.byref(info)), "gb_last_plan")
+        return {name: int(getattr(info, name)) for name, _ in abi.PlanInfo._fields_}
+
+    # ---- host <-> device, `Gpu.upload` / `Gpu.download` (src/gpu/gpu.zig:412-431) ---------------------
+    def upload(self, dst: torch.Tensor, src: torch.Tensor):
+        dst.copy_(src, non_blocking=True)
+
+    def download(self, dst: torch.Tensor, src: torch.Tensor):
+        dst.copy_(src, non_blocking=True)
+
     def _epilogue(self, ep: Optional[Epilogue]):
         if ep is None:
             return None
@@ -178,7 +196,7 @@ class Gpu:
         rc = self.lib.gb_gemm(self.handle, self._stream(), C.byref(d), _ptr(a), _ptr(b), _ptr(out), self._epilogue(epilogue),
                               _ptr(ws), need.value)
         abi.check(rc, "gb_gemm")
-        self.launches += 1
+        self.launches += self._count()
 
     # ---- convolution ------------------------------------------------------------------------------
     def _conv_desc(self, geo: ConvGeometry, x_like, w_like, y_like, math: Optional[int], accumulate: bool) -> abi.ConvDesc:
@@ -207,7 +225,7 @@ class Gpu:
         rc = self.lib.gb_conv_fprop(self.handle, self._stream(), C.byref(d), _ptr(x), _ptr(w), _ptr(out), self._epilogue(epilogue),
                                     _ptr(ws), n)
         abi.check(rc, "gb_conv_fprop")
-        self.launches += 1
+        self.launches += self._count()
 
     convImplicitForward = convForward
     convF32Forward = convForward
@@ -220,7 +238,7 @@ class Gpu:
         ws, n = self._conv_ws(abi.PASS_DGRAD, d)
         rc = self.lib.gb_conv_dgrad(self.handle, self._stream(), C.byref(d), _ptr(dy), _ptr(w), _ptr(dx), _ptr(ws), n)
         abi.check(rc, "gb_conv_dgrad")
-        self.launches += 1
+        self.launches += self._count()
 
     def convWeightGrad(self, dy, x, out, geo: ConvGeometry, math: Optional[int] = None, accumulate: bool = True):
         """`convImplicitWeightGrad` (gpu.zig:983-1022) / `convF32WeightGrad` (:828-866): out (taps, c_out) f32 += ...;
@@ -229,7 +247,7 @@ class Gpu:
         ws, n = self._conv_ws(abi.PASS_WGRAD, d)
         rc = self.lib.gb_conv_wgrad(self.handle, self._stream(), C.byref(d), _ptr(dy), _ptr(x), _ptr(out), _ptr(ws), n)
         abi.check(rc, "gb_conv_wgrad")
-        self.launches += 1
+        self.launches += self._count()
 
     convImplicitWeightGrad = convWeightGrad
     convF32WeightGrad = convWeightGrad

@@ -112,6 +112,17 @@ int gb_last_status(gb_handle* h, void* stream, uint32_t* device_status);
 /* Multiprocessor count the tile/split heuristics use (src/gpu/gpu.zig `multiprocessors`). */
 int gb_sm_count(const gb_handle* h);
 
+/* How the last gb_gemm / gb_conv_* call on this handle was cut up -- the counterpart of reading
+ * `gemmTile`, `splits` and `forwardPlan` in src/gpu/gpu.zig:659-697, 890-913 when profiling.
+ * operand kinds: 0 TMA K-major tile, 1 TMA MN-major tile, 2 TMA NHWC patch box (K-major), 3 TMA NHWC
+ * patch box (MN-major, weight gradient), 4 TMA weight box (input gradient), 5 gathered with plain loads. */
+typedef struct {
+  uint32_t tensor_path;     /* 1 = tcgen05 kernel, 0 = strict-f32 CUDA-core kernel */
+  uint32_t a_kind, b_kind;
+  uint32_t tile_m, tile_n, stages, splits, k_blocks, work_items, kernel_launches;
+} gb_plan_info;
+int gb_last_plan(const gb_handle* h, gb_plan_info* out);
+
 /* ---- matmul family ---------------------------------------------------------------------------- */
 /* Replaces `Gpu.matmul` (src/gpu/gpu.zig:642-679), `Gpu.matmulTensor` / `packMatrix` / `matmulPacked`
  * (:1066-1073, :711-722, :1036-1064) and the kernels `sgemm*` / `sgemmTensor`
