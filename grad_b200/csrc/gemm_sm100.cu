@@ -17,6 +17,10 @@
 // descriptors, no packed or transposed copies) and the implicit-GEMM convolutions (forward, input
 // gradient, weight gradient) whose activation operand is fetched as 4-D TMA boxes of the NHWC tensor.
 // Replaces grad's `tileGemm` (src/gpu/device.zig:1162-1708) and `Gemm` (:122-201) tensor paths.
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+
 #include "gemm_sm100.cuh"
 #include "sm100_ptx.cuh"
 
@@ -196,17 +200,30 @@ __device__ __forceinline__ void patch_coords(const GemmParams& p, uint32_t p0, u
   }
 }
 
-__device__ __forceinline__ void issue_a(const GemmParams& p, const CUtensorMap* tmap, uint8_t* tile, uint64_t* bar,
-                                        const Work& w, uint32_t kb) {
+// One tile load, either on this CTA's own barrier or, for a CTA pair, on the pair leader's barrier.
+template <bool kPair>
+__device__ __forceinline__ void load_3d(uint8_t* dst, const CUtensorMap* tmap, uint64_t* bar, uint32_t pair_bar, int32_t x, int32_t y, int32_t z) {
+  if constexpr (kPair) tma_pair_load_3d(smem_u32(dst), tmap, pair_bar, x, y, z);
+  else tma_load_3d(dst, tmap, bar, x, y, z);
+}
+template <bool kPair>
+__device__ __forceinline__ void load_4d(uint8_t* dst, const CUtensorMap* tmap, uint64_t* bar, uint32_t pair_bar, int32_t x, int32_t y, int32_t z, int32_t w) {
+  if constexpr (kPair) tma_pair_load_4d(smem_u32(dst), tmap, pair_bar, x, y, z, w);
+  else tma_load_4d(dst, tmap, bar, x, y, z, w);
+}
+
+// Loads the 128 A rows that start at m0 for K block kb.
+template <bool kPair>
+__device__ __forceinline__ void issue_a(const GemmParams& p, const CUtensorMap* tmap, uint8_t* tile, uint64_t* bar, uint32_t pair_bar,
+                                        const Work& w, uint32_t kb, uint32_t m0) {
   const uint32_t epl = p.tf32 ? 32u : 64u;
-  const uint32_t m0 = w.m_tile * kBM;
   switch (p.a_kind) {
     case kDenseK:
-      tma_load_3d(tile, tmap, bar, (int32_t)(kb * epl), (int32_t)m0, (int32_t)w.batch);
+      load_3d<kPair>(tile, tmap, bar, pair_bar, (int32_t)(kb * epl), (int32_t)m0, (int32_t)w.batch);
       break;
     case kDenseMN:
       for (uint32_t j = 0; j < kBM / epl; ++j)
-        tma_load_3d(tile + j * epl * kLineBytes, tmap, bar, (int32_t)(m0 + j * epl), (int32_t)(kb * epl), (int32_t)w.batch);
+        load_3d<kPair>(tile + j * epl * kLineBytes, tmap, bar, pair_bar, (int32_t)(m0 + j * epl), (int32_t)(kb * epl), (int32_t)w.batch);
       break;
     case kPatchK: {
       // K runs over (tap, channel block); the box is 128 positions x 128 bytes of channels.
@@ -215,7 +232,7 @@ __device__ __forceinline__ void issue_a(const GemmParams& p, const CUtensorMap* 
       const uint32_t tap = kb / cblocks, cb = kb - tap * cblocks;
       int32_t w0, h0, n0;
       patch_coords(p, m0, tap, w0, h0, n0);
-      tma_load_4d(tile, tmap, bar, (int32_t)(cb * epl), w0, h0, n0);
+      load_4d<kPair>(tile, tmap, bar, pair_bar, (int32_t)(cb * epl), w0, h0, n0);
       break;
     }
     case kPatchMN: {
@@ -227,7 +244,7 @@ __device__ __forceinline__ void issue_a(const GemmParams& p, const CUtensorMap* 
         const uint32_t c0 = kk0 >= taps * p.geo.c ? 0u : kk0 - tap * p.geo.c;
         int32_t w0, h0, n0;
         patch_coords(p, kb * epl, tap, w0, h0, n0);
-        tma_load_4d(tile + j * epl * kLineBytes, tmap, bar, (int32_t)c0, w0, h0, n0);
+        load_4d<kPair>(tile + j * epl * kLineBytes, tmap, bar, pair_bar, (int32_t)c0, w0, h0, n0);
       }
       break;
     }
@@ -236,22 +253,23 @@ __device__ __forceinline__ void issue_a(const GemmParams& p, const CUtensorMap* 
   }
 }
 
-__device__ __forceinline__ void issue_b(const GemmParams& p, const CUtensorMap* tmap, uint8_t* tile, uint64_t* bar,
-                                        const Work& w, uint32_t kb) {
+// Loads `b_lines` lines of B (N values n0 .. n0 + b_lines) for K block kb.
+template <bool kPair>
+__device__ __forceinline__ void issue_b(const GemmParams& p, const CUtensorMap* tmap, uint8_t* tile, uint64_t* bar, uint32_t pair_bar,
+                                        const Work& w, uint32_t kb, uint32_t n0, uint32_t b_lines) {
   const uint32_t epl = p.tf32 ? 32u : 64u;
-  const uint32_t n0 = w.n_tile * p.bn;
   switch (p.b_kind) {
     case kDenseK:
-      tma_load_3d(tile, tmap, bar, (int32_t)(kb * epl), (int32_t)n0, (int32_t)w.batch);
+      load_3d<kPair>(tile, tmap, bar, pair_bar, (int32_t)(kb * epl), (int32_t)n0, (int32_t)w.batch);
       break;
     case kDenseMN:
-      for (uint32_t j = 0; j < p.bn / epl; ++j)
-        tma_load_3d(tile + j * epl * kLineBytes, tmap, bar, (int32_t)(n0 + j * epl), (int32_t)(kb * epl), (int32_t)w.batch);
+      for (uint32_t j = 0; j < b_lines / epl; ++j)
+        load_3d<kPair>(tile + j * epl * kLineBytes, tmap, bar, pair_bar, (int32_t)(n0 + j * epl), (int32_t)(kb * epl), (int32_t)w.batch);
       break;
     case kWeightK: {
       const uint32_t cblocks = p.geo.c_out / epl;
       const uint32_t tap = kb / cblocks, cb = kb - tap * cblocks;
-      tma_load_3d(tile, tmap, bar, (int32_t)(cb * epl), (int32_t)n0, (int32_t)tap);
+      load_3d<kPair>(tile, tmap, bar, pair_bar, (int32_t)(cb * epl), (int32_t)n0, (int32_t)tap);
       break;
     }
     default:
@@ -366,6 +384,50 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
 }
 
+// ---- MMA issue loop -------------------------------------------------------------------------------------
+// One thread feeds the tensor core, so the loop body must stay far below the 512 cycles a K block takes:
+// descriptors are built once and advanced by adding byte offsets (>> 4) to their address field, and the
+// barrier waits take the one-instruction path when the stage is already full.  (The first version
+// rebuilt both descriptors for each of the four slices; its ~150 dependent instructions per K block
+// capped the kernel at half the tensor rate.)
+struct MmaSetup {
+  uint32_t idesc;
+  uint32_t a_step16, b_step16;      // descriptor increment per K slice (bytes >> 4)
+  uint32_t stage16;                 // descriptor increment per pipeline stage
+  uint64_t a_desc0, b_desc0;        // descriptors of stage 0, slice 0
+};
+
+__device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t tile_rows, uint32_t tiles_addr, uint32_t stage_bytes) {
+  const uint32_t epl = p.tf32 ? 32u : 64u;
+  // K-major: the four K slices of a stage sit 32 bytes apart inside each line.  MN-major: a slice is 16
+  // (bf16) or 8 (tf32) whole lines, and 64-/32-wide MN blocks follow each other every epl lines.
+  const uint32_t slice_lines = p.tf32 ? 8u : 16u;
+  const uint32_t a_lbo = p.a_mn_major ? epl * kLineBytes : 16u, a_step = p.a_mn_major ? slice_lines * kLineBytes : 32u;
+  const uint32_t b_lbo = p.b_mn_major ? epl * kLineBytes : 16u, b_step = p.b_mn_major ? slice_lines * kLineBytes : 32u;
+  // MN-major tf32 tiles use the 32-byte-chunk swizzle whose atom is four lines (512 bytes).
+  const uint32_t a_mode = (p.tf32 && p.a_mn_major) ? kSwizzle128Base32 : kSwizzle128, a_sbo = (p.tf32 && p.a_mn_major) ? 512u : 1024u;
+  const uint32_t b_mode = (p.tf32 && p.b_mn_major) ? kSwizzle128Base32 : kSwizzle128, b_sbo = (p.tf32 && p.b_mn_major) ? 512u : 1024u;
+  MmaSetup s;
+  s.idesc = make_instr_desc(p.tf32 ? 2u : 1u, p.a_mn_major, p.b_mn_major, tile_rows, p.bn);
+  s.a_step16 = a_step >> 4;
+  s.b_step16 = b_step >> 4;
+  s.stage16 = stage_bytes >> 4;
+  s.a_desc0 = make_smem_desc(tiles_addr, a_lbo, a_sbo, a_mode);
+  s.b_desc0 = make_smem_desc(tiles_addr + kATileBytes, b_lbo, b_sbo, b_mode);
+  return s;
+}
+
+// Issues the four K slices of one stage.
+template <bool kPair, bool kTf32>
+__device__ __forceinline__ void mma_stage(const MmaSetup& s, uint32_t tmem_d, uint32_t stage, uint32_t first_accumulate) {
+  const uint64_t da = s.a_desc0 + (uint64_t)(stage * s.stage16);
+  const uint64_t db = s.b_desc0 + (uint64_t)(stage * s.stage16);
+  mma_issue<kPair, kTf32>(tmem_d, da, db, s.idesc, first_accumulate);
+  mma_issue<kPair, kTf32>(tmem_d, da + s.a_step16, db + s.b_step16, s.idesc, 1u);
+  mma_issue<kPair, kTf32>(tmem_d, da + 2 * s.a_step16, db + 2 * s.b_step16, s.idesc, 1u);
+  mma_issue<kPair, kTf32>(tmem_d, da + 3 * s.a_step16, db + 3 * s.b_step16, s.idesc, 1u);
+}
+
 // ---- the kernel ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(320, 1)
 gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
@@ -420,8 +482,8 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           if (!(ok = mbar_wait(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
           uint8_t* a_tile = tiles + stage * stage_bytes;
           mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
-          issue_a(p, &tmap_a, a_tile, &hdr->full[stage], work, kb);
-          issue_b(p, &tmap_b, a_tile + kATileBytes, &hdr->full[stage], work, kb);
+          issue_a<false>(p, &tmap_a, a_tile, &hdr->full[stage], 0, work, kb, work.m_tile * kBM);
+          issue_b<false>(p, &tmap_b, a_tile + kATileBytes, &hdr->full[stage], 0, work, kb, work.n_tile * p.bn, p.bn);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
@@ -429,35 +491,19 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   } else if (warp == 1) {
     // ===== MMA issuer =====
     if (lane == 0) {
-      const uint32_t idesc = make_instr_desc(p.tf32 ? 2u : 1u, p.a_mn_major, p.b_mn_major, kBM, p.bn);
-      // K-major: the four K slices of a stage sit 32 bytes apart inside each line.  MN-major: a slice
-      // is 16 (bf16) or 8 (tf32) whole lines, and 64-/32-wide MN blocks follow each other every epl lines.
-      const uint32_t slice_lines = p.tf32 ? 8u : 16u;
-      const uint32_t a_lbo = p.a_mn_major ? epl * kLineBytes : 16u, a_step = p.a_mn_major ? slice_lines * kLineBytes : 32u;
-      const uint32_t b_lbo = p.b_mn_major ? epl * kLineBytes : 16u, b_step = p.b_mn_major ? slice_lines * kLineBytes : 32u;
-      // MN-major tf32 tiles use the 32-byte-chunk swizzle whose atom is four lines (512 bytes).
-      const uint32_t a_mode = (p.tf32 && p.a_mn_major) ? kSwizzle128Base32 : kSwizzle128, a_sbo = (p.tf32 && p.a_mn_major) ? 512u : 1024u;
-      const uint32_t b_mode = (p.tf32 && p.b_mn_major) ? kSwizzle128Base32 : kSwizzle128, b_sbo = (p.tf32 && p.b_mn_major) ? 512u : 1024u;
+      const MmaSetup ms = make_mma_setup(p, kBM, smem_u32(tiles), stage_bytes);
       uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const Work work = decode_work(p, w);
-        if (!(ok = mbar_wait(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
+        if (!(ok = mbar_wait_fast(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * p.bn;
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
-          if (!(ok = mbar_wait(&hdr->full[stage], phase, abort_flag, kStatusMmaTimeout))) break;
+          if (!(ok = mbar_wait_fast(&hdr->full[stage], phase, abort_flag, kStatusMmaTimeout))) break;
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(tiles + stage * stage_bytes);
-          const uint32_t b_addr = a_addr + kATileBytes;
-#pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {
-            const uint64_t da = make_smem_desc(a_addr + j * a_step, a_lbo, a_sbo, a_mode);
-            const uint64_t db = make_smem_desc(b_addr + j * b_step, b_lbo, b_sbo, b_mode);
-            const uint32_t acc = (kb > work.kb_begin || j > 0) ? 1u : 0u;
-            if (p.tf32) mma_tf32_ss(tmem_d, da, db, idesc, acc);
-            else mma_bf16_ss(tmem_d, da, db, idesc, acc);
-          }
+          if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, kb > work.kb_begin);
+          else mma_stage<false, false>(ms, tmem_d, stage, kb > work.kb_begin);
           mma_commit(&hdr->empty[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -525,6 +571,149 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
 
+// ---- the CTA-pair kernel ------------------------------------------------------------------------------
+// Two CTAs of a cluster (two neighbouring SMs) share one 256 x BN tile: CTA r owns rows r*128..r*128+127
+// and columns r*BN/2.. of the B tile.  One tcgen05.mma.cta_group::2 (M = 256) issued by the leader reads
+// A from each CTA's own shared memory and each half of B once, so every SM moves half as many B bytes
+// through shared memory as in the single-CTA kernel -- the single-CTA 128 x 256 tile is bound by
+// shared-memory bandwidth (operand reads plus TMA writes exceed 128 B/clk), this one is not.
+// Both CTAs run their own TMA producer (own tiles only, bytes counted on the leader's "full" barrier)
+// and their own epilogue (own 128 accumulator rows); only the leader issues MMAs and commits, once per
+// CTA, to the "empty" and "accumulator full" barriers of both.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
+                       const __grid_constant__ CUtensorMap tmap_b) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  SmemHeader* hdr = (SmemHeader*)smem;
+  uint8_t* tiles = smem + kHeaderBytes;
+  const uint32_t b_lines = p.bn / 2;                 // this CTA's share of the B tile
+  const uint32_t b_tile_bytes = b_lines * kLineBytes;
+  const uint32_t stage_bytes = kATileBytes + b_tile_bytes;
+  volatile uint32_t* abort_flag = &hdr->abort_flag;
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
+  const uint32_t tmem_cols = p.bn * 2 <= 32 ? 32u : (p.bn * 2 <= 64 ? 64u : (p.bn * 2 <= 128 ? 128u : (p.bn * 2 <= 256 ? 256u : 512u)));
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_init(&hdr->full[s], 1);      // the leader's arrive.expect_tx covers both CTAs' bytes (used on the leader only)
+      mbar_init(&hdr->empty[s], 1);     // one commit from the leader
+    }
+    for (uint32_t b = 0; b < 2; ++b) {
+      mbar_init(&hdr->acc_full[b], 1);  // one commit from the leader
+      mbar_init(&hdr->acc_empty[b], 8); // four epilogue warps in each CTA (used on the leader only)
+    }
+    hdr->abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_pair_alloc(&hdr->tmem_base, tmem_cols);
+    tmem_pair_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                   // the partner's barriers are initialised before anyone signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = hdr->tmem_base;
+  const uint32_t epl = p.tf32 ? 32u : 64u;
+
+  if (warp == 0) {
+    // ===== TMA producer (both CTAs) =====
+    if (lane == 0) {
+      const uint32_t tx_bytes = kATileBytes + b_tile_bytes;
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t w = pair; ok && w < total_work; w += pairs) {
+        const Work work = decode_work(p, w);
+        const uint32_t m0 = work.m_tile * 2 * kBM + rank * kBM;
+        const uint32_t n0 = work.n_tile * p.bn + rank * b_lines;
+        for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
+          if (!(ok = mbar_wait(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
+          uint8_t* a_tile = tiles + stage * stage_bytes;
+          // The leader announces the bytes of both CTAs with a plain local arrive; the partner only issues
+          // its copies against the leader's barrier.  (A cluster-scope release arrive from each producer
+          // made every K block wait for the previous block's copies: 1 us per block.)  The partner cannot
+          // run a phase ahead: its stage is freed by the leader's commit, which follows the phase's end.
+          const uint32_t leader_full = map_to_cta(smem_u32(&hdr->full[stage]), 0);
+          if (rank == 0) mbar_arrive_expect_tx(&hdr->full[stage], 2 * tx_bytes);
+          const uint32_t kb_load = p.debug_variant == 5 ? 0u : kb;
+          issue_a<true>(p, &tmap_a, a_tile, nullptr, leader_full, work, kb_load, m0);
+          issue_b<true>(p, &tmap_b, a_tile + kATileBytes, nullptr, leader_full, work, kb_load, n0, b_lines);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer (leader CTA only) =====
+    if (lane == 0 && rank == 0) {
+      const MmaSetup ms = make_mma_setup(p, 2 * kBM, smem_u32(tiles), stage_bytes);
+      uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
+      bool ok = true;
+      for (uint32_t w = pair; ok && w < total_work; w += pairs) {
+        const Work work = decode_work(p, w);
+        if (!(ok = mbar_wait_fast(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + buf * p.bn;
+        for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
+          if (!(ok = mbar_wait_fast(&hdr->full[stage], phase, abort_flag, kStatusMmaTimeout))) break;
+          tc_fence_after_sync();
+          if (p.debug_variant == 4 || p.debug_variant >= 60) mma_issue<true, false>(tmem_d, ms.a_desc0, ms.b_desc0, ms.idesc, 1u);
+          else if (p.tf32) mma_stage<true, true>(ms, tmem_d, stage, kb > work.kb_begin);
+          else mma_stage<true, false>(ms, tmem_d, stage, kb > work.kb_begin);
+          // One arrival on the "empty" barrier of both CTAs (mask 0b11): each producer may refill its stage.
+          mma_pair_commit_both(&hdr->empty[stage], 3);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_pair_commit_both(&hdr->acc_full[buf], 3);
+        if ((buf ^= 1) == 0) buf_phase ^= 1;
+      }
+    }
+  } else {
+    // ===== epilogue (both CTAs, own 128 rows) =====
+    const uint32_t quarter = warp & 3;
+    uint32_t buf = 0, buf_phase = 0;
+    bool ok = true;
+    for (uint32_t w = pair; ok && w < total_work; w += pairs) {
+      const Work work = decode_work(p, w);
+      ok = mbar_wait(&hdr->acc_full[buf], buf_phase, abort_flag, kStatusEpilogueTimeout);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t row = work.m_tile * 2 * kBM + rank * kBM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
+      for (uint32_t c = 0; c < (p.debug_variant == 3 ? 0u : p.bn); c += 32) {
+        uint32_t acc[32];
+        tmem_ld_32x32(taddr + c, acc);
+        tmem_ld_wait();
+        epilogue_chunk(p, acc, work.batch, work.split, row, work.n_tile * p.bn + c);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->acc_empty[buf]), 0));
+      if ((buf ^= 1) == 0) buf_phase ^= 1;
+    }
+  }
+
+  // ===== teardown =====
+  __syncwarp();
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                   // neither CTA leaves while the partner may still signal its barriers
+  tc_fence_after_sync();
+  if (threadIdx.x == 0 && hdr->abort_flag != 0 && p.status != nullptr) atomicCAS(p.status, 0u, hdr->abort_flag);
+  if (warp == 1) tmem_pair_dealloc(tmem_base, tmem_cols);
+}
+
 // Ordered combine of split-K partials followed by the epilogue; one thread per output element.
 // Takes the place of grad's `splitCombine` (src/gpu/device.zig:664-670), which only deterministic runs use.
 __global__ void splitk_reduce_kernel(const GemmParams p) {
@@ -548,16 +737,63 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
 }  // namespace
 
 size_t gemm_smem_bytes(const GemmParams& p) {
-  return 1024 /* alignment slack */ + kHeaderBytes + (size_t)p.stages * (kATileBytes + (size_t)p.bn * kLineBytes);
+  const size_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
+  return 1024 /* alignment slack */ + kHeaderBytes + (size_t)p.stages * (kATileBytes + b_lines * kLineBytes);
+}
+
+// Co-resident 2-CTA clusters of the pair kernel for a given dynamic shared-memory size (cached per size).
+static uint32_t max_resident_pairs(size_t smem_bytes, int sm_count) {
+  static size_t cached_smem[8] = {};
+  static int cached_pairs[8] = {};
+  static int cached_device[8] = {-1, -1, -1, -1, -1, -1, -1, -1};
+  int device = 0;
+  cudaGetDevice(&device);
+  for (int i = 0; i < 8; ++i)
+    if (cached_device[i] == device && cached_smem[i] == smem_bytes) return (uint32_t)cached_pairs[i];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)sm_count / 2 * 2, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, gemm_sm100_pair_kernel, &cfg) != cudaSuccess || clusters <= 0) {
+    cudaGetLastError();
+    clusters = sm_count / 2 > 8 ? sm_count / 2 - 8 : 1;   // conservative guess when the query is unavailable
+  }
+  if (getenv("GB_DEBUG")) fprintf(stderr, "[gradb200] resident 2-CTA clusters at %zu B smem: %d (SMs %d)\n", smem_bytes, clusters, sm_count);
+  static int next = 0;
+  const int slot = next++ % 8;
+  cached_device[slot] = device;
+  cached_smem[slot] = smem_bytes;
+  cached_pairs[slot] = clusters;
+  return (uint32_t)clusters;
 }
 
 cudaError_t gemm_sm100_configure() {
-  return cudaFuncSetAttribute(gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gemm_sm100_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
 cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, int sm_count, cudaStream_t stream) {
   const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
   if (total_work == 0) return cudaSuccess;
+  if (p.cta_pair) {
+    // tiles_m counts 256-row tiles here; one cluster of two CTAs per SM pair, persistent over the tiles.
+    // A persistent grid must not exceed what the device can keep resident at once: the number of
+    // co-resident 2-CTA clusters can be below sm_count / 2 (SMs are paired within a GPC), and a cluster
+    // left waiting would run its whole share of tiles after the others have finished.
+    uint32_t pairs = std::min<uint32_t>(total_work, max_resident_pairs(gemm_smem_bytes(p), sm_count));
+    if (p.debug_variant >= 60) pairs = std::min<uint32_t>(pairs, p.debug_variant - 60);   // experiment: fewer SM pairs
+    gemm_sm100_pair_kernel<<<2 * pairs, 192, gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b);
+    return cudaGetLastError();
+  }
   const bool gather = p.a_kind == kGather || p.b_kind == kGather;
   const uint32_t grid = total_work < (uint32_t)sm_count ? total_work : (uint32_t)sm_count;
   gemm_sm100_kernel<<<grid, gather ? 320 : 192, gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b);

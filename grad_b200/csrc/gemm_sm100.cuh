@@ -50,6 +50,7 @@ struct GemmParams {
   uint32_t a_kind, b_kind;  // OperandKind
   uint32_t a_mn_major, b_mn_major;
   uint32_t group_m;         // tile rasterisation band height
+  uint32_t cta_pair;        // 1: two CTAs share a 256 x bn tile (tiles_m counts 256-row tiles)
   // TMA patch boxes (conv): positions per box and its decomposition
   uint32_t box_w, box_h, box_n;
   ConvGeo geo;
@@ -65,6 +66,7 @@ struct GemmParams {
   uint32_t ldc;
   uint32_t c_is_bf16, transpose_out, accumulate, relu, vec_store;
   uint32_t* status;
+  uint32_t debug_variant;   // experiment switch, 0 in production
 };
 
 size_t gemm_smem_bytes(const GemmParams& p);

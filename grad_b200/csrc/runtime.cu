@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -154,6 +155,7 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
   p.residual = ep ? ep->residual : nullptr;
   p.relu = ep && ep->activation == GB_ACT_RELU;
   p.status = h->status;
+  if (const char* v = getenv("GB_VARIANT")) p.debug_variant = (uint32_t)atoi(v);
   p.group_m = 8;
   if (plan.tensor) {
     const uint32_t epl = p.tf32 ? 32 : 64;
@@ -181,6 +183,35 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
   }
   plan.workspace = p.splits > 1 ? (size_t)p.splits * p.batch * p.m * p.n * sizeof(float) : 0;
   return GB_OK;
+}
+
+// Switches a planned tensor-path product to the CTA-pair kernel (256 x bn tiles over two SMs) when both
+// operands arrive by TMA and there are enough 256-row tiles to occupy every SM pair without splitting K.
+// `encode_b(rows)` re-encodes B's map for the `rows` lines one CTA of the pair loads; false keeps the
+// single-CTA plan.
+template <class EncodeB>
+bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b) {
+  GemmParams& p = plan.p;
+  if (!plan.tensor || p.a_kind == gb::kGather || p.b_kind == gb::kGather || p.m <= 128) return false;
+  if (p.debug_variant == 2) return false;
+  const uint32_t pairs = (uint32_t)h->sm_count / 2;
+  const uint32_t tiles_m = ceil_div(p.m, 256) * p.batch;
+  const uint32_t n_cap = std::max(min_bn, ceil_div(p.n, min_bn) * min_bn);
+  for (uint32_t cand : {256u, 128u, 64u}) {
+    if (cand / 2 < min_bn || cand > std::max(n_cap, 2 * min_bn)) continue;
+    if (tiles_m * ceil_div(p.n, cand) < pairs) continue;
+    if (!encode_b(cand / 2)) return false;
+    p.cta_pair = 1;
+    p.bn = cand;
+    p.tiles_m = ceil_div(p.m, 256);
+    p.tiles_n = ceil_div(p.n, cand);
+    p.splits = 1;
+    p.k_blocks_per_split = p.k_blocks_total;
+    p.stages = std::min<uint32_t>(8, (227 * 1024 - 2048) / (128 * 128 + cand / 2 * 128));
+    plan.workspace = 0;
+    return true;
+  }
+  return false;
 }
 
 void set_output(GemmParams& p, void* c, uint32_t dtype_c, uint32_t ldc, uint64_t stride_c, bool transpose_out, bool accumulate,
@@ -246,6 +277,9 @@ int plan_gemm(const gb_handle* h, const gb_gemm_desc* d, const void* a, const vo
   if (plan.tensor) {
     p.a_kind = dense_tma(&plan.tmap_a, oa, smem_bf16, batch, 128, epl) ? (oa.mn_major ? gb::kDenseMN : gb::kDenseK) : gb::kGather;
     p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, batch, p.bn, epl) ? (ob.mn_major ? gb::kDenseMN : gb::kDenseK) : gb::kGather;
+    CUtensorMap single = plan.tmap_b;
+    if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, batch, rows, epl); }))
+      plan.tmap_b = single;
   }
   return GB_OK;
 }
@@ -266,7 +300,7 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
   info.tensor_path = plan.tensor;
   info.a_kind = plan.tensor ? p.a_kind : (uint32_t)gb::kGather;
   info.b_kind = plan.tensor ? p.b_kind : (uint32_t)gb::kGather;
-  info.tile_m = plan.tensor ? 128 : 64;
+  info.tile_m = plan.tensor ? (p.cta_pair ? 256 : 128) : 64;
   info.tile_n = p.bn;
   info.stages = p.stages;
   info.splits = p.splits;
@@ -378,6 +412,9 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
           nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n))
         p.a_kind = gb::kPatchK;
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
+      CUtensorMap single = plan.tmap_b;
+      if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }))
+        plan.tmap_b = single;
     }
   } else if (pass == 1) {
     // dx[pixels, c] = patchesT(dy)[pixels, taps*c_out] * wT[taps*c_out, c]
@@ -403,6 +440,12 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
         const uint64_t strides[2] = {(uint64_t)g.c_out * es, (uint64_t)g.c_out * es * g.c};
         const uint32_t box[3] = {epl, p.bn, 1};
         if (encode_map(&plan.tmap_b, smem_bf16, other, 3, dims, strides, box)) p.b_kind = gb::kWeightK;
+        CUtensorMap single = plan.tmap_b;
+        if (!try_pair(h, plan, 32, [&](uint32_t rows) {
+              const uint32_t half_box[3] = {epl, rows, 1};
+              return encode_map(&plan.tmap_b, smem_bf16, other, 3, dims, strides, half_box);
+            }))
+          plan.tmap_b = single;
       }
     }
   } else {

@@ -62,6 +62,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
 // error status instead of hanging the device.
 constexpr uint32_t kSpinLimit = 1u << 22;
 
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
+  }
+  atomicCAS((uint32_t*)abort_flag, 0u, code);
+  return false;
+}
+// Hot-loop flavour: the common case (the phase has already completed) costs one try_wait.
+__device__ __forceinline__ bool mbar_wait_fast(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, code);
+}
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -101,6 +116,45 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const void* tmap, uint64_
       : "memory");
 }
 
+// The same loads for a CTA pair (cta_group::2): `dst` is this CTA's own shared memory, `bar_addr` a
+// shared::cluster address that may name the partner CTA's mbarrier (the pair's leader collects the bytes
+// of both CTAs on one barrier).  Each CTA still fetches only its own tiles.
+__device__ __forceinline__ void tma_pair_load_3d(uint32_t dst, const void* tmap, uint32_t bar_addr, int32_t x, int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"((uint64_t)tmap), "r"(bar_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_pair_load_4d(uint32_t dst, const void* tmap, uint32_t bar_addr, int32_t x, int32_t y, int32_t z, int32_t w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"((uint64_t)tmap), "r"(bar_addr), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
+// ---- thread-block clusters ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t bar_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes) : "memory");
+}
+
 // ---- tensor memory --------------------------------------------------------------------------------
 // Allocation is warp-wide (.sync.aligned): one whole warp calls it, the base address lands in smem.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t columns) {
@@ -109,6 +163,15 @@ __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t colum
 __device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t columns) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
+}
+
+// CTA-pair flavours: both CTAs of the pair call these with the same arguments from the same warp index.
+__device__ __forceinline__ void tmem_pair_alloc(uint32_t* smem_result, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tmem_pair_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_pair_dealloc(uint32_t base, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
 }
 
 // ---- tcgen05.mma ----------------------------------------------------------------------------------
@@ -161,6 +224,55 @@ __device__ __forceinline__ void mma_tf32_ss(uint32_t tmem_d, uint64_t desc_a, ui
 // writing TMEM.  Implies tcgen05.fence::before_thread_sync.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// One instruction across a CTA pair: M = 256 (128 rows per CTA), each CTA supplies its half of A's rows
+// and half of B's columns from its own shared memory, each accumulates its 128 rows in its own TMEM.
+// Issued by one thread of the leader CTA (cluster rank 0).
+__device__ __forceinline__ void mma_pair_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_pair_tf32_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier at shared::cluster address `bar_addr` (either CTA of the pair) once every
+// pair-MMA issued so far has completed in both CTAs.
+__device__ __forceinline__ void mma_pair_commit(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
+
+// The same arrival delivered by one instruction to the mbarrier at this shared-memory offset in every CTA
+// named by `cta_mask` (bit r = cluster rank r).  This is a barrier signal, not a data copy.
+__device__ __forceinline__ void mma_pair_commit_both(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+
+// Templated issue used by the mainloops: kPair selects cta_group::2, kTf32 the operand kind.  The
+// accumulate flag is a register for the first K slice of a tile and the constant 1 for every other slice.
+template <bool kPair, bool kTf32>
+__device__ __forceinline__ void mma_issue(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (kPair) {
+    if constexpr (kTf32) mma_pair_tf32_ss(tmem_d, desc_a, desc_b, idesc, accumulate);
+    else mma_pair_bf16_ss(tmem_d, desc_a, desc_b, idesc, accumulate);
+  } else {
+    if constexpr (kTf32) mma_tf32_ss(tmem_d, desc_a, desc_b, idesc, accumulate);
+    else mma_bf16_ss(tmem_d, desc_a, desc_b, idesc, accumulate);
+  }
 }
 
 // ---- TMEM -> registers ------------------------------------------------------------------------------
