@@ -182,24 +182,6 @@ __device__ __forceinline__ void gather_tile(const GemmParams& p, const GatherDes
 }
 
 // ---- TMA issue ----------------------------------------------------------------------------------------
-__device__ __forceinline__ void patch_coords(const GemmParams& p, uint32_t p0, uint32_t tap, int32_t& w0, int32_t& h0, int32_t& n0) {
-  // Grid the positions of this pass run over: the output grid (forward, weight gradient) or the input grid
-  // (input gradient, whose patches are taken from dy).
-  const uint32_t grid_h = p.dgrad ? p.geo.h : p.geo.out_h;
-  const uint32_t grid_w = p.dgrad ? p.geo.w : p.geo.out_w;
-  const uint32_t per_image = grid_h * grid_w;
-  const uint32_t ky = tap / p.geo.k, kx = tap - ky * p.geo.k;
-  n0 = (int32_t)(p0 / per_image);
-  const uint32_t row0 = p.box_n > 1 ? 0u : (p0 - (uint32_t)n0 * per_image) / grid_w;
-  if (p.dgrad) {
-    w0 = (int32_t)p.geo.pad - (int32_t)(kx * p.geo.dilation);
-    h0 = (int32_t)row0 + (int32_t)p.geo.pad - (int32_t)(ky * p.geo.dilation);
-  } else {
-    w0 = (int32_t)(kx * p.geo.dilation) - (int32_t)p.geo.pad;
-    h0 = (int32_t)row0 + (int32_t)(ky * p.geo.dilation) - (int32_t)p.geo.pad;
-  }
-}
-
 // One tile load, either on this CTA's own barrier or, for a CTA pair, on the pair leader's barrier.
 template <bool kPair>
 __device__ __forceinline__ void load_3d(uint8_t* dst, const CUtensorMap* tmap, uint64_t* bar, uint32_t pair_bar, int32_t x, int32_t y, int32_t z) {
@@ -212,69 +194,126 @@ __device__ __forceinline__ void load_4d(uint8_t* dst, const CUtensorMap* tmap, u
   else tma_load_4d(dst, tmap, bar, x, y, z, w);
 }
 
-// Loads the 128 A rows that start at m0 for K block kb.
-template <bool kPair>
-__device__ __forceinline__ void issue_a(const GemmParams& p, const CUtensorMap* tmap, uint8_t* tile, uint64_t* bar, uint32_t pair_bar,
-                                        const Work& w, uint32_t kb, uint32_t m0) {
-  const uint32_t epl = p.tf32 ? 32u : 64u;
-  switch (p.a_kind) {
-    case kDenseK:
-      load_3d<kPair>(tile, tmap, bar, pair_bar, (int32_t)(kb * epl), (int32_t)m0, (int32_t)w.batch);
-      break;
-    case kDenseMN:
-      for (uint32_t j = 0; j < kBM / epl; ++j)
-        load_3d<kPair>(tile + j * epl * kLineBytes, tmap, bar, pair_bar, (int32_t)(m0 + j * epl), (int32_t)(kb * epl), (int32_t)w.batch);
-      break;
-    case kPatchK: {
-      // K runs over (tap, channel block); the box is 128 positions x 128 bytes of channels.
-      const uint32_t channels = p.dgrad ? p.geo.c_out : p.geo.c;
-      const uint32_t cblocks = channels / epl;
-      const uint32_t tap = kb / cblocks, cb = kb - tap * cblocks;
-      int32_t w0, h0, n0;
-      patch_coords(p, m0, tap, w0, h0, n0);
-      load_4d<kPair>(tile, tmap, bar, pair_bar, (int32_t)(cb * epl), w0, h0, n0);
-      break;
-    }
-    case kPatchMN: {
-      // Weight gradient: M runs over (tap, channel), K over positions; each box is `epl` positions deep.
-      const uint32_t taps = p.geo.k * p.geo.k;
-      for (uint32_t j = 0; j < kBM / epl; ++j) {
-        const uint32_t kk0 = m0 + j * epl;
-        const uint32_t tap = min(kk0 / p.geo.c, taps - 1);   // rows past the last tap are never stored
-        const uint32_t c0 = kk0 >= taps * p.geo.c ? 0u : kk0 - tap * p.geo.c;
-        int32_t w0, h0, n0;
-        patch_coords(p, kb * epl, tap, w0, h0, n0);
-        load_4d<kPair>(tile + j * epl * kLineBytes, tmap, bar, pair_bar, (int32_t)c0, w0, h0, n0);
-      }
-      break;
-    }
-    default:
-      break;
+// ---- per-lane tile loads ----------------------------------------------------------------------------------
+// The producer warp gives every TMA box of a stage to its own lane, and each lane keeps its box's
+// coordinates in registers, stepping them from one K block to the next without divisions.  One thread
+// issuing every box with freshly computed coordinates took 400-700 cycles per K block, more than the 512
+// the tensor core needs for it.
+struct BoxLane {
+  uint32_t active, four_d, kind, smem_off;
+  const CUtensorMap* tmap;
+  int32_t x, y, z, w;
+  uint32_t cb, cblocks, kx, ky, tap;     // K walk over (tap, channel block): patch-K and weight boxes
+  int32_t sign, origin, row0;            // patch-K: coordinate = origin + sign * tap offset
+  uint32_t row, img;                     // K walk over positions: patch-MN boxes
+  int32_t w_off, h_off;
+};
+
+__device__ __forceinline__ uint32_t boxes_of(uint32_t kind, uint32_t lines, uint32_t epl) {
+  if (kind == kGather) return 0;
+  return (kind == kDenseMN || kind == kPatchMN) ? lines / epl : 1u;
+}
+
+__device__ __forceinline__ void box_refresh(const GemmParams& p, BoxLane& b, uint32_t epl) {
+  if (b.kind == kPatchK) {
+    b.x = (int32_t)(b.cb * epl);
+    b.y = b.origin + b.sign * (int32_t)(b.kx * p.geo.dilation);
+    b.z = b.row0 + b.origin + b.sign * (int32_t)(b.ky * p.geo.dilation);
+  } else if (b.kind == kWeightK) {
+    b.x = (int32_t)(b.cb * epl);
+    b.z = (int32_t)b.tap;
+  } else if (b.kind == kPatchMN) {
+    b.z = (int32_t)b.row + b.h_off;
+    b.w = (int32_t)b.img;
   }
 }
 
-// Loads `b_lines` lines of B (N values n0 .. n0 + b_lines) for K block kb.
-template <bool kPair>
-__device__ __forceinline__ void issue_b(const GemmParams& p, const CUtensorMap* tmap, uint8_t* tile, uint64_t* bar, uint32_t pair_bar,
-                                        const Work& w, uint32_t kb, uint32_t n0, uint32_t b_lines) {
+// Sets lane `lane`'s box up for the K block kb_begin of a tile whose A rows start at m0 and B lines at n0.
+__device__ __forceinline__ void box_init(const GemmParams& p, BoxLane& b, uint32_t lane, const CUtensorMap* tmap_a,
+                                         const CUtensorMap* tmap_b, const Work& work, uint32_t m0, uint32_t n0, uint32_t b_lines) {
   const uint32_t epl = p.tf32 ? 32u : 64u;
-  switch (p.b_kind) {
+  const uint32_t na = boxes_of(p.a_kind, kBM, epl), nb = boxes_of(p.b_kind, b_lines, epl);
+  b.active = lane < na + nb;
+  if (!b.active) return;
+  const bool is_b = lane >= na;
+  const uint32_t j = is_b ? lane - na : lane;
+  b.kind = is_b ? p.b_kind : p.a_kind;
+  b.tmap = is_b ? tmap_b : tmap_a;
+  b.smem_off = (is_b ? kATileBytes : 0u) + j * epl * kLineBytes;
+  b.four_d = b.kind == kPatchK || b.kind == kPatchMN;
+  const uint32_t mn0 = is_b ? n0 : m0;
+  const uint32_t k0 = work.kb_begin;
+  b.w = 0;
+  switch (b.kind) {
     case kDenseK:
-      load_3d<kPair>(tile, tmap, bar, pair_bar, (int32_t)(kb * epl), (int32_t)n0, (int32_t)w.batch);
+      b.x = (int32_t)(k0 * epl); b.y = (int32_t)mn0; b.z = (int32_t)work.batch;
       break;
     case kDenseMN:
-      for (uint32_t j = 0; j < b_lines / epl; ++j)
-        load_3d<kPair>(tile + j * epl * kLineBytes, tmap, bar, pair_bar, (int32_t)(n0 + j * epl), (int32_t)(kb * epl), (int32_t)w.batch);
+      b.x = (int32_t)(mn0 + j * epl); b.y = (int32_t)(k0 * epl); b.z = (int32_t)work.batch;
       break;
-    case kWeightK: {
-      const uint32_t cblocks = p.geo.c_out / epl;
-      const uint32_t tap = kb / cblocks, cb = kb - tap * cblocks;
-      load_3d<kPair>(tile, tmap, bar, pair_bar, (int32_t)(cb * epl), (int32_t)n0, (int32_t)tap);
+    case kPatchK: {
+      const uint32_t grid_h = p.dgrad ? p.geo.h : p.geo.out_h, grid_w = p.dgrad ? p.geo.w : p.geo.out_w;
+      const uint32_t per_image = grid_h * grid_w;
+      b.cblocks = (p.dgrad ? p.geo.c_out : p.geo.c) / epl;
+      b.tap = k0 / b.cblocks; b.cb = k0 - b.tap * b.cblocks;
+      b.ky = b.tap / p.geo.k; b.kx = b.tap - b.ky * p.geo.k;
+      const uint32_t img = mn0 / per_image;
+      b.row0 = p.box_n > 1 ? 0 : (int32_t)((mn0 - img * per_image) / grid_w);
+      b.sign = p.dgrad ? -1 : 1;
+      b.origin = p.dgrad ? (int32_t)p.geo.pad : -(int32_t)p.geo.pad;
+      b.w = (int32_t)img;
       break;
     }
+    case kPatchMN: {
+      // Rows (tap, channel) kk0 .. kk0 + epl of the weight gradient; rows past the last tap are never stored.
+      const uint32_t taps = p.geo.k * p.geo.k, kk0 = mn0 + j * epl;
+      const uint32_t tap = min(kk0 / p.geo.c, taps - 1);
+      const uint32_t ky = tap / p.geo.k, kx = tap - ky * p.geo.k;
+      const uint32_t per_image = p.geo.out_h * p.geo.out_w, p0 = k0 * epl;
+      b.x = kk0 >= taps * p.geo.c ? 0 : (int32_t)(kk0 - tap * p.geo.c);
+      b.w_off = (int32_t)(kx * p.geo.dilation) - (int32_t)p.geo.pad;
+      b.h_off = (int32_t)(ky * p.geo.dilation) - (int32_t)p.geo.pad;
+      b.y = b.w_off;
+      b.img = p0 / per_image;
+      b.row = p.box_n > 1 ? 0u : (p0 - b.img * per_image) / p.geo.out_w;
+      break;
+    }
+    case kWeightK:
+      b.cblocks = p.geo.c_out / epl;
+      b.tap = k0 / b.cblocks; b.cb = k0 - b.tap * b.cblocks;
+      b.y = (int32_t)mn0;
+      break;
     default:
       break;
   }
+  box_refresh(p, b, epl);
+}
+
+// Steps the box to the next K block.
+__device__ __forceinline__ void box_advance(const GemmParams& p, BoxLane& b) {
+  const uint32_t epl = p.tf32 ? 32u : 64u;
+  switch (b.kind) {
+    case kDenseK: b.x += (int32_t)epl; return;
+    case kDenseMN: b.y += (int32_t)epl; return;
+    case kPatchK:
+      if (++b.cb == b.cblocks) { b.cb = 0; if (++b.kx == p.geo.k) { b.kx = 0; ++b.ky; } }
+      break;
+    case kWeightK:
+      if (++b.cb == b.cblocks) { b.cb = 0; ++b.tap; }
+      break;
+    case kPatchMN:
+      if (p.box_n > 1) b.img += p.box_n;
+      else if ((b.row += p.box_h) >= p.geo.out_h) { b.row = 0; ++b.img; }
+      break;
+    default: return;
+  }
+  box_refresh(p, b, epl);
+}
+
+template <bool kPair>
+__device__ __forceinline__ void box_issue(const BoxLane& b, uint8_t* stage_base, uint64_t* bar, uint32_t pair_bar) {
+  if (b.four_d) load_4d<kPair>(stage_base + b.smem_off, b.tmap, bar, pair_bar, b.x, b.y, b.z, b.w);
+  else load_3d<kPair>(stage_base + b.smem_off, b.tmap, bar, pair_bar, b.x, b.y, b.z);
 }
 
 // ---- epilogue -----------------------------------------------------------------------------------------
@@ -471,19 +510,23 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const uint32_t epl = p.tf32 ? 32u : 64u;
 
   if (warp == 0) {
-    // ===== TMA producer =====
-    if (lane == 0) {
-      const uint32_t tx_bytes = (p.a_kind != kGather ? kATileBytes : 0u) + (p.b_kind != kGather ? b_tile_bytes : 0u);
+    // ===== TMA producer: one lane per box =====
+    const uint32_t tx_bytes = (p.a_kind != kGather ? kATileBytes : 0u) + (p.b_kind != kGather ? b_tile_bytes : 0u);
+    const uint32_t n_boxes = boxes_of(p.a_kind, kBM, epl) + boxes_of(p.b_kind, p.bn, epl);
+    if (lane < max(n_boxes, 1u)) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      BoxLane box;
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const Work work = decode_work(p, w);
+        box_init(p, box, lane, &tmap_a, &tmap_b, work, work.m_tile * kBM, work.n_tile * p.bn, p.bn);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
-          if (!(ok = mbar_wait(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
-          uint8_t* a_tile = tiles + stage * stage_bytes;
-          mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
-          issue_a<false>(p, &tmap_a, a_tile, &hdr->full[stage], 0, work, kb, work.m_tile * kBM);
-          issue_b<false>(p, &tmap_b, a_tile + kATileBytes, &hdr->full[stage], 0, work, kb, work.n_tile * p.bn, p.bn);
+          if (!(ok = mbar_wait_fast(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
+          if (lane == 0) mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
+          if (box.active) {
+            box_issue<false>(box, tiles + stage * stage_bytes, &hdr->full[stage], 0);
+            box_advance(p, box);
+          }
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
@@ -624,27 +667,25 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
   const uint32_t epl = p.tf32 ? 32u : 64u;
 
   if (warp == 0) {
-    // ===== TMA producer (both CTAs) =====
-    if (lane == 0) {
-      const uint32_t tx_bytes = kATileBytes + b_tile_bytes;
+    // ===== TMA producer (both CTAs): one lane per box =====
+    // The leader announces the bytes of both CTAs with a plain local arrive; the partner only issues its
+    // copies against the leader's barrier.  (A cluster-scope release arrive from each producer made every K
+    // block wait for the previous block's copies: 1 us per block.)  The partner cannot run a phase ahead:
+    // its stage is freed by the leader's commit, which follows the end of the phase.
+    const uint32_t tx_bytes = kATileBytes + b_tile_bytes;
+    const uint32_t n_boxes = boxes_of(p.a_kind, kBM, epl) + boxes_of(p.b_kind, b_lines, epl);
+    if (lane < n_boxes) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      BoxLane box;
       for (uint32_t w = pair; ok && w < total_work; w += pairs) {
         const Work work = decode_work(p, w);
-        const uint32_t m0 = work.m_tile * 2 * kBM + rank * kBM;
-        const uint32_t n0 = work.n_tile * p.bn + rank * b_lines;
+        box_init(p, box, lane, &tmap_a, &tmap_b, work, work.m_tile * 2 * kBM + rank * kBM, work.n_tile * p.bn + rank * b_lines, b_lines);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
-          if (!(ok = mbar_wait(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
-          uint8_t* a_tile = tiles + stage * stage_bytes;
-          // The leader announces the bytes of both CTAs with a plain local arrive; the partner only issues
-          // its copies against the leader's barrier.  (A cluster-scope release arrive from each producer
-          // made every K block wait for the previous block's copies: 1 us per block.)  The partner cannot
-          // run a phase ahead: its stage is freed by the leader's commit, which follows the phase's end.
-          const uint32_t leader_full = map_to_cta(smem_u32(&hdr->full[stage]), 0);
-          if (rank == 0) mbar_arrive_expect_tx(&hdr->full[stage], 2 * tx_bytes);
-          const uint32_t kb_load = p.debug_variant == 5 ? 0u : kb;
-          issue_a<true>(p, &tmap_a, a_tile, nullptr, leader_full, work, kb_load, m0);
-          issue_b<true>(p, &tmap_b, a_tile + kATileBytes, nullptr, leader_full, work, kb_load, n0, b_lines);
+          if (!(ok = mbar_wait_fast(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
+          if (lane == 0 && rank == 0) mbar_arrive_expect_tx(&hdr->full[stage], 2 * tx_bytes);
+          box_issue<true>(box, tiles + stage * stage_bytes, nullptr, map_to_cta(smem_u32(&hdr->full[stage]), 0));
+          box_advance(p, box);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
