@@ -325,11 +325,16 @@ __device__ __forceinline__ void store_out(void* base, uint32_t is_bf16, uint64_t
   else ((float*)base)[idx] = v;
 }
 
+// Applies the epilogue to 32 accumulator columns of one row and stores them.  `bias_lane` is bias[col0 + lane]
+// (one coalesced load per warp, fetched a chunk ahead by the caller); lanes trade it with shuffles, so every
+// lane runs the arithmetic and only the memory accesses are guarded by `live`.
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&acc)[32], uint32_t batch, uint32_t split,
-                                               uint32_t row, uint32_t col0) {
-  if (row >= p.m || col0 >= p.n) return;
+                                               uint32_t row, uint32_t col0, float bias_lane) {
+  if (col0 >= p.n) return;
+  const bool live = row < p.m;
   const uint32_t cols = min(32u, p.n - col0);
   if (p.splits > 1) {
+    if (!live) return;
     float* dst = p.partial + (((uint64_t)split * p.batch + batch) * p.m + row) * p.n + col0;
     if (cols == 32 && (p.n & 3) == 0) {
 #pragma unroll
@@ -346,7 +351,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   const bool vec = p.vec_store && !p.transpose_out && cols == 32;
   if (vec) {
     const uint64_t off = cbase + (uint64_t)row * p.ldc + col0;
-    if (p.accumulate) {
+    if (p.accumulate && live) {
       if (p.c_is_bf16) {
 #pragma unroll
         for (uint32_t i = 0; i < 32; i += 8) {
@@ -368,12 +373,9 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
     }
     if (p.bias) {
 #pragma unroll
-      for (uint32_t i = 0; i < 32; i += 4) {
-        const float4 q = *(const float4*)(p.bias + col0 + i);
-        v[i] += q.x; v[i + 1] += q.y; v[i + 2] += q.z; v[i + 3] += q.w;
-      }
+      for (uint32_t i = 0; i < 32; ++i) v[i] += __shfl_sync(0xFFFFFFFFu, bias_lane, i);
     }
-    if (p.residual) {
+    if (p.residual && live) {
       if (p.c_is_bf16) {
 #pragma unroll
         for (uint32_t i = 0; i < 32; i += 8) {
@@ -397,6 +399,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
 #pragma unroll
       for (uint32_t i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
     }
+    if (!live) return;
     if (p.c_is_bf16) {
 #pragma unroll
       for (uint32_t i = 0; i < 32; i += 8)
@@ -408,6 +411,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
     }
     return;
   }
+  if (!live) return;
 #pragma unroll
   for (uint32_t i = 0; i < 32; ++i) {
     if (i < cols) {
@@ -419,6 +423,36 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
       if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
       if (p.relu) x = fmaxf(x, 0.0f);
       store_out(p.c, p.c_is_bf16, idx, x);
+    }
+  }
+}
+
+// Drains one accumulator of `ncols` columns: TMEM reads are double-buffered in registers (the next 32 columns
+// are in flight while the current ones are processed) and the bias slice is fetched one chunk ahead.
+// `wide` selects the column order of a two-half tile (see the pair kernel).
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, uint32_t ncols, uint32_t batch, uint32_t split,
+                                              uint32_t row, uint32_t col_base, bool wide, uint32_t lane) {
+  auto tile_col = [&](uint32_t c) { return wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c; };
+  auto bias_at = [&](uint32_t c) {
+    const uint32_t col = col_base + tile_col(c) + lane;
+    return (p.bias != nullptr && c < ncols && col < p.n) ? p.bias[col] : 0.0f;
+  };
+  uint32_t acc_a[32], acc_b[32];
+  float bias_next = bias_at(0);
+  tmem_ld_32x32(taddr, acc_a);
+  for (uint32_t c = 0; c < ncols; c += 64) {
+    const bool has_b = c + 32 < ncols;
+    tmem_ld_wait();
+    if (has_b) tmem_ld_32x32(taddr + c + 32, acc_b);
+    float bias_cur = bias_next;
+    bias_next = bias_at(c + 32);
+    epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur);
+    if (has_b) {
+      tmem_ld_wait();
+      if (c + 64 < ncols) tmem_ld_32x32(taddr + c + 64, acc_a);
+      bias_cur = bias_next;
+      bias_next = bias_at(c + 64);
+      epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + 32), bias_cur);
     }
   }
 }
@@ -436,7 +470,7 @@ struct MmaSetup {
   uint64_t a_desc0, b_desc0;        // descriptors of stage 0, slice 0
 };
 
-__device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t tile_rows, uint32_t tiles_addr, uint32_t stage_bytes) {
+__device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t tile_rows, uint32_t instr_n, uint32_t tiles_addr, uint32_t stage_bytes) {
   const uint32_t epl = p.tf32 ? 32u : 64u;
   // K-major: the four K slices of a stage sit 32 bytes apart inside each line.  MN-major: a slice is 16
   // (bf16) or 8 (tf32) whole lines, and 64-/32-wide MN blocks follow each other every epl lines.
@@ -447,7 +481,7 @@ __device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t
   const uint32_t a_mode = (p.tf32 && p.a_mn_major) ? kSwizzle128Base32 : kSwizzle128, a_sbo = (p.tf32 && p.a_mn_major) ? 512u : 1024u;
   const uint32_t b_mode = (p.tf32 && p.b_mn_major) ? kSwizzle128Base32 : kSwizzle128, b_sbo = (p.tf32 && p.b_mn_major) ? 512u : 1024u;
   MmaSetup s;
-  s.idesc = make_instr_desc(p.tf32 ? 2u : 1u, p.a_mn_major, p.b_mn_major, tile_rows, p.bn);
+  s.idesc = make_instr_desc(p.tf32 ? 2u : 1u, p.a_mn_major, p.b_mn_major, tile_rows, instr_n);
   s.a_step16 = a_step >> 4;
   s.b_step16 = b_step >> 4;
   s.stage16 = stage_bytes >> 4;
@@ -458,9 +492,9 @@ __device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t
 
 // Issues the four K slices of one stage.
 template <bool kPair, bool kTf32>
-__device__ __forceinline__ void mma_stage(const MmaSetup& s, uint32_t tmem_d, uint32_t stage, uint32_t first_accumulate) {
+__device__ __forceinline__ void mma_stage(const MmaSetup& s, uint32_t tmem_d, uint32_t stage, uint32_t first_accumulate, uint32_t b_extra16 = 0) {
   const uint64_t da = s.a_desc0 + (uint64_t)(stage * s.stage16);
-  const uint64_t db = s.b_desc0 + (uint64_t)(stage * s.stage16);
+  const uint64_t db = s.b_desc0 + (uint64_t)(stage * s.stage16 + b_extra16);
   mma_issue<kPair, kTf32>(tmem_d, da, db, s.idesc, first_accumulate);
   mma_issue<kPair, kTf32>(tmem_d, da + s.a_step16, db + s.b_step16, s.idesc, 1u);
   mma_issue<kPair, kTf32>(tmem_d, da + 2 * s.a_step16, db + 2 * s.b_step16, s.idesc, 1u);
@@ -534,7 +568,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   } else if (warp == 1) {
     // ===== MMA issuer =====
     if (lane == 0) {
-      const MmaSetup ms = make_mma_setup(p, kBM, smem_u32(tiles), stage_bytes);
+      const MmaSetup ms = make_mma_setup(p, kBM, p.bn, smem_u32(tiles), stage_bytes);
       uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
@@ -568,12 +602,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       tc_fence_after_sync();
       const uint32_t row = work.m_tile * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
-      for (uint32_t c = 0; c < p.bn; c += 32) {
-        uint32_t acc[32];
-        tmem_ld_32x32(taddr + c, acc);
-        tmem_ld_wait();
-        epilogue_chunk(p, acc, work.batch, work.split, row, work.n_tile * p.bn + c);
-      }
+      epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->acc_empty[buf]);
@@ -630,6 +659,12 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   SmemHeader* hdr = (SmemHeader*)smem;
   uint8_t* tiles = smem + kHeaderBytes;
+  // A tile wider than 256 columns is two 256-column halves accumulated side by side in TMEM by two MMAs per
+  // K slice (one accumulator buffer instead of two, so the epilogue no longer overlaps the next tile's
+  // mainloop, but a quarter fewer operand bytes cross the L2 fabric and shared memory per flop).  CTA r
+  // supplies tile columns r*bn/2 .. (r+1)*bn/2; half h uses the h-th 128-line block of each CTA's share, so
+  // accumulator column c of half h is tile column (c / 128) * (bn / 2) + h * 128 + c % 128.
+  const uint32_t halves = p.bn > 256 ? 2u : 1u, bufs = halves == 2 ? 1u : 2u;
   const uint32_t b_lines = p.bn / 2;                 // this CTA's share of the B tile
   const uint32_t b_tile_bytes = b_lines * kLineBytes;
   const uint32_t stage_bytes = kATileBytes + b_tile_bytes;
@@ -683,6 +718,11 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
         box_init(p, box, lane, &tmap_a, &tmap_b, work, work.m_tile * 2 * kBM + rank * kBM, work.n_tile * p.bn + rank * b_lines, b_lines);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_fast(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
+          if (p.debug_variant == 8) {   // experiment: no copies at all, the tensor core runs on whatever smem holds
+            if (lane == 0 && rank == 0) mbar_arrive(&hdr->full[stage]);
+            if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (lane == 0 && rank == 0) mbar_arrive_expect_tx(&hdr->full[stage], 2 * tx_bytes);
           box_issue<true>(box, tiles + stage * stage_bytes, nullptr, map_to_cta(smem_u32(&hdr->full[stage]), 0));
           box_advance(p, box);
@@ -693,27 +733,32 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
   } else if (warp == 1) {
     // ===== MMA issuer (leader CTA only) =====
     if (lane == 0 && rank == 0) {
-      const MmaSetup ms = make_mma_setup(p, 2 * kBM, smem_u32(tiles), stage_bytes);
+      const MmaSetup ms = make_mma_setup(p, 2 * kBM, p.bn / halves, smem_u32(tiles), stage_bytes);
+      const uint32_t acc_stride = p.bn / halves;
       uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
       for (uint32_t w = pair; ok && w < total_work; w += pairs) {
         const Work work = decode_work(p, w);
         if (!(ok = mbar_wait_fast(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
         tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + buf * p.bn;
+        const uint32_t tmem_d = tmem_base + buf * acc_stride;
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_fast(&hdr->full[stage], phase, abort_flag, kStatusMmaTimeout))) break;
           tc_fence_after_sync();
           if (p.debug_variant == 4 || p.debug_variant >= 60) mma_issue<true, false>(tmem_d, ms.a_desc0, ms.b_desc0, ms.idesc, 1u);
           else if (p.tf32) mma_stage<true, true>(ms, tmem_d, stage, kb > work.kb_begin);
           else mma_stage<true, false>(ms, tmem_d, stage, kb > work.kb_begin);
+          if (halves == 2) {   // second half: 128 B lines (16 KB) further on, 256 TMEM columns further on
+            if (p.tf32) mma_stage<true, true>(ms, tmem_d + 256, stage, kb > work.kb_begin, (128 * kLineBytes) >> 4);
+            else mma_stage<true, false>(ms, tmem_d + 256, stage, kb > work.kb_begin, (128 * kLineBytes) >> 4);
+          }
           // One arrival on the "empty" barrier of both CTAs (mask 0b11): each producer may refill its stage.
           mma_pair_commit_both(&hdr->empty[stage], 3);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         mma_pair_commit_both(&hdr->acc_full[buf], 3);
-        if ((buf ^= 1) == 0) buf_phase ^= 1;
+        if (++buf == bufs) { buf = 0; buf_phase ^= 1; }
       }
     }
   } else {
@@ -728,17 +773,12 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t row = work.m_tile * 2 * kBM + rank * kBM + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
-      for (uint32_t c = 0; c < (p.debug_variant == 3 ? 0u : p.bn); c += 32) {
-        uint32_t acc[32];
-        tmem_ld_32x32(taddr + c, acc);
-        tmem_ld_wait();
-        epilogue_chunk(p, acc, work.batch, work.split, row, work.n_tile * p.bn + c);
-      }
+      const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * (p.bn / halves);
+      if (p.debug_variant != 3) epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->acc_empty[buf]), 0));
-      if ((buf ^= 1) == 0) buf_phase ^= 1;
+      if (++buf == bufs) { buf = 0; buf_phase ^= 1; }
     }
   }
 

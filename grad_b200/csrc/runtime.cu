@@ -157,6 +157,7 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
   p.status = h->status;
   if (const char* v = getenv("GB_VARIANT")) p.debug_variant = (uint32_t)atoi(v);
   p.group_m = 8;
+  if (const char* v = getenv("GB_GROUP_M")) p.group_m = (uint32_t)std::max(1, atoi(v));
   if (plan.tensor) {
     const uint32_t epl = p.tf32 ? 32 : 64;
     p.k_blocks_total = ceil_div(p.k, epl);
@@ -197,8 +198,9 @@ bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b)
   const uint32_t pairs = (uint32_t)h->sm_count / 2;
   const uint32_t tiles_m = ceil_div(p.m, 256) * p.batch;
   const uint32_t n_cap = std::max(min_bn, ceil_div(p.n, min_bn) * min_bn);
-  for (uint32_t cand : {256u, 128u, 64u}) {
+  for (uint32_t cand : {512u, 256u, 128u, 64u}) {
     if (cand / 2 < min_bn || cand > std::max(n_cap, 2 * min_bn)) continue;
+    if (cand == 512 && (p.debug_variant == 9 || p.k_blocks_total < 32)) continue;   // the wide tile exposes its epilogue: long K only
     if (tiles_m * ceil_div(p.n, cand) < pairs) continue;
     if (!encode_b(cand / 2)) return false;
     p.cta_pair = 1;
