@@ -614,3 +614,70 @@ int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
 }
 
 }  // extern "C"
+
+// =====================================================================================================
+// gb_gemm_static_scratch: the product of gb_gemm for callers that must not allocate device memory.
+//
+// Some hosts of this library run where cudaMalloc is off limits: inside a stream capture or a replayed
+// graph step, in a plugin whose memory is owned by an arena that hands out nothing after start-up, or in
+// a process with a fixed device-memory budget.  gb_gemm needs two things such a caller cannot provide: a
+// handle (gb_create allocates a status word) and, when K is split, a workspace for the partial sums.  This
+// entry point needs neither.  Its split-K partials live in the array below, which is part of the library
+// image: every GPU that loads the library carries these 8 MiB until the process exits.
+//
+// The array's name is only a stand-in on the host; the kernels need its device address, which is looked up
+// once per device with cudaGetSymbolAddress while that device is current.  That look-up happens on the
+// first call made with a given device current, so make that first call outside any stream capture.
+// All calls share the one array and it keeps whatever the previous call left: every element a call reads
+// is written by the same call first (each K part stores its whole partial tile), so nothing has to be
+// cleared, but two calls that overlap on the GPU -- different streams, or different host threads -- race on
+// it.  Serialise them.
+namespace {
+
+__device__ __align__(256) unsigned char g_static_scratch[GB_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxStaticDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_scratch_ptr[kMaxStaticDevices] = {};
+int g_static_sm_count[kMaxStaticDevices] = {};
+
+// Resolves the device address of the scratch array for the current device (once), without allocating.
+int static_setup(int device, void** scratch, int* sm_count) {
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (device < 0 || device >= kMaxStaticDevices) return GB_ERR_NO_DEVICE;
+  if (g_static_scratch_ptr[device] == nullptr) {
+    int major = 0, sms = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess || major != 10) return GB_ERR_NO_DEVICE;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return GB_ERR_CUDA;
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return GB_ERR_CUDA;
+    if (gb::gemm_sm100_configure() != cudaSuccess || encode_tiled_fn() == nullptr) return GB_ERR_CUDA;
+    g_static_sm_count[device] = sms;
+    g_static_scratch_ptr[device] = ptr;
+  }
+  *scratch = g_static_scratch_ptr[device];
+  *sm_count = g_static_sm_count[device];
+  return GB_OK;
+}
+
+}  // namespace
+
+extern "C" int gb_gemm_static_scratch(void* stream, const gb_gemm_desc* desc, const void* a, const void* b, void* c,
+                                      const gb_epilogue* epilogue) {
+  int rc = validate_gemm(desc);
+  if (rc != GB_OK) return rc;
+  if (desc->m != 0 && desc->n != 0 && (!c || (desc->k != 0 && (!a || !b)))) return GB_ERR_INVALID;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return GB_ERR_NO_DEVICE;
+  void* scratch = nullptr;
+  gb_handle local;            // lives on the host stack: no status word, so bounded-wait failures go unreported here
+  local.device = device;
+  rc = static_setup(device, &scratch, &local.sm_count);
+  if (rc != GB_OK) return rc;
+  Plan plan;
+  rc = plan_gemm(&local, desc, a, b, c, epilogue, plan);
+  if (rc != GB_OK) return rc;
+  // A product whose partial sums do not fit the fixed array is refused, not silently run another way.
+  if (plan.workspace > (size_t)GB_STATIC_SCRATCH_BYTES) return GB_ERR_WORKSPACE;
+  return run_plan(&local, (cudaStream_t)stream, plan, scratch, GB_STATIC_SCRATCH_BYTES);
+}

@@ -131,6 +131,18 @@ int gb_gemm_workspace(const gb_handle* h, const gb_gemm_desc* desc, size_t* byte
 int gb_gemm(gb_handle* h, void* stream, const gb_gemm_desc* desc, const void* a, const void* b, void* c,
             const gb_epilogue* epilogue, void* workspace, size_t workspace_bytes);
 
+/* gb_gemm for callers that cannot allocate device memory (no counterpart in the reference, whose callers
+ * always own an arena: src/gpu/gpu.zig:395-410).  It takes no handle -- gb_create allocates -- and no
+ * workspace: split-K partial sums go to a fixed GB_STATIC_SCRATCH_BYTES array inside the library image,
+ * held by every GPU that loads the library until the process exits.  It uses the CURRENT device.  The
+ * first call with a given device current resolves the array's device address; make that call outside
+ * stream capture.  A product whose partials exceed the array returns GB_ERR_WORKSPACE.  All calls share
+ * the array: calls that overlap on the GPU (two streams, two threads) race and must be serialised.
+ * Device-side wait time-outs are not reported (there is no status word to report them into). */
+#define GB_STATIC_SCRATCH_BYTES (8u << 20)
+int gb_gemm_static_scratch(void* stream, const gb_gemm_desc* desc, const void* a, const void* b, void* c,
+                           const gb_epilogue* epilogue);
+
 /* ---- implicit-GEMM convolution ---------------------------------------------------------------- */
 /* Forward: replaces `Gpu.convImplicitForward` (src/gpu/gpu.zig:926-929), `Gpu.convF32Forward`
  * (:789-826), the im2col+GEMM paths `chooseConvPath` picks for strided or narrow layers
