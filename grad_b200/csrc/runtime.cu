@@ -618,9 +618,8 @@ int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
 // =====================================================================================================
 // gb_gemm_static_scratch: the product of gb_gemm for callers that must not allocate device memory.
 //
-// Some hosts of this library run where cudaMalloc is off limits: inside a stream capture or a replayed
-// graph step, in a plugin whose memory is owned by an arena that hands out nothing after start-up, or in
-// a process with a fixed device-memory budget.  gb_gemm needs two things such a caller cannot provide: a
+// Some hosts of this library run where cudaMalloc is off limits: a plugin whose memory is owned by an
+// arena that hands out nothing after start-up, or a process with a fixed device-memory budget.  gb_gemm needs two things such a caller cannot provide: a
 // handle (gb_create allocates a status word) and, when K is split, a workspace for the partial sums.  This
 // entry point needs neither.  Its split-K partials live in the array below, which is part of the library
 // image: every GPU that loads the library carries these 8 MiB until the process exits.

@@ -1,6 +1,6 @@
 """gb_gemm_static_scratch: the split-K product for callers that may not allocate device memory.
 
-A host that runs inside a captured step, or on a fixed device-memory budget, cannot call cudaMalloc and so
+A host on a fixed device-memory budget, or one whose arena is closed after start-up, cannot call cudaMalloc and so
 can neither create a handle nor bring a workspace.  This entry point keeps its split-K partial sums in a
 fixed array inside the library instead.  The test drives it through the C ABI on a shape that splits K,
 twice in a row with different operands (the shared array keeps the first call's partials), and expects the
