@@ -14,6 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 F32, BF16 = 0, 1
 MATH_F32, MATH_TF32, MATH_BF16 = 0, 1, 2
 ACT_NONE, ACT_RELU = 0, 1
+EPILOGUE_ROUND_TF32 = 1
 PASS_FPROP, PASS_DGRAD, PASS_WGRAD = 0, 1, 2
 
 STATUS_NAMES = {0: "GB_OK", 1: "GB_ERR_INVALID", 2: "GB_ERR_CUDA", 3: "GB_ERR_WORKSPACE", 4: "GB_ERR_UNSUPPORTED",
@@ -29,7 +30,7 @@ class GbError(RuntimeError):
 
 
 class Epilogue(C.Structure):
-    _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("activation", C.c_int32), ("reserved", C.c_int32)]
+    _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("activation", C.c_int32), ("flags", C.c_int32)]
 
 
 class GemmDesc(C.Structure):
@@ -79,6 +80,11 @@ SIGNATURES = {
                       C.c_int),
     "gb_conv_wgrad": ([C.c_void_p, C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t],
                       C.c_int),
+    "gb_pool2d": ([C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p] + [C.c_uint32] * 7, C.c_int),
+    "gb_elementwise": ([C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint32], C.c_int),
+    "gb_cast": ([C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t], C.c_int),
+    "gb_reorder_oihw": ([C.c_void_p, C.c_int, C.c_void_p, C.c_void_p] + [C.c_uint32] * 4, C.c_int),
+    "gb_permute_layout": ([C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p] + [C.c_uint32] * 4, C.c_int),
     "gb_comm_unique_id": ([C.c_void_p], C.c_int),
     "gb_comm_create": ([C.c_int, C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "gb_allreduce_mean": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t], C.c_int),

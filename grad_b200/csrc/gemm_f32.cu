@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmParams p) {
       if (p.bias) x += p.bias[col];
       if (p.residual) x += p.c_is_bf16 ? bf16_to_f32(((const uint16_t*)p.residual)[idx]) : ((const float*)p.residual)[idx];
       if (p.relu) x = fmaxf(x, 0.0f);
+      if (p.round_tf32) x = round_tf32(x);
       if (p.c_is_bf16) ((uint16_t*)p.c)[idx] = (uint16_t)bf16_bits(x);
       else ((float*)p.c)[idx] = x;
     }

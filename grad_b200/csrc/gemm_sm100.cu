@@ -399,6 +399,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
 #pragma unroll
       for (uint32_t i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
     }
+    if (p.round_tf32) {
+#pragma unroll
+      for (uint32_t i = 0; i < 32; ++i) v[i] = round_tf32(v[i]);
+    }
     if (!live) return;
     if (p.c_is_bf16) {
 #pragma unroll
@@ -422,6 +426,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
       if (p.bias) x += p.bias[col];
       if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
       if (p.relu) x = fmaxf(x, 0.0f);
+      if (p.round_tf32) x = round_tf32(x);
       store_out(p.c, p.c_is_bf16, idx, x);
     }
   }
@@ -811,6 +816,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
     if (p.bias) x += p.bias[col];
     if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
     if (p.relu) x = fmaxf(x, 0.0f);
+    if (p.round_tf32) x = round_tf32(x);
     store_out(p.c, p.c_is_bf16, idx, x);
   }
 }

@@ -1,0 +1,139 @@
+// The few bandwidth-bound kernels the ONNX executor needs between contractions so that a whole ResNet graph
+// stays on the device: 2-D pooling on NHWC, element-wise add / ReLU for node windows that were not folded
+// into a convolution epilogue, dtype casts, and the OIHW -> (taps, c_out) weight reorder.  They follow the
+// per-element definitions of grad's shared math (src/gpu/math/conv.zig:132-205 pooling,
+// src/onnx/runtime.zig:845-862 `reorderOihw`); none of them is on the contraction path itself.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/gradb200.h"
+#include "sm100_ptx.cuh"
+
+namespace {
+
+__device__ __forceinline__ float load_elem(const void* p, int bf16, size_t i) {
+  return bf16 ? gb::bf16_to_f32(((const uint16_t*)p)[i]) : ((const float*)p)[i];
+}
+__device__ __forceinline__ void store_elem(void* p, int bf16, size_t i, float v) {
+  if (bf16) ((uint16_t*)p)[i] = (uint16_t)gb::bf16_bits(v);
+  else ((float*)p)[i] = v;
+}
+
+// One thread per output element; window clipped to the image like `boundsOf` (conv.zig:152-161); the average
+// divides by the number of in-bounds taps (`windowCount`, :183-186).
+__global__ void pool2d_kernel(const void* x, void* y, int bf16, int is_max, uint32_t n, uint32_t h, uint32_t w, uint32_t c, uint32_t k,
+                              uint32_t stride, uint32_t pad, uint32_t oh, uint32_t ow) {
+  const size_t total = (size_t)n * oh * ow * c;
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t ch = (uint32_t)(t % c), ox = (uint32_t)(t / c % ow), oy = (uint32_t)(t / c / ow % oh), img = (uint32_t)(t / c / ow / oh);
+    const uint32_t top = oy * stride, left = ox * stride;
+    const uint32_t y0 = top < pad ? 0 : top - pad, y1 = min(top + k - pad, h);
+    const uint32_t x0 = left < pad ? 0 : left - pad, x1 = min(left + k - pad, w);
+    float best = -INFINITY, sum = 0.0f;
+    for (uint32_t yy = y0; yy < y1; ++yy)
+      for (uint32_t xx = x0; xx < x1; ++xx) {
+        const float v = load_elem(x, bf16, (((size_t)img * h + yy) * w + xx) * c + ch);
+        best = fmaxf(best, v);
+        sum += v;
+      }
+    const float count = (float)((y1 - y0) * (x1 - x0));
+    store_elem(y, bf16, t, is_max ? best : sum / count);
+  }
+}
+
+// op 0: out = a + b; 1: out = relu(a); 2: out = relu(a + b); 3: out = a + bias[i % cols] (b is f32 bias)
+__global__ void elementwise_kernel(const void* a, const void* b, void* out, int bf16, int op, size_t total, uint32_t cols) {
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+    float v = load_elem(a, bf16, t);
+    if (op == 0 || op == 2) v += load_elem(b, bf16, t);
+    if (op == 3) v += ((const float*)b)[t % cols];
+    if (op == 1 || op == 2) v = fmaxf(v, 0.0f);
+    store_elem(out, bf16, t, v);
+  }
+}
+
+__global__ void cast_kernel(const void* src, void* dst, int src_bf16, int dst_bf16, size_t total) {
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x)
+    store_elem(dst, dst_bf16, t, load_elem(src, src_bf16, t));
+}
+
+// w is (m, c, kh, kw) f32; wt is (kh*kw*c, m): wt[(tap*c + ic)*m + oc] = w[(oc*c + ic)*khkw + tap].
+__global__ void reorder_oihw_kernel(const float* w, void* wt, int dst_bf16, uint32_t m, uint32_t c, uint32_t khkw) {
+  const size_t total = (size_t)m * c * khkw;
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t oc = (uint32_t)(t % m);
+    const size_t item = t / m;
+    const uint32_t ic = (uint32_t)(item % c), tap = (uint32_t)(item / c);
+    store_elem(wt, dst_bf16, t, w[((size_t)oc * c + ic) * khkw + tap]);
+  }
+}
+
+// (n, c, h, w) <-> (n, h, w, c) for graphs that arrive in NCHW (src/onnx/gpu.zig:525-542).
+__global__ void permute_kernel(const void* src, void* dst, int bf16, int to_nhwc, uint32_t n, uint32_t c, uint32_t h, uint32_t w) {
+  const size_t total = (size_t)n * c * h * w;
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+    // t indexes the destination
+    size_t s;
+    if (to_nhwc) {
+      const uint32_t ch = (uint32_t)(t % c), x = (uint32_t)(t / c % w), y = (uint32_t)(t / c / w % h), img = (uint32_t)(t / c / w / h);
+      s = (((size_t)img * c + ch) * h + y) * w + x;
+    } else {
+      const uint32_t x = (uint32_t)(t % w), y = (uint32_t)(t / w % h), ch = (uint32_t)(t / w / h % c), img = (uint32_t)(t / w / h / c);
+      s = (((size_t)img * h + y) * w + x) * c + ch;
+    }
+    store_elem(dst, bf16, t, load_elem(src, bf16, s));
+  }
+}
+
+unsigned blocks_for(size_t total) {
+  const size_t want = (total + 255) / 256;
+  return (unsigned)(want < 148 * 8 ? (want == 0 ? 1 : want) : 148 * 8);
+}
+
+int finish() { return cudaGetLastError() == cudaSuccess ? GB_OK : GB_ERR_CUDA; }
+
+}  // namespace
+
+extern "C" {
+
+int gb_pool2d(void* stream, int is_max, int dtype, const void* x, void* y, uint32_t n, uint32_t h, uint32_t w, uint32_t c, uint32_t k,
+              uint32_t stride, uint32_t pad) {
+  if (!x || !y || k == 0 || stride == 0 || h + 2 * pad < k || w + 2 * pad < k) return GB_ERR_INVALID;
+  const uint32_t oh = (h + 2 * pad - k) / stride + 1, ow = (w + 2 * pad - k) / stride + 1;
+  const size_t total = (size_t)n * oh * ow * c;
+  if (total == 0) return GB_OK;
+  pool2d_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(x, y, dtype == GB_BF16, is_max, n, h, w, c, k, stride, pad, oh, ow);
+  return finish();
+}
+
+int gb_elementwise(void* stream, int op, int dtype, const void* a, const void* b, void* out, size_t total, uint32_t cols) {
+  if (!a || !out || op < 0 || op > 3 || ((op == 0 || op == 2 || op == 3) && !b) || (op == 3 && cols == 0)) return GB_ERR_INVALID;
+  if (total == 0) return GB_OK;
+  elementwise_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(a, b, out, dtype == GB_BF16, op, total, cols);
+  return finish();
+}
+
+int gb_cast(void* stream, int src_dtype, int dst_dtype, const void* src, void* dst, size_t total) {
+  if (!src || !dst) return GB_ERR_INVALID;
+  if (total == 0) return GB_OK;
+  cast_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(src, dst, src_dtype == GB_BF16, dst_dtype == GB_BF16, total);
+  return finish();
+}
+
+int gb_reorder_oihw(void* stream, int dst_dtype, const float* w, void* wt, uint32_t m, uint32_t c, uint32_t kh, uint32_t kw) {
+  if (!w || !wt) return GB_ERR_INVALID;
+  const size_t total = (size_t)m * c * kh * kw;
+  if (total == 0) return GB_OK;
+  reorder_oihw_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(w, wt, dst_dtype == GB_BF16, m, c, kh * kw);
+  return finish();
+}
+
+int gb_permute_layout(void* stream, int dtype, int to_nhwc, const void* src, void* dst, uint32_t n, uint32_t c, uint32_t h, uint32_t w) {
+  if (!src || !dst) return GB_ERR_INVALID;
+  const size_t total = (size_t)n * c * h * w;
+  if (total == 0) return GB_OK;
+  permute_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(src, dst, dtype == GB_BF16, to_nhwc, n, c, h, w);
+  return finish();
+}
+
+}  // extern "C"

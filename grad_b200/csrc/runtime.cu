@@ -154,6 +154,7 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
   p.bias = ep ? ep->bias : nullptr;
   p.residual = ep ? ep->residual : nullptr;
   p.relu = ep && ep->activation == GB_ACT_RELU;
+  p.round_tf32 = ep && (ep->flags & GB_EPILOGUE_ROUND_TF32) && !p.c_is_bf16;
   p.status = h->status;
   if (const char* v = getenv("GB_VARIANT")) p.debug_variant = (uint32_t)atoi(v);
   p.group_m = 8;

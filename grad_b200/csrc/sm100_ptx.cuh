@@ -308,6 +308,12 @@ __device__ __forceinline__ uint32_t bf16_bits(float x) {
   return (bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16;
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) { return bf16_bits(lo) | (bf16_bits(hi) << 16); }
+// f32 -> TF32 precision, round to nearest with ties away from zero (cvt.rna.tf32.f32), kept in an f32.
+__device__ __forceinline__ float round_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
 __device__ __forceinline__ float bf16_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
 
 }  // namespace gb

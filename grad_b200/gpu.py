@@ -41,6 +41,7 @@ class Epilogue:
     bias: Optional[torch.Tensor] = None        # f32[n]
     residual: Optional[torch.Tensor] = None    # same shape / dtype as the output
     relu: bool = False
+    round_tf32: bool = False                   # store the f32 result rounded to TF32 (nearest, ties away)
 
 
 @dataclass
@@ -162,7 +163,7 @@ class Gpu:
     def _epilogue(self, ep: Optional[Epilogue]):
         if ep is None:
             return None
-        e = abi.Epilogue(_ptr(ep.bias), _ptr(ep.residual), ACT_RELU if ep.relu else ACT_NONE, 0)
+        e = abi.Epilogue(_ptr(ep.bias), _ptr(ep.residual), ACT_RELU if ep.relu else ACT_NONE, abi.EPILOGUE_ROUND_TF32 if ep.round_tf32 else 0)
         return C.byref(e)
 
     # ---- matmul family ----------------------------------------------------------------------------

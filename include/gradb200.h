@@ -59,8 +59,12 @@ typedef struct {
   const float* bias;        /* f32[n] (per output column / output channel) or NULL */
   const void* residual;     /* same shape, pitch and dtype as the output, or NULL (ONNX Add before Relu) */
   int32_t activation;       /* gb_activation */
-  int32_t reserved;
+  int32_t flags;            /* GB_EPILOGUE_* bits */
 } gb_epilogue;
+/* Round the stored f32 result to TF32 (nearest, ties away: cvt.rna.tf32.f32, src/gpu/device.zig:1888-1893).
+ * The tensor core reads TF32 operands by dropping the low mantissa bits; a chain of TF32 layers whose
+ * activations were rounded when stored sees the reference's round-to-nearest instead of a truncation. */
+#define GB_EPILOGUE_ROUND_TF32 1
 
 /* One product C[m,n] (+)= op(A) * op(B), row-major.  Replaces `MatmulShape` + `MatmulOpts`
  * (src/gpu/gpu.zig:22,29), `GemmShape` (src/gpu/args.zig:2-12) and the fields of `TensorShape`
@@ -161,6 +165,24 @@ int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
  * (:775-787, :828-866).  Partials of the split over positions are combined in order. */
 int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* x, void* dw,
                   void* workspace, size_t workspace_bytes);
+
+/* ---- executor glue (ONNX inference graphs) ------------------------------------------------------ */
+/* The bandwidth-bound node kinds `grad.onnx_gpu.Executor` runs between contractions, so a ResNet graph
+ * never leaves the device (src/onnx/gpu.zig:304-470): all take the caller's stream, none allocates.
+ * dtype is a gb_dtype; tensors are NHWC. */
+/* MaxPool / AveragePool with a square window; windows are clipped to the image and the average divides by
+ * the in-bounds count (src/gpu/math/conv.zig:152-205). */
+int gb_pool2d(void* stream, int is_max, int dtype, const void* x, void* y, uint32_t n, uint32_t h, uint32_t w, uint32_t c,
+              uint32_t k, uint32_t stride, uint32_t pad);
+/* op 0: out = a + b; 1: out = relu(a); 2: out = relu(a + b); 3: out = a + bias[i % cols] with b an f32 bias
+ * (`elementwise(.add)` + `Relu`, src/onnx/gpu.zig:318, 372-377, 518-519). */
+int gb_elementwise(void* stream, int op, int dtype, const void* a, const void* b, void* out, size_t total, uint32_t cols);
+int gb_cast(void* stream, int src_dtype, int dst_dtype, const void* src, void* dst, size_t total);
+/* OIHW f32 filters -> (kh*kw*c, m) in dst_dtype: `reorderedWeights` / `reorderOihw`
+ * (src/onnx/gpu.zig:566-574, src/onnx/runtime.zig:845-862); done once per weight and cached by the caller. */
+int gb_reorder_oihw(void* stream, int dst_dtype, const float* w, void* wt, uint32_t m, uint32_t c, uint32_t kh, uint32_t kw);
+/* NCHW <-> NHWC copy for graphs that arrive in NCHW (src/onnx/gpu.zig:525-542). */
+int gb_permute_layout(void* stream, int dtype, int to_nhwc, const void* src, void* dst, uint32_t n, uint32_t c, uint32_t h, uint32_t w);
 
 /* ---- data-parallel gradient mean -------------------------------------------------------------- */
 /* Replaces `Replicas.averageGrads` (src/nn/replicas.zig:57-91): the mean over replicas of one flat

@@ -1,0 +1,91 @@
+"""`Executor.run` against the CPU walk of the same in-memory graph, as tests/onnx_gpu.zig:15-278 compares
+`Executor.run` with `Model.run`: logits within tolerance, argmax identical, every node on the device."""
+import numpy as np
+import pytest
+
+from tests.util import TOL_BF16, TOL_F32, TOL_TF32, rel_fro, seeded
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    import grad_b200
+
+    g = grad_b200.Gpu(0)
+    yield g
+    g.check_status()
+    g.close()
+
+
+@pytest.fixture(scope="module")
+def small_case():
+    from grad_b200.onnx_gpu import resnet14_model
+    from oracle import onnx_cpu
+
+    model = resnet14_model(64, 128, 256, seed=1238)   # the narrower net keeps the CPU walk to a few seconds
+    x = seeded(1238, 24, 3072)
+    want = onnx_cpu.run(model, {"input": x})["logits"]
+    return model, x, want
+
+
+@pytest.mark.parametrize("mode,tol", [("f32", 1e-4), ("tf32", TOL_TF32), ("bf16", TOL_BF16)])
+@pytest.mark.parametrize("fuse", [True, False])
+def test_resnet14_logits_match_cpu_walk(gpu, small_case, mode, tol, fuse):
+    from grad_b200.onnx_gpu import Executor
+
+    model, x, want = small_case
+    ex = Executor(model, gpu, mode=mode, fuse=fuse)
+    got = ex.run({"input": x})["logits"]
+    assert got.shape == want.shape == (24, 10)
+    assert rel_fro(got, want) <= tol, rel_fro(got, want)
+    # argmax-identical wherever the CPU's own top-2 margin exceeds the error bound of the mode
+    top2 = np.sort(want, axis=1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 4 * tol * np.abs(want).max()
+    assert np.array_equal(got.argmax(1)[clear], want.argmax(1)[clear])
+    assert ex.stats.host_nodes == 0 and ex.stats.uploads >= 1 and ex.stats.downloads == 1
+    if fuse:
+        # 15 convs and 1 product (one launch each, two when K is split), 5 pools, 15 first-run weight reorders
+        assert ex.stats.launches <= 2 * (15 + 1) + 5 + 15
+
+
+def test_fusion_changes_launch_count_not_results(gpu, small_case):
+    from grad_b200.onnx_gpu import Executor
+
+    model, x, _ = small_case
+    fused, plain = Executor(model, gpu, "tf32", fuse=True), Executor(model, gpu, "tf32", fuse=False)
+    a, b = fused.run({"input": x})["logits"], plain.run({"input": x})["logits"]
+    assert rel_fro(a, b) <= TOL_TF32   # the unfused walk rounds to TF32 before Add / Relu, the fused one after
+    fused.run({"input": x}); plain.run({"input": x})      # second run: weight caches are warm
+    assert 21 <= fused.stats.launches <= 37 and plain.stats.launches >= fused.stats.launches + 15
+
+
+def test_graph_replay_equals_eager_run(gpu, small_case):
+    import torch
+    from grad_b200.onnx_gpu import Executor
+
+    model, x, _ = small_case
+    ex = Executor(model, gpu, "bf16")
+    xd = torch.from_numpy(x).cuda()
+    eager = ex.run_device({"input": xd})["logits"].clone()
+    ex.capture({"input": xd})
+    again = ex.replay({"input": xd})["logits"]
+    torch.cuda.synchronize()
+    assert torch.equal(eager, again)
+    other = torch.from_numpy(seeded(99, 24, 3072)).cuda()
+    want = ex.run_device({"input": other})["logits"].clone()
+    got = ex.replay({"input": other})["logits"]
+    torch.cuda.synchronize()
+    assert torch.equal(want, got)
+
+
+def test_full_width_model_runs_at_batch_100(gpu):
+    """The benchmark's graph (64-192-384) at batch 100: shape, finiteness, and bf16 vs tf32 agreement."""
+    from grad_b200.onnx_gpu import Executor, resnet14_model
+
+    model = resnet14_model(64, 192, 384)
+    x = seeded(5, 100, 3072)
+    a = Executor(model, gpu, "tf32").run({"input": x})["logits"]
+    b = Executor(model, gpu, "bf16").run({"input": x})["logits"]
+    assert a.shape == (100, 10) and np.isfinite(a).all()
+    assert rel_fro(b, a) <= TOL_BF16
