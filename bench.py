@@ -147,6 +147,58 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def resnet_inference(gpu, rank, world, dist, torch):
+    """Second half of the metric: ONNX-executor inference of ResNet-14 64-192-384 (batch norm folded), bf16,
+    images/s.  The batch is split across the GPUs (rank r runs images [B*r/N, B*(r+1)/N), full weight replica,
+    no collective); time is the maximum over ranks.  `value` replays a captured run on device-resident
+    inputs; `e2e` copies the rank's images from pinned host memory and brings its logits back every step."""
+    from grad_b200.onnx_gpu import Executor, resnet14_model
+    from grad_b200.replicas import shard
+
+    model = resnet14_model(64, 192, 384)
+    out = {"unit": "images/s", "model": "ResNet-14 64-192-384, 3x32x32 inputs N(0,1), He-normal weights, bf16 activations",
+           "gflop_per_image": 1.482, "scaling": "strong (batch sharded)"}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for batch, iters in ((4096, 10), (100, 50)):
+        lo, hi = shard(batch, world, rank)
+        if hi - lo == 0:
+            continue
+        gen = torch.Generator(device="cuda").manual_seed(1234 + 3)
+        x = torch.randn((batch, 3072), generator=gen, device="cuda")[lo:hi].contiguous()
+        ex = Executor(model, gpu, "bf16")
+        ex.capture({"input": x})
+        ms = timed(lambda: ex.replay({"input": x}), iters)
+        hx = x.cpu().pin_memory()
+        hlogits = torch.empty((hi - lo, 10), dtype=torch.float32).pin_memory()
+
+        def e2e():
+            hlogits.copy_(ex.replay({"input": hx})["logits"], non_blocking=True)
+
+        ms_e2e = timed(e2e, iters)
+        out[f"batch_{batch}"] = {"value": round(batch / ms * 1e3, 1), "ms": round(ms, 4), "tflops": round(batch * 1.482e9 / ms / 1e9, 1),
+                                 "e2e": round(batch / ms_e2e * 1e3, 1), "launches_per_run": 21, "per_gpu_batch": hi - lo}
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -238,6 +290,8 @@ def run_ours(args):
     h2d = ha.numel() * 2 + hb.numel() * 2
     d2h = hout.numel() * 2
 
+    resnet = resnet_inference(gpu, rank, world, dist, torch)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -269,6 +323,7 @@ def run_ours(args):
                      "traffic": traffic, "peak_source": f"{peak_kind} cuBLAS bf16 {'sustained' if sustained else 'burst'}",
                      "frac_of_nominal_2250": round(achieved / 2250.0, 4)},
     }
+    line["resnet14_inference"] = resnet
     if world == 1 and not args.no_cpu_baseline:
         rows = 4096 if size >= 4096 else size
         cpu_value, cores, secs = cpu_sample(size, rows, 2)
