@@ -107,8 +107,74 @@ __device__ __forceinline__ float load_as_f32(const GatherDesc& d, int64_t idx) {
   return d.src_is_bf16 ? bf16_to_f32(((const uint16_t*)d.base)[idx]) : ((const float*)d.base)[idx];
 }
 
-// Fills one 128-byte line of an operand tile.  `l` is the line's index within the tile (its low three
-// bits select the swizzle), `line_major`/`inner0` locate it in the source.
+// What a gathered line needs from its line-major index, computed once per line instead of once per element.
+struct LineCtx {
+  uint32_t line, valid;
+  uint32_t img;
+  int32_t y0, x0;   // patch: top-left input coordinate of the window (may be negative); patchT: pixel + pad
+};
+
+__device__ __forceinline__ LineCtx make_line_ctx(const GatherDesc& d, const ConvGeo& g, uint32_t line) {
+  LineCtx c;
+  c.line = line;
+  c.valid = line < d.lines_total;
+  c.img = 0; c.y0 = 0; c.x0 = 0;
+  if (!c.valid) return c;
+  if (d.source == kSrcPatch) {
+    const uint32_t per_image = g.out_h * g.out_w;
+    c.img = line / per_image;
+    const uint32_t rem = line - c.img * per_image, oy = rem / g.out_w, ox = rem - oy * g.out_w;
+    c.y0 = (int32_t)(oy * g.stride) - (int32_t)g.pad;
+    c.x0 = (int32_t)(ox * g.stride) - (int32_t)g.pad;
+  } else if (d.source == kSrcPatchT) {
+    const uint32_t per_image = g.h * g.w;
+    c.img = line / per_image;
+    const uint32_t rem = line - c.img * per_image, y = rem / g.w, x = rem - y * g.w;
+    c.y0 = (int32_t)(y + g.pad);
+    c.x0 = (int32_t)(x + g.pad);
+  }
+  return c;
+}
+
+// Source index of element `inner` of the line, or -1 for an implicit zero; `run` receives how many elements
+// from there on are contiguous in memory and share that answer (capped at `want`).
+__device__ __forceinline__ int64_t gather_run(const GatherDesc& d, const ConvGeo& g, const LineCtx& c, uint32_t inner, uint32_t want, uint32_t& run) {
+  run = want;
+  if (!c.valid || inner >= d.inner_total) return -1;
+  run = min(want, d.inner_total - inner);
+  switch (d.source) {
+    case kSrcDense:
+      return (int64_t)c.line * d.ld + inner;
+    case kSrcPatch: {
+      const uint32_t tap = inner / g.c, ci = inner - tap * g.c;
+      const uint32_t ky = tap / g.k, kx = tap - ky * g.k;
+      run = min(run, g.c - ci);
+      const int32_t py = c.y0 + (int32_t)(ky * g.dilation), px = c.x0 + (int32_t)(kx * g.dilation);
+      if (py < 0 || px < 0 || py >= (int32_t)g.h || px >= (int32_t)g.w) return -1;
+      return ((int64_t)(c.img * g.h + py) * g.w + px) * g.c_step + ci;
+    }
+    case kSrcPatchT: {
+      const uint32_t tap = inner / g.c_out, co = inner - tap * g.c_out;
+      const uint32_t ky = tap / g.k, kx = tap - ky * g.k;
+      run = min(run, g.c_out - co);
+      const int32_t ty = c.y0 - (int32_t)(ky * g.dilation), tx = c.x0 - (int32_t)(kx * g.dilation);
+      if (ty < 0 || tx < 0) return -1;
+      const uint32_t oy = (uint32_t)ty / g.stride, ox = (uint32_t)tx / g.stride;
+      if (oy * g.stride != (uint32_t)ty || ox * g.stride != (uint32_t)tx || oy >= g.out_h || ox >= g.out_w) return -1;
+      return ((int64_t)(c.img * g.out_h + oy) * g.out_w + ox) * g.c_out + co;
+    }
+    default: {
+      const uint32_t tap = inner / g.c_out, co = inner - tap * g.c_out;
+      run = min(run, g.c_out - co);
+      return ((int64_t)tap * g.c + c.line) * g.c_out + co;
+    }
+  }
+}
+
+// Fills one 128-byte line of an operand tile.  `l` is the line's index within the tile (its low bits select
+// the swizzle).  All eight 16-byte chunks are fetched before any is stored, so their latencies overlap;
+// a chunk that is one aligned contiguous run (or all padding) takes vector loads, anything else goes
+// element by element.
 __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDesc& d, uint8_t* tile, uint32_t l,
                                             uint32_t line_major, uint32_t inner0, uint64_t batch_off) {
   uint8_t* line = tile + l * kLineBytes;
@@ -117,56 +183,43 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
   const uint32_t epc = p.tf32 ? 4u : 8u;   // elements per 16-byte chunk
   GatherDesc src = d;
   src.base = (const uint8_t*)d.base + batch_off * (d.src_is_bf16 ? 2 : 4);
-#pragma unroll 1
+  const LineCtx ctx = make_line_ctx(src, p.geo, line_major);
+  const bool convert = !p.tf32 && !src.src_is_bf16;   // f32 in memory, bf16 in the tile: two 16-byte loads per chunk
+  uint4 lo[8], hi[8];
+  uint32_t slow = 0;
+#pragma unroll
   for (uint32_t chunk = 0; chunk < 8; ++chunk) {
-    const uint32_t inner = inner0 + chunk * epc;
-    float v[8];
-    // Fast path: the chunk is one contiguous, fully valid, 16-byte-aligned run in the source.
-    const int64_t first = gather_index(src, p.geo, line_major, inner);
-    const int64_t last = gather_index(src, p.geo, line_major, inner + epc - 1);
-    bool vec = first >= 0 && last == first + (int64_t)epc - 1;
-    uint4 out;
-    if (vec && !p.tf32 && src.src_is_bf16) {
-      const uint16_t* ptr = (const uint16_t*)src.base + first;
-      if (((uintptr_t)ptr & 15) == 0) {
-        out = *(const uint4*)ptr;
-        *(uint4*)(line + ((chunk ^ sw) << 4)) = out;
-        continue;
+    uint32_t run;
+    const int64_t first = gather_run(src, p.geo, ctx, inner0 + chunk * epc, epc, run);
+    lo[chunk] = make_uint4(0, 0, 0, 0);
+    hi[chunk] = make_uint4(0, 0, 0, 0);
+    if (run < epc) { slow |= 1u << chunk; continue; }
+    if (first < 0) continue;
+    const uint8_t* ptr = (const uint8_t*)src.base + first * (src.src_is_bf16 ? 2 : 4);
+    if (((uintptr_t)ptr & 15) != 0 || (p.tf32 && src.src_is_bf16)) { slow |= 1u << chunk; continue; }
+    lo[chunk] = *(const uint4*)ptr;
+    if (convert) hi[chunk] = *(const uint4*)(ptr + 16);
+  }
+#pragma unroll
+  for (uint32_t chunk = 0; chunk < 8; ++chunk) {
+    uint4 out = lo[chunk];
+    if (slow & (1u << chunk)) {
+      float v[8];
+      for (uint32_t e = 0; e < epc; ++e) {
+        uint32_t run;
+        const int64_t idx = gather_run(src, p.geo, ctx, inner0 + chunk * epc + e, 1, run);
+        v[e] = load_as_f32(src, idx);
       }
-    } else if (vec && !src.src_is_bf16) {
-      const float* ptr = (const float*)src.base + first;
-      if (((uintptr_t)ptr & 15) == 0) {
-        const float4 lo = *(const float4*)ptr;
-        if (p.tf32) {
-          *(float4*)(line + ((chunk ^ sw) << 4)) = lo;
-          continue;
-        }
-        const float4 hi = *(const float4*)(ptr + 4);
-        out.x = pack_bf16x2(lo.x, lo.y);
-        out.y = pack_bf16x2(lo.z, lo.w);
-        out.z = pack_bf16x2(hi.x, hi.y);
-        out.w = pack_bf16x2(hi.z, hi.w);
-        *(uint4*)(line + ((chunk ^ sw) << 4)) = out;
-        continue;
-      }
-    }
-    for (uint32_t e = 0; e < epc; ++e) v[e] = load_as_f32(src, gather_index(src, p.geo, line_major, inner + e));
-    if (p.tf32) {
-      out.x = __float_as_uint(v[0]);
-      out.y = __float_as_uint(v[1]);
-      out.z = __float_as_uint(v[2]);
-      out.w = __float_as_uint(v[3]);
-    } else {
-      out.x = pack_bf16x2(v[0], v[1]);
-      out.y = pack_bf16x2(v[2], v[3]);
-      out.z = pack_bf16x2(v[4], v[5]);
-      out.w = pack_bf16x2(v[6], v[7]);
+      if (p.tf32) out = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+      else out = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+    } else if (convert) {
+      const uint4 a = lo[chunk], b2 = hi[chunk];
+      out = make_uint4(pack_bf16x2(__uint_as_float(a.x), __uint_as_float(a.y)), pack_bf16x2(__uint_as_float(a.z), __uint_as_float(a.w)),
+                       pack_bf16x2(__uint_as_float(b2.x), __uint_as_float(b2.y)), pack_bf16x2(__uint_as_float(b2.z), __uint_as_float(b2.w)));
     }
     *(uint4*)(line + ((chunk ^ sw) << 4)) = out;
   }
 }
-
-// Fills operand tile `tile` (lines_in_tile lines) for the K block starting at element k0.
 __device__ __forceinline__ void gather_tile(const GemmParams& p, const GatherDesc& d, uint8_t* tile, uint32_t lines_in_tile,
                                             uint32_t mn0, uint32_t k0, uint32_t batch, uint32_t tid) {
   const uint32_t epl = p.tf32 ? 32u : 64u;
