@@ -51,7 +51,7 @@ class ConvGeometryC(C.Structure):
 
 class ConvDesc(C.Structure):
     _fields_ = [("geo", ConvGeometryC), ("dtype_x", C.c_uint8), ("dtype_w", C.c_uint8), ("dtype_y", C.c_uint8), ("math", C.c_uint8),
-                ("accumulate", C.c_uint8), ("deterministic", C.c_uint8), ("reserved", C.c_uint8 * 2)]
+                ("accumulate", C.c_uint8), ("deterministic", C.c_uint8), ("w_layout", C.c_uint8), ("reserved", C.c_uint8)]
 
 
 class PlanInfo(C.Structure):
@@ -84,6 +84,7 @@ SIGNATURES = {
     "gb_elementwise": ([C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint32], C.c_int),
     "gb_cast": ([C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t], C.c_int),
     "gb_reorder_oihw": ([C.c_void_p, C.c_int, C.c_void_p, C.c_void_p] + [C.c_uint32] * 4, C.c_int),
+    "gb_reorder_oihw_rows": ([C.c_void_p, C.c_int, C.c_void_p, C.c_void_p] + [C.c_uint32] * 4, C.c_int),
     "gb_permute_layout": ([C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p] + [C.c_uint32] * 4, C.c_int),
     "gb_comm_unique_id": ([C.c_void_p], C.c_int),
     "gb_comm_create": ([C.c_int, C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)], C.c_int),

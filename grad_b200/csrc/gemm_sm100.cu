@@ -26,6 +26,16 @@
 
 namespace gb {
 
+// Optional stage timestamps of CTA 0 (globaltimer ns), written only when the experiment switch is 7.
+__device__ unsigned long long g_stage_times[16];
+__device__ __forceinline__ void stamp(uint32_t variant, int slot) {
+  if (variant == 7 && blockIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_stage_times[slot] = t;
+  }
+}
+
 namespace {
 
 constexpr uint32_t kBM = 128;            // tile rows = TMEM lanes
@@ -271,12 +281,12 @@ __device__ __forceinline__ void box_refresh(const GemmParams& p, BoxLane& b, uin
   if (b.kind == kPatchK) {
     b.x = (int32_t)(b.cb * epl);
     b.y = b.origin + b.sign * (int32_t)(b.kx * p.geo.dilation);
-    b.z = b.row0 + b.origin + b.sign * (int32_t)(b.ky * p.geo.dilation);
+    b.z = b.row0 + b.origin + b.sign * (int32_t)(b.ky * p.geo.dilation);   // row0 is already in input rows
   } else if (b.kind == kWeightK) {
     b.x = (int32_t)(b.cb * epl);
     b.z = (int32_t)b.tap;
   } else if (b.kind == kPatchMN) {
-    b.z = (int32_t)b.row + b.h_off;
+    b.z = (int32_t)(b.row * p.geo.stride) + b.h_off;
     b.w = (int32_t)b.img;
   }
 }
@@ -311,7 +321,7 @@ __device__ __forceinline__ void box_init(const GemmParams& p, BoxLane& b, uint32
       b.tap = k0 / b.cblocks; b.cb = k0 - b.tap * b.cblocks;
       b.ky = b.tap / p.geo.k; b.kx = b.tap - b.ky * p.geo.k;
       const uint32_t img = mn0 / per_image;
-      b.row0 = p.box_n > 1 ? 0 : (int32_t)((mn0 - img * per_image) / grid_w);
+      b.row0 = p.box_n > 1 ? 0 : (int32_t)((mn0 - img * per_image) / grid_w * (p.dgrad ? 1u : p.geo.stride));
       b.sign = p.dgrad ? -1 : 1;
       b.origin = p.dgrad ? (int32_t)p.geo.pad : -(int32_t)p.geo.pad;
       b.w = (int32_t)img;
@@ -476,7 +486,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
       const uint64_t idx = cbase + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
       float x = v[i];
       if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx);
-      if (p.bias) x += p.bias[col];
+      if (p.bias) x += p.bias[p.bias_per_row ? row : col];
       if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
       if (p.relu) x = fmaxf(x, 0.0f);
       if (p.round_tf32) x = round_tf32(x);
@@ -485,32 +495,122 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
 }
 
+// Transposed store of 32 accumulator columns x 32 rows of one warp: the tile's rows are the output's
+// contiguous index (output channels when a convolution is computed transposed), so writing them straight
+// from the accumulator layout (one row per thread) would take 32 two- or four-byte stores per thread.
+// The warp instead parks the 32 x 32 f32 block in its private shared-memory buffer as [column][row]
+// (row pitch 36 words: conflict-free for the scalar writes and for the float4 reads), then every lane picks
+// up runs of 8 (bf16) or 4 (f32) consecutive rows of one column, applies the epilogue on vectors
+// (old value, bias per row, residual, ReLU, rounding) and stores 16 bytes.
+constexpr uint32_t kStagePitch = 36;                          // words per staged column
+constexpr uint32_t kStageBytesPerWarp = 32 * kStagePitch * 4;  // 4608
+constexpr uint32_t kStageBytes = 8 * kStageBytesPerWarp;       // up to eight epilogue warps
+
+__device__ __forceinline__ void epilogue_chunk_transposed(const GemmParams& p, const uint32_t (&acc)[32], float* buf, uint32_t batch,
+                                                          uint32_t row_base, uint32_t col0, uint32_t lane) {
+  if (col0 >= p.n) return;
+#pragma unroll
+  for (uint32_t i = 0; i < 32; ++i) buf[i * kStagePitch + lane] = __uint_as_float(acc[i]);
+  __syncwarp();
+  const uint32_t per = p.c_is_bf16 ? 8u : 4u, segs = 32 / per;
+  const uint64_t cbase = (uint64_t)batch * p.stride_c;
+  for (uint32_t item = lane; item < 32 * segs; item += 32) {
+    const uint32_t pos = item / segs, seg = item - pos * segs;
+    const uint32_t col = col0 + pos, row0 = row_base + seg * per;
+    if (col >= p.n || row0 >= p.m) continue;
+    float v[8];
+    const float4 a = *(const float4*)(buf + pos * kStagePitch + seg * per);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    if (per == 8) {
+      const float4 b = *(const float4*)(buf + pos * kStagePitch + seg * per + 4);
+      v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    const uint64_t idx = cbase + (uint64_t)col * p.ldc + row0;
+    const bool full = row0 + per <= p.m;
+    if (full) {
+      if (p.accumulate) {
+        if (p.c_is_bf16) {
+          const uint4 q = *(const uint4*)((const uint16_t*)p.c + idx);
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) { v[2 * j] += __uint_as_float(w[j] << 16); v[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u); }
+        } else {
+          const float4 q = *(const float4*)((const float*)p.c + idx);
+          v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
+        }
+      }
+      if (p.bias) {
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j)
+          if (j < per) v[j] += p.bias[p.bias_per_row ? row0 + j : col];
+      }
+      if (p.residual) {
+        if (p.c_is_bf16) {
+          const uint4 q = *(const uint4*)((const uint16_t*)p.residual + idx);
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) { v[2 * j] += __uint_as_float(w[j] << 16); v[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u); }
+        } else {
+          const float4 q = *(const float4*)((const float*)p.residual + idx);
+          v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
+        }
+      }
+#pragma unroll
+      for (uint32_t j = 0; j < 8; ++j) {
+        if (p.relu) v[j] = fmaxf(v[j], 0.0f);
+        if (p.round_tf32) v[j] = round_tf32(v[j]);
+      }
+      if (p.c_is_bf16)
+        *(uint4*)((uint16_t*)p.c + idx) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+      else
+        *(float4*)((float*)p.c + idx) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+      for (uint32_t j = 0; j < per && row0 + j < p.m; ++j) {
+        float x = v[j];
+        if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx + j);
+        if (p.bias) x += p.bias[p.bias_per_row ? row0 + j : col];
+        if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx + j);
+        if (p.relu) x = fmaxf(x, 0.0f);
+        if (p.round_tf32) x = round_tf32(x);
+        store_out(p.c, p.c_is_bf16, idx + j, x);
+      }
+    }
+  }
+  __syncwarp();
+}
+
 // Drains one accumulator of `ncols` columns: TMEM reads are double-buffered in registers (the next 32 columns
 // are in flight while the current ones are processed) and the bias slice is fetched one chunk ahead.
 // `wide` selects the column order of a two-half tile (see the pair kernel).
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, uint32_t ncols, uint32_t batch, uint32_t split,
-                                              uint32_t row, uint32_t col_base, bool wide, uint32_t lane) {
+                                              uint32_t row, uint32_t col_base, bool wide, uint32_t lane, float* stage_buf,
+                                              uint32_t first, uint32_t step) {
+  const bool staged = p.staged_transpose && p.splits == 1;
   auto tile_col = [&](uint32_t c) { return wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c; };
   auto bias_at = [&](uint32_t c) {
     const uint32_t col = col_base + tile_col(c) + lane;
-    return (p.bias != nullptr && c < ncols && col < p.n) ? p.bias[col] : 0.0f;
+    return (p.bias != nullptr && !p.bias_per_row && c < ncols && col < p.n) ? p.bias[col] : 0.0f;
   };
+  // This warp drains the 32-column chunks first, first + step, ...; two chunks are in flight (A and B registers).
+  if (first >= ncols) return;
   uint32_t acc_a[32], acc_b[32];
-  float bias_next = bias_at(0);
-  tmem_ld_32x32(taddr, acc_a);
-  for (uint32_t c = 0; c < ncols; c += 64) {
-    const bool has_b = c + 32 < ncols;
+  float bias_next = bias_at(first);
+  tmem_ld_32x32(taddr + first, acc_a);
+  for (uint32_t c = first; c < ncols; c += 2 * step) {
+    const bool has_b = c + step < ncols;
     tmem_ld_wait();
-    if (has_b) tmem_ld_32x32(taddr + c + 32, acc_b);
+    if (has_b) tmem_ld_32x32(taddr + c + step, acc_b);
     float bias_cur = bias_next;
-    bias_next = bias_at(c + 32);
-    epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur);
+    bias_next = bias_at(c + step);
+    if (staged) epilogue_chunk_transposed(p, acc_a, stage_buf, batch, row - lane, col_base + tile_col(c), lane);
+    else epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur);
     if (has_b) {
       tmem_ld_wait();
-      if (c + 64 < ncols) tmem_ld_32x32(taddr + c + 64, acc_a);
+      if (c + 2 * step < ncols) tmem_ld_32x32(taddr + c + 2 * step, acc_a);
       bias_cur = bias_next;
-      bias_next = bias_at(c + 64);
-      epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + 32), bias_cur);
+      bias_next = bias_at(c + 2 * step);
+      if (staged) epilogue_chunk_transposed(p, acc_b, stage_buf, batch, row - lane, col_base + tile_col(c + step), lane);
+      else epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur);
     }
   }
 }
@@ -560,10 +660,11 @@ __device__ __forceinline__ void mma_stage(const MmaSetup& s, uint32_t tmem_d, ui
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(448, 1)
 gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b) {
   extern __shared__ uint8_t smem_raw[];
+  if (threadIdx.x == 0) stamp(p.debug_variant, 0);
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   SmemHeader* hdr = (SmemHeader*)smem;
   uint8_t* tiles = smem + kHeaderBytes;
@@ -572,7 +673,8 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   volatile uint32_t* abort_flag = &hdr->abort_flag;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool has_gather = blockDim.x > 192;
+  const uint32_t epi_threads = 128 * p.epi_groups;
+  const bool has_gather = blockDim.x > 64 + epi_threads;
   const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
   const uint32_t tmem_cols = p.bn * 2 <= 32 ? 32u : (p.bn * 2 <= 64 ? 64u : (p.bn * 2 <= 128 ? 128u : (p.bn * 2 <= 256 ? 256u : 512u)));
 
@@ -584,7 +686,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     }
     for (uint32_t b = 0; b < 2; ++b) {
       mbar_init(&hdr->acc_full[b], 1);
-      mbar_init(&hdr->acc_empty[b], 4);
+      mbar_init(&hdr->acc_empty[b], 4 * p.epi_groups);
     }
     hdr->abort_flag = 0;
     fence_barrier_init();
@@ -600,6 +702,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   tc_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
   const uint32_t epl = p.tf32 ? 32u : 64u;
+  if (threadIdx.x == 0) stamp(p.debug_variant, 1);
 
   if (warp == 0) {
     // ===== TMA producer: one lane per box =====
@@ -614,6 +717,11 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         box_init(p, box, lane, &tmap_a, &tmap_b, work, work.m_tile * kBM, work.n_tile * p.bn, p.bn);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_fast(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
+          if (p.debug_variant == 8) {   // experiment: no copies
+            if (lane == 0) mbar_arrive(&hdr->full[stage]);
+            if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (lane == 0) mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
           if (box.active) {
             box_issue<false>(box, tiles + stage * stage_bytes, &hdr->full[stage], 0);
@@ -634,10 +742,38 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         if (!(ok = mbar_wait_fast(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * p.bn;
+        if (p.debug_variant == 14) {
+          // experiment: issue the MMAs of two K blocks before committing either stage
+          uint32_t kb = work.kb_begin;
+          while (kb < work.kb_end) {
+            const uint32_t pairn = min(2u, work.kb_end - kb);
+            uint32_t st[2], ph[2];
+            for (uint32_t u = 0; u < pairn; ++u) {
+              st[u] = stage; ph[u] = phase;
+              if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            }
+            for (uint32_t u = 0; u < pairn && ok; ++u) ok = mbar_wait_fast(&hdr->full[st[u]], ph[u], abort_flag, kStatusMmaTimeout);
+            if (!ok) break;
+            tc_fence_after_sync();
+            for (uint32_t u = 0; u < pairn; ++u) mma_stage<false, false>(ms, tmem_d, st[u], (kb + u) > work.kb_begin);
+            for (uint32_t u = 0; u < pairn; ++u) mma_commit(&hdr->empty[st[u]]);
+            kb += pairn;
+          }
+          if (!ok) break;
+          mma_commit(&hdr->acc_full[buf]);
+          if ((buf ^= 1) == 0) buf_phase ^= 1;
+          continue;
+        }
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_fast(&hdr->full[stage], phase, abort_flag, kStatusMmaTimeout))) break;
           tc_fence_after_sync();
-          if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, kb > work.kb_begin);
+          if (w == blockIdx.x && kb == work.kb_begin) stamp(p.debug_variant, 2);
+          if (w == blockIdx.x + gridDim.x && kb - work.kb_begin < 8) stamp(p.debug_variant, 8 + kb - work.kb_begin);
+          if (p.debug_variant == 4) mma_issue<false, false>(tmem_d, ms.a_desc0, ms.b_desc0, ms.idesc, 1u);
+          else if (p.debug_variant == 10) {   // experiment: four independent accumulators instead of one dependent chain
+            for (uint32_t j = 0; j < 4; ++j) mma_issue<false, false>(tmem_base + ((j * 64) & 255), ms.a_desc0 + stage * ms.stage16 + j * ms.a_step16, ms.b_desc0 + stage * ms.stage16 + j * ms.b_step16, ms.idesc, 1u);
+          }
+          else if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, kb > work.kb_begin);
           else mma_stage<false, false>(ms, tmem_d, stage, kb > work.kb_begin);
           mma_commit(&hdr->empty[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
@@ -647,7 +783,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         if ((buf ^= 1) == 0) buf_phase ^= 1;
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + 4 * p.epi_groups) {
     // ===== epilogue =====
     const uint32_t quarter = warp & 3;
     uint32_t buf = 0, buf_phase = 0;
@@ -658,9 +794,13 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (w == blockIdx.x && threadIdx.x == 64) stamp(p.debug_variant, 3);
       const uint32_t row = work.m_tile * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
-      epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane);
+      if (p.debug_variant != 3) epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane,
+                                               (float*)(tiles + p.stages * stage_bytes) + (warp - 2) * (kStageBytesPerWarp / 4),
+                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
+      if (w == blockIdx.x && threadIdx.x == 64) stamp(p.debug_variant, 7);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->acc_empty[buf]);
@@ -668,7 +808,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     }
   } else {
     // ===== gather warps =====
-    const uint32_t tid = threadIdx.x - 192;
+    const uint32_t tid = threadIdx.x - 64 - epi_threads;
     uint32_t stage = 0, phase = 0;
     bool ok = true;
     for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
@@ -690,6 +830,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 
   // ===== teardown =====
   __syncwarp();
+  if (threadIdx.x == 64) stamp(p.debug_variant, 4);
   if (*abort_flag != 0) {
     // A wait gave up: let copies and MMAs already in flight land before shared and tensor memory go away.
     for (int i = 0; i < 64; ++i) __nanosleep(10000);
@@ -698,7 +839,9 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   if (threadIdx.x == 0 && hdr->abort_flag != 0 && p.status != nullptr) atomicCAS(p.status, 0u, hdr->abort_flag);
+  if (threadIdx.x == 0) stamp(p.debug_variant, 5);
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+  if (threadIdx.x == 32) stamp(p.debug_variant, 6);
 }
 
 // ---- the CTA-pair kernel ------------------------------------------------------------------------------
@@ -710,7 +853,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 // Both CTAs run their own TMA producer (own tiles only, bytes counted on the leader's "full" barrier)
 // and their own epilogue (own 128 accumulator rows); only the leader issues MMAs and commits, once per
 // CTA, to the "empty" and "accumulator full" barriers of both.
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b) {
   extern __shared__ uint8_t smem_raw[];
@@ -741,7 +884,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     }
     for (uint32_t b = 0; b < 2; ++b) {
       mbar_init(&hdr->acc_full[b], 1);  // one commit from the leader
-      mbar_init(&hdr->acc_empty[b], 8); // four epilogue warps in each CTA (used on the leader only)
+      mbar_init(&hdr->acc_empty[b], 8 * p.epi_groups); // every epilogue warp of both CTAs (used on the leader only)
     }
     hdr->abort_flag = 0;
     fence_barrier_init();
@@ -832,7 +975,9 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       tc_fence_after_sync();
       const uint32_t row = work.m_tile * 2 * kBM + rank * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * (p.bn / halves);
-      if (p.debug_variant != 3) epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane);
+      if (p.debug_variant != 3) epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane,
+                                               (float*)(tiles + p.stages * stage_bytes) + (warp - 2) * (kStageBytesPerWarp / 4),
+                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->acc_empty[buf]), 0));
@@ -866,7 +1011,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
     for (uint32_t s = 0; s < p.splits; ++s) x += p.partial[(uint64_t)s * total + t];
     const uint64_t idx = (uint64_t)batch * p.stride_c + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
     if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx);
-    if (p.bias) x += p.bias[col];
+    if (p.bias) x += p.bias[p.bias_per_row ? row : col];
     if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
     if (p.relu) x = fmaxf(x, 0.0f);
     if (p.round_tf32) x = round_tf32(x);
@@ -878,7 +1023,8 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
 
 size_t gemm_smem_bytes(const GemmParams& p) {
   const size_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
-  return 1024 /* alignment slack */ + kHeaderBytes + (size_t)p.stages * (kATileBytes + b_lines * kLineBytes);
+  return 1024 /* alignment slack */ + kHeaderBytes + (size_t)p.stages * (kATileBytes + b_lines * kLineBytes) +
+         (p.staged_transpose ? kStageBytes : 0);
 }
 
 // Co-resident 2-CTA clusters of the pair kernel for a given dynamic shared-memory size (cached per size).
@@ -892,7 +1038,7 @@ static uint32_t max_resident_pairs(size_t smem_bytes, int sm_count) {
     if (cached_device[i] == device && cached_smem[i] == smem_bytes) return (uint32_t)cached_pairs[i];
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)sm_count / 2 * 2, 1, 1);
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(320, 1, 1);
   cfg.dynamicSmemBytes = smem_bytes;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -915,6 +1061,10 @@ static uint32_t max_resident_pairs(size_t smem_bytes, int sm_count) {
   return (uint32_t)clusters;
 }
 
+cudaError_t read_stage_times(unsigned long long* out16) {
+  return cudaMemcpyFromSymbol(out16, g_stage_times, sizeof(unsigned long long) * 16);
+}
+
 cudaError_t gemm_sm100_configure() {
   cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e != cudaSuccess) return e;
@@ -931,12 +1081,12 @@ cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, co
     // left waiting would run its whole share of tiles after the others have finished.
     uint32_t pairs = std::min<uint32_t>(total_work, max_resident_pairs(gemm_smem_bytes(p), sm_count));
     if (p.debug_variant >= 60) pairs = std::min<uint32_t>(pairs, p.debug_variant - 60);   // experiment: fewer SM pairs
-    gemm_sm100_pair_kernel<<<2 * pairs, 192, gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b);
+    gemm_sm100_pair_kernel<<<2 * pairs, 64 + 128 * p.epi_groups, gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b);
     return cudaGetLastError();
   }
   const bool gather = p.a_kind == kGather || p.b_kind == kGather;
   const uint32_t grid = total_work < (uint32_t)sm_count ? total_work : (uint32_t)sm_count;
-  gemm_sm100_kernel<<<grid, gather ? 320 : 192, gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b);
+  gemm_sm100_kernel<<<grid, 64 + 128 * p.epi_groups + (gather ? 128 : 0), gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b);
   return cudaGetLastError();
 }
 

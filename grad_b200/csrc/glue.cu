@@ -68,6 +68,15 @@ __global__ void reorder_oihw_kernel(const float* w, void* wt, int dst_bf16, uint
   }
 }
 
+// wt is (m, kh*kw*c): wt[oc*(khkw*c) + tap*c + ic] = w[(oc*c + ic)*khkw + tap].
+__global__ void reorder_oihw_rows_kernel(const float* w, void* wt, int dst_bf16, uint32_t m, uint32_t c, uint32_t khkw) {
+  const size_t total = (size_t)m * c * khkw;
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t ic = (uint32_t)(t % c), tap = (uint32_t)(t / c % khkw), oc = (uint32_t)(t / c / khkw);
+    store_elem(wt, dst_bf16, t, w[((size_t)oc * c + ic) * khkw + tap]);
+  }
+}
+
 // (n, c, h, w) <-> (n, h, w, c) for graphs that arrive in NCHW (src/onnx/gpu.zig:525-542).
 __global__ void permute_kernel(const void* src, void* dst, int bf16, int to_nhwc, uint32_t n, uint32_t c, uint32_t h, uint32_t w) {
   const size_t total = (size_t)n * c * h * w;
@@ -125,6 +134,14 @@ int gb_reorder_oihw(void* stream, int dst_dtype, const float* w, void* wt, uint3
   const size_t total = (size_t)m * c * kh * kw;
   if (total == 0) return GB_OK;
   reorder_oihw_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(w, wt, dst_dtype == GB_BF16, m, c, kh * kw);
+  return finish();
+}
+
+int gb_reorder_oihw_rows(void* stream, int dst_dtype, const float* w, void* wt, uint32_t m, uint32_t c, uint32_t kh, uint32_t kw) {
+  if (!w || !wt) return GB_ERR_INVALID;
+  const size_t total = (size_t)m * c * kh * kw;
+  if (total == 0) return GB_OK;
+  reorder_oihw_rows_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(w, wt, dst_dtype == GB_BF16, m, c, kh * kw);
   return finish();
 }
 

@@ -17,7 +17,9 @@
 
 namespace gb {
 cudaError_t launch_gemm_f32(const GemmParams& p, cudaStream_t stream);
+cudaError_t read_stage_times(unsigned long long* out16);
 }
+extern "C" int gb_debug_stage_times(unsigned long long* out16) { return gb::read_stage_times(out16) == cudaSuccess ? 0 : 2; }
 
 struct gb_handle {
   int device = 0;
@@ -58,7 +60,7 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 // Encodes a tiled map with 128-byte swizzle.  dims/strides/box follow the driver's convention: dims[0] is
 // the contiguous one, strides (bytes) start at dims[1].
 bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                const uint32_t* box, bool swizzle_32b_chunks = false) {
+                const uint32_t* box, bool swizzle_32b_chunks = false, const uint32_t* elem_strides = nullptr) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t gdims[5];
@@ -67,7 +69,7 @@ bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, co
   for (uint32_t i = 0; i < rank; ++i) {
     gdims[i] = dims[i];
     gbox[i] = box[i];
-    estr[i] = 1;
+    estr[i] = elem_strides ? elem_strides[i] : 1;
     if (i + 1 < rank) gstrides[i] = strides_bytes[i];
   }
   const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<void*>(base),
@@ -124,27 +126,41 @@ uint32_t pick_stages(uint32_t bn) {
   return std::min<uint32_t>(8, (227 * 1024 - 2048) / stage);
 }
 
-// Tile width and K split for an m x n x k_blocks product on `sms` multiprocessors: the widest tile that
-// still gives every SM a tile; when no width does, a 128-wide (or narrower, for a narrow n) tile with K
-// split so that about one work item per SM exists, each at least four K blocks long (the role of
-// `splits` in src/gpu/gpu.zig:664, 1000, 1041).
+// Estimated cycles of a product cut into 128- (single CTA) or 256-row (CTA pair) tiles of width bn.  Per K
+// block an SM needs max(MMA time, shared-memory fill time): 128 x bn x 64 MACs at 4096 MACs/clk, and
+// 16 KB of A plus its lines of B at the ~48 B/clk TMA sustains per SM.  A tile also pays a fixed cost
+// (barrier round trips, epilogue tail; the 512-wide tile's whole epilogue, which nothing overlaps), and
+// tiles are dealt to `units` persistent CTAs (or CTA pairs) in waves.
+double tile_cost(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint32_t bn, bool pair, uint32_t sms) {
+  const uint32_t rows = pair ? 256 : 128, units = pair ? sms / 2 : sms;
+  const uint64_t tiles = (uint64_t)ceil_div(m, rows) * ceil_div(n, bn) * batch;
+  if (tiles == 0 || units == 0) return 0.0;
+  const double b_lines = pair ? bn / 2.0 : bn;
+  // One tcgen05.mma never takes less than about 215 cycles here whatever its N (measured 115-125 ns per
+  // instruction for N = 32..128), so narrow tiles are issue-bound, not math-bound.
+  const double fill = (16384.0 + b_lines * 128.0) / 48.0, mma = 4.0 * std::max(bn / 2.0, 215.0);
+  const double per_tile = k_blocks * std::max(fill, mma) + (bn > 256 ? 6000.0 : 1200.0);
+  const double waves = (double)((tiles + units - 1) / units);
+  return waves * per_tile + 3000.0;
+}
+
+// Tile width and K split for an m x n x k_blocks product on `sms` multiprocessors: the width with the
+// lowest estimated time; when it leaves SMs idle, K is split so that about one work item per SM exists,
+// each at least four K blocks long (the role of `splits` in src/gpu/gpu.zig:664, 1000, 1041).
 void pick_tiling(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint32_t min_bn, uint32_t sms, bool allow_split,
                  uint32_t& bn, uint32_t& splits, uint32_t& kbps) {
-  const uint32_t tiles_m = ceil_div(m, 128) * batch;
   const uint32_t n_cap = std::max(min_bn, ceil_div(n, min_bn) * min_bn);   // n rounded up to the narrowest tile
   bn = 0;
+  double best = 0.0;
   for (uint32_t cand : {256u, 128u, 64u, 32u}) {
     if (cand < min_bn || cand > n_cap) continue;
-    if (tiles_m * ceil_div(n, cand) >= sms) { bn = cand; break; }
+    const double cost = tile_cost(m, n, batch, k_blocks, cand, false, sms);
+    if (bn == 0 || cost < best) { bn = cand; best = cost; }
   }
-  if (bn == 0) {
-    bn = std::min(n_cap, 128u);
-    while (bn > min_bn && (bn & (bn - 1)) != 0) bn &= bn - 1;   // round down to a power of two
-    bn = std::max(bn, min_bn);
-  }
-  const uint32_t tiles = tiles_m * ceil_div(n, bn);
+  if (bn == 0) bn = min_bn;
+  const uint32_t tiles = ceil_div(m, 128) * batch * ceil_div(n, bn);
   splits = 1;
-  if (allow_split && tiles > 0 && tiles < sms && k_blocks >= 8) splits = std::max(1u, std::min(ceil_div(sms, tiles), k_blocks / 4));
+  if (allow_split && tiles > 0 && tiles * 2 <= sms && k_blocks >= 8) splits = std::max(1u, std::min(sms / tiles, k_blocks / 4));
   kbps = std::max(1u, ceil_div(k_blocks, splits));
   splits = std::max(1u, ceil_div(k_blocks, kbps));
 }
@@ -156,6 +172,7 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
   p.relu = ep && ep->activation == GB_ACT_RELU;
   p.round_tf32 = ep && (ep->flags & GB_EPILOGUE_ROUND_TF32) && !p.c_is_bf16;
   p.status = h->status;
+  p.epi_groups = 2;
   if (const char* v = getenv("GB_VARIANT")) p.debug_variant = (uint32_t)atoi(v);
   p.group_m = 8;
   if (const char* v = getenv("GB_GROUP_M")) p.group_m = (uint32_t)std::max(1, atoi(v));
@@ -188,33 +205,34 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
 }
 
 // Switches a planned tensor-path product to the CTA-pair kernel (256 x bn tiles over two SMs) when both
-// operands arrive by TMA and there are enough 256-row tiles to occupy every SM pair without splitting K.
-// `encode_b(rows)` re-encodes B's map for the `rows` lines one CTA of the pair loads; false keeps the
-// single-CTA plan.
+// operands arrive by TMA, K is not split, and a pair tile has a lower estimated time than the single-CTA
+// plan.  `encode_b(rows)` re-encodes B's map for the `rows` lines one CTA of the pair loads; false keeps
+// the single-CTA plan.
 template <class EncodeB>
 bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b) {
   GemmParams& p = plan.p;
-  if (!plan.tensor || p.a_kind == gb::kGather || p.b_kind == gb::kGather || p.m <= 128) return false;
-  if (p.debug_variant == 2) return false;
-  const uint32_t pairs = (uint32_t)h->sm_count / 2;
-  const uint32_t tiles_m = ceil_div(p.m, 256) * p.batch;
+  if (!plan.tensor || p.a_kind == gb::kGather || p.b_kind == gb::kGather || p.m <= 128 || p.splits > 1) return false;
+  if (p.debug_variant == 2 || getenv("GB_NO_PAIR")) return false;
+  const uint32_t sms = (uint32_t)h->sm_count;
   const uint32_t n_cap = std::max(min_bn, ceil_div(p.n, min_bn) * min_bn);
+  double best = tile_cost(p.m, p.n, p.batch, p.k_blocks_total, p.bn, false, sms);
+  uint32_t pick = 0;
   for (uint32_t cand : {512u, 256u, 128u, 64u}) {
-    if (cand / 2 < min_bn || cand > std::max(n_cap, 2 * min_bn)) continue;
-    if (cand == 512 && (p.debug_variant == 9 || p.k_blocks_total < 32)) continue;   // the wide tile exposes its epilogue: long K only
-    if (tiles_m * ceil_div(p.n, cand) < pairs) continue;
-    if (!encode_b(cand / 2)) return false;
-    p.cta_pair = 1;
-    p.bn = cand;
-    p.tiles_m = ceil_div(p.m, 256);
-    p.tiles_n = ceil_div(p.n, cand);
-    p.splits = 1;
-    p.k_blocks_per_split = p.k_blocks_total;
-    p.stages = std::min<uint32_t>(8, (227 * 1024 - 2048) / (128 * 128 + cand / 2 * 128));
-    plan.workspace = 0;
-    return true;
+    if (cand / 2 < min_bn || cand > n_cap) continue;
+    if (cand == 512 && p.debug_variant == 9) continue;
+    const double cost = tile_cost(p.m, p.n, p.batch, p.k_blocks_total, cand, true, sms);
+    if (cost <= best) { best = cost; pick = cand; }   // a tie goes to the pair: half as many MMA instructions per row
   }
-  return false;
+  if (pick == 0 || !encode_b(pick / 2)) return false;
+  p.cta_pair = 1;
+  p.bn = pick;
+  p.tiles_m = ceil_div(p.m, 256);
+  p.tiles_n = ceil_div(p.n, pick);
+  p.splits = 1;
+  p.k_blocks_per_split = p.k_blocks_total;
+  p.stages = std::min<uint32_t>(8, (227 * 1024 - 2048) / (128 * 128 + pick / 2 * 128));
+  plan.workspace = 0;
+  return true;
 }
 
 void set_output(GemmParams& p, void* c, uint32_t dtype_c, uint32_t ldc, uint64_t stride_c, bool transpose_out, bool accumulate,
@@ -339,7 +357,7 @@ int validate_conv(const gb_conv_desc* d) {
   if (g.out_h != oh || g.out_w != ow) return GB_ERR_INVALID;
   if ((uint64_t)g.positions != (uint64_t)g.n * oh * ow) return GB_ERR_INVALID;
   if (g.c_step != 0 && g.c_step < g.c) return GB_ERR_INVALID;
-  if (d->dtype_x > GB_BF16 || d->dtype_w > GB_BF16 || d->dtype_y > GB_BF16 || d->math > GB_MATH_BF16) return GB_ERR_INVALID;
+  if (d->dtype_x > GB_BF16 || d->dtype_w > GB_BF16 || d->dtype_y > GB_BF16 || d->math > GB_MATH_BF16 || d->w_layout > 1) return GB_ERR_INVALID;
   return GB_OK;
 }
 
@@ -369,14 +387,81 @@ bool patch_box(uint32_t count, uint32_t grid_h, uint32_t grid_w, uint32_t& bw, u
 
 // 4-D map over an NHWC tensor {channels, width, height, images} with a box of `epl` channels x (bw, bh, bn).
 bool nhwc_tma(CUtensorMap* map, const void* base, bool smem_bf16, uint32_t dtype, uint32_t channels, uint32_t c_step, uint32_t width,
-              uint32_t height, uint32_t images, uint32_t epl, uint32_t bw, uint32_t bh, uint32_t bn, bool mn_major = false) {
+              uint32_t height, uint32_t images, uint32_t epl, uint32_t bw, uint32_t bh, uint32_t bn, bool mn_major = false,
+              uint32_t conv_stride = 1) {
   const uint32_t es = smem_bf16 ? 2 : 4;
   if ((dtype == GB_BF16) != smem_bf16) return false;
   if (channels % epl != 0 || !aligned16(base) || ((uint64_t)c_step * es) % 16 != 0) return false;
   const uint64_t dims[4] = {channels, width, height, images};
   const uint64_t strides[3] = {(uint64_t)c_step * es, (uint64_t)c_step * es * width, (uint64_t)c_step * es * width * height};
-  const uint32_t box[4] = {epl, bw, bh, bn};
-  return encode_map(map, smem_bf16, base, 4, dims, strides, box, !smem_bf16 && mn_major);
+  // A strided convolution visits every conv_stride-th column and row: the box spans bw*stride x bh*stride
+  // input pixels and TMA's traversal stride keeps one in conv_stride of them, landing compact in shared memory.
+  const uint32_t box[4] = {epl, bw * conv_stride, bh * conv_stride, bn};
+  const uint32_t estr[4] = {1, conv_stride, conv_stride, 1};
+  if (box[1] > 256 || box[2] > 256) return false;
+  return encode_map(map, smem_bf16, base, 4, dims, strides, box, !smem_bf16 && mn_major, estr);
+}
+
+// Forward convolution computed transposed: y^T[c_out, positions] = w^T[c_out, K] * patches^T[K, positions].
+// The output channels become the M rows of the tile and 128-256 positions its N columns, so a layer with
+// 64 or 128 channels still issues 256-wide MMAs (an MMA costs the same ~215 cycles whether N is 64 or 256)
+// instead of four times as many narrow ones.  A is the filter matrix read MN-major (c_out contiguous), B the
+// NHWC patch boxes with one line per position; the epilogue stores transposed, which is NHWC again.
+// Returns false when the geometry cannot be fetched by TMA this way (the caller keeps the direct plan).
+bool plan_fprop_swapped(const gb_handle* h, const gb_conv_desc* d, const gb::ConvGeo& g, const void* x, const void* w, void* y,
+                        const gb_epilogue* ep, bool smem_bf16, uint32_t epl, double direct_cost, Plan& plan) {
+  GemmParams& p = plan.p;
+  if (!getenv("GB_SWAP") || g.stride != 1 || (d->dtype_x == GB_BF16) != smem_bf16 || g.c % epl != 0) return false;
+  const uint32_t taps = g.k * g.k, positions = d->geo.positions, k_blocks = taps * g.c / epl, sms = (uint32_t)h->sm_count;
+  // candidates: (pair, positions per tile)
+  struct Cand { bool pair; uint32_t bn; };
+  const Cand cands[] = {{true, 256}, {false, 256}, {false, 128}, {true, 128}};
+  double best = direct_cost;
+  int pick = -1;
+  uint32_t bw = 0, bh = 0, bnn = 0;
+  for (int i = 0; i < 4; ++i) {
+    const Cand& c = cands[i];
+    if (c.pair && g.c_out <= 128) continue;
+    uint32_t tw, th, tn;
+    if (!patch_box(c.pair ? c.bn / 2 : c.bn, g.out_h, g.out_w, tw, th, tn)) continue;
+    const double cost = tile_cost(g.c_out, positions, 1, k_blocks, c.bn, c.pair, sms);
+    if (cost < best) { best = cost; pick = i; bw = tw; bh = th; bnn = tn; }
+  }
+  if (pick < 0) return false;
+  const Cand c = cands[pick];
+  DenseOperand oa{w, d->dtype_w, taps * g.c, g.c_out, g.c_out, 0, true};
+  CUtensorMap map_a, map_b;
+  const bool a_tma = dense_tma(&map_a, oa, smem_bf16, 1, 128, epl);
+  if (!a_tma && c.pair) return false;
+  if (!nhwc_tma(&map_b, x, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, bw, bh, bnn)) return false;
+  p.m = g.c_out; p.n = positions; p.k = taps * g.c;
+  fill_dense_gather(p.ga, oa);
+  p.gbsrc.base = x; p.gbsrc.source = gb::kSrcPatch; p.gbsrc.src_is_bf16 = d->dtype_x == GB_BF16;
+  p.gbsrc.lines_total = positions; p.gbsrc.inner_total = p.k; p.gbsrc.mn_major = 0; p.gbsrc.batch_stride = 0;
+  p.a_mn_major = 1; p.b_mn_major = 0;
+  set_output(p, y, d->dtype_y, g.c_out, 0, true, d->accumulate, ep);
+  p.bias = ep ? ep->bias : nullptr;
+  p.residual = ep ? ep->residual : nullptr;
+  p.bias_per_row = 1;
+  p.k_blocks_total = k_blocks;
+  p.k_blocks_per_split = k_blocks;
+  p.splits = 1;
+  p.bn = c.bn;
+  p.cta_pair = c.pair;
+  p.tiles_m = ceil_div(g.c_out, c.pair ? 256 : 128);
+  p.tiles_n = ceil_div(positions, c.bn);
+  p.box_w = bw; p.box_h = bh; p.box_n = bnn;
+  // 16-byte transposed stores need a 16-byte-aligned run of channels per position; 20 KB of shared memory stage them
+  p.staged_transpose = aligned16(y) && ((uint64_t)g.c_out * elem_size(d->dtype_y)) % 16 == 0 &&
+                       (!p.residual || aligned16(p.residual));
+  p.stages = std::min<uint32_t>(8, (227 * 1024 - 2048 - (p.staged_transpose ? 36864 : 0)) / (128 * 128 + (c.pair ? c.bn / 2 : c.bn) * 128));
+  p.a_kind = a_tma ? gb::kDenseMN : gb::kGather;
+  p.b_kind = gb::kPatchK;
+  p.group_m = 1;   // few M tiles (channels): walk the positions, keeping the filters in L2
+  plan.tmap_a = map_a;
+  plan.tmap_b = map_b;
+  plan.workspace = 0;
+  return true;
 }
 
 int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* act, const void* other, void* out,
@@ -402,22 +487,31 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     p.m = positions; p.n = g.c_out; p.k = taps * g.c;
     p.ga.base = act; p.ga.source = gb::kSrcPatch; p.ga.src_is_bf16 = d->dtype_x == GB_BF16;
     p.ga.lines_total = positions; p.ga.inner_total = p.k; p.ga.mn_major = 0;
-    DenseOperand ob{other, d->dtype_w, p.k, g.c_out, g.c_out, 0, true};
+    // Filters as grad stores them, (K, c_out), are an MN-major B; the prepared (c_out, K) copy is a K-major B.
+    const bool w_rows = d->w_layout == 1;
+    DenseOperand ob = w_rows ? DenseOperand{other, d->dtype_w, g.c_out, p.k, p.k, 0, false} : DenseOperand{other, d->dtype_w, p.k, g.c_out, g.c_out, 0, true};
     fill_dense_gather(p.gbsrc, ob);
-    p.a_mn_major = 0; p.b_mn_major = 1;
-    min_bn = plan.tensor ? epl : 32;
+    p.a_mn_major = 0; p.b_mn_major = w_rows ? 0 : 1;
+    min_bn = (plan.tensor && !w_rows) ? epl : 32;
     set_output(p, out, d->dtype_y, g.c_out, 0, false, d->accumulate, ep);
     int rc = finish_plan(h, plan, true, min_bn, ep);
     if (rc != GB_OK) return rc;
     if (plan.tensor) {
       p.a_kind = gb::kGather;
-      if (g.stride == 1 && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
-          nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n))
+      if ((g.stride == 1 || !getenv("GB_NO_STRIDED_TMA")) && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+          nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, false, g.stride))
         p.a_kind = gb::kPatchK;
-      p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
+      p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? (w_rows ? gb::kDenseK : gb::kDenseMN) : gb::kGather;
       CUtensorMap single = plan.tmap_b;
       if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }))
         plan.tmap_b = single;
+      const double direct = p.a_kind == gb::kGather || p.b_kind == gb::kGather || p.splits > 1
+                                ? 1e30
+                                : tile_cost(p.m, p.n, 1, p.k_blocks_total, p.bn, p.cta_pair != 0, (uint32_t)h->sm_count);
+      if (p.a_kind != gb::kGather && p.splits == 1 && !w_rows) {
+        Plan swapped = plan;
+        if (plan_fprop_swapped(h, d, g, act, other, out, ep, smem_bf16, epl, direct, swapped)) plan = swapped;
+      }
     }
   } else if (pass == 1) {
     // dx[pixels, c] = patchesT(dy)[pixels, taps*c_out] * wT[taps*c_out, c]
@@ -465,8 +559,8 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     if (rc != GB_OK) return rc;
     if (plan.tensor) {
       p.a_kind = gb::kGather;
-      if (g.stride == 1 && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
-          nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, true))
+      if ((g.stride == 1 || !getenv("GB_NO_STRIDED_TMA")) && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+          nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, true, g.stride))
         p.a_kind = gb::kPatchMN;
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
     }
@@ -596,6 +690,7 @@ int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   if (!h || !dy || !w || !dx) return GB_ERR_INVALID;
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
+  if (desc->w_layout != 0) return GB_ERR_UNSUPPORTED;   // the prepared filter copy is a forward-only format
   Plan plan;
   rc = plan_conv(h, 1, desc, dy, w, dx, nullptr, plan);
   if (rc != GB_OK) return rc;
@@ -607,7 +702,7 @@ int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   if (!h || !dy || !x || !dw) return GB_ERR_INVALID;
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
-  if (desc->dtype_w != GB_F32) return GB_ERR_UNSUPPORTED;   // weight gradients accumulate in f32 (gpu.zig:983)
+  if (desc->dtype_w != GB_F32 || desc->w_layout != 0) return GB_ERR_UNSUPPORTED;   // weight gradients accumulate in f32 (gpu.zig:983)
   Plan plan;
   rc = plan_conv(h, 2, desc, dy, x, dw, nullptr, plan);
   if (rc != GB_OK) return rc;

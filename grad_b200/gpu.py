@@ -200,7 +200,7 @@ class Gpu:
         self.launches += self._count()
 
     # ---- convolution ------------------------------------------------------------------------------
-    def _conv_desc(self, geo: ConvGeometry, x_like, w_like, y_like, math: Optional[int], accumulate: bool) -> abi.ConvDesc:
+    def _conv_desc(self, geo: ConvGeometry, x_like, w_like, y_like, math: Optional[int], accumulate: bool, w_layout: int = 0) -> abi.ConvDesc:
         d = abi.ConvDesc()
         d.geo = geo.c_struct()
         d.dtype_x, d.dtype_w, d.dtype_y = _dtype_code(x_like), _dtype_code(w_like), _dtype_code(y_like)
@@ -210,6 +210,7 @@ class Gpu:
         d.math = math
         d.accumulate = accumulate
         d.deterministic = self.deterministic
+        d.w_layout = w_layout
         return d
 
     def _conv_ws(self, which: int, d: abi.ConvDesc):
@@ -218,10 +219,10 @@ class Gpu:
         return self.scratch(need.value), need.value
 
     def convForward(self, x, w, out, geo: ConvGeometry, accumulate: bool = False, epilogue: Optional[Epilogue] = None,
-                    math: Optional[int] = None):
+                    math: Optional[int] = None, w_rows: bool = False):
         """Forward implicit GEMM: `convImplicitForward` (gpu.zig:926-929) for bf16 data, `convF32Forward` (:789-826)
-        for f32 data; x is NHWC, w is (k*k*c, c_out)."""
-        d = self._conv_desc(geo, x, w, out, math, accumulate)
+        for f32 data; x is NHWC, w is (k*k*c, c_out), or the prepared (c_out, k*k*c) copy when `w_rows`."""
+        d = self._conv_desc(geo, x, w, out, math, accumulate, 1 if w_rows else 0)
         ws, n = self._conv_ws(abi.PASS_FPROP, d)
         rc = self.lib.gb_conv_fprop(self.handle, self._stream(), C.byref(d), _ptr(x), _ptr(w), _ptr(out), self._epilogue(epilogue),
                                     _ptr(ws), n)

@@ -102,9 +102,10 @@ class Executor:
             m, c, kh, kw = w.shape
             if self.mode == "tf32":   # filters are rounded to TF32 once (nearest), not truncated at every use
                 w = (w.view(torch.int32) + 0x1000).bitwise_and(-8192).view(torch.float32)
-            out = torch.empty((kh * kw * c, m), dtype=self.act_dtype, device=self.gpu.device)
-            abi.check(self.gpu.lib.gb_reorder_oihw(self._stream(), self._code(out), C.c_void_p(w.data_ptr()), C.c_void_p(out.data_ptr()),
-                                                   m, c, kh, kw), "gb_reorder_oihw")
+            # filters are kept as (c_out, kh*kw*c): K contiguous per output channel (gb_conv_desc.w_layout = 1)
+            out = torch.empty((m, kh * kw * c), dtype=self.act_dtype, device=self.gpu.device)
+            abi.check(self.gpu.lib.gb_reorder_oihw_rows(self._stream(), self._code(out), C.c_void_p(w.data_ptr()), C.c_void_p(out.data_ptr()),
+                                                        m, c, kh, kw), "gb_reorder_oihw_rows")
             self.derived[key] = out
             self.stats.launches += 1
         return self.derived[key]
@@ -158,9 +159,9 @@ class Executor:
         if int(node.attrs.get("group", 1)) != 1:
             raise NotImplementedError("grouped convolution takes the NCHW host path in the reference (runtime.zig:871)")
         w = self._conv_weights(node.inputs[1])
-        m = w.shape[1]
+        m = w.shape[0]
         n, h, width, c = x.shape
-        k = int(round((w.shape[0] // c) ** 0.5))
+        k = int(round((w.shape[1] // c) ** 0.5))
         stride, pad, dil = _pair(node.attrs, "strides", 1), _pair(node.attrs, "pads", 0), _pair(node.attrs, "dilations", 1)
         geo = conv_geometry(n, h, width, c, k, m, stride, pad, dil)
         bias = self._constant(node.inputs[2]) if len(node.inputs) > 2 else None
@@ -177,7 +178,7 @@ class Executor:
                 relu, result, consumed = True, nxt.outputs[0], consumed + 1
         y = torch.empty((n, geo.out_h, geo.out_w, m), dtype=self.act_dtype, device=self.gpu.device)
         before = self.gpu.launches
-        self.gpu.convForward(x.contiguous(), w, y, geo, epilogue=Epilogue(bias, residual, relu, self.mode == "tf32"), math=self.math)
+        self.gpu.convForward(x.contiguous(), w, y, geo, epilogue=Epilogue(bias, residual, relu, self.mode == "tf32"), math=self.math, w_rows=True)
         self.stats.launches += self.gpu.launches - before
         values[result] = y
         self.stats.device_nodes += 3 + consumed

@@ -98,7 +98,12 @@ typedef struct {
 typedef struct {
   gb_conv_geometry geo;
   uint8_t dtype_x, dtype_w, dtype_y, math;   /* dtype of x (or dx), of w (or dw), of y (or dy); gb_math */
-  uint8_t accumulate, deterministic, reserved[2];
+  uint8_t accumulate, deterministic;
+  uint8_t w_layout;          /* 0: w is (k*k*c, c_out) as grad stores it; 1 (forward only): w is (c_out, k*k*c), a copy
+                              * prepared once per weight -- the role of the executor's `reorderedWeights` cache
+                              * (src/onnx/gpu.zig:566-574).  With K contiguous per output channel two CTAs can
+                              * split even a 64-channel filter bank, so 256 positions share one MMA. */
+  uint8_t reserved;
 } gb_conv_desc;
 
 /* ---- lifetime --------------------------------------------------------------------------------- */
@@ -181,6 +186,8 @@ int gb_cast(void* stream, int src_dtype, int dst_dtype, const void* src, void* d
 /* OIHW f32 filters -> (kh*kw*c, m) in dst_dtype: `reorderedWeights` / `reorderOihw`
  * (src/onnx/gpu.zig:566-574, src/onnx/runtime.zig:845-862); done once per weight and cached by the caller. */
 int gb_reorder_oihw(void* stream, int dst_dtype, const float* w, void* wt, uint32_t m, uint32_t c, uint32_t kh, uint32_t kw);
+/* The same filters as (m, kh*kw*c): layout 1 of gb_conv_desc.w_layout. */
+int gb_reorder_oihw_rows(void* stream, int dst_dtype, const float* w, void* wt, uint32_t m, uint32_t c, uint32_t kh, uint32_t kw);
 /* NCHW <-> NHWC copy for graphs that arrive in NCHW (src/onnx/gpu.zig:525-542). */
 int gb_permute_layout(void* stream, int dtype, int to_nhwc, const void* src, void* dst, uint32_t n, uint32_t c, uint32_t h, uint32_t w);
 

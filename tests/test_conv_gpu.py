@@ -216,3 +216,19 @@ def test_full_size_adjoint_identity(gpu, case):
     c_ = (gw.double() * w.double()).sum().item()
     scale = (y.double().norm() * dy.double().norm()).item()
     assert abs(a - b) <= 1e-4 * scale and abs(a - c_) <= 1e-4 * scale, (a, b, c_, scale)
+
+
+@pytest.mark.parametrize("case", [RESNET[1], RESNET[2], RESNET[0], RESNET[7], SMALL[7]])
+@pytest.mark.parametrize("math,tol,half", [(0, TOL_F32, False), (1, TOL_TF32, False), (2, TOL_BF16, True)])
+def test_forward_with_prepared_filter_rows(gpu, case, math, tol, half):
+    """gb_conv_desc.w_layout = 1: the filters as (c_out, k*k*c), the copy the executor prepares once per weight."""
+    import torch
+    from oracle import binding as orc
+
+    d, x, w, _ = _inputs(case, 500)
+    geo = _geo(case)
+    want = orc.conv_forward(x, w, d, orc.host_threads())
+    y = torch.empty((d.n, d.out_h, d.out_w, d.c_out), dtype=torch.bfloat16 if half else torch.float32, device="cuda")
+    gpu.convForward(to_dev(x, half), to_dev(np.ascontiguousarray(w.T), half), y, geo, math=math, w_rows=True)
+    torch.cuda.synchronize()
+    assert rel_fro(to_host(y), want) <= tol
