@@ -1,15 +1,17 @@
 // The tcgen05 contraction kernel: one persistent, warp-specialised CTA per SM computes 128 x BN output
 // tiles of C = A * B with f32 accumulators in tensor memory.
 //
-//   warp 0      TMA producer: one elected thread streams 128-byte-swizzled operand tiles into a ring of
-//               shared-memory stages and signals each stage's "full" mbarrier with the byte count.
+//   warp 0      TMA producer: every box of a stage has its own lane, which keeps the box's coordinates in
+//               registers and steps them from K block to K block; the stage's "full" mbarrier counts the bytes.
 //   warp 1      MMA issuer: owns the TMEM allocation; one thread issues four tcgen05.mma per stage
-//               (K = 16 bf16 or 8 tf32 each) and commits the stage's "empty" barrier; after the last
-//               K block of a tile it commits the accumulator's "full" barrier.
-//   warps 2-5   epilogue: each warp owns one 32-lane quarter of TMEM, reads the accumulator with
-//               tcgen05.ld, applies (+C) (+bias) (+residual) (ReLU), rounds to the output type and
-//               stores.  Two accumulator buffers let the epilogue of tile i overlap the mainloop of i+1.
-//   warps 6-9   (only when an operand cannot be fetched by TMA) gather warps fill the stage with plain
+//               (K = 16 bf16 or 8 tf32 each) from descriptors built once per kernel, and commits the
+//               stage's "empty" barrier; after the last K block of a tile it commits the accumulator's
+//               "full" barrier.
+//   warps 2-9   epilogue, two warps per 32-lane quarter of TMEM (they split the column chunks): tcgen05.ld
+//               double-buffered in registers, (+C) (+bias) (+residual) (ReLU), rounding to the output type,
+//               16-byte stores.  Two accumulator buffers let the epilogue of tile i overlap the mainloop of
+//               tile i+1.
+//   warps 10-13 (only when an operand cannot be fetched by TMA) gather warps fill the stage with plain
 //               loads: any pitch, f32 -> bf16 conversion on the fly, implicit im2col of NHWC activations
 //               for any stride / dilation / padding / channel count.
 //
@@ -25,16 +27,6 @@
 #include "sm100_ptx.cuh"
 
 namespace gb {
-
-// Optional stage timestamps of CTA 0 (globaltimer ns), written only when the experiment switch is 7.
-__device__ unsigned long long g_stage_times[16];
-__device__ __forceinline__ void stamp(uint32_t variant, int slot) {
-  if (variant == 7 && blockIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_stage_times[slot] = t;
-  }
-}
 
 namespace {
 
@@ -664,7 +656,6 @@ __global__ void __launch_bounds__(448, 1)
 gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b) {
   extern __shared__ uint8_t smem_raw[];
-  if (threadIdx.x == 0) stamp(p.debug_variant, 0);
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   SmemHeader* hdr = (SmemHeader*)smem;
   uint8_t* tiles = smem + kHeaderBytes;
@@ -702,7 +693,6 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   tc_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
   const uint32_t epl = p.tf32 ? 32u : 64u;
-  if (threadIdx.x == 0) stamp(p.debug_variant, 1);
 
   if (warp == 0) {
     // ===== TMA producer: one lane per box =====
@@ -717,11 +707,6 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         box_init(p, box, lane, &tmap_a, &tmap_b, work, work.m_tile * kBM, work.n_tile * p.bn, p.bn);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_fast(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
-          if (p.debug_variant == 8) {   // experiment: no copies
-            if (lane == 0) mbar_arrive(&hdr->full[stage]);
-            if (++stage == p.stages) { stage = 0; phase ^= 1; }
-            continue;
-          }
           if (lane == 0) mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
           if (box.active) {
             box_issue<false>(box, tiles + stage * stage_bytes, &hdr->full[stage], 0);
@@ -742,38 +727,10 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         if (!(ok = mbar_wait_fast(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * p.bn;
-        if (p.debug_variant == 14) {
-          // experiment: issue the MMAs of two K blocks before committing either stage
-          uint32_t kb = work.kb_begin;
-          while (kb < work.kb_end) {
-            const uint32_t pairn = min(2u, work.kb_end - kb);
-            uint32_t st[2], ph[2];
-            for (uint32_t u = 0; u < pairn; ++u) {
-              st[u] = stage; ph[u] = phase;
-              if (++stage == p.stages) { stage = 0; phase ^= 1; }
-            }
-            for (uint32_t u = 0; u < pairn && ok; ++u) ok = mbar_wait_fast(&hdr->full[st[u]], ph[u], abort_flag, kStatusMmaTimeout);
-            if (!ok) break;
-            tc_fence_after_sync();
-            for (uint32_t u = 0; u < pairn; ++u) mma_stage<false, false>(ms, tmem_d, st[u], (kb + u) > work.kb_begin);
-            for (uint32_t u = 0; u < pairn; ++u) mma_commit(&hdr->empty[st[u]]);
-            kb += pairn;
-          }
-          if (!ok) break;
-          mma_commit(&hdr->acc_full[buf]);
-          if ((buf ^= 1) == 0) buf_phase ^= 1;
-          continue;
-        }
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_fast(&hdr->full[stage], phase, abort_flag, kStatusMmaTimeout))) break;
           tc_fence_after_sync();
-          if (w == blockIdx.x && kb == work.kb_begin) stamp(p.debug_variant, 2);
-          if (w == blockIdx.x + gridDim.x && kb - work.kb_begin < 8) stamp(p.debug_variant, 8 + kb - work.kb_begin);
-          if (p.debug_variant == 4) mma_issue<false, false>(tmem_d, ms.a_desc0, ms.b_desc0, ms.idesc, 1u);
-          else if (p.debug_variant == 10) {   // experiment: four independent accumulators instead of one dependent chain
-            for (uint32_t j = 0; j < 4; ++j) mma_issue<false, false>(tmem_base + ((j * 64) & 255), ms.a_desc0 + stage * ms.stage16 + j * ms.a_step16, ms.b_desc0 + stage * ms.stage16 + j * ms.b_step16, ms.idesc, 1u);
-          }
-          else if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, kb > work.kb_begin);
+          if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, kb > work.kb_begin);
           else mma_stage<false, false>(ms, tmem_d, stage, kb > work.kb_begin);
           mma_commit(&hdr->empty[stage]);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
@@ -794,13 +751,11 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      if (w == blockIdx.x && threadIdx.x == 64) stamp(p.debug_variant, 3);
       const uint32_t row = work.m_tile * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
-      if (p.debug_variant != 3) epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane,
+      epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane,
                                                (float*)(tiles + p.stages * stage_bytes) + (warp - 2) * (kStageBytesPerWarp / 4),
                                                ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
-      if (w == blockIdx.x && threadIdx.x == 64) stamp(p.debug_variant, 7);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->acc_empty[buf]);
@@ -830,7 +785,6 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 
   // ===== teardown =====
   __syncwarp();
-  if (threadIdx.x == 64) stamp(p.debug_variant, 4);
   if (*abort_flag != 0) {
     // A wait gave up: let copies and MMAs already in flight land before shared and tensor memory go away.
     for (int i = 0; i < 64; ++i) __nanosleep(10000);
@@ -839,9 +793,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   if (threadIdx.x == 0 && hdr->abort_flag != 0 && p.status != nullptr) atomicCAS(p.status, 0u, hdr->abort_flag);
-  if (threadIdx.x == 0) stamp(p.debug_variant, 5);
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
-  if (threadIdx.x == 32) stamp(p.debug_variant, 6);
 }
 
 // ---- the CTA-pair kernel ------------------------------------------------------------------------------
@@ -919,11 +871,6 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
         box_init(p, box, lane, &tmap_a, &tmap_b, work, work.m_tile * 2 * kBM + rank * kBM, work.n_tile * p.bn + rank * b_lines, b_lines);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_fast(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
-          if (p.debug_variant == 8) {   // experiment: no copies at all, the tensor core runs on whatever smem holds
-            if (lane == 0 && rank == 0) mbar_arrive(&hdr->full[stage]);
-            if (++stage == p.stages) { stage = 0; phase ^= 1; }
-            continue;
-          }
           if (lane == 0 && rank == 0) mbar_arrive_expect_tx(&hdr->full[stage], 2 * tx_bytes);
           box_issue<true>(box, tiles + stage * stage_bytes, nullptr, map_to_cta(smem_u32(&hdr->full[stage]), 0));
           box_advance(p, box);
@@ -946,8 +893,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_fast(&hdr->full[stage], phase, abort_flag, kStatusMmaTimeout))) break;
           tc_fence_after_sync();
-          if (p.debug_variant == 4 || p.debug_variant >= 60) mma_issue<true, false>(tmem_d, ms.a_desc0, ms.b_desc0, ms.idesc, 1u);
-          else if (p.tf32) mma_stage<true, true>(ms, tmem_d, stage, kb > work.kb_begin);
+          if (p.tf32) mma_stage<true, true>(ms, tmem_d, stage, kb > work.kb_begin);
           else mma_stage<true, false>(ms, tmem_d, stage, kb > work.kb_begin);
           if (halves == 2) {   // second half: 128 B lines (16 KB) further on, 256 TMEM columns further on
             if (p.tf32) mma_stage<true, true>(ms, tmem_d + 256, stage, kb > work.kb_begin, (128 * kLineBytes) >> 4);
@@ -975,7 +921,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       tc_fence_after_sync();
       const uint32_t row = work.m_tile * 2 * kBM + rank * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * (p.bn / halves);
-      if (p.debug_variant != 3) epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane,
+      epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane,
                                                (float*)(tiles + p.stages * stage_bytes) + (warp - 2) * (kStageBytesPerWarp / 4),
                                                ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
       tc_fence_before_sync();
@@ -1061,10 +1007,6 @@ static uint32_t max_resident_pairs(size_t smem_bytes, int sm_count) {
   return (uint32_t)clusters;
 }
 
-cudaError_t read_stage_times(unsigned long long* out16) {
-  return cudaMemcpyFromSymbol(out16, g_stage_times, sizeof(unsigned long long) * 16);
-}
-
 cudaError_t gemm_sm100_configure() {
   cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e != cudaSuccess) return e;
@@ -1079,8 +1021,7 @@ cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, co
     // A persistent grid must not exceed what the device can keep resident at once: the number of
     // co-resident 2-CTA clusters can be below sm_count / 2 (SMs are paired within a GPC), and a cluster
     // left waiting would run its whole share of tiles after the others have finished.
-    uint32_t pairs = std::min<uint32_t>(total_work, max_resident_pairs(gemm_smem_bytes(p), sm_count));
-    if (p.debug_variant >= 60) pairs = std::min<uint32_t>(pairs, p.debug_variant - 60);   // experiment: fewer SM pairs
+    const uint32_t pairs = std::min<uint32_t>(total_work, max_resident_pairs(gemm_smem_bytes(p), sm_count));
     gemm_sm100_pair_kernel<<<2 * pairs, 64 + 128 * p.epi_groups, gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b);
     return cudaGetLastError();
   }

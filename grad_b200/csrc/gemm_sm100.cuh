@@ -70,7 +70,6 @@ struct GemmParams {
   uint32_t bias_per_row;    // bias is indexed by the row (M) index: products computed transposed (M = output channels)
   uint32_t round_tf32;      // round the stored f32 result to TF32 (nearest, ties away)
   uint32_t* status;
-  uint32_t debug_variant;   // experiment switch, 0 in production
 };
 
 size_t gemm_smem_bytes(const GemmParams& p);

@@ -17,9 +17,7 @@
 
 namespace gb {
 cudaError_t launch_gemm_f32(const GemmParams& p, cudaStream_t stream);
-cudaError_t read_stage_times(unsigned long long* out16);
 }
-extern "C" int gb_debug_stage_times(unsigned long long* out16) { return gb::read_stage_times(out16) == cudaSuccess ? 0 : 2; }
 
 struct gb_handle {
   int device = 0;
@@ -173,7 +171,6 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
   p.round_tf32 = ep && (ep->flags & GB_EPILOGUE_ROUND_TF32) && !p.c_is_bf16;
   p.status = h->status;
   p.epi_groups = 2;
-  if (const char* v = getenv("GB_VARIANT")) p.debug_variant = (uint32_t)atoi(v);
   p.group_m = 8;
   if (const char* v = getenv("GB_GROUP_M")) p.group_m = (uint32_t)std::max(1, atoi(v));
   if (plan.tensor) {
@@ -212,14 +209,13 @@ template <class EncodeB>
 bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b) {
   GemmParams& p = plan.p;
   if (!plan.tensor || p.a_kind == gb::kGather || p.b_kind == gb::kGather || p.m <= 128 || p.splits > 1) return false;
-  if (p.debug_variant == 2 || getenv("GB_NO_PAIR")) return false;
+  if (getenv("GB_NO_PAIR")) return false;   // tuning knob: keep the single-CTA plan
   const uint32_t sms = (uint32_t)h->sm_count;
   const uint32_t n_cap = std::max(min_bn, ceil_div(p.n, min_bn) * min_bn);
   double best = tile_cost(p.m, p.n, p.batch, p.k_blocks_total, p.bn, false, sms);
   uint32_t pick = 0;
   for (uint32_t cand : {512u, 256u, 128u, 64u}) {
     if (cand / 2 < min_bn || cand > n_cap) continue;
-    if (cand == 512 && p.debug_variant == 9) continue;
     const double cost = tile_cost(p.m, p.n, p.batch, p.k_blocks_total, cand, true, sms);
     if (cost <= best) { best = cost; pick = cand; }   // a tie goes to the pair: half as many MMA instructions per row
   }
