@@ -702,38 +702,52 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       BoxLane box;
+      uint32_t ready = 1;   // the first pass over the ring finds every stage free
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const Work work = decode_work(p, w);
         box_init(p, box, lane, &tmap_a, &tmap_b, work, work.m_tile * kBM, work.n_tile * p.bn, p.bn);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
-          if (!(ok = mbar_wait_fast(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
+          if (!(ok = mbar_wait_peeked(&hdr->empty[stage], phase ^ 1, ready, abort_flag, kStatusProducerTimeout))) break;
+          uint32_t next_stage = stage + 1, next_phase = phase;
+          if (next_stage == p.stages) { next_stage = 0; next_phase ^= 1; }
+          const bool more = kb + 1 < work.kb_end || w + gridDim.x < total_work;
+          ready = more ? mbar_try_wait(&hdr->empty[next_stage], next_phase ^ 1) : 0u;
           if (lane == 0) mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
           if (box.active) {
             box_issue<false>(box, tiles + stage * stage_bytes, &hdr->full[stage], 0);
             box_advance(p, box);
           }
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          stage = next_stage;
+          phase = next_phase;
         }
       }
     }
   } else if (warp == 1) {
     // ===== MMA issuer =====
-    if (lane == 0) {
+    // The issuing thread is chosen with elect.sync, not `lane == 0`: the compiler then keeps descriptors and
+    // addresses in uniform registers, and one tcgen05.mma costs ~40-48 issue cycles instead of ~92.
+    if (elect_one()) {
       const MmaSetup ms = make_mma_setup(p, kBM, p.bn, smem_u32(tiles), stage_bytes);
       uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
+      uint32_t ready = 0;   // the first stage is waited for in the ordinary way
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const Work work = decode_work(p, w);
         if (!(ok = mbar_wait_fast(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * p.bn;
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
-          if (!(ok = mbar_wait_fast(&hdr->full[stage], phase, abort_flag, kStatusMmaTimeout))) break;
+          if (!(ok = mbar_wait_peeked(&hdr->full[stage], phase, ready, abort_flag, kStatusMmaTimeout))) break;
+          uint32_t next_stage = stage + 1, next_phase = phase;
+          if (next_stage == p.stages) { next_stage = 0; next_phase ^= 1; }
+          const bool more = kb + 1 < work.kb_end || w + gridDim.x < total_work;
+          ready = more ? mbar_try_wait(&hdr->full[next_stage], next_phase) : 0u;
           tc_fence_after_sync();
           if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, kb > work.kb_begin);
           else mma_stage<false, false>(ms, tmem_d, stage, kb > work.kb_begin);
           mma_commit(&hdr->empty[stage]);
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          stage = next_stage;
+          phase = next_phase;
         }
         if (!ok) break;
         mma_commit(&hdr->acc_full[buf]);
@@ -866,32 +880,43 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       BoxLane box;
+      uint32_t ready = 1;   // the first pass over the ring finds every stage free
       for (uint32_t w = pair; ok && w < total_work; w += pairs) {
         const Work work = decode_work(p, w);
         box_init(p, box, lane, &tmap_a, &tmap_b, work, work.m_tile * 2 * kBM + rank * kBM, work.n_tile * p.bn + rank * b_lines, b_lines);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
-          if (!(ok = mbar_wait_fast(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout))) break;
+          if (!(ok = mbar_wait_peeked(&hdr->empty[stage], phase ^ 1, ready, abort_flag, kStatusProducerTimeout))) break;
+          uint32_t next_stage = stage + 1, next_phase = phase;
+          if (next_stage == p.stages) { next_stage = 0; next_phase ^= 1; }
+          const bool more = kb + 1 < work.kb_end || w + pairs < total_work;
+          ready = more ? mbar_try_wait(&hdr->empty[next_stage], next_phase ^ 1) : 0u;
           if (lane == 0 && rank == 0) mbar_arrive_expect_tx(&hdr->full[stage], 2 * tx_bytes);
           box_issue<true>(box, tiles + stage * stage_bytes, nullptr, map_to_cta(smem_u32(&hdr->full[stage]), 0));
           box_advance(p, box);
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          stage = next_stage;
+          phase = next_phase;
         }
       }
     }
   } else if (warp == 1) {
     // ===== MMA issuer (leader CTA only) =====
-    if (lane == 0 && rank == 0) {
+    if (rank == 0 && elect_one()) {
       const MmaSetup ms = make_mma_setup(p, 2 * kBM, p.bn / halves, smem_u32(tiles), stage_bytes);
       const uint32_t acc_stride = p.bn / halves;
       uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
+      uint32_t ready = 0;
       for (uint32_t w = pair; ok && w < total_work; w += pairs) {
         const Work work = decode_work(p, w);
         if (!(ok = mbar_wait_fast(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * acc_stride;
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
-          if (!(ok = mbar_wait_fast(&hdr->full[stage], phase, abort_flag, kStatusMmaTimeout))) break;
+          if (!(ok = mbar_wait_peeked(&hdr->full[stage], phase, ready, abort_flag, kStatusMmaTimeout))) break;
+          uint32_t next_stage = stage + 1, next_phase = phase;
+          if (next_stage == p.stages) { next_stage = 0; next_phase ^= 1; }
+          const bool more = kb + 1 < work.kb_end || w + pairs < total_work;
+          ready = more ? mbar_try_wait(&hdr->full[next_stage], next_phase) : 0u;
           tc_fence_after_sync();
           if (p.tf32) mma_stage<true, true>(ms, tmem_d, stage, kb > work.kb_begin);
           else mma_stage<true, false>(ms, tmem_d, stage, kb > work.kb_begin);
@@ -901,7 +926,8 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
           }
           // One arrival on the "empty" barrier of both CTAs (mask 0b11): each producer may refill its stage.
           mma_pair_commit_both(&hdr->empty[stage], 3);
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          stage = next_stage;
+          phase = next_phase;
         }
         if (!ok) break;
         mma_pair_commit_both(&hdr->acc_full[buf], 3);

@@ -77,6 +77,15 @@ __device__ __forceinline__ bool mbar_wait_fast(uint64_t* bar, uint32_t parity, v
   return mbar_wait_slow(bar, parity, abort_flag, code);
 }
 
+// Pipelined flavour.  A poll whose result feeds a branch costs the issuing thread 100-250 cycles (the round
+// trip to the barrier), more than the 40-50 cycles of a tcgen05.mma issue or the ~95 of a 16 KB TMA box.  The
+// per-stage loops therefore poll the NEXT stage's barrier before they issue the current stage's work and pass
+// the answer in here one iteration later; only a poll that came back "not yet" falls into the spinning wait.
+__device__ __forceinline__ bool mbar_wait_peeked(uint64_t* bar, uint32_t parity, uint32_t peeked, volatile uint32_t* abort_flag, uint32_t code) {
+  if (peeked) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, code);
+}
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
