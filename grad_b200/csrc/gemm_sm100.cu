@@ -571,13 +571,182 @@ __device__ __forceinline__ void epilogue_chunk_transposed(const GemmParams& p, c
   __syncwarp();
 }
 
+// The guarded path for a ragged chunk met on the TMA-store route.  It works on its own copy of the chunk: the
+// guarded path indexes the values with a run-time index, which puts its array in local memory, and the
+// caller's accumulator registers must not follow it there.
+__device__ __noinline__ void epilogue_chunk_ragged(const GemmParams& p, const uint32_t* vals, uint32_t batch, uint32_t split, uint32_t row,
+                                                   uint32_t col0, float bias_lane) {
+  uint32_t copy[32];
+#pragma unroll
+  for (uint32_t i = 0; i < 32; ++i) copy[i] = vals[i];
+  epilogue_chunk(p, copy, batch, split, row, col0, bias_lane);
+}
+__device__ __forceinline__ void epilogue_chunk_copy(const GemmParams& p, const uint32_t (&acc)[32], uint32_t batch, uint32_t split, uint32_t row,
+                                                    uint32_t col0, float bias_lane) {
+  uint32_t spill[32];
+#pragma unroll
+  for (uint32_t i = 0; i < 32; ++i) spill[i] = acc[i];
+  epilogue_chunk_ragged(p, spill, batch, split, row, col0, bias_lane);
+}
+
+// Full 32-column chunk of 32 rows through shared memory and one TMA store.  Straight from the accumulator
+// layout a lane owns a row, so a warp-wide 16-byte store touches 32 different lines and fills half a sector
+// of each; with all SMs storing at once that took as long again as the rest of the epilogue.  Here the warp
+// parks the chunk in its 2 KB staging block as 32 rows of 64 bytes (64-byte swizzle: the eight lanes of a
+// quarter-warp hit eight different 16-byte bank groups) and lane 0 hands it to the TMA unit, which writes whole
+// rows and clips the box at the edges of C.  The block is reused as soon as the previous store has read it.
+__device__ __forceinline__ void stage_and_store(const CUtensorMap* tmap_c, uint8_t* stage, const uint4 (&q)[4], uint32_t lane, int32_t x,
+                                                int32_t y, int32_t z) {
+  if (lane == 0) bulk_wait_read_all();
+  __syncwarp();
+  const uint32_t sw = (lane >> 1) & 3;
+  uint8_t* line = stage + lane * 64;
+#pragma unroll
+  for (uint32_t j = 0; j < 4; ++j) *(uint4*)(line + ((j ^ sw) << 4)) = q[j];
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_3d(tmap_c, stage, x, y, z);
+    bulk_commit_group();
+  }
+}
+
+__device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
+                                                   const float* sbias, uint32_t batch, uint32_t row, uint32_t col0, uint32_t lane) {
+  const bool live = row < p.m;
+  const uint64_t off = (uint64_t)batch * p.stride_c + (uint64_t)row * p.ldc + col0;
+  float v[32];
+#pragma unroll
+  for (uint32_t i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
+  if (p.accumulate && live) {
+    if (p.c_is_bf16) {
+#pragma unroll
+      for (uint32_t i = 0; i < 32; i += 8) {
+        const uint4 q = *(const uint4*)((const uint16_t*)p.c + off + i);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+          v[i + 2 * j] += __uint_as_float(w[j] << 16);
+          v[i + 2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (uint32_t i = 0; i < 32; i += 4) {
+        const float4 q = *(const float4*)((const float*)p.c + off + i);
+        v[i] += q.x; v[i + 1] += q.y; v[i + 2] += q.z; v[i + 3] += q.w;
+      }
+    }
+  }
+  if (p.bias) {
+#pragma unroll
+    for (uint32_t i = 0; i < 32; i += 4) {
+      const float4 b = *(const float4*)(sbias + i);   // same address in every lane: a broadcast read
+      v[i] += b.x; v[i + 1] += b.y; v[i + 2] += b.z; v[i + 3] += b.w;
+    }
+  }
+  if (p.residual && live) {
+    if (p.c_is_bf16) {
+#pragma unroll
+      for (uint32_t i = 0; i < 32; i += 8) {
+        const uint4 q = *(const uint4*)((const uint16_t*)p.residual + off + i);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+          v[i + 2 * j] += __uint_as_float(w[j] << 16);
+          v[i + 2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (uint32_t i = 0; i < 32; i += 4) {
+        const float4 q = *(const float4*)((const float*)p.residual + off + i);
+        v[i] += q.x; v[i + 1] += q.y; v[i + 2] += q.z; v[i + 3] += q.w;
+      }
+    }
+  }
+  if (p.relu) {
+#pragma unroll
+    for (uint32_t i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.0f);
+  }
+  if (p.round_tf32) {
+#pragma unroll
+    for (uint32_t i = 0; i < 32; ++i) v[i] = round_tf32(v[i]);
+  }
+  const int32_t y = (int32_t)(row - lane);
+  if (p.c_is_bf16) {
+    uint4 q[4];
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j)
+      q[j] = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]), pack_bf16x2(v[8 * j + 4], v[8 * j + 5]),
+                        pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+    stage_and_store(tmap_c, stage, q, lane, (int32_t)col0, y, (int32_t)batch);
+  } else {
+#pragma unroll
+    for (uint32_t half = 0; half < 2; ++half) {   // 16 f32 columns = 64 bytes per row and store
+      uint4 q[4];
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j)
+        q[j] = make_uint4(__float_as_uint(v[16 * half + 4 * j]), __float_as_uint(v[16 * half + 4 * j + 1]), __float_as_uint(v[16 * half + 4 * j + 2]),
+                          __float_as_uint(v[16 * half + 4 * j + 3]));
+      stage_and_store(tmap_c, stage, q, lane, (int32_t)(col0 + 16 * half), y, (int32_t)batch);
+    }
+  }
+}
+
+// The bias values of every chunk this warp will drain from the next accumulator, fetched into the warp's own
+// shared memory before it waits for that accumulator: chunk i's 32 values sit at sbias[32 * i].  (Fetched
+// chunk by chunk from global memory, each load's latency stood between two chunks.)
+__device__ __forceinline__ void stage_bias(const GemmParams& p, float* sbias, uint32_t ncols, uint32_t col_base, bool wide, uint32_t lane,
+                                           uint32_t first, uint32_t step) {
+  if (p.bias == nullptr) return;
+  __syncwarp();
+#pragma unroll
+  for (uint32_t i = 0; i < 8; ++i) {
+    const uint32_t c = first + i * step;
+    if (c < ncols) {
+      const uint32_t tc = wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c;
+      const uint32_t col = col_base + tc + lane;
+      sbias[32 * i + lane] = col < p.n ? p.bias[col] : 0.0f;
+    }
+  }
+  __syncwarp();
+}
+
 // Drains one accumulator of `ncols` columns: TMEM reads are double-buffered in registers (the next 32 columns
 // are in flight while the current ones are processed) and the bias slice is fetched one chunk ahead.
 // `wide` selects the column order of a two-half tile (see the pair kernel).
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, uint32_t ncols, uint32_t batch, uint32_t split,
                                               uint32_t row, uint32_t col_base, bool wide, uint32_t lane, float* stage_buf,
-                                              uint32_t first, uint32_t step) {
+                                              uint32_t first, uint32_t step, const CUtensorMap* tmap_c, uint8_t* store_stage, const float* sbias) {
   const bool staged = p.staged_transpose && p.splits == 1;
+  if (p.tma_store && p.splits == 1) {
+    // Chunks that lie wholly inside C and rows that begin inside it go through the TMA store; a ragged last
+    // chunk takes the guarded scalar path with its bias read back from the staged values.
+    if (first >= ncols) return;
+    auto tile_col = [&](uint32_t c) { return wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c; };
+    uint32_t acc_a[32], acc_b[32];
+    tmem_ld_32x32(taddr + first, acc_a);
+    uint32_t i = 0;
+    for (uint32_t c = first; c < ncols; c += 2 * step, i += 2) {
+      const bool has_b = c + step < ncols;
+      tmem_ld_wait();
+      if (has_b) tmem_ld_32x32(taddr + c + step, acc_b);
+      {
+        const uint32_t col0 = col_base + tile_col(c);
+        if (col0 + 32 <= p.n && row - lane < p.m) epilogue_chunk_tma(p, tmap_c, acc_a, store_stage, sbias + 32 * i, batch, row, col0, lane);
+        else epilogue_chunk_copy(p, acc_a, batch, split, row, col0, p.bias ? sbias[32 * i + lane] : 0.0f);
+      }
+      if (has_b) {
+        tmem_ld_wait();
+        if (c + 2 * step < ncols) tmem_ld_32x32(taddr + c + 2 * step, acc_a);
+        const uint32_t col0 = col_base + tile_col(c + step);
+        if (col0 + 32 <= p.n && row - lane < p.m) epilogue_chunk_tma(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), batch, row, col0, lane);
+        else epilogue_chunk_copy(p, acc_b, batch, split, row, col0, p.bias ? sbias[32 * (i + 1) + lane] : 0.0f);
+      }
+    }
+    return;
+  }
   auto tile_col = [&](uint32_t c) { return wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c; };
   auto bias_at = [&](uint32_t c) {
     const uint32_t col = col_base + tile_col(c) + lane;
@@ -654,7 +823,7 @@ __device__ __forceinline__ void mma_stage(const MmaSetup& s, uint32_t tmem_d, ui
 // ---- the kernel ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(448, 1)
 gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
-                  const __grid_constant__ CUtensorMap tmap_b) {
+                  const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   SmemHeader* hdr = (SmemHeader*)smem;
@@ -759,8 +928,14 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     const uint32_t quarter = warp & 3;
     uint32_t buf = 0, buf_phase = 0;
     bool ok = true;
+    const bool tma_out = p.tma_store && p.splits == 1;
+    uint8_t* epi_smem = tiles + p.stages * stage_bytes;
+    uint8_t* store_stage = epi_smem + (warp - 2) * kStoreStageBytesPerWarp;
+    float* sbias = (float*)(epi_smem + 8 * kStoreStageBytesPerWarp + (warp - 2) * kStoreBiasBytesPerWarp);
+    if (tma_out && warp == 2 && lane == 0) prefetch_tmap(&tmap_c);
     for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       const Work work = decode_work(p, w);
+      if (tma_out) stage_bias(p, sbias, p.bn, work.n_tile * p.bn, false, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
       ok = mbar_wait(&hdr->acc_full[buf], buf_phase, abort_flag, kStatusEpilogueTimeout);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
@@ -769,12 +944,13 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
       epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane,
                                                (float*)(tiles + p.stages * stage_bytes) + (warp - 2) * (kStageBytesPerWarp / 4),
-                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
+                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&hdr->acc_empty[buf]);
       if ((buf ^= 1) == 0) buf_phase ^= 1;
     }
+    if (tma_out && lane == 0) bulk_wait_all();   // the staging block must outlive its last store
   } else {
     // ===== gather warps =====
     const uint32_t tid = threadIdx.x - 64 - epi_threads;
@@ -821,7 +997,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 // CTA, to the "empty" and "accumulator full" barriers of both.
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
-                       const __grid_constant__ CUtensorMap tmap_b) {
+                       const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   SmemHeader* hdr = (SmemHeader*)smem;
@@ -939,8 +1115,14 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     const uint32_t quarter = warp & 3;
     uint32_t buf = 0, buf_phase = 0;
     bool ok = true;
+    const bool tma_out = p.tma_store && p.splits == 1;
+    uint8_t* epi_smem = tiles + p.stages * stage_bytes;
+    uint8_t* store_stage = epi_smem + (warp - 2) * kStoreStageBytesPerWarp;
+    float* sbias = (float*)(epi_smem + 8 * kStoreStageBytesPerWarp + (warp - 2) * kStoreBiasBytesPerWarp);
+    if (tma_out && warp == 2 && lane == 0) prefetch_tmap(&tmap_c);
     for (uint32_t w = pair; ok && w < total_work; w += pairs) {
       const Work work = decode_work(p, w);
+      if (tma_out) stage_bias(p, sbias, p.bn, work.n_tile * p.bn, halves == 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
       ok = mbar_wait(&hdr->acc_full[buf], buf_phase, abort_flag, kStatusEpilogueTimeout);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
@@ -949,12 +1131,13 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * (p.bn / halves);
       epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane,
                                                (float*)(tiles + p.stages * stage_bytes) + (warp - 2) * (kStageBytesPerWarp / 4),
-                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
+                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->acc_empty[buf]), 0));
       if (++buf == bufs) { buf = 0; buf_phase ^= 1; }
     }
+    if (tma_out && lane == 0) bulk_wait_all();   // the staging block must outlive its last store
   }
 
   // ===== teardown =====
@@ -996,7 +1179,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
 size_t gemm_smem_bytes(const GemmParams& p) {
   const size_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
   return 1024 /* alignment slack */ + kHeaderBytes + (size_t)p.stages * (kATileBytes + b_lines * kLineBytes) +
-         (p.staged_transpose ? kStageBytes : 0);
+         (p.staged_transpose ? kStageBytes : 0) + (p.tma_store ? kStoreSmemBytes : 0);
 }
 
 // Co-resident 2-CTA clusters of the pair kernel for a given dynamic shared-memory size (cached per size).
@@ -1039,7 +1222,8 @@ cudaError_t gemm_sm100_configure() {
   return cudaFuncSetAttribute(gemm_sm100_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
-cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, int sm_count, cudaStream_t stream) {
+cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c, int sm_count,
+                              cudaStream_t stream) {
   const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
   if (total_work == 0) return cudaSuccess;
   if (p.cta_pair) {
@@ -1048,12 +1232,12 @@ cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, co
     // co-resident 2-CTA clusters can be below sm_count / 2 (SMs are paired within a GPC), and a cluster
     // left waiting would run its whole share of tiles after the others have finished.
     const uint32_t pairs = std::min<uint32_t>(total_work, max_resident_pairs(gemm_smem_bytes(p), sm_count));
-    gemm_sm100_pair_kernel<<<2 * pairs, 64 + 128 * p.epi_groups, gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b);
+    gemm_sm100_pair_kernel<<<2 * pairs, 64 + 128 * p.epi_groups, gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b, tmap_c);
     return cudaGetLastError();
   }
   const bool gather = p.a_kind == kGather || p.b_kind == kGather;
   const uint32_t grid = total_work < (uint32_t)sm_count ? total_work : (uint32_t)sm_count;
-  gemm_sm100_kernel<<<grid, 64 + 128 * p.epi_groups + (gather ? 128 : 0), gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b);
+  gemm_sm100_kernel<<<grid, 64 + 128 * p.epi_groups + (gather ? 128 : 0), gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b, tmap_c);
   return cudaGetLastError();
 }
 

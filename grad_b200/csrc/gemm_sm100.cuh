@@ -69,11 +69,18 @@ struct GemmParams {
   uint32_t staged_transpose;  // transpose_out through a shared-memory staging buffer placed after the stages (vector stores)
   uint32_t bias_per_row;    // bias is indexed by the row (M) index: products computed transposed (M = output channels)
   uint32_t round_tf32;      // round the stored f32 result to TF32 (nearest, ties away)
+  uint32_t tma_store;       // full 32-column chunks leave through shared memory and a TMA store (map of C passed to the kernel)
   uint32_t* status;
 };
 
+// Shared memory the epilogue warps own when p.tma_store is set: per warp a 2 KB staging block (32 rows x 64
+// bytes, 64-byte swizzle) and 1 KB of bias values (eight 32-column chunks).
+constexpr uint32_t kStoreStageBytesPerWarp = 2048;
+constexpr uint32_t kStoreBiasBytesPerWarp = 1024;
+constexpr uint32_t kStoreSmemBytes = 8 * (kStoreStageBytesPerWarp + kStoreBiasBytesPerWarp);
 size_t gemm_smem_bytes(const GemmParams& p);
-cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, int sm_count, cudaStream_t stream);
+cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c, int sm_count,
+                              cudaStream_t stream);
 cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream);
 cudaError_t gemm_sm100_configure();
 

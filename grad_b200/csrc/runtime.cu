@@ -58,7 +58,7 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 // Encodes a tiled map with 128-byte swizzle.  dims/strides/box follow the driver's convention: dims[0] is
 // the contiguous one, strides (bytes) start at dims[1].
 bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                const uint32_t* box, bool swizzle_32b_chunks = false, const uint32_t* elem_strides = nullptr) {
+                const uint32_t* box, bool swizzle_32b_chunks = false, const uint32_t* elem_strides = nullptr, bool swizzle_64b = false) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t gdims[5];
@@ -72,14 +72,15 @@ bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, co
   }
   const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<void*>(base),
                         gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle_32b_chunks ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        swizzle_64b ? CU_TENSOR_MAP_SWIZZLE_64B
+                                    : (swizzle_32b_chunks ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B),
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
 struct Plan {
   GemmParams p;
-  CUtensorMap tmap_a, tmap_b;
+  CUtensorMap tmap_a, tmap_b, tmap_c;
   bool tensor = false;      // tcgen05 path, else strict-f32
   size_t workspace = 0;     // bytes of split-K partials
 };
@@ -324,6 +325,26 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
   info.k_blocks = p.k_blocks_total;
   info.work_items = p.tiles_m * p.tiles_n * p.batch * p.splits;
   info.kernel_launches = p.k == 0 ? 1 : (p.splits > 1 ? 2 : 1);
+  // Row-major results whose rows start on 16-byte boundaries leave through a TMA store: a map of C as
+  // {n, m, batch} with a box of 64 bytes x 32 rows, the block one epilogue warp stages per chunk.
+  p.tma_store = 0;
+  std::memset(&plan.tmap_c, 0, sizeof(plan.tmap_c));
+  if (plan.tensor && p.k != 0 && p.vec_store && !p.transpose_out && !p.bias_per_row && !p.staged_transpose && p.epi_groups == 2 &&
+      !getenv("GB_NO_TMA_STORE")) {
+    const uint32_t es = p.c_is_bf16 ? 2 : 4;
+    const uint64_t dims[3] = {p.n, p.m, p.batch};
+    const uint64_t strides[2] = {(uint64_t)p.ldc * es, p.batch > 1 ? p.stride_c * es : (uint64_t)p.ldc * es * p.m};
+    const uint32_t box[3] = {64 / es, 32, 1};
+    p.tma_store = encode_map(&plan.tmap_c, p.c_is_bf16, p.c, 3, dims, strides, box, false, nullptr, true) ? 1 : 0;
+  }
+  if (plan.tensor) {
+    // The stage ring takes what the epilogue's own shared memory leaves of the 227 KB a CTA can have.
+    const uint32_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
+    const size_t fixed = gb::gemm_smem_bytes(p) - (size_t)p.stages * (128 * 128 + b_lines * 128);
+    const uint32_t fit = (uint32_t)((227 * 1024 - fixed) / (128 * 128 + b_lines * 128));
+    p.stages = std::max(2u, std::min(p.stages, fit));
+  }
+  info.stages = p.stages;
   cudaError_t e;
   if (p.k == 0) {
     // An empty contraction is a zero product: only the epilogue runs (through the reduce kernel, zero parts).
@@ -332,7 +353,7 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
     e = gb::launch_splitk_reduce(p, stream);
     return e == cudaSuccess ? GB_OK : cuda_fail(h, e);
   }
-  e = plan.tensor ? gb::launch_gemm_sm100(p, plan.tmap_a, plan.tmap_b, h->sm_count, stream) : gb::launch_gemm_f32(p, stream);
+  e = plan.tensor ? gb::launch_gemm_sm100(p, plan.tmap_a, plan.tmap_b, plan.tmap_c, h->sm_count, stream) : gb::launch_gemm_f32(p, stream);
   if (e != cudaSuccess) return cuda_fail(h, e);
   if (p.splits > 1) {
     e = gb::launch_splitk_reduce(p, stream);
