@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmParams p) {
       }
       const uint64_t idx = (uint64_t)batch * p.stride_c + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
       if (p.accumulate) x += p.c_is_bf16 ? bf16_to_f32(((const uint16_t*)p.c)[idx]) : ((const float*)p.c)[idx];
-      if (p.bias) x += p.bias[p.bias_per_row ? row : col];
+      if (p.bias) x += p.bias[col];
       if (p.residual) x += p.c_is_bf16 ? bf16_to_f32(((const uint16_t*)p.residual)[idx]) : ((const float*)p.residual)[idx];
       if (p.relu) x = fmaxf(x, 0.0f);
       if (p.round_tf32) x = round_tf32(x);

@@ -239,136 +239,160 @@ __device__ __forceinline__ void gather_tile(const GemmParams& p, const GatherDes
 // ---- TMA issue ----------------------------------------------------------------------------------------
 // One tile load, either on this CTA's own barrier or, for a CTA pair, on the pair leader's barrier.
 template <bool kPair>
-__device__ __forceinline__ void load_3d(uint8_t* dst, const CUtensorMap* tmap, uint64_t* bar, uint32_t pair_bar, int32_t x, int32_t y, int32_t z) {
-  if constexpr (kPair) tma_pair_load_3d(smem_u32(dst), tmap, pair_bar, x, y, z);
-  else tma_load_3d(dst, tmap, bar, x, y, z);
-}
-template <bool kPair>
 __device__ __forceinline__ void load_4d(uint8_t* dst, const CUtensorMap* tmap, uint64_t* bar, uint32_t pair_bar, int32_t x, int32_t y, int32_t z, int32_t w) {
   if constexpr (kPair) tma_pair_load_4d(smem_u32(dst), tmap, pair_bar, x, y, z, w);
   else tma_load_4d(dst, tmap, bar, x, y, z, w);
 }
 
 // ---- per-lane tile loads ----------------------------------------------------------------------------------
-// The producer warp gives every TMA box of a stage to its own lane, and each lane keeps its box's
-// coordinates in registers, stepping them from one K block to the next without divisions.  One thread
-// issuing every box with freshly computed coordinates took 400-700 cycles per K block, more than the 512
-// the tensor core needs for it.
+// The producer warp gives every TMA box of a stage to its own lane.  A lone thread runs dependent
+// instructions at 5-10 cycles each, so what a lane does per K block must be short AND the same instruction
+// stream in every lane, whatever operand its box belongs to: lanes that took different branches (a 4-D
+// activation box beside a 3-D filter box, a switch over the operand kind) ran one after the other and the
+// producer, not the copy engine, set the pace (~1000 cycles per K block for a convolution that needs 130-500).
+// Hence: every tensor map has four dimensions (unused ones of extent 1), a box is four coordinates, and the
+// walk along K is two nested counters with three precomputed coordinate steps:
+//   A step  - neither counter wraps (next channel block, next 64 K values of a dense operand, next image rows)
+//   B step  - the inner counter wraps (next tap column; next filter tap; next image)
+//   C step  - both wrap (next tap row)
 struct BoxLane {
-  uint32_t active, four_d, kind, smem_off;
+  uint32_t active, smem_off;
   const CUtensorMap* tmap;
   int32_t x, y, z, w;
-  uint32_t cb, cblocks, kx, ky, tap;     // K walk over (tap, channel block): patch-K and weight boxes
-  int32_t sign, origin, row0;            // patch-K: coordinate = origin + sign * tap offset
-  uint32_t row, img;                     // K walk over positions: patch-MN boxes
-  int32_t w_off, h_off;
+  uint32_t i0, n0, i1, n1;
+  int32_t ax, ay, az, aw, bx, by, bz, bw, cx, cy, cz, cw;
 };
+constexpr uint32_t kNever = 0xFFFFFFFFu;
 
 __device__ __forceinline__ uint32_t boxes_of(uint32_t kind, uint32_t lines, uint32_t epl) {
   if (kind == kGather) return 0;
   return (kind == kDenseMN || kind == kPatchMN) ? lines / epl : 1u;
 }
 
-__device__ __forceinline__ void box_refresh(const GemmParams& p, BoxLane& b, uint32_t epl) {
-  if (b.kind == kPatchK) {
-    b.x = (int32_t)(b.cb * epl);
-    b.y = b.origin + b.sign * (int32_t)(b.kx * p.geo.dilation);
-    b.z = b.row0 + b.origin + b.sign * (int32_t)(b.ky * p.geo.dilation);   // row0 is already in input rows
-  } else if (b.kind == kWeightK) {
-    b.x = (int32_t)(b.cb * epl);
-    b.z = (int32_t)b.tap;
-  } else if (b.kind == kPatchMN) {
-    b.z = (int32_t)(b.row * p.geo.stride) + b.h_off;
-    b.w = (int32_t)b.img;
+// Once per kernel: which box this lane owns and how its coordinates step along K.
+__device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint32_t lane, const CUtensorMap* tmap_a, const CUtensorMap* tmap_b,
+                                          uint32_t b_lines, uint32_t& kind, uint32_t& index) {
+  const int32_t epl = p.tf32 ? 32 : 64;
+  const uint32_t na = boxes_of(p.a_kind, kBM, epl), nb = boxes_of(p.b_kind, b_lines, epl);
+  b.active = lane < na + nb;
+  const bool is_b = lane >= na;
+  index = is_b ? lane - na : lane;
+  kind = is_b ? p.b_kind : p.a_kind;
+  b.tmap = is_b ? tmap_b : tmap_a;
+  b.smem_off = (is_b ? kATileBytes : 0u) + index * epl * kLineBytes;
+  b.n0 = b.n1 = kNever;
+  b.i0 = b.i1 = 0;
+  b.ax = b.ay = b.az = b.aw = b.bx = b.by = b.bz = b.bw = b.cx = b.cy = b.cz = b.cw = 0;
+  b.x = b.y = b.z = b.w = 0;
+  if (!b.active) return;
+  switch (kind) {
+    case kDenseK: b.ax = epl; break;
+    case kDenseMN: b.ay = epl; break;
+    case kPatchK: {
+      const int32_t cblocks = (int32_t)((p.dgrad ? p.geo.c_out : p.geo.c) / (uint32_t)epl);
+      const int32_t tap_step = (p.dgrad ? -1 : 1) * (int32_t)p.geo.dilation, k = (int32_t)p.geo.k;
+      b.n0 = (uint32_t)cblocks; b.n1 = p.geo.k;
+      b.ax = epl;
+      b.bx = -(cblocks - 1) * epl; b.by = tap_step;
+      b.cx = b.bx; b.cy = -(k - 1) * tap_step; b.cz = tap_step;
+      break;
+    }
+    case kWeightK: {
+      const int32_t cblocks = (int32_t)(p.geo.c_out / (uint32_t)epl);
+      b.n0 = (uint32_t)cblocks;
+      b.ax = epl;
+      b.bx = -(cblocks - 1) * epl; b.bz = 1;
+      break;
+    }
+    case kPatchMN:
+      if (p.box_n > 1) {
+        b.aw = (int32_t)p.box_n;
+      } else {
+        const int32_t rows = (int32_t)(p.box_h * p.geo.stride);
+        b.n0 = p.geo.out_h / p.box_h;
+        b.az = rows;
+        b.bz = -((int32_t)b.n0 - 1) * rows; b.bw = 1;
+      }
+      break;
+    default: break;
   }
 }
 
-// Sets lane `lane`'s box up for the K block kb_begin of a tile whose A rows start at m0 and B lines at n0.
-__device__ __forceinline__ void box_init(const GemmParams& p, BoxLane& b, uint32_t lane, const CUtensorMap* tmap_a,
-                                         const CUtensorMap* tmap_b, const Work& work, uint32_t m0, uint32_t n0, uint32_t b_lines) {
-  const uint32_t epl = p.tf32 ? 32u : 64u;
-  const uint32_t na = boxes_of(p.a_kind, kBM, epl), nb = boxes_of(p.b_kind, b_lines, epl);
-  b.active = lane < na + nb;
+// Once per tile: the box's coordinates and counters at K block work.kb_begin of a tile whose A rows start at m0
+// and B lines at n0.
+__device__ __forceinline__ void box_start(const GemmParams& p, BoxLane& b, uint32_t kind, uint32_t index, const Work& work, uint32_t m0,
+                                          uint32_t n0, bool is_b) {
   if (!b.active) return;
-  const bool is_b = lane >= na;
-  const uint32_t j = is_b ? lane - na : lane;
-  b.kind = is_b ? p.b_kind : p.a_kind;
-  b.tmap = is_b ? tmap_b : tmap_a;
-  b.smem_off = (is_b ? kATileBytes : 0u) + j * epl * kLineBytes;
-  b.four_d = b.kind == kPatchK || b.kind == kPatchMN;
+  const uint32_t epl = p.tf32 ? 32u : 64u;
   const uint32_t mn0 = is_b ? n0 : m0;
   const uint32_t k0 = work.kb_begin;
+  b.i0 = b.i1 = 0;
   b.w = 0;
-  switch (b.kind) {
+  switch (kind) {
     case kDenseK:
       b.x = (int32_t)(k0 * epl); b.y = (int32_t)mn0; b.z = (int32_t)work.batch;
       break;
     case kDenseMN:
-      b.x = (int32_t)(mn0 + j * epl); b.y = (int32_t)(k0 * epl); b.z = (int32_t)work.batch;
+      b.x = (int32_t)(mn0 + index * epl); b.y = (int32_t)(k0 * epl); b.z = (int32_t)work.batch;
       break;
     case kPatchK: {
       const uint32_t grid_h = p.dgrad ? p.geo.h : p.geo.out_h, grid_w = p.dgrad ? p.geo.w : p.geo.out_w;
       const uint32_t per_image = grid_h * grid_w;
-      b.cblocks = (p.dgrad ? p.geo.c_out : p.geo.c) / epl;
-      b.tap = k0 / b.cblocks; b.cb = k0 - b.tap * b.cblocks;
-      b.ky = b.tap / p.geo.k; b.kx = b.tap - b.ky * p.geo.k;
+      const uint32_t tap = k0 / b.n0, cb = k0 - tap * b.n0;
+      const uint32_t ky = tap / p.geo.k, kx = tap - ky * p.geo.k;
       const uint32_t img = mn0 / per_image;
-      b.row0 = p.box_n > 1 ? 0 : (int32_t)((mn0 - img * per_image) / grid_w * (p.dgrad ? 1u : p.geo.stride));
-      b.sign = p.dgrad ? -1 : 1;
-      b.origin = p.dgrad ? (int32_t)p.geo.pad : -(int32_t)p.geo.pad;
+      const int32_t row0 = p.box_n > 1 ? 0 : (int32_t)((mn0 - img * per_image) / grid_w * (p.dgrad ? 1u : p.geo.stride));
+      const int32_t sign = p.dgrad ? -1 : 1, origin = p.dgrad ? (int32_t)p.geo.pad : -(int32_t)p.geo.pad;
+      b.i0 = cb; b.i1 = kx;
+      b.x = (int32_t)(cb * epl);
+      b.y = origin + sign * (int32_t)(kx * p.geo.dilation);
+      b.z = row0 + origin + sign * (int32_t)(ky * p.geo.dilation);   // row0 is already in input rows
       b.w = (int32_t)img;
+      break;
+    }
+    case kWeightK: {
+      const uint32_t tap = k0 / b.n0, cb = k0 - tap * b.n0;
+      b.i0 = cb;
+      b.x = (int32_t)(cb * epl); b.y = (int32_t)mn0; b.z = (int32_t)tap;
       break;
     }
     case kPatchMN: {
       // Rows (tap, channel) kk0 .. kk0 + epl of the weight gradient; rows past the last tap are never stored.
-      const uint32_t taps = p.geo.k * p.geo.k, kk0 = mn0 + j * epl;
+      const uint32_t taps = p.geo.k * p.geo.k, kk0 = mn0 + index * epl;
       const uint32_t tap = min(kk0 / p.geo.c, taps - 1);
       const uint32_t ky = tap / p.geo.k, kx = tap - ky * p.geo.k;
       const uint32_t per_image = p.geo.out_h * p.geo.out_w, p0 = k0 * epl;
+      const uint32_t img = p0 / per_image;
+      const uint32_t row = p.box_n > 1 ? 0u : (p0 - img * per_image) / p.geo.out_w;
       b.x = kk0 >= taps * p.geo.c ? 0 : (int32_t)(kk0 - tap * p.geo.c);
-      b.w_off = (int32_t)(kx * p.geo.dilation) - (int32_t)p.geo.pad;
-      b.h_off = (int32_t)(ky * p.geo.dilation) - (int32_t)p.geo.pad;
-      b.y = b.w_off;
-      b.img = p0 / per_image;
-      b.row = p.box_n > 1 ? 0u : (p0 - b.img * per_image) / p.geo.out_w;
+      b.y = (int32_t)(kx * p.geo.dilation) - (int32_t)p.geo.pad;
+      b.z = (int32_t)(row * p.geo.stride) + (int32_t)(ky * p.geo.dilation) - (int32_t)p.geo.pad;
+      b.w = (int32_t)img;
+      b.i0 = p.box_n > 1 ? 0u : row / p.box_h;
       break;
     }
-    case kWeightK:
-      b.cblocks = p.geo.c_out / epl;
-      b.tap = k0 / b.cblocks; b.cb = k0 - b.tap * b.cblocks;
-      b.y = (int32_t)mn0;
-      break;
     default:
       break;
   }
-  box_refresh(p, b, epl);
 }
 
-// Steps the box to the next K block.
-__device__ __forceinline__ void box_advance(const GemmParams& p, BoxLane& b) {
-  const uint32_t epl = p.tf32 ? 32u : 64u;
-  switch (b.kind) {
-    case kDenseK: b.x += (int32_t)epl; return;
-    case kDenseMN: b.y += (int32_t)epl; return;
-    case kPatchK:
-      if (++b.cb == b.cblocks) { b.cb = 0; if (++b.kx == p.geo.k) { b.kx = 0; ++b.ky; } }
-      break;
-    case kWeightK:
-      if (++b.cb == b.cblocks) { b.cb = 0; ++b.tap; }
-      break;
-    case kPatchMN:
-      if (p.box_n > 1) b.img += p.box_n;
-      else if ((b.row += p.box_h) >= p.geo.out_h) { b.row = 0; ++b.img; }
-      break;
-    default: return;
-  }
-  box_refresh(p, b, epl);
+// Steps the box to the next K block: the same dozen instructions in every lane.
+__device__ __forceinline__ void box_step(BoxLane& b) {
+  const uint32_t i0 = b.i0 + 1;
+  const bool w0 = i0 == b.n0;
+  const uint32_t i1 = b.i1 + (w0 ? 1u : 0u);
+  const bool w1 = i1 == b.n1;
+  b.i0 = w0 ? 0u : i0;
+  b.i1 = w1 ? 0u : i1;
+  b.x += w1 ? b.cx : (w0 ? b.bx : b.ax);
+  b.y += w1 ? b.cy : (w0 ? b.by : b.ay);
+  b.z += w1 ? b.cz : (w0 ? b.bz : b.az);
+  b.w += w1 ? b.cw : (w0 ? b.bw : b.aw);
 }
 
 template <bool kPair>
 __device__ __forceinline__ void box_issue(const BoxLane& b, uint8_t* stage_base, uint64_t* bar, uint32_t pair_bar) {
-  if (b.four_d) load_4d<kPair>(stage_base + b.smem_off, b.tmap, bar, pair_bar, b.x, b.y, b.z, b.w);
-  else load_3d<kPair>(stage_base + b.smem_off, b.tmap, bar, pair_bar, b.x, b.y, b.z);
+  load_4d<kPair>(stage_base + b.smem_off, b.tmap, bar, pair_bar, b.x, b.y, b.z, b.w);
 }
 
 // ---- epilogue -----------------------------------------------------------------------------------------
@@ -478,97 +502,13 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
       const uint64_t idx = cbase + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
       float x = v[i];
       if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx);
-      if (p.bias) x += p.bias[p.bias_per_row ? row : col];
+      if (p.bias) x += p.bias[col];
       if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
       if (p.relu) x = fmaxf(x, 0.0f);
       if (p.round_tf32) x = round_tf32(x);
       store_out(p.c, p.c_is_bf16, idx, x);
     }
   }
-}
-
-// Transposed store of 32 accumulator columns x 32 rows of one warp: the tile's rows are the output's
-// contiguous index (output channels when a convolution is computed transposed), so writing them straight
-// from the accumulator layout (one row per thread) would take 32 two- or four-byte stores per thread.
-// The warp instead parks the 32 x 32 f32 block in its private shared-memory buffer as [column][row]
-// (row pitch 36 words: conflict-free for the scalar writes and for the float4 reads), then every lane picks
-// up runs of 8 (bf16) or 4 (f32) consecutive rows of one column, applies the epilogue on vectors
-// (old value, bias per row, residual, ReLU, rounding) and stores 16 bytes.
-constexpr uint32_t kStagePitch = 36;                          // words per staged column
-constexpr uint32_t kStageBytesPerWarp = 32 * kStagePitch * 4;  // 4608
-constexpr uint32_t kStageBytes = 8 * kStageBytesPerWarp;       // up to eight epilogue warps
-
-__device__ __forceinline__ void epilogue_chunk_transposed(const GemmParams& p, const uint32_t (&acc)[32], float* buf, uint32_t batch,
-                                                          uint32_t row_base, uint32_t col0, uint32_t lane) {
-  if (col0 >= p.n) return;
-#pragma unroll
-  for (uint32_t i = 0; i < 32; ++i) buf[i * kStagePitch + lane] = __uint_as_float(acc[i]);
-  __syncwarp();
-  const uint32_t per = p.c_is_bf16 ? 8u : 4u, segs = 32 / per;
-  const uint64_t cbase = (uint64_t)batch * p.stride_c;
-  for (uint32_t item = lane; item < 32 * segs; item += 32) {
-    const uint32_t pos = item / segs, seg = item - pos * segs;
-    const uint32_t col = col0 + pos, row0 = row_base + seg * per;
-    if (col >= p.n || row0 >= p.m) continue;
-    float v[8];
-    const float4 a = *(const float4*)(buf + pos * kStagePitch + seg * per);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    if (per == 8) {
-      const float4 b = *(const float4*)(buf + pos * kStagePitch + seg * per + 4);
-      v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    }
-    const uint64_t idx = cbase + (uint64_t)col * p.ldc + row0;
-    const bool full = row0 + per <= p.m;
-    if (full) {
-      if (p.accumulate) {
-        if (p.c_is_bf16) {
-          const uint4 q = *(const uint4*)((const uint16_t*)p.c + idx);
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) { v[2 * j] += __uint_as_float(w[j] << 16); v[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u); }
-        } else {
-          const float4 q = *(const float4*)((const float*)p.c + idx);
-          v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
-        }
-      }
-      if (p.bias) {
-#pragma unroll
-        for (uint32_t j = 0; j < 8; ++j)
-          if (j < per) v[j] += p.bias[p.bias_per_row ? row0 + j : col];
-      }
-      if (p.residual) {
-        if (p.c_is_bf16) {
-          const uint4 q = *(const uint4*)((const uint16_t*)p.residual + idx);
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) { v[2 * j] += __uint_as_float(w[j] << 16); v[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u); }
-        } else {
-          const float4 q = *(const float4*)((const float*)p.residual + idx);
-          v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
-        }
-      }
-#pragma unroll
-      for (uint32_t j = 0; j < 8; ++j) {
-        if (p.relu) v[j] = fmaxf(v[j], 0.0f);
-        if (p.round_tf32) v[j] = round_tf32(v[j]);
-      }
-      if (p.c_is_bf16)
-        *(uint4*)((uint16_t*)p.c + idx) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-      else
-        *(float4*)((float*)p.c + idx) = make_float4(v[0], v[1], v[2], v[3]);
-    } else {
-      for (uint32_t j = 0; j < per && row0 + j < p.m; ++j) {
-        float x = v[j];
-        if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx + j);
-        if (p.bias) x += p.bias[p.bias_per_row ? row0 + j : col];
-        if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx + j);
-        if (p.relu) x = fmaxf(x, 0.0f);
-        if (p.round_tf32) x = round_tf32(x);
-        store_out(p.c, p.c_is_bf16, idx + j, x);
-      }
-    }
-  }
-  __syncwarp();
 }
 
 // The guarded path for a ragged chunk met on the TMA-store route.  It works on its own copy of the chunk: the
@@ -717,9 +657,8 @@ __device__ __forceinline__ void stage_bias(const GemmParams& p, float* sbias, ui
 // are in flight while the current ones are processed) and the bias slice is fetched one chunk ahead.
 // `wide` selects the column order of a two-half tile (see the pair kernel).
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, uint32_t ncols, uint32_t batch, uint32_t split,
-                                              uint32_t row, uint32_t col_base, bool wide, uint32_t lane, float* stage_buf,
+                                              uint32_t row, uint32_t col_base, bool wide, uint32_t lane,
                                               uint32_t first, uint32_t step, const CUtensorMap* tmap_c, uint8_t* store_stage, const float* sbias) {
-  const bool staged = p.staged_transpose && p.splits == 1;
   if (p.tma_store && p.splits == 1) {
     // Chunks that lie wholly inside C and rows that begin inside it go through the TMA store; a ragged last
     // chunk takes the guarded scalar path with its bias read back from the staged values.
@@ -750,7 +689,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
   auto tile_col = [&](uint32_t c) { return wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c; };
   auto bias_at = [&](uint32_t c) {
     const uint32_t col = col_base + tile_col(c) + lane;
-    return (p.bias != nullptr && !p.bias_per_row && c < ncols && col < p.n) ? p.bias[col] : 0.0f;
+    return (p.bias != nullptr && c < ncols && col < p.n) ? p.bias[col] : 0.0f;
   };
   // This warp drains the 32-column chunks first, first + step, ...; two chunks are in flight (A and B registers).
   if (first >= ncols) return;
@@ -763,15 +702,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     if (has_b) tmem_ld_32x32(taddr + c + step, acc_b);
     float bias_cur = bias_next;
     bias_next = bias_at(c + step);
-    if (staged) epilogue_chunk_transposed(p, acc_a, stage_buf, batch, row - lane, col_base + tile_col(c), lane);
-    else epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur);
+    epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur);
     if (has_b) {
       tmem_ld_wait();
       if (c + 2 * step < ncols) tmem_ld_32x32(taddr + c + 2 * step, acc_a);
       bias_cur = bias_next;
       bias_next = bias_at(c + 2 * step);
-      if (staged) epilogue_chunk_transposed(p, acc_b, stage_buf, batch, row - lane, col_base + tile_col(c + step), lane);
-      else epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur);
+      epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur);
     }
   }
 }
@@ -871,10 +808,13 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       BoxLane box;
+      uint32_t box_kind, box_index;
+      box_setup(p, box, lane, &tmap_a, &tmap_b, p.bn, box_kind, box_index);
+      const bool box_is_b = lane >= boxes_of(p.a_kind, kBM, epl);
       uint32_t ready = 1;   // the first pass over the ring finds every stage free
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const Work work = decode_work(p, w);
-        box_init(p, box, lane, &tmap_a, &tmap_b, work, work.m_tile * kBM, work.n_tile * p.bn, p.bn);
+        box_start(p, box, box_kind, box_index, work, work.m_tile * kBM, work.n_tile * p.bn, box_is_b);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_peeked(&hdr->empty[stage], phase ^ 1, ready, abort_flag, kStatusProducerTimeout))) break;
           uint32_t next_stage = stage + 1, next_phase = phase;
@@ -882,10 +822,8 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           const bool more = kb + 1 < work.kb_end || w + gridDim.x < total_work;
           ready = more ? mbar_try_wait(&hdr->empty[next_stage], next_phase ^ 1) : 0u;
           if (lane == 0) mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
-          if (box.active) {
-            box_issue<false>(box, tiles + stage * stage_bytes, &hdr->full[stage], 0);
-            box_advance(p, box);
-          }
+          if (box.active) box_issue<false>(box, tiles + stage * stage_bytes, &hdr->full[stage], 0);
+          box_step(box);
           stage = next_stage;
           phase = next_phase;
         }
@@ -943,7 +881,6 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       const uint32_t row = work.m_tile * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
       epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane,
-                                               (float*)(tiles + p.stages * stage_bytes) + (warp - 2) * (kStageBytesPerWarp / 4),
                                                ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias);
       tc_fence_before_sync();
       __syncwarp();
@@ -1056,10 +993,13 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       BoxLane box;
+      uint32_t box_kind, box_index;
+      box_setup(p, box, lane, &tmap_a, &tmap_b, b_lines, box_kind, box_index);
+      const bool box_is_b = lane >= boxes_of(p.a_kind, kBM, epl);
       uint32_t ready = 1;   // the first pass over the ring finds every stage free
       for (uint32_t w = pair; ok && w < total_work; w += pairs) {
         const Work work = decode_work(p, w);
-        box_init(p, box, lane, &tmap_a, &tmap_b, work, work.m_tile * 2 * kBM + rank * kBM, work.n_tile * p.bn + rank * b_lines, b_lines);
+        box_start(p, box, box_kind, box_index, work, work.m_tile * 2 * kBM + rank * kBM, work.n_tile * p.bn + rank * b_lines, box_is_b);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_peeked(&hdr->empty[stage], phase ^ 1, ready, abort_flag, kStatusProducerTimeout))) break;
           uint32_t next_stage = stage + 1, next_phase = phase;
@@ -1068,7 +1008,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
           ready = more ? mbar_try_wait(&hdr->empty[next_stage], next_phase ^ 1) : 0u;
           if (lane == 0 && rank == 0) mbar_arrive_expect_tx(&hdr->full[stage], 2 * tx_bytes);
           box_issue<true>(box, tiles + stage * stage_bytes, nullptr, map_to_cta(smem_u32(&hdr->full[stage]), 0));
-          box_advance(p, box);
+          box_step(box);
           stage = next_stage;
           phase = next_phase;
         }
@@ -1130,7 +1070,6 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       const uint32_t row = work.m_tile * 2 * kBM + rank * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * (p.bn / halves);
       epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane,
-                                               (float*)(tiles + p.stages * stage_bytes) + (warp - 2) * (kStageBytesPerWarp / 4),
                                                ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias);
       tc_fence_before_sync();
       __syncwarp();
@@ -1166,7 +1105,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
     for (uint32_t s = 0; s < p.splits; ++s) x += p.partial[(uint64_t)s * total + t];
     const uint64_t idx = (uint64_t)batch * p.stride_c + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
     if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx);
-    if (p.bias) x += p.bias[p.bias_per_row ? row : col];
+    if (p.bias) x += p.bias[col];
     if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
     if (p.relu) x = fmaxf(x, 0.0f);
     if (p.round_tf32) x = round_tf32(x);
@@ -1179,7 +1118,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
 size_t gemm_smem_bytes(const GemmParams& p) {
   const size_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
   return 1024 /* alignment slack */ + kHeaderBytes + (size_t)p.stages * (kATileBytes + b_lines * kLineBytes) +
-         (p.staged_transpose ? kStageBytes : 0) + (p.tma_store ? kStoreSmemBytes : 0);
+         (p.tma_store ? kStoreSmemBytes : 0);
 }
 
 // Co-resident 2-CTA clusters of the pair kernel for a given dynamic shared-memory size (cached per size).

@@ -66,8 +66,6 @@ struct GemmParams {
   uint32_t ldc;
   uint32_t c_is_bf16, transpose_out, accumulate, relu, vec_store;
   uint32_t epi_groups;      // epilogue warps = 4 * epi_groups; group g drains column chunks g, g + groups, ...
-  uint32_t staged_transpose;  // transpose_out through a shared-memory staging buffer placed after the stages (vector stores)
-  uint32_t bias_per_row;    // bias is indexed by the row (M) index: products computed transposed (M = output channels)
   uint32_t round_tf32;      // round the stored f32 result to TF32 (nearest, ties away)
   uint32_t tma_store;       // full 32-column chunks leave through shared memory and a TMA store (map of C passed to the kernel)
   uint32_t* status;

@@ -104,20 +104,21 @@ void fill_dense_gather(gb::GatherDesc& g, const DenseOperand& o) {
   g.mn_major = o.mn_major;
 }
 
-// Tries to describe a dense operand by a 3-D TMA map {inner, lines, batch}; false means "gather it".
+// Tries to describe a dense operand by a TMA map {inner, lines, batch, 1}; false means "gather it".
 bool dense_tma(CUtensorMap* map, const DenseOperand& o, bool smem_bf16, uint32_t batch, uint32_t tile_mn, uint32_t epl) {
   const uint32_t es = smem_bf16 ? 2 : 4;
   if ((o.dtype == GB_BF16) != smem_bf16) return false;
   if (!aligned16(o.base) || ((uint64_t)o.ld * es) % 16 != 0) return false;
   if (batch > 1 && (o.batch_stride == 0 || (o.batch_stride * es) % 16 != 0)) return false;
-  const uint64_t dims[3] = {o.inner, o.lines, batch};
+  // Every operand map has four dimensions (the kernel issues one form of copy); a dense one ends in an extent of 1.
+  const uint64_t dims[4] = {o.inner, o.lines, batch, 1};
   const uint64_t batch_bytes = batch > 1 ? o.batch_stride * es : (uint64_t)o.ld * es * std::max<uint64_t>(o.lines, 1);
-  const uint64_t strides[2] = {(uint64_t)o.ld * es, batch_bytes};
+  const uint64_t strides[3] = {(uint64_t)o.ld * es, batch_bytes, batch_bytes * batch};
   // K-major: box = 128 bytes of K x tile_mn lines.  MN-major: box = 128 bytes of MN x epl K lines.
-  const uint32_t box[3] = {epl, o.mn_major ? epl : tile_mn, 1};
+  const uint32_t box[4] = {epl, o.mn_major ? epl : tile_mn, 1, 1};
   if (box[1] > 256) return false;
   // MN-major 32-bit tiles must use the 32-byte-chunk flavour of the 128-byte swizzle.
-  return encode_map(map, smem_bf16, o.base, 3, dims, strides, box, !smem_bf16 && o.mn_major);
+  return encode_map(map, smem_bf16, o.base, 4, dims, strides, box, !smem_bf16 && o.mn_major);
 }
 
 uint32_t pick_stages(uint32_t bn) {
@@ -329,7 +330,7 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
   // {n, m, batch} with a box of 64 bytes x 32 rows, the block one epilogue warp stages per chunk.
   p.tma_store = 0;
   std::memset(&plan.tmap_c, 0, sizeof(plan.tmap_c));
-  if (plan.tensor && p.k != 0 && p.vec_store && !p.transpose_out && !p.bias_per_row && !p.staged_transpose && p.epi_groups == 2 &&
+  if (plan.tensor && p.k != 0 && p.vec_store && !p.transpose_out  && p.epi_groups == 2 &&
       !getenv("GB_NO_TMA_STORE")) {
     const uint32_t es = p.c_is_bf16 ? 2 : 4;
     const uint64_t dims[3] = {p.n, p.m, p.batch};
@@ -419,68 +420,6 @@ bool nhwc_tma(CUtensorMap* map, const void* base, bool smem_bf16, uint32_t dtype
   return encode_map(map, smem_bf16, base, 4, dims, strides, box, !smem_bf16 && mn_major, estr);
 }
 
-// Forward convolution computed transposed: y^T[c_out, positions] = w^T[c_out, K] * patches^T[K, positions].
-// The output channels become the M rows of the tile and 128-256 positions its N columns, so a layer with
-// 64 or 128 channels still issues 256-wide MMAs (an MMA costs the same ~215 cycles whether N is 64 or 256)
-// instead of four times as many narrow ones.  A is the filter matrix read MN-major (c_out contiguous), B the
-// NHWC patch boxes with one line per position; the epilogue stores transposed, which is NHWC again.
-// Returns false when the geometry cannot be fetched by TMA this way (the caller keeps the direct plan).
-bool plan_fprop_swapped(const gb_handle* h, const gb_conv_desc* d, const gb::ConvGeo& g, const void* x, const void* w, void* y,
-                        const gb_epilogue* ep, bool smem_bf16, uint32_t epl, double direct_cost, Plan& plan) {
-  GemmParams& p = plan.p;
-  if (!getenv("GB_SWAP") || g.stride != 1 || (d->dtype_x == GB_BF16) != smem_bf16 || g.c % epl != 0) return false;
-  const uint32_t taps = g.k * g.k, positions = d->geo.positions, k_blocks = taps * g.c / epl, sms = (uint32_t)h->sm_count;
-  // candidates: (pair, positions per tile)
-  struct Cand { bool pair; uint32_t bn; };
-  const Cand cands[] = {{true, 256}, {false, 256}, {false, 128}, {true, 128}};
-  double best = direct_cost;
-  int pick = -1;
-  uint32_t bw = 0, bh = 0, bnn = 0;
-  for (int i = 0; i < 4; ++i) {
-    const Cand& c = cands[i];
-    if (c.pair && g.c_out <= 128) continue;
-    uint32_t tw, th, tn;
-    if (!patch_box(c.pair ? c.bn / 2 : c.bn, g.out_h, g.out_w, tw, th, tn)) continue;
-    const double cost = tile_cost(g.c_out, positions, 1, k_blocks, c.bn, c.pair, sms);
-    if (cost < best) { best = cost; pick = i; bw = tw; bh = th; bnn = tn; }
-  }
-  if (pick < 0) return false;
-  const Cand c = cands[pick];
-  DenseOperand oa{w, d->dtype_w, taps * g.c, g.c_out, g.c_out, 0, true};
-  CUtensorMap map_a, map_b;
-  const bool a_tma = dense_tma(&map_a, oa, smem_bf16, 1, 128, epl);
-  if (!a_tma && c.pair) return false;
-  if (!nhwc_tma(&map_b, x, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, bw, bh, bnn)) return false;
-  p.m = g.c_out; p.n = positions; p.k = taps * g.c;
-  fill_dense_gather(p.ga, oa);
-  p.gbsrc.base = x; p.gbsrc.source = gb::kSrcPatch; p.gbsrc.src_is_bf16 = d->dtype_x == GB_BF16;
-  p.gbsrc.lines_total = positions; p.gbsrc.inner_total = p.k; p.gbsrc.mn_major = 0; p.gbsrc.batch_stride = 0;
-  p.a_mn_major = 1; p.b_mn_major = 0;
-  set_output(p, y, d->dtype_y, g.c_out, 0, true, d->accumulate, ep);
-  p.bias = ep ? ep->bias : nullptr;
-  p.residual = ep ? ep->residual : nullptr;
-  p.bias_per_row = 1;
-  p.k_blocks_total = k_blocks;
-  p.k_blocks_per_split = k_blocks;
-  p.splits = 1;
-  p.bn = c.bn;
-  p.cta_pair = c.pair;
-  p.tiles_m = ceil_div(g.c_out, c.pair ? 256 : 128);
-  p.tiles_n = ceil_div(positions, c.bn);
-  p.box_w = bw; p.box_h = bh; p.box_n = bnn;
-  // 16-byte transposed stores need a 16-byte-aligned run of channels per position; 20 KB of shared memory stage them
-  p.staged_transpose = aligned16(y) && ((uint64_t)g.c_out * elem_size(d->dtype_y)) % 16 == 0 &&
-                       (!p.residual || aligned16(p.residual));
-  p.stages = std::min<uint32_t>(8, (227 * 1024 - 2048 - (p.staged_transpose ? 36864 : 0)) / (128 * 128 + (c.pair ? c.bn / 2 : c.bn) * 128));
-  p.a_kind = a_tma ? gb::kDenseMN : gb::kGather;
-  p.b_kind = gb::kPatchK;
-  p.group_m = 1;   // few M tiles (channels): walk the positions, keeping the filters in L2
-  plan.tmap_a = map_a;
-  plan.tmap_b = map_b;
-  plan.workspace = 0;
-  return true;
-}
-
 int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* act, const void* other, void* out,
               const gb_epilogue* ep, Plan& plan) {
   std::memset(&plan.p, 0, sizeof(plan.p));
@@ -522,13 +461,6 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       CUtensorMap single = plan.tmap_b;
       if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }))
         plan.tmap_b = single;
-      const double direct = p.a_kind == gb::kGather || p.b_kind == gb::kGather || p.splits > 1
-                                ? 1e30
-                                : tile_cost(p.m, p.n, 1, p.k_blocks_total, p.bn, p.cta_pair != 0, (uint32_t)h->sm_count);
-      if (p.a_kind != gb::kGather && p.splits == 1 && !w_rows) {
-        Plan swapped = plan;
-        if (plan_fprop_swapped(h, d, g, act, other, out, ep, smem_bf16, epl, direct, swapped)) plan = swapped;
-      }
     }
   } else if (pass == 1) {
     // dx[pixels, c] = patchesT(dy)[pixels, taps*c_out] * wT[taps*c_out, c]
@@ -550,14 +482,14 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       p.b_kind = gb::kGather;
       const uint32_t es = smem_bf16 ? 2 : 4;
       if ((d->dtype_w == GB_BF16) == smem_bf16 && g.c_out % epl == 0 && aligned16(other) && p.bn <= 256) {
-        const uint64_t dims[3] = {g.c_out, g.c, taps};
-        const uint64_t strides[2] = {(uint64_t)g.c_out * es, (uint64_t)g.c_out * es * g.c};
-        const uint32_t box[3] = {epl, p.bn, 1};
-        if (encode_map(&plan.tmap_b, smem_bf16, other, 3, dims, strides, box)) p.b_kind = gb::kWeightK;
+        const uint64_t dims[4] = {g.c_out, g.c, taps, 1};
+        const uint64_t strides[3] = {(uint64_t)g.c_out * es, (uint64_t)g.c_out * es * g.c, (uint64_t)g.c_out * es * g.c * taps};
+        const uint32_t box[4] = {epl, p.bn, 1, 1};
+        if (encode_map(&plan.tmap_b, smem_bf16, other, 4, dims, strides, box)) p.b_kind = gb::kWeightK;
         CUtensorMap single = plan.tmap_b;
         if (!try_pair(h, plan, 32, [&](uint32_t rows) {
-              const uint32_t half_box[3] = {epl, rows, 1};
-              return encode_map(&plan.tmap_b, smem_bf16, other, 3, dims, strides, half_box);
+              const uint32_t half_box[4] = {epl, rows, 1, 1};
+              return encode_map(&plan.tmap_b, smem_bf16, other, 4, dims, strides, half_box);
             }))
           plan.tmap_b = single;
       }

@@ -324,11 +324,20 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 // bf16 round-to-nearest-even of an f32, the rounding grad's bf16 stores use
 // (src/gpu/math/bf16.zig:1-5: (bits + 0x7FFF + ((bits >> 16) & 1)) >> 16, NaN handling included).
+// f32 -> bf16, round to nearest even, by the conversion instruction.  On every finite value and on the
+// infinities this is the integer formula (bits + 0x7FFF + ((bits >> 16) & 1)) >> 16; a NaN comes out as the
+// canonical 0x7FFF where the formula would carry its payload into other bits.  Done with integer
+// instructions the conversion was ~200 instructions per 32-column chunk, the largest part of a chunk's time.
 __device__ __forceinline__ uint32_t bf16_bits(float x) {
-  const uint32_t bits = __float_as_uint(x);
-  return (bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16;
+  uint16_t h;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(x));
+  return h;
 }
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) { return bf16_bits(lo) | (bf16_bits(hi) << 16); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
 // f32 -> TF32 precision, round to nearest with ties away from zero (cvt.rna.tf32.f32), kept in an f32.
 __device__ __forceinline__ float round_tf32(float x) {
   uint32_t r;
