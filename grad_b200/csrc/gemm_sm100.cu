@@ -49,19 +49,48 @@ struct Work {
   uint32_t batch, m_tile, n_tile, split, kb_begin, kb_end;
 };
 
+// Division by a run-time constant without the ~100-cycle integer divide: an under-estimate from the high
+// product with floor((2^32 - 1) / d), then at most two corrections.
+struct FastDiv {
+  uint32_t d, m;
+};
+__device__ __forceinline__ FastDiv make_fastdiv(uint32_t d) { return FastDiv{d, 0xFFFFFFFFu / d}; }
+__device__ __forceinline__ uint32_t fast_div(uint32_t a, const FastDiv& f) {
+  uint32_t q = __umulhi(a, f.m);
+  uint32_t r = a - q * f.d;
+  if (r >= f.d) { r -= f.d; ++q; }
+  if (r >= f.d) { ++q; }
+  return q;
+}
+
+// Work item -> tile.  Every role of a CTA decodes every item, and a short-K tile (a convolution layer is 9-36 K
+// blocks) is over in a few thousand cycles, so the common shapes skip the divisions: no K split, one batch
+// entry, one column of tiles.
 __device__ __forceinline__ Work decode_work(const GemmParams& p, uint32_t w) {
   Work out;
-  out.split = w % p.splits;
-  uint32_t t = w / p.splits;
-  const uint32_t per_batch = p.tiles_m * p.tiles_n;
-  out.batch = t / per_batch;
-  t -= out.batch * per_batch;
-  const uint32_t band_size = p.group_m * p.tiles_n;
-  const uint32_t band = t / band_size;
-  const uint32_t within = t - band * band_size;
-  const uint32_t rows_in_band = min(p.group_m, p.tiles_m - band * p.group_m);
-  out.m_tile = band * p.group_m + within % rows_in_band;
-  out.n_tile = within / rows_in_band;
+  uint32_t t = w;
+  out.split = 0;
+  if (p.splits > 1) {
+    out.split = w % p.splits;
+    t = w / p.splits;
+  }
+  out.batch = 0;
+  if (p.batch > 1) {
+    const uint32_t per_batch = p.tiles_m * p.tiles_n;
+    out.batch = t / per_batch;
+    t -= out.batch * per_batch;
+  }
+  if (p.tiles_n == 1) {
+    out.m_tile = t;
+    out.n_tile = 0;
+  } else {
+    const uint32_t band_size = p.group_m * p.tiles_n;
+    const uint32_t band = t / band_size;
+    const uint32_t within = t - band * band_size;
+    const uint32_t rows_in_band = min(p.group_m, p.tiles_m - band * p.group_m);
+    out.n_tile = within / rows_in_band;
+    out.m_tile = band * p.group_m + within - out.n_tile * rows_in_band;
+  }
   out.kb_begin = out.split * p.k_blocks_per_split;
   out.kb_end = min(out.kb_begin + p.k_blocks_per_split, p.k_blocks_total);
   return out;
@@ -261,6 +290,7 @@ struct BoxLane {
   int32_t x, y, z, w;
   uint32_t i0, n0, i1, n1;
   int32_t ax, ay, az, aw, bx, by, bz, bw, cx, cy, cz, cw;
+  FastDiv per_image, grid_w;   // patch boxes: tile row -> (image, image row)
 };
 constexpr uint32_t kNever = 0xFFFFFFFFu;
 
@@ -284,7 +314,13 @@ __device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint3
   b.i0 = b.i1 = 0;
   b.ax = b.ay = b.az = b.aw = b.bx = b.by = b.bz = b.bw = b.cx = b.cy = b.cz = b.cw = 0;
   b.x = b.y = b.z = b.w = 0;
+  b.per_image = b.grid_w = FastDiv{1, 0};
   if (!b.active) return;
+  if (kind == kPatchK) {
+    const uint32_t grid_h = p.dgrad ? p.geo.h : p.geo.out_h, grid_w = p.dgrad ? p.geo.w : p.geo.out_w;
+    b.per_image = make_fastdiv(grid_h * grid_w);
+    b.grid_w = make_fastdiv(grid_w);
+  }
   switch (kind) {
     case kDenseK: b.ax = epl; break;
     case kDenseMN: b.ay = epl; break;
@@ -336,12 +372,15 @@ __device__ __forceinline__ void box_start(const GemmParams& p, BoxLane& b, uint3
       b.x = (int32_t)(mn0 + index * epl); b.y = (int32_t)(k0 * epl); b.z = (int32_t)work.batch;
       break;
     case kPatchK: {
-      const uint32_t grid_h = p.dgrad ? p.geo.h : p.geo.out_h, grid_w = p.dgrad ? p.geo.w : p.geo.out_w;
-      const uint32_t per_image = grid_h * grid_w;
-      const uint32_t tap = k0 / b.n0, cb = k0 - tap * b.n0;
-      const uint32_t ky = tap / p.geo.k, kx = tap - ky * p.geo.k;
-      const uint32_t img = mn0 / per_image;
-      const int32_t row0 = p.box_n > 1 ? 0 : (int32_t)((mn0 - img * per_image) / grid_w * (p.dgrad ? 1u : p.geo.stride));
+      uint32_t cb = 0, kx = 0, ky = 0;
+      if (k0 != 0) {   // only a K split starts inside the tap walk
+        const uint32_t tap = k0 / b.n0;
+        cb = k0 - tap * b.n0;
+        ky = tap / p.geo.k;
+        kx = tap - ky * p.geo.k;
+      }
+      const uint32_t img = fast_div(mn0, b.per_image);
+      const int32_t row0 = p.box_n > 1 ? 0 : (int32_t)(fast_div(mn0 - img * b.per_image.d, b.grid_w) * (p.dgrad ? 1u : p.geo.stride));
       const int32_t sign = p.dgrad ? -1 : 1, origin = p.dgrad ? (int32_t)p.geo.pad : -(int32_t)p.geo.pad;
       b.i0 = cb; b.i1 = kx;
       b.x = (int32_t)(cb * epl);
@@ -351,7 +390,7 @@ __device__ __forceinline__ void box_start(const GemmParams& p, BoxLane& b, uint3
       break;
     }
     case kWeightK: {
-      const uint32_t tap = k0 / b.n0, cb = k0 - tap * b.n0;
+      const uint32_t tap = k0 == 0 ? 0u : k0 / b.n0, cb = k0 - tap * b.n0;
       b.i0 = cb;
       b.x = (int32_t)(cb * epl); b.y = (int32_t)mn0; b.z = (int32_t)tap;
       break;
