@@ -49,12 +49,6 @@ struct Work {
   uint32_t batch, m_tile, n_tile, split, kb_begin, kb_end;
 };
 
-// Division by a run-time constant without the ~100-cycle integer divide: an under-estimate from the high
-// product with floor((2^32 - 1) / d), then at most two corrections.
-struct FastDiv {
-  uint32_t d, m;
-};
-__device__ __forceinline__ FastDiv make_fastdiv(uint32_t d) { return FastDiv{d, 0xFFFFFFFFu / d}; }
 __device__ __forceinline__ uint32_t fast_div(uint32_t a, const FastDiv& f) {
   uint32_t q = __umulhi(a, f.m);
   uint32_t r = a - q * f.d;
@@ -317,27 +311,26 @@ __device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint3
   b.per_image = b.grid_w = FastDiv{1, 0};
   if (!b.active) return;
   if (kind == kPatchK) {
-    const uint32_t grid_h = p.dgrad ? p.geo.h : p.geo.out_h, grid_w = p.dgrad ? p.geo.w : p.geo.out_w;
-    b.per_image = make_fastdiv(grid_h * grid_w);
-    b.grid_w = make_fastdiv(grid_w);
+    b.per_image = p.walk.div_image;
+    b.grid_w = p.walk.div_w;
   }
   switch (kind) {
     case kDenseK: b.ax = epl; break;
     case kDenseMN: b.ay = epl; break;
     case kPatchK: {
-      const int32_t cblocks = (int32_t)((p.dgrad ? p.geo.c_out : p.geo.c) / (uint32_t)epl);
-      const int32_t tap_step = (p.dgrad ? -1 : 1) * (int32_t)p.geo.dilation, k = (int32_t)p.geo.k;
-      b.n0 = (uint32_t)cblocks; b.n1 = p.geo.k;
+      const int32_t cblocks = (int32_t)p.walk.cblocks;
+      b.n0 = p.walk.cblocks; b.n1 = p.walk.n1;
       b.ax = epl;
-      b.bx = -(cblocks - 1) * epl; b.by = tap_step;
-      b.cx = b.bx; b.cy = -(k - 1) * tap_step; b.cz = tap_step;
+      b.bx = -(cblocks - 1) * epl; b.by = p.walk.y_step;
+      b.cx = b.bx; b.cy = -((int32_t)p.walk.n1 - 1) * p.walk.y_step; b.cz = p.walk.z_step;
       break;
     }
     case kWeightK: {
-      const int32_t cblocks = (int32_t)(p.geo.c_out / (uint32_t)epl);
-      b.n0 = (uint32_t)cblocks;
+      const int32_t cblocks = (int32_t)p.walk.cblocks;
+      b.n0 = p.walk.cblocks; b.n1 = p.walk.n1;
       b.ax = epl;
-      b.bx = -(cblocks - 1) * epl; b.bz = 1;
+      b.bx = -(cblocks - 1) * epl; b.bz = p.walk.tap_x;
+      b.cx = b.bx; b.cz = p.walk.tap_y - ((int32_t)p.walk.n1 - 1) * p.walk.tap_x;
       break;
     }
     case kPatchMN:
@@ -372,27 +365,33 @@ __device__ __forceinline__ void box_start(const GemmParams& p, BoxLane& b, uint3
       b.x = (int32_t)(mn0 + index * epl); b.y = (int32_t)(k0 * epl); b.z = (int32_t)work.batch;
       break;
     case kPatchK: {
-      uint32_t cb = 0, kx = 0, ky = 0;
+      uint32_t cb = 0, tx = 0, ty = 0;
       if (k0 != 0) {   // only a K split starts inside the tap walk
         const uint32_t tap = k0 / b.n0;
         cb = k0 - tap * b.n0;
-        ky = tap / p.geo.k;
-        kx = tap - ky * p.geo.k;
+        ty = tap / b.n1;
+        tx = tap - ty * b.n1;
       }
       const uint32_t img = fast_div(mn0, b.per_image);
-      const int32_t row0 = p.box_n > 1 ? 0 : (int32_t)(fast_div(mn0 - img * b.per_image.d, b.grid_w) * (p.dgrad ? 1u : p.geo.stride));
-      const int32_t sign = p.dgrad ? -1 : 1, origin = p.dgrad ? (int32_t)p.geo.pad : -(int32_t)p.geo.pad;
-      b.i0 = cb; b.i1 = kx;
+      const int32_t row0 = p.box_n > 1 ? 0 : (int32_t)(fast_div(mn0 - img * b.per_image.d, b.grid_w) * p.walk.row_scale);
+      b.i0 = cb; b.i1 = tx;
       b.x = (int32_t)(cb * epl);
-      b.y = origin + sign * (int32_t)(kx * p.geo.dilation);
-      b.z = row0 + origin + sign * (int32_t)(ky * p.geo.dilation);   // row0 is already in input rows
+      b.y = p.walk.y0 + (int32_t)tx * p.walk.y_step;
+      b.z = row0 + p.walk.z0 + (int32_t)ty * p.walk.z_step;
       b.w = (int32_t)img;
       break;
     }
     case kWeightK: {
-      const uint32_t tap = k0 == 0 ? 0u : k0 / b.n0, cb = k0 - tap * b.n0;
-      b.i0 = cb;
-      b.x = (int32_t)(cb * epl); b.y = (int32_t)mn0; b.z = (int32_t)tap;
+      uint32_t cb = 0, tx = 0, ty = 0;
+      if (k0 != 0) {
+        const uint32_t tap = k0 / b.n0;
+        cb = k0 - tap * b.n0;
+        ty = tap / b.n1;
+        tx = tap - ty * b.n1;
+      }
+      b.i0 = cb; b.i1 = tx;
+      b.x = (int32_t)(cb * epl); b.y = (int32_t)mn0;
+      b.z = p.walk.tap0 + (int32_t)tx * p.walk.tap_x + (int32_t)ty * p.walk.tap_y;
       break;
     }
     case kPatchMN: {
@@ -446,8 +445,18 @@ __device__ __forceinline__ void store_out(void* base, uint32_t is_bf16, uint64_t
 // Applies the epilogue to 32 accumulator columns of one row and stores them.  `bias_lane` is bias[col0 + lane]
 // (one coalesced load per warp, fetched a chunk ahead by the caller); lanes trade it with shuffles, so every
 // lane runs the arithmetic and only the memory accesses are guarded by `live`.
+// Element offset of the start of product row `row` within one batch entry of C.
+__device__ __forceinline__ uint64_t out_row_offset(const GemmParams& p, uint32_t row) {
+  if (!p.rowmap.enabled) return (uint64_t)row * p.ldc;
+  const uint32_t img = fast_div(row, p.rowmap.per_image);
+  const uint32_t rem = row - img * p.rowmap.per_image.d;
+  const uint32_t i = fast_div(rem, p.rowmap.grid_w), j = rem - i * p.rowmap.grid_w.d;
+  const uint64_t pixel = ((uint64_t)img * p.rowmap.h + i * p.rowmap.scale + p.rowmap.off_y) * p.rowmap.w + j * p.rowmap.scale + p.rowmap.off_x;
+  return pixel * p.ldc;
+}
+
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&acc)[32], uint32_t batch, uint32_t split,
-                                               uint32_t row, uint32_t col0, float bias_lane) {
+                                               uint32_t row, uint32_t col0, float bias_lane, uint64_t row_off) {
   if (col0 >= p.n) return;
   const bool live = row < p.m;
   const uint32_t cols = min(32u, p.n - col0);
@@ -468,7 +477,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   for (uint32_t i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
   const bool vec = p.vec_store && !p.transpose_out && cols == 32;
   if (vec) {
-    const uint64_t off = cbase + (uint64_t)row * p.ldc + col0;
+    const uint64_t off = cbase + row_off + col0;
     if (p.accumulate && live) {
       if (p.c_is_bf16) {
 #pragma unroll
@@ -538,7 +547,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   for (uint32_t i = 0; i < 32; ++i) {
     if (i < cols) {
       const uint32_t col = col0 + i;
-      const uint64_t idx = cbase + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
+      const uint64_t idx = cbase + (p.transpose_out ? (uint64_t)col * p.ldc + row : row_off + col);
       float x = v[i];
       if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx);
       if (p.bias) x += p.bias[col];
@@ -558,7 +567,7 @@ __device__ __noinline__ void epilogue_chunk_ragged(const GemmParams& p, const ui
   uint32_t copy[32];
 #pragma unroll
   for (uint32_t i = 0; i < 32; ++i) copy[i] = vals[i];
-  epilogue_chunk(p, copy, batch, split, row, col0, bias_lane);
+  epilogue_chunk(p, copy, batch, split, row, col0, bias_lane, (uint64_t)row * p.ldc);
 }
 __device__ __forceinline__ void epilogue_chunk_copy(const GemmParams& p, const uint32_t (&acc)[32], uint32_t batch, uint32_t split, uint32_t row,
                                                     uint32_t col0, float bias_lane) {
@@ -732,6 +741,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
   };
   // This warp drains the 32-column chunks first, first + step, ...; two chunks are in flight (A and B registers).
   if (first >= ncols) return;
+  const uint64_t row_off = out_row_offset(p, row);
   uint32_t acc_a[32], acc_b[32];
   float bias_next = bias_at(first);
   tmem_ld_32x32(taddr + first, acc_a);
@@ -741,13 +751,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     if (has_b) tmem_ld_32x32(taddr + c + step, acc_b);
     float bias_cur = bias_next;
     bias_next = bias_at(c + step);
-    epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur);
+    epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur, row_off);
     if (has_b) {
       tmem_ld_wait();
       if (c + 2 * step < ncols) tmem_ld_32x32(taddr + c + 2 * step, acc_a);
       bias_cur = bias_next;
       bias_next = bias_at(c + 2 * step);
-      epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur);
+      epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur, row_off);
     }
   }
 }

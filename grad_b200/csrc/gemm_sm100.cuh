@@ -40,6 +40,34 @@ struct GatherDesc {
   uint32_t mn_major;       // 1: lines are K indices and inner is MN; 0: lines are MN and inner is K
 };
 
+// Division by a run-time constant without the ~100-cycle integer divide: an under-estimate from the high
+// product with floor((2^32 - 1) / d), then at most two corrections (device side: `fast_div`).
+struct FastDiv {
+  uint32_t d, m;
+};
+inline FastDiv make_fastdiv_host(uint32_t d) { return FastDiv{d ? d : 1u, 0xFFFFFFFFu / (d ? d : 1u)}; }
+
+// How a patch operand (kPatchK) and the filter operand of an input gradient (kWeightK) walk along K: channel
+// blocks innermost, then `n1` taps along x, then the taps along y.  A forward pass, a stride-1 input gradient
+// and one parity class of a strided input gradient differ only in these numbers.
+struct TapWalk {
+  uint32_t cblocks, n1;        // channel blocks per tap; taps along x
+  uint32_t grid_h, grid_w;     // a tile's rows enumerate (image, i, j) over this grid
+  FastDiv div_image, div_w;    // dividers by grid_h * grid_w and by grid_w
+  uint32_t row_scale;          // patch row of grid row i at the first tap: i * row_scale + z0
+  int32_t y0, z0;              // patch column / row of grid position (0, 0) at the first tap
+  int32_t y_step, z_step;      // patch column step per tap along x, patch row step per tap along y
+  int32_t tap0, tap_x, tap_y;  // filter tap index: first tap, step per tap along x, step per tap along y
+};
+
+// Where row m of the product lands when it is not row m of C: one parity class of a strided input gradient
+// writes pixel (image, i * scale + off_y, j * scale + off_x) of an NHWC tensor for row (image, i, j).
+struct RowMap {
+  uint32_t enabled;
+  FastDiv per_image, grid_w;
+  uint32_t h, w, scale, off_y, off_x;
+};
+
 struct GemmParams {
   // problem
   uint32_t m, n, k, batch;
@@ -54,7 +82,9 @@ struct GemmParams {
   // TMA patch boxes (conv): positions per box and its decomposition
   uint32_t box_w, box_h, box_n;
   ConvGeo geo;
-  uint32_t dgrad;           // 1: patches are taken from dy with flipped taps (stride-1 input gradient)
+  uint32_t dgrad;           // 1: patches are taken from dy with flipped taps (input gradient)
+  TapWalk walk;             // K walk of patch / filter-tap boxes
+  RowMap rowmap;            // output row placement (disabled: row m of C)
   // gather sources
   GatherDesc ga, gbsrc;
   // output

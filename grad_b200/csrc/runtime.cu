@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 #include <mutex>
 
 #include "../../include/gradb200.h"
@@ -330,7 +331,7 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
   // {n, m, batch} with a box of 64 bytes x 32 rows, the block one epilogue warp stages per chunk.
   p.tma_store = 0;
   std::memset(&plan.tmap_c, 0, sizeof(plan.tmap_c));
-  if (plan.tensor && p.k != 0 && p.vec_store && !p.transpose_out  && p.epi_groups == 2 &&
+  if (plan.tensor && p.k != 0 && p.vec_store && !p.transpose_out && !p.rowmap.enabled && p.epi_groups == 2 &&
       !getenv("GB_NO_TMA_STORE")) {
     const uint32_t es = p.c_is_bf16 ? 2 : 4;
     const uint64_t dims[3] = {p.n, p.m, p.batch};
@@ -420,6 +421,28 @@ bool nhwc_tma(CUtensorMap* map, const void* base, bool smem_bf16, uint32_t dtype
   return encode_map(map, smem_bf16, base, 4, dims, strides, box, !smem_bf16 && mn_major, estr);
 }
 
+// K walk of the patch boxes of a forward pass (taps in storage order, patch origin at -pad).
+void walk_forward(gb::TapWalk& wk, const gb::ConvGeo& g, uint32_t epl) {
+  wk.cblocks = std::max(1u, g.c / epl); wk.n1 = g.k;
+  wk.grid_h = g.out_h; wk.grid_w = g.out_w;
+  wk.div_image = gb::make_fastdiv_host(g.out_h * g.out_w); wk.div_w = gb::make_fastdiv_host(g.out_w);
+  wk.row_scale = g.stride;
+  wk.y0 = wk.z0 = -(int32_t)g.pad;
+  wk.y_step = wk.z_step = (int32_t)g.dilation;
+  wk.tap0 = 0; wk.tap_x = 1; wk.tap_y = (int32_t)g.k;
+}
+
+// K walk of a stride-1 input gradient: dy patches with mirrored tap offsets, filter taps in storage order.
+void walk_dgrad_unit(gb::TapWalk& wk, const gb::ConvGeo& g, uint32_t epl) {
+  wk.cblocks = std::max(1u, g.c_out / epl); wk.n1 = g.k;
+  wk.grid_h = g.h; wk.grid_w = g.w;
+  wk.div_image = gb::make_fastdiv_host(g.h * g.w); wk.div_w = gb::make_fastdiv_host(g.w);
+  wk.row_scale = 1;
+  wk.y0 = wk.z0 = (int32_t)g.pad;
+  wk.y_step = wk.z_step = -(int32_t)g.dilation;
+  wk.tap0 = 0; wk.tap_x = 1; wk.tap_y = (int32_t)g.k;
+}
+
 int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* act, const void* other, void* out,
               const gb_epilogue* ep, Plan& plan) {
   std::memset(&plan.p, 0, sizeof(plan.p));
@@ -454,6 +477,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     if (rc != GB_OK) return rc;
     if (plan.tensor) {
       p.a_kind = gb::kGather;
+      walk_forward(p.walk, g, epl);
       if ((g.stride == 1 || !getenv("GB_NO_STRIDED_TMA")) && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
           nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, false, g.stride))
         p.a_kind = gb::kPatchK;
@@ -476,6 +500,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     if (rc != GB_OK) return rc;
     if (plan.tensor) {
       p.a_kind = gb::kGather;
+      walk_dgrad_unit(p.walk, g, epl);
       if (g.stride == 1 && patch_box(128, g.h, g.w, p.box_w, p.box_h, p.box_n) &&
           nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_y, g.c_out, g.c_out, g.out_w, g.out_h, g.n, epl, p.box_w, p.box_h, p.box_n))
         p.a_kind = gb::kPatchK;
@@ -514,6 +539,101 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
     }
   }
+  return GB_OK;
+}
+
+// Input gradient of a strided convolution as up to stride^2 products, one per parity class of input pixels.
+// Pixel (s*i + py, s*j + px) only receives taps ky with (py + pad - ky*dil) divisible by s (likewise kx), and
+// through such a tap it reads dy at (i + (py + pad - ky*dil)/s, j + ...): a stride-1 walk over dy.  So each
+// class is an ordinary patch product over its own taps -- TMA boxes of dy, filter taps through the
+// {c_out, c_in, taps} map, 1/s^2 of the dense work, no multiplication by inserted zeros -- whose rows land on
+// every s-th pixel of dx (`RowMap`).  Returns GB_ERR_UNSUPPORTED, with nothing launched, when a class
+// cannot be fetched this way; the caller then takes the single gathered product.
+int run_dgrad_classes(gb_handle* h, cudaStream_t stream, const gb_conv_desc* d, const void* dy, const void* w, void* dx) {
+  const gb::ConvGeo g = to_geo(d->geo);
+  const uint32_t s = g.stride, dil = g.dilation;
+  uint32_t math = d->math;
+  if (math == GB_MATH_F32 && (d->dtype_x == GB_BF16 || d->dtype_y == GB_BF16)) math = GB_MATH_BF16;
+  if (math == GB_MATH_F32 || s < 2 || s > 4 || getenv("GB_NO_DGRAD_CLASSES")) return GB_ERR_UNSUPPORTED;
+  const bool tf32 = math == GB_MATH_TF32, smem_bf16 = !tf32;
+  const uint32_t epl = tf32 ? 32 : 64, es = smem_bf16 ? 2 : 4;
+  if ((d->dtype_y == GB_BF16) != smem_bf16 || (d->dtype_w == GB_BF16) != smem_bf16) return GB_ERR_UNSUPPORTED;
+  if (g.c_out % epl != 0 || !aligned16(dy) || !aligned16(w)) return GB_ERR_UNSUPPORTED;
+  uint32_t gcd = s, t = dil;
+  while (t) { const uint32_t r = gcd % t; gcd = t; t = r; }
+  const uint32_t tk = s / gcd;                       // taps of one class are tk apart
+  struct Axis { uint32_t count, taps, k0; int32_t off0; };
+  auto axis = [&](uint32_t len, uint32_t r) {
+    Axis a{len > r ? (len - r + s - 1) / s : 0u, 0u, 0u, 0};
+    for (uint32_t kk = 0; kk < g.k; ++kk) {
+      const int32_t v = (int32_t)(r + g.pad) - (int32_t)(kk * dil);
+      if (((v % (int32_t)s) + (int32_t)s) % (int32_t)s == 0) {
+        a.k0 = kk; a.off0 = v / (int32_t)s; a.taps = (g.k - 1 - kk) / tk + 1;
+        break;
+      }
+    }
+    return a;
+  };
+  std::vector<Plan> plans;
+  bool any_empty = false;
+  const uint32_t taps = g.k * g.k;
+  for (uint32_t py = 0; py < s; ++py)
+    for (uint32_t px = 0; px < s; ++px) {
+      const Axis ay = axis(g.h, py), ax = axis(g.w, px);
+      if (ay.count == 0 || ax.count == 0) continue;
+      if (ay.taps == 0 || ax.taps == 0) { any_empty = true; continue; }
+      plans.emplace_back();
+      Plan& plan = plans.back();
+      std::memset(&plan.p, 0, sizeof(plan.p));
+      GemmParams& p = plan.p;
+      p.geo = g; p.batch = 1; p.dgrad = 1; p.tf32 = tf32;
+      plan.tensor = true;
+      p.m = g.n * ay.count * ax.count; p.n = g.c; p.k = ay.taps * ax.taps * g.c_out;
+      set_output(p, dx, d->dtype_x, g.c_step, 0, false, d->accumulate, nullptr);
+      if (finish_plan(h, plan, false, 32, nullptr) != GB_OK) return GB_ERR_UNSUPPORTED;
+      if (!patch_box(128, ay.count, ax.count, p.box_w, p.box_h, p.box_n) ||
+          !nhwc_tma(&plan.tmap_a, dy, smem_bf16, d->dtype_y, g.c_out, g.c_out, g.out_w, g.out_h, g.n, epl, p.box_w, p.box_h, p.box_n))
+        return GB_ERR_UNSUPPORTED;
+      p.a_kind = gb::kPatchK;
+      const uint64_t dims[4] = {g.c_out, g.c, taps, 1};
+      const uint64_t strides[3] = {(uint64_t)g.c_out * es, (uint64_t)g.c_out * es * g.c, (uint64_t)g.c_out * es * g.c * taps};
+      const uint32_t box[4] = {epl, p.bn, 1, 1};
+      if (p.bn > 256 || !encode_map(&plan.tmap_b, smem_bf16, w, 4, dims, strides, box)) return GB_ERR_UNSUPPORTED;
+      p.b_kind = gb::kWeightK;
+      CUtensorMap single = plan.tmap_b;
+      if (!try_pair(h, plan, 32, [&](uint32_t rows) {
+            const uint32_t half_box[4] = {epl, rows, 1, 1};
+            return encode_map(&plan.tmap_b, smem_bf16, w, 4, dims, strides, half_box);
+          }))
+        plan.tmap_b = single;
+      gb::TapWalk& wk = p.walk;
+      wk.cblocks = g.c_out / epl; wk.n1 = ax.taps;
+      wk.grid_h = ay.count; wk.grid_w = ax.count;
+      wk.div_image = gb::make_fastdiv_host(ay.count * ax.count); wk.div_w = gb::make_fastdiv_host(ax.count);
+      wk.row_scale = 1;
+      wk.y0 = ax.off0; wk.z0 = ay.off0;
+      wk.y_step = wk.z_step = -(int32_t)(dil * tk / s);
+      wk.tap0 = (int32_t)(ay.k0 * g.k + ax.k0); wk.tap_x = (int32_t)tk; wk.tap_y = (int32_t)(tk * g.k);
+      gb::RowMap& rm = p.rowmap;
+      rm.enabled = 1;
+      rm.per_image = wk.div_image; rm.grid_w = wk.div_w;
+      rm.h = g.h; rm.w = g.w; rm.scale = s; rm.off_y = py; rm.off_x = px;
+    }
+  if (any_empty && !d->accumulate) {
+    // Pixels of a class without taps get no product; they are zero.  Only a dense dx can be cleared as a block.
+    if (g.c_step != g.c) return GB_ERR_UNSUPPORTED;
+    const cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)g.n * g.h * g.w * g.c * elem_size(d->dtype_x), stream);
+    if (e != cudaSuccess) return cuda_fail(h, e);
+  }
+  uint32_t launches = 0, items = 0;
+  for (Plan& plan : plans) {
+    const int rc = run_plan(h, stream, plan, nullptr, 0);
+    if (rc != GB_OK) return rc;
+    launches += h->last_plan.kernel_launches;
+    items += h->last_plan.work_items;
+  }
+  h->last_plan.kernel_launches = launches;
+  h->last_plan.work_items = items;
   return GB_OK;
 }
 
@@ -640,6 +760,10 @@ int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
   if (desc->w_layout != 0) return GB_ERR_UNSUPPORTED;   // the prepared filter copy is a forward-only format
+  if (desc->geo.stride > 1) {
+    rc = run_dgrad_classes(h, (cudaStream_t)stream, desc, dy, w, dx);
+    if (rc != GB_ERR_UNSUPPORTED) return rc;
+  }
   Plan plan;
   rc = plan_conv(h, 1, desc, dy, w, dx, nullptr, plan);
   if (rc != GB_OK) return rc;

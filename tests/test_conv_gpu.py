@@ -232,3 +232,42 @@ def test_forward_with_prepared_filter_rows(gpu, case, math, tol, half):
     gpu.convForward(to_dev(x, half), to_dev(np.ascontiguousarray(w.T), half), y, geo, math=math, w_rows=True)
     torch.cuda.synchronize()
     assert rel_fro(to_host(y), want) <= tol
+
+
+STRIDED = [
+    ((4, 32, 32, 64, 3, 128, 2, 1, 1), True),     # ResNet transition: four classes of 1, 2, 2 and 4 taps
+    ((4, 32, 32, 64, 1, 128, 2, 0, 1), True),     # 1x1 shortcut: three of the four classes have no tap and are zero
+    ((3, 16, 16, 128, 3, 256, 2, 1, 1), True),
+    ((2, 16, 16, 64, 3, 64, 2, 1, 2), True),      # dilation 2 under stride 2: all taps fall into one class per axis
+    ((2, 24, 24, 64, 3, 64, 3, 1, 1), True),      # stride 3: nine classes of one tap each
+    ((2, 16, 16, 64, 5, 64, 2, 2, 1), True),      # 5x5: classes of 3 and 2 taps per axis
+    ((2, 15, 15, 64, 3, 64, 2, 1, 1), False),     # odd image: a 7-wide class grid is no whole-row box -> gathered product
+]
+
+
+@pytest.mark.parametrize("case,by_classes", STRIDED)
+@pytest.mark.parametrize("math,tol,half", [(1, TOL_TF32, False), (2, TOL_BF16, True)])
+def test_strided_input_gradient_by_parity_classes(gpu, case, by_classes, math, tol, half):
+    """The input gradient of a strided layer runs as one patch product per parity class of input pixels when
+    dy and the filters are stored in the tile's type; it must equal the reference's single product
+    (src/gpu/math/conv.zig:105-130) on overwrite (stale contents, empty classes zeroed) and on accumulate."""
+    import torch
+    from oracle import binding as orc
+
+    d, x, w, dy = _inputs(case, 700)
+    geo = _geo(case)
+    w_used = to_host(to_dev(w, half)).astype(np.float32)     # the filters as the device sees them
+    dy_used = to_host(to_dev(dy, half)).astype(np.float32)
+    want = orc.conv_input_grad(dy_used, w_used, d, orc.host_threads())
+    act = torch.bfloat16 if half else torch.float32
+    gx = torch.full((d.n, d.h, d.w, d.c), 5.0, dtype=act, device="cuda")
+    gpu.convInputGrad(to_dev(dy, half), to_dev(w, half), gx, geo, accumulate=False, math=math)
+    plan = gpu.last_plan()
+    torch.cuda.synchronize()
+    assert rel_fro(to_host(gx), want) <= tol, (case, math, rel_fro(to_host(gx), want))
+    assert (plan["a_kind"] == 2) == by_classes, plan     # 2 = TMA patch boxes, 5 = gathered
+    gx32 = torch.full((d.n, d.h, d.w, d.c), 1.0, dtype=torch.float32, device="cuda")
+    if not half:
+        gpu.convInputGrad(to_dev(dy, half), to_dev(w, half), gx32, geo, accumulate=True, math=math)
+        torch.cuda.synchronize()
+        assert rel_fro(to_host(gx32) - 1.0, want) <= tol
