@@ -285,6 +285,7 @@ struct BoxLane {
   uint32_t i0, n0, i1, n1;
   int32_t ax, ay, az, aw, bx, by, bz, bw, cx, cy, cz, cw;
   FastDiv per_image, grid_w;   // patch boxes: tile row -> (image, image row)
+  uint32_t tap;                // column-patch stages: the tap (along y) whose B tile this box fills
 };
 constexpr uint32_t kNever = 0xFFFFFFFFu;
 
@@ -297,13 +298,18 @@ __device__ __forceinline__ uint32_t boxes_of(uint32_t kind, uint32_t lines, uint
 __device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint32_t lane, const CUtensorMap* tmap_a, const CUtensorMap* tmap_b,
                                           uint32_t b_lines, uint32_t& kind, uint32_t& index) {
   const int32_t epl = p.tf32 ? 32 : 64;
-  const uint32_t na = boxes_of(p.a_kind, kBM, epl), nb = boxes_of(p.b_kind, b_lines, epl);
+  const uint32_t nb_tap = boxes_of(p.b_kind, b_lines, epl);                   // B boxes of one tap
+  const uint32_t na = boxes_of(p.a_kind, kBM, epl), nb = nb_tap * max(p.col_taps, 1u);
   b.active = lane < na + nb;
   const bool is_b = lane >= na;
   index = is_b ? lane - na : lane;
   kind = is_b ? p.b_kind : p.a_kind;
   b.tmap = is_b ? tmap_b : tmap_a;
-  b.smem_off = (is_b ? kATileBytes : 0u) + index * epl * kLineBytes;
+  const uint32_t a_bytes = p.a_stage_bytes ? p.a_stage_bytes : kATileBytes;
+  const uint32_t b_tap = p.col_taps ? index / max(nb_tap, 1u) : 0u;           // which tap's B tile this box fills
+  b.tap = b_tap;
+  if (p.col_taps && is_b) index -= b_tap * nb_tap;
+  b.smem_off = (is_b ? a_bytes + b_tap * b_lines * kLineBytes : 0u) + index * epl * kLineBytes;
   b.n0 = b.n1 = kNever;
   b.i0 = b.i1 = 0;
   b.ax = b.ay = b.az = b.aw = b.bx = b.by = b.bz = b.bw = b.cx = b.cy = b.cz = b.cw = 0;
@@ -313,6 +319,16 @@ __device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint3
   if (kind == kPatchK) {
     b.per_image = p.walk.div_image;
     b.grid_w = p.walk.div_w;
+  }
+  if (p.col_taps && is_b) {
+    // B of a column-patch plan: channel blocks innermost, then the next tap column; the tap along y is fixed.
+    const int32_t cblocks = (int32_t)p.walk.cblocks, chan = cblocks * epl;
+    b.n0 = p.walk.cblocks;
+    const int32_t next_col = p.walk.tap_x * chan - (cblocks - 1) * epl;
+    if (kind == kDenseK) { b.ax = epl; b.bx = next_col; }
+    if (kind == kDenseMN) { b.ay = epl; b.by = next_col; }
+    if (kind == kWeightK) { b.ax = epl; b.bx = -(cblocks - 1) * epl; b.bz = p.walk.tap_x; }
+    return;
   }
   switch (kind) {
     case kDenseK: b.ax = epl; break;
@@ -357,6 +373,22 @@ __device__ __forceinline__ void box_start(const GemmParams& p, BoxLane& b, uint3
   const uint32_t k0 = work.kb_begin;
   b.i0 = b.i1 = 0;
   b.w = 0;
+  if (p.col_taps) {   // column-patch plans never split K: every tile starts at the first tap column
+    const int32_t tap = p.walk.tap0 + (int32_t)b.tap * p.walk.tap_y, chan = (int32_t)(p.walk.cblocks * epl);
+    if (!is_b) {
+      const uint32_t img = fast_div(mn0, b.per_image);
+      const int32_t row0 = (int32_t)fast_div(mn0 - img * b.per_image.d, b.grid_w);
+      const int32_t top = p.walk.z_step < 0 ? p.walk.z0 + ((int32_t)p.col_taps - 1) * p.walk.z_step : p.walk.z0;
+      b.x = 0; b.y = p.walk.y0; b.z = row0 + top; b.w = (int32_t)img;
+    } else if (kind == kDenseK) {
+      b.x = tap * chan; b.y = (int32_t)mn0; b.z = 0;
+    } else if (kind == kDenseMN) {
+      b.x = (int32_t)(mn0 + index * epl); b.y = tap * chan; b.z = 0;
+    } else {
+      b.x = 0; b.y = (int32_t)mn0; b.z = tap;
+    }
+    return;
+  }
   switch (kind) {
     case kDenseK:
       b.x = (int32_t)(k0 * epl); b.y = (int32_t)mn0; b.z = (int32_t)work.batch;
@@ -775,7 +807,8 @@ struct MmaSetup {
   uint64_t a_desc0, b_desc0;        // descriptors of stage 0, slice 0
 };
 
-__device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t tile_rows, uint32_t instr_n, uint32_t tiles_addr, uint32_t stage_bytes) {
+__device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t tile_rows, uint32_t instr_n, uint32_t tiles_addr, uint32_t stage_bytes,
+                                                   uint32_t a_bytes) {
   const uint32_t epl = p.tf32 ? 32u : 64u;
   // K-major: the four K slices of a stage sit 32 bytes apart inside each line.  MN-major: a slice is 16
   // (bf16) or 8 (tf32) whole lines, and 64-/32-wide MN blocks follow each other every epl lines.
@@ -791,14 +824,15 @@ __device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t
   s.b_step16 = b_step >> 4;
   s.stage16 = stage_bytes >> 4;
   s.a_desc0 = make_smem_desc(tiles_addr, a_lbo, a_sbo, a_mode);
-  s.b_desc0 = make_smem_desc(tiles_addr + kATileBytes, b_lbo, b_sbo, b_mode);
+  s.b_desc0 = make_smem_desc(tiles_addr + a_bytes, b_lbo, b_sbo, b_mode);
   return s;
 }
 
 // Issues the four K slices of one stage.
 template <bool kPair, bool kTf32>
-__device__ __forceinline__ void mma_stage(const MmaSetup& s, uint32_t tmem_d, uint32_t stage, uint32_t first_accumulate, uint32_t b_extra16 = 0) {
-  const uint64_t da = s.a_desc0 + (uint64_t)(stage * s.stage16);
+__device__ __forceinline__ void mma_stage(const MmaSetup& s, uint32_t tmem_d, uint32_t stage, uint32_t first_accumulate, uint32_t b_extra16 = 0,
+                                          uint32_t a_extra16 = 0) {
+  const uint64_t da = s.a_desc0 + (uint64_t)(stage * s.stage16 + a_extra16);
   const uint64_t db = s.b_desc0 + (uint64_t)(stage * s.stage16 + b_extra16);
   mma_issue<kPair, kTf32>(tmem_d, da, db, s.idesc, first_accumulate);
   mma_issue<kPair, kTf32>(tmem_d, da + s.a_step16, db + s.b_step16, s.idesc, 1u);
@@ -815,7 +849,8 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   SmemHeader* hdr = (SmemHeader*)smem;
   uint8_t* tiles = smem + kHeaderBytes;
   const uint32_t b_tile_bytes = p.bn * kLineBytes;
-  const uint32_t stage_bytes = kATileBytes + b_tile_bytes;
+  const uint32_t a_bytes = p.a_stage_bytes ? p.a_stage_bytes : kATileBytes, b_tiles = max(p.col_taps, 1u);
+  const uint32_t stage_bytes = a_bytes + b_tiles * b_tile_bytes;
   volatile uint32_t* abort_flag = &hdr->abort_flag;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -851,8 +886,8 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 
   if (warp == 0) {
     // ===== TMA producer: one lane per box =====
-    const uint32_t tx_bytes = (p.a_kind != kGather ? kATileBytes : 0u) + (p.b_kind != kGather ? b_tile_bytes : 0u);
-    const uint32_t n_boxes = boxes_of(p.a_kind, kBM, epl) + boxes_of(p.b_kind, p.bn, epl);
+    const uint32_t tx_bytes = (p.a_kind != kGather ? (p.col_taps ? p.a_box_bytes : kATileBytes) : 0u) + (p.b_kind != kGather ? b_tiles * b_tile_bytes : 0u);
+    const uint32_t n_boxes = boxes_of(p.a_kind, kBM, epl) + b_tiles * boxes_of(p.b_kind, p.bn, epl);
     if (lane < max(n_boxes, 1u)) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
@@ -883,7 +918,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     // The issuing thread is chosen with elect.sync, not `lane == 0`: the compiler then keeps descriptors and
     // addresses in uniform registers, and one tcgen05.mma costs ~40-48 issue cycles instead of ~92.
     if (elect_one()) {
-      const MmaSetup ms = make_mma_setup(p, kBM, p.bn, smem_u32(tiles), stage_bytes);
+      const MmaSetup ms = make_mma_setup(p, kBM, p.bn, smem_u32(tiles), stage_bytes, a_bytes);
       uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
       uint32_t ready = 0;   // the first stage is waited for in the ordinary way
@@ -899,7 +934,13 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           const bool more = kb + 1 < work.kb_end || w + gridDim.x < total_work;
           ready = more ? mbar_try_wait(&hdr->full[next_stage], next_phase) : 0u;
           tc_fence_after_sync();
-          if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, kb > work.kb_begin);
+          if (p.col_taps) {
+            for (uint32_t t = 0; t < p.col_taps; ++t) {
+              const uint32_t a16 = (uint32_t)(p.col_a_first16 + (int32_t)t * p.col_a_step16), b16 = t * (b_tile_bytes >> 4);
+              if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, (kb > work.kb_begin) | (t > 0), b16, a16);
+              else mma_stage<false, false>(ms, tmem_d, stage, (kb > work.kb_begin) | (t > 0), b16, a16);
+            }
+          } else if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, kb > work.kb_begin);
           else mma_stage<false, false>(ms, tmem_d, stage, kb > work.kb_begin);
           mma_commit(&hdr->empty[stage]);
           stage = next_stage;
@@ -996,7 +1037,8 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
   const uint32_t halves = p.bn > 256 ? 2u : 1u, bufs = halves == 2 ? 1u : 2u;
   const uint32_t b_lines = p.bn / 2;                 // this CTA's share of the B tile
   const uint32_t b_tile_bytes = b_lines * kLineBytes;
-  const uint32_t stage_bytes = kATileBytes + b_tile_bytes;
+  const uint32_t a_bytes = p.a_stage_bytes ? p.a_stage_bytes : kATileBytes, b_tiles = max(p.col_taps, 1u);
+  const uint32_t stage_bytes = a_bytes + b_tiles * b_tile_bytes;
   volatile uint32_t* abort_flag = &hdr->abort_flag;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1036,8 +1078,8 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     // copies against the leader's barrier.  (A cluster-scope release arrive from each producer made every K
     // block wait for the previous block's copies: 1 us per block.)  The partner cannot run a phase ahead:
     // its stage is freed by the leader's commit, which follows the end of the phase.
-    const uint32_t tx_bytes = kATileBytes + b_tile_bytes;
-    const uint32_t n_boxes = boxes_of(p.a_kind, kBM, epl) + boxes_of(p.b_kind, b_lines, epl);
+    const uint32_t tx_bytes = (p.col_taps ? p.a_box_bytes : kATileBytes) + b_tiles * b_tile_bytes;
+    const uint32_t n_boxes = boxes_of(p.a_kind, kBM, epl) + b_tiles * boxes_of(p.b_kind, b_lines, epl);
     if (lane < n_boxes) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
@@ -1066,7 +1108,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
   } else if (warp == 1) {
     // ===== MMA issuer (leader CTA only) =====
     if (rank == 0 && elect_one()) {
-      const MmaSetup ms = make_mma_setup(p, 2 * kBM, p.bn / halves, smem_u32(tiles), stage_bytes);
+      const MmaSetup ms = make_mma_setup(p, 2 * kBM, p.bn / halves, smem_u32(tiles), stage_bytes, a_bytes);
       const uint32_t acc_stride = p.bn / halves;
       uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
@@ -1083,7 +1125,13 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
           const bool more = kb + 1 < work.kb_end || w + pairs < total_work;
           ready = more ? mbar_try_wait(&hdr->full[next_stage], next_phase) : 0u;
           tc_fence_after_sync();
-          if (p.tf32) mma_stage<true, true>(ms, tmem_d, stage, kb > work.kb_begin);
+          if (p.col_taps) {
+            for (uint32_t t = 0; t < p.col_taps; ++t) {
+              const uint32_t a16 = (uint32_t)(p.col_a_first16 + (int32_t)t * p.col_a_step16), b16 = t * (b_tile_bytes >> 4);
+              if (p.tf32) mma_stage<true, true>(ms, tmem_d, stage, (kb > work.kb_begin) | (t > 0), b16, a16);
+              else mma_stage<true, false>(ms, tmem_d, stage, (kb > work.kb_begin) | (t > 0), b16, a16);
+            }
+          } else if (p.tf32) mma_stage<true, true>(ms, tmem_d, stage, kb > work.kb_begin);
           else mma_stage<true, false>(ms, tmem_d, stage, kb > work.kb_begin);
           if (halves == 2) {   // second half: 128 B lines (16 KB) further on, 256 TMEM columns further on
             if (p.tf32) mma_stage<true, true>(ms, tmem_d + 256, stage, kb > work.kb_begin, (128 * kLineBytes) >> 4);
@@ -1166,7 +1214,8 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
 
 size_t gemm_smem_bytes(const GemmParams& p) {
   const size_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
-  return 1024 /* alignment slack */ + kHeaderBytes + (size_t)p.stages * (kATileBytes + b_lines * kLineBytes) +
+  return 1024 /* alignment slack */ + kHeaderBytes +
+         (size_t)p.stages * ((p.a_stage_bytes ? p.a_stage_bytes : kATileBytes) + (p.col_taps ? p.col_taps : 1u) * b_lines * kLineBytes) +
          (p.tma_store ? kStoreSmemBytes : 0);
 }
 

@@ -51,7 +51,7 @@ inline FastDiv make_fastdiv_host(uint32_t d) { return FastDiv{d ? d : 1u, 0xFFFF
 // blocks innermost, then `n1` taps along x, then the taps along y.  A forward pass, a stride-1 input gradient
 // and one parity class of a strided input gradient differ only in these numbers.
 struct TapWalk {
-  uint32_t cblocks, n1;        // channel blocks per tap; taps along x
+  uint32_t cblocks, n1, n2;    // channel blocks per tap; taps along x; taps along y
   uint32_t grid_h, grid_w;     // a tile's rows enumerate (image, i, j) over this grid
   FastDiv div_image, div_w;    // dividers by grid_h * grid_w and by grid_w
   uint32_t row_scale;          // patch row of grid row i at the first tap: i * row_scale + z0
@@ -84,6 +84,14 @@ struct GemmParams {
   ConvGeo geo;
   uint32_t dgrad;           // 1: patches are taken from dy with flipped taps (input gradient)
   TapWalk walk;             // K walk of patch / filter-tap boxes
+  // Column-patch stages (col_taps > 0): one stage holds, for one (tap column, channel block), the activation
+  // rows that ALL col_taps taps of that column read -- box_h + (col_taps - 1) * |row step| image rows in one
+  // box -- and one B tile per tap; tap t's A operand starts col_a_first16 + t * col_a_step16 (bytes >> 4)
+  // into the A part.  K blocks then count (tap column, channel block) pairs.
+  uint32_t col_taps;
+  uint32_t a_stage_bytes;   // A part of a stage (multiple of 1024); 0 means the plain 16 KB tile
+  uint32_t a_box_bytes;     // bytes the A box really delivers
+  int32_t col_a_first16, col_a_step16;
   RowMap rowmap;            // output row placement (disabled: row m of C)
   // gather sources
   GatherDesc ga, gbsrc;

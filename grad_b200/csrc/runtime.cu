@@ -342,8 +342,9 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
   if (plan.tensor) {
     // The stage ring takes what the epilogue's own shared memory leaves of the 227 KB a CTA can have.
     const uint32_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
-    const size_t fixed = gb::gemm_smem_bytes(p) - (size_t)p.stages * (128 * 128 + b_lines * 128);
-    const uint32_t fit = (uint32_t)((227 * 1024 - fixed) / (128 * 128 + b_lines * 128));
+    const size_t stage = (p.a_stage_bytes ? p.a_stage_bytes : 128 * 128) + (size_t)std::max(p.col_taps, 1u) * b_lines * 128;
+    const size_t fixed = gb::gemm_smem_bytes(p) - (size_t)p.stages * stage;
+    const uint32_t fit = (uint32_t)((227 * 1024 - fixed) / stage);
     p.stages = std::max(2u, std::min(p.stages, fit));
   }
   info.stages = p.stages;
@@ -423,7 +424,7 @@ bool nhwc_tma(CUtensorMap* map, const void* base, bool smem_bf16, uint32_t dtype
 
 // K walk of the patch boxes of a forward pass (taps in storage order, patch origin at -pad).
 void walk_forward(gb::TapWalk& wk, const gb::ConvGeo& g, uint32_t epl) {
-  wk.cblocks = std::max(1u, g.c / epl); wk.n1 = g.k;
+  wk.cblocks = std::max(1u, g.c / epl); wk.n1 = g.k; wk.n2 = g.k;
   wk.grid_h = g.out_h; wk.grid_w = g.out_w;
   wk.div_image = gb::make_fastdiv_host(g.out_h * g.out_w); wk.div_w = gb::make_fastdiv_host(g.out_w);
   wk.row_scale = g.stride;
@@ -434,13 +435,48 @@ void walk_forward(gb::TapWalk& wk, const gb::ConvGeo& g, uint32_t epl) {
 
 // K walk of a stride-1 input gradient: dy patches with mirrored tap offsets, filter taps in storage order.
 void walk_dgrad_unit(gb::TapWalk& wk, const gb::ConvGeo& g, uint32_t epl) {
-  wk.cblocks = std::max(1u, g.c_out / epl); wk.n1 = g.k;
+  wk.cblocks = std::max(1u, g.c_out / epl); wk.n1 = g.k; wk.n2 = g.k;
   wk.grid_h = g.h; wk.grid_w = g.w;
   wk.div_image = gb::make_fastdiv_host(g.h * g.w); wk.div_w = gb::make_fastdiv_host(g.w);
   wk.row_scale = 1;
   wk.y0 = wk.z0 = (int32_t)g.pad;
   wk.y_step = wk.z_step = -(int32_t)g.dilation;
   wk.tap0 = 0; wk.tap_x = 1; wk.tap_y = (int32_t)g.k;
+}
+
+// Switches a planned patch product to column-patch stages when its geometry allows: the tile is whole rows of
+// one image, patch rows step one image row per output row, every operand arrives by TMA, K is not split, and
+// a tap's row offset keeps the 1024-byte swizzle atoms of the A part aligned (box width x row step a multiple of
+// eight lines).  One stage then serves all taps of a tap column: a third as many stages, barrier round trips
+// and producer iterations per tile for a 3x3 filter, and (box_h + 2) / (3 * box_h) of the activation bytes.
+// `encode_a(rows)` re-encodes the activation map for a box of `rows` image rows.
+template <class EncodeA>
+void try_column_stages(Plan& plan, EncodeA encode_a) {
+  GemmParams& p = plan.p;
+  if (getenv("GB_NO_COLUMN_STAGES")) return;
+  const gb::TapWalk& wk = p.walk;
+  if (!plan.tensor || p.a_kind != gb::kPatchK || p.b_kind == gb::kGather || p.splits != 1 || p.box_n != 1 || p.bn > 256) return;
+  if (wk.n2 < 2 || wk.n2 > 7 || wk.row_scale != 1 || wk.z_step == 0) return;
+  const uint32_t row_step = (uint32_t)std::abs(wk.z_step), epl = p.tf32 ? 32 : 64;
+  if ((p.box_w * row_step) % 8 != 0) return;
+  const uint32_t rows = p.box_h + (wk.n2 - 1) * row_step;
+  if (rows > 256) return;
+  const uint32_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
+  const uint32_t boxes_b = (p.b_kind == gb::kDenseMN ? b_lines / epl : 1u) * wk.n2;
+  if (1 + boxes_b > 32) return;
+  const uint32_t a_box = rows * p.box_w * 128, a_stage = (a_box + 1023) & ~1023u;
+  const size_t stage = a_stage + (size_t)wk.n2 * b_lines * 128;
+  const size_t room = 227 * 1024 - 2048 - gb::kStoreSmemBytes;
+  if (room / stage < 3) return;
+  if (!encode_a(rows)) return;
+  p.col_taps = wk.n2;
+  p.a_stage_bytes = a_stage;
+  p.a_box_bytes = a_box;
+  p.col_a_step16 = wk.z_step * (int32_t)(p.box_w * 8);
+  p.col_a_first16 = wk.z_step < 0 ? (int32_t)((wk.n2 - 1) * row_step * p.box_w * 8) : 0;
+  p.k_blocks_total = wk.n1 * wk.cblocks;
+  p.k_blocks_per_split = p.k_blocks_total;
+  p.stages = (uint32_t)std::min<size_t>(8, room / stage);
 }
 
 int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* act, const void* other, void* out,
@@ -485,6 +521,10 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       CUtensorMap single = plan.tmap_b;
       if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }))
         plan.tmap_b = single;
+      if (g.stride == 1)
+        try_column_stages(plan, [&](uint32_t rows) {
+          return nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, rows, 1);
+        });
     }
   } else if (pass == 1) {
     // dx[pixels, c] = patchesT(dy)[pixels, taps*c_out] * wT[taps*c_out, c]
@@ -517,6 +557,9 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
               return encode_map(&plan.tmap_b, smem_bf16, other, 4, dims, strides, half_box);
             }))
           plan.tmap_b = single;
+        try_column_stages(plan, [&](uint32_t rows) {
+          return nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_y, g.c_out, g.c_out, g.out_w, g.out_h, g.n, epl, p.box_w, rows, 1);
+        });
       }
     }
   } else {
@@ -607,7 +650,7 @@ int run_dgrad_classes(gb_handle* h, cudaStream_t stream, const gb_conv_desc* d, 
           }))
         plan.tmap_b = single;
       gb::TapWalk& wk = p.walk;
-      wk.cblocks = g.c_out / epl; wk.n1 = ax.taps;
+      wk.cblocks = g.c_out / epl; wk.n1 = ax.taps; wk.n2 = ay.taps;
       wk.grid_h = ay.count; wk.grid_w = ax.count;
       wk.div_image = gb::make_fastdiv_host(ay.count * ax.count); wk.div_w = gb::make_fastdiv_host(ax.count);
       wk.row_scale = 1;
