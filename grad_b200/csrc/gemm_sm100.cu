@@ -735,14 +735,22 @@ __device__ __forceinline__ void stage_bias(const GemmParams& p, float* sbias, ui
 
 // Drains one accumulator of `ncols` columns: TMEM reads are double-buffered in registers (the next 32 columns
 // are in flight while the current ones are processed) and the bias slice is fetched one chunk ahead.
-// `wide` selects the column order of a two-half tile (see the pair kernel).
+// `wide` selects the column order of a two-half tile (see the pair kernel).  `release()` hands the accumulator
+// back to the MMA issuer; it is called as soon as this warp's last TMEM read has landed in registers, before
+// that chunk's arithmetic and stores: with short-K tiles (a convolution layer) the time from "accumulator
+// full" to "accumulator free" is what paces the kernel.
+template <class Release>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, uint32_t ncols, uint32_t batch, uint32_t split,
                                               uint32_t row, uint32_t col_base, bool wide, uint32_t lane,
-                                              uint32_t first, uint32_t step, const CUtensorMap* tmap_c, uint8_t* store_stage, const float* sbias) {
+                                              uint32_t first, uint32_t step, const CUtensorMap* tmap_c, uint8_t* store_stage, const float* sbias,
+                                              Release release) {
+  if (first >= ncols) {
+    release();
+    return;
+  }
   if (p.tma_store && p.splits == 1) {
     // Chunks that lie wholly inside C and rows that begin inside it go through the TMA store; a ragged last
     // chunk takes the guarded scalar path with its bias read back from the staged values.
-    if (first >= ncols) return;
     auto tile_col = [&](uint32_t c) { return wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c; };
     uint32_t acc_a[32], acc_b[32];
     tmem_ld_32x32(taddr + first, acc_a);
@@ -751,6 +759,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
       const bool has_b = c + step < ncols;
       tmem_ld_wait();
       if (has_b) tmem_ld_32x32(taddr + c + step, acc_b);
+      else release();
       {
         const uint32_t col0 = col_base + tile_col(c);
         if (col0 + 32 <= p.n && row - lane < p.m) epilogue_chunk_tma(p, tmap_c, acc_a, store_stage, sbias + 32 * i, batch, row, col0, lane);
@@ -759,6 +768,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
       if (has_b) {
         tmem_ld_wait();
         if (c + 2 * step < ncols) tmem_ld_32x32(taddr + c + 2 * step, acc_a);
+        else release();
         const uint32_t col0 = col_base + tile_col(c + step);
         if (col0 + 32 <= p.n && row - lane < p.m) epilogue_chunk_tma(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), batch, row, col0, lane);
         else epilogue_chunk_copy(p, acc_b, batch, split, row, col0, p.bias ? sbias[32 * (i + 1) + lane] : 0.0f);
@@ -772,7 +782,6 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     return (p.bias != nullptr && c < ncols && col < p.n) ? p.bias[col] : 0.0f;
   };
   // This warp drains the 32-column chunks first, first + step, ...; two chunks are in flight (A and B registers).
-  if (first >= ncols) return;
   const uint64_t row_off = out_row_offset(p, row);
   uint32_t acc_a[32], acc_b[32];
   float bias_next = bias_at(first);
@@ -781,12 +790,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     const bool has_b = c + step < ncols;
     tmem_ld_wait();
     if (has_b) tmem_ld_32x32(taddr + c + step, acc_b);
+    else release();
     float bias_cur = bias_next;
     bias_next = bias_at(c + step);
     epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur, row_off);
     if (has_b) {
       tmem_ld_wait();
       if (c + 2 * step < ncols) tmem_ld_32x32(taddr + c + 2 * step, acc_a);
+      else release();
       bias_cur = bias_next;
       bias_next = bias_at(c + 2 * step);
       epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur, row_off);
@@ -961,9 +972,13 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     uint8_t* store_stage = epi_smem + (warp - 2) * kStoreStageBytesPerWarp;
     float* sbias = (float*)(epi_smem + 8 * kStoreStageBytesPerWarp + (warp - 2) * kStoreBiasBytesPerWarp);
     if (tma_out && warp == 2 && lane == 0) prefetch_tmap(&tmap_c);
+    uint32_t bias_tile = 0xFFFFFFFFu;   // the column tile whose bias values sit in shared memory
     for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       const Work work = decode_work(p, w);
-      if (tma_out) stage_bias(p, sbias, p.bn, work.n_tile * p.bn, false, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
+      if (tma_out && bias_tile != work.n_tile) {
+        stage_bias(p, sbias, p.bn, work.n_tile * p.bn, false, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
+        bias_tile = work.n_tile;
+      }
       ok = mbar_wait(&hdr->acc_full[buf], buf_phase, abort_flag, kStatusEpilogueTimeout);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
@@ -971,10 +986,11 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       const uint32_t row = work.m_tile * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
       epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane,
-                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias);
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&hdr->acc_empty[buf]);
+                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, [&] {
+                                                 tc_fence_before_sync();
+                                                 __syncwarp();
+                                                 if (lane == 0) mbar_arrive(&hdr->acc_empty[buf]);
+                                               });
       if ((buf ^= 1) == 0) buf_phase ^= 1;
     }
     if (tma_out && lane == 0) bulk_wait_all();   // the staging block must outlive its last store
@@ -1157,9 +1173,13 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     uint8_t* store_stage = epi_smem + (warp - 2) * kStoreStageBytesPerWarp;
     float* sbias = (float*)(epi_smem + 8 * kStoreStageBytesPerWarp + (warp - 2) * kStoreBiasBytesPerWarp);
     if (tma_out && warp == 2 && lane == 0) prefetch_tmap(&tmap_c);
+    uint32_t bias_tile = 0xFFFFFFFFu;   // the column tile whose bias values sit in shared memory
     for (uint32_t w = pair; ok && w < total_work; w += pairs) {
       const Work work = decode_work(p, w);
-      if (tma_out) stage_bias(p, sbias, p.bn, work.n_tile * p.bn, halves == 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
+      if (tma_out && bias_tile != work.n_tile) {
+        stage_bias(p, sbias, p.bn, work.n_tile * p.bn, halves == 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
+        bias_tile = work.n_tile;
+      }
       ok = mbar_wait(&hdr->acc_full[buf], buf_phase, abort_flag, kStatusEpilogueTimeout);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
@@ -1167,10 +1187,11 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       const uint32_t row = work.m_tile * 2 * kBM + rank * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * (p.bn / halves);
       epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane,
-                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias);
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->acc_empty[buf]), 0));
+                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, [&] {
+                                                 tc_fence_before_sync();
+                                                 __syncwarp();
+                                                 if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->acc_empty[buf]), 0));
+                                               });
       if (++buf == bufs) { buf = 0; buf_phase ^= 1; }
     }
     if (tma_out && lane == 0) bulk_wait_all();   // the staging block must outlive its last store
