@@ -43,6 +43,11 @@ def parse_args():
     ap.add_argument("--layout", default="NN", choices=["NN", "NT", "TN"])
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-resnet", action="store_true", help="skip the ResNet-14 inference and convolution-layer parts (small profiler captures)")
+    ap.add_argument("--profile-resnet", type=int, default=0, metavar="BATCH",
+                    help="run only three eager ResNet-14 inference passes at this batch and exit (launch lists under a profiler)")
+    ap.add_argument("--profile-conv", default="", metavar="N,H,W,C,K,COUT,STRIDE,PAD",
+                    help="run only six forward launches of this bf16 convolution layer (bias + ReLU fused) and exit")
     return ap.parse_args()
 
 
@@ -199,6 +204,79 @@ def resnet_inference(gpu, rank, world, dist, torch):
     return out
 
 
+def conv_layers(gpu, torch):
+    """Kernel times of the ResNet-14 convolution layers at batch 128 (bf16 storage, f32 accumulation), all three
+    passes, each taken from the replay of a CUDA graph of 20 launches so that host cost does not enter."""
+    from grad_b200 import Epilogue, conv_geometry
+
+    def graph_ms(fn, calls=20, reps=5):
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(calls):
+                    fn()
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (reps * calls)
+
+    n = 128
+    layers = (("64->64 3x3 @32", 32, 64, 3, 64, 1), ("64->192 3x3 s2 @32", 32, 64, 3, 192, 2), ("192->192 3x3 @16", 16, 192, 3, 192, 1),
+              ("192->384 3x3 s2 @16", 16, 192, 3, 384, 2), ("384->384 3x3 @8", 8, 384, 3, 384, 1), ("64->192 1x1 s2 @32", 32, 64, 1, 192, 2))
+    gen = torch.Generator(device="cuda").manual_seed(1234 + 2)
+    rows = []
+    for name, hw, c, k, co, stride in layers:
+        geo = conv_geometry(n, hw, hw, c, k, co, stride, k // 2)
+        x = torch.randn((n, hw, hw, c), generator=gen, device="cuda").bfloat16()
+        w = (torch.randn((k * k * c, co), generator=gen, device="cuda") * (2.0 / (k * k * c)) ** 0.5).bfloat16()
+        dy = torch.randn((n, geo.out_h, geo.out_w, co), generator=gen, device="cuda").bfloat16()
+        y, dx = torch.empty_like(dy), torch.empty_like(x)
+        dw = torch.zeros((k * k * c, co), device="cuda")
+        bias = torch.randn(co, generator=gen, device="cuda")
+        flop = 2.0 * geo.positions * k * k * c * co
+        row = {"layer": name, "batch": n, "gflop": round(flop / 1e9, 2)}
+        for key, fn in (("fprop", lambda: gpu.convForward(x, w, y, geo, epilogue=Epilogue(bias, None, True))),
+                        ("dgrad", lambda: gpu.convInputGrad(dy, w, dx, geo)), ("wgrad", lambda: gpu.convWeightGrad(dy, x, dw, geo))):
+            ms = graph_ms(fn)
+            row[key] = {"us": round(ms * 1e3, 1), "tflops": round(flop / ms / 1e9, 1)}
+        rows.append(row)
+    return rows
+
+
+def profile_only(args, gpu, torch):
+    """Small fixed workloads for profiler captures; nothing is timed or printed as a bench line."""
+    from grad_b200 import Epilogue, conv_geometry
+
+    if args.profile_resnet:
+        from grad_b200.onnx_gpu import Executor, resnet14_model
+
+        ex = Executor(resnet14_model(64, 192, 384), gpu, "bf16")
+        x = torch.randn((args.profile_resnet, 3072), device="cuda")
+        for _ in range(3):
+            ex.run_device({"input": x})
+    else:
+        n, h, w_, c, k, co, stride, pad = (int(v) for v in args.profile_conv.split(","))
+        geo = conv_geometry(n, h, w_, c, k, co, stride, pad)
+        x = torch.randn((n, h, w_, c), device="cuda").bfloat16()
+        w = (torch.randn((k * k * c, co), device="cuda") * (2.0 / (k * k * c)) ** 0.5).bfloat16()
+        y = torch.empty((n, geo.out_h, geo.out_w, co), dtype=torch.bfloat16, device="cuda")
+        bias = torch.randn(co, device="cuda")
+        for _ in range(6):
+            gpu.convForward(x, w, y, geo, epilogue=Epilogue(bias, None, True))
+    torch.cuda.synchronize()
+    gpu.check_status()
+    print(json.dumps({"profile_only": True, "plan": gpu.last_plan()}), flush=True)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -216,6 +294,10 @@ def run_ours(args):
     from grad_b200 import Epilogue, MatmulOpts, MatmulShape
 
     gpu = grad_b200.Gpu(local)
+    if args.profile_resnet or args.profile_conv:
+        if rank == 0:
+            profile_only(args, gpu, torch)
+        return
     size = args.size
     m = n = k = size
     ta, tb = args.layout == "TN", args.layout == "NT"
@@ -290,7 +372,8 @@ def run_ours(args):
     h2d = ha.numel() * 2 + hb.numel() * 2
     d2h = hout.numel() * 2
 
-    resnet = resnet_inference(gpu, rank, world, dist, torch)
+    resnet = None if args.no_resnet else resnet_inference(gpu, rank, world, dist, torch)
+    convs = conv_layers(gpu, torch) if (rank == 0 and not args.no_resnet) else None
 
     if rank != 0:
         if world > 1:
@@ -321,9 +404,12 @@ def run_ours(args):
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": peak, "unit": UNIT, "frac": round(achieved / peak, 4),
                      "traffic": traffic, "peak_source": f"{peak_kind} cuBLAS bf16 {'sustained' if sustained else 'burst'}",
-                     "frac_of_nominal_2250": round(achieved / 2250.0, 4)},
+                     "frac_of_nominal_2250": round(achieved / 2250.0, 4),
+                     "frac_of_measured_sustained": round(achieved / peaks["bf16_tflops_sustained"], 4)},
     }
-    line["resnet14_inference"] = resnet
+    if resnet is not None:
+        line["resnet14_inference"] = resnet
+        line["conv_layers"] = convs
     if world == 1 and not args.no_cpu_baseline:
         rows = 4096 if size >= 4096 else size
         cpu_value, cores, secs = cpu_sample(size, rows, 2)
