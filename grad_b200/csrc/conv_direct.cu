@@ -1,0 +1,138 @@
+// Forward convolution of a layer with very few input channels (the 3-channel stem of ResNet-14: K = 3*3*3 = 27).
+// Such a layer is no tensor-core shape: K fills less than half of one 64-wide K block, its input rows are 6 bytes
+// apart (no TMA box can start there), and the gather warps of the contraction kernel spent ~12 us per 128-row
+// tile building a mostly-zero operand tile -- a fifth of a whole ResNet-14 inference pass.  Here one thread
+// owns one output position and accumulates 32 output channels at a time in registers with FMAs; the filters
+// sit in shared memory as f32 and every lane reads the same 16 bytes of them (a broadcast).  The products are
+// those of the tensor path: operands rounded to bf16 (GB_MATH_BF16) or to TF32 (GB_MATH_TF32), f32
+// accumulation, then the same epilogue (old value, bias, residual, ReLU, rounding).  Follows the per-position
+// definition in grad's src/gpu/math/conv.zig:47-65 (`patchOf`, `patchSource`) and :84-103 (forward).
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gemm_sm100.cuh"
+#include "sm100_ptx.cuh"
+
+namespace gb {
+
+namespace {
+
+constexpr uint32_t kCoChunk = 32;   // output channels a thread accumulates at a time
+
+__device__ __forceinline__ float round_operand(float v, uint32_t tf32) {
+  return tf32 ? round_tf32(v) : bf16_to_f32((uint16_t)bf16_bits(v));
+}
+
+// Dynamic shared memory: filters as f32 [taps * c][c_out], already rounded to the operand type.
+__global__ void __launch_bounds__(128) conv_direct_kernel(const GemmParams p) {
+  extern __shared__ float w_s[];
+  const ConvGeo& g = p.geo;
+  const uint32_t kk = g.k * g.k * g.c;
+  for (uint32_t i = threadIdx.x; i < kk * g.c_out; i += blockDim.x) {
+    const uint32_t row = i / g.c_out, co = i - row * g.c_out;
+    const uint64_t idx = p.gbsrc.mn_major ? (uint64_t)row * p.gbsrc.ld + co : (uint64_t)co * p.gbsrc.ld + row;   // (K, c_out) or (c_out, K) rows
+    const float v = p.gbsrc.src_is_bf16 ? bf16_to_f32(((const uint16_t*)p.gbsrc.base)[idx]) : ((const float*)p.gbsrc.base)[idx];
+    w_s[i] = round_operand(v, p.tf32);
+  }
+  __syncthreads();
+  const uint32_t per_image = g.out_h * g.out_w;
+  for (uint32_t pos = blockIdx.x * blockDim.x + threadIdx.x; pos < p.m; pos += gridDim.x * blockDim.x) {
+    const uint32_t img = pos / per_image, rem = pos - img * per_image;
+    const uint32_t oy = rem / g.out_w, ox = rem - oy * g.out_w;
+    const uint64_t out_off = (uint64_t)pos * p.ldc;
+    for (uint32_t co0 = 0; co0 < g.c_out; co0 += kCoChunk) {
+      float acc[kCoChunk];
+#pragma unroll
+      for (uint32_t j = 0; j < kCoChunk; ++j) acc[j] = 0.0f;
+      for (uint32_t ky = 0; ky < g.k; ++ky) {
+        const uint32_t py = oy * g.stride + ky * g.dilation;
+        if (py < g.pad || py - g.pad >= g.h) continue;
+        for (uint32_t kx = 0; kx < g.k; ++kx) {
+          const uint32_t px = ox * g.stride + kx * g.dilation;
+          if (px < g.pad || px - g.pad >= g.w) continue;
+          const uint64_t src = ((uint64_t)(img * g.h + py - g.pad) * g.w + px - g.pad) * g.c_step;
+          const float* wrow = w_s + (uint64_t)((ky * g.k + kx) * g.c) * g.c_out + co0;
+          for (uint32_t ci = 0; ci < g.c; ++ci) {
+            const float raw = p.ga.src_is_bf16 ? bf16_to_f32(((const uint16_t*)p.ga.base)[src + ci]) : ((const float*)p.ga.base)[src + ci];
+            const float xv = p.ga.src_is_bf16 ? raw : round_operand(raw, p.tf32);
+            const float4* w4 = (const float4*)(wrow + (uint64_t)ci * g.c_out);
+#pragma unroll
+            for (uint32_t j = 0; j < kCoChunk / 4; ++j) {
+              const float4 wv = w4[j];
+              acc[4 * j] = fmaf(xv, wv.x, acc[4 * j]);
+              acc[4 * j + 1] = fmaf(xv, wv.y, acc[4 * j + 1]);
+              acc[4 * j + 2] = fmaf(xv, wv.z, acc[4 * j + 2]);
+              acc[4 * j + 3] = fmaf(xv, wv.w, acc[4 * j + 3]);
+            }
+          }
+        }
+      }
+      // epilogue on 8 channels at a time: 16 bytes of bf16 or two 16-byte halves of f32
+#pragma unroll
+      for (uint32_t j = 0; j < kCoChunk; j += 8) {
+        const uint64_t off = out_off + co0 + j;
+        float v[8];
+#pragma unroll
+        for (uint32_t e = 0; e < 8; ++e) v[e] = acc[j + e];
+        if (p.accumulate) {
+          if (p.c_is_bf16) {
+            const uint4 q = *(const uint4*)((const uint16_t*)p.c + off);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (uint32_t e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(w[e] << 16); v[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u); }
+          } else {
+#pragma unroll
+            for (uint32_t e = 0; e < 8; ++e) v[e] += ((const float*)p.c)[off + e];
+          }
+        }
+        if (p.bias) {
+#pragma unroll
+          for (uint32_t e = 0; e < 8; ++e) v[e] += p.bias[co0 + j + e];
+        }
+        if (p.residual) {
+          if (p.c_is_bf16) {
+            const uint4 q = *(const uint4*)((const uint16_t*)p.residual + off);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (uint32_t e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(w[e] << 16); v[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u); }
+          } else {
+#pragma unroll
+            for (uint32_t e = 0; e < 8; ++e) v[e] += ((const float*)p.residual)[off + e];
+          }
+        }
+#pragma unroll
+        for (uint32_t e = 0; e < 8; ++e) {
+          if (p.relu) v[e] = fmaxf(v[e], 0.0f);
+          if (p.round_tf32) v[e] = round_tf32(v[e]);
+        }
+        if (p.c_is_bf16) {
+          *(uint4*)((uint16_t*)p.c + off) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+        } else {
+          *(float4*)((float*)p.c + off) = make_float4(v[0], v[1], v[2], v[3]);
+          *(float4*)((float*)p.c + off + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+// The shapes this kernel takes: a forward pass whose whole filter fits 48 KB of shared memory as f32, output
+// channels in whole chunks, and a result that can be stored 16 bytes at a time.
+bool conv_direct_applies(const GemmParams& p) {
+  const ConvGeo& g = p.geo;
+  const uint64_t kk = (uint64_t)g.k * g.k * g.c;
+  return g.c <= 4 && g.c_out % kCoChunk == 0 && kk * g.c_out * 4 <= 48 * 1024 && p.vec_store && !p.transpose_out;
+}
+
+cudaError_t launch_conv_direct(const GemmParams& p, int sm_count, cudaStream_t stream) {
+  if (p.m == 0) return cudaSuccess;
+  const ConvGeo& g = p.geo;
+  const size_t smem = (size_t)g.k * g.k * g.c * g.c_out * 4;
+  const uint32_t want = (p.m + 127) / 128, cap = (uint32_t)sm_count * 8;
+  conv_direct_kernel<<<want < cap ? want : cap, 128, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace gb

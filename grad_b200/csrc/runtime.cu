@@ -18,6 +18,8 @@
 
 namespace gb {
 cudaError_t launch_gemm_f32(const GemmParams& p, cudaStream_t stream);
+bool conv_direct_applies(const GemmParams& p);
+cudaError_t launch_conv_direct(const GemmParams& p, int sm_count, cudaStream_t stream);
 }
 
 struct gb_handle {
@@ -82,6 +84,7 @@ bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, co
 struct Plan {
   GemmParams p;
   CUtensorMap tmap_a, tmap_b, tmap_c;
+  bool direct = false;      // forward convolution with very few input channels: the FMA kernel of conv_direct.cu
   bool tensor = false;      // tcgen05 path, else strict-f32
   size_t workspace = 0;     // bytes of split-K partials
 };
@@ -307,6 +310,15 @@ int plan_gemm(const gb_handle* h, const gb_gemm_desc* d, const void* a, const vo
 int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, size_t workspace_bytes) {
   GemmParams& p = plan.p;
   if (p.m == 0 || p.n == 0 || p.batch == 0) return GB_OK;   // an empty grid is a no-op (src/gpu/gpu.zig:612)
+  if (plan.direct) {
+    gb_plan_info& di = h->last_plan;
+    di = gb_plan_info{};
+    di.tensor_path = 0; di.a_kind = di.b_kind = (uint32_t)gb::kGather;
+    di.tile_m = 128; di.tile_n = 32; di.stages = 1; di.splits = 1; di.k_blocks = 1;
+    di.work_items = (p.m + 127) / 128; di.kernel_launches = 1;
+    const cudaError_t de = gb::launch_conv_direct(p, h->sm_count, stream);
+    return de == cudaSuccess ? GB_OK : cuda_fail(h, de);
+  }
   if (p.splits > 1) {
     if (workspace == nullptr || workspace_bytes < plan.workspace || !aligned16(workspace)) {
       // Without room for partials the product runs unsplit rather than failing.
@@ -511,6 +523,11 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     set_output(p, out, d->dtype_y, g.c_out, 0, false, d->accumulate, ep);
     int rc = finish_plan(h, plan, true, min_bn, ep);
     if (rc != GB_OK) return rc;
+    if (plan.tensor && gb::conv_direct_applies(p) && !getenv("GB_NO_DIRECT_CONV")) {
+      plan.direct = true;
+      plan.workspace = 0;
+      return GB_OK;
+    }
     if (plan.tensor) {
       p.a_kind = gb::kGather;
       walk_forward(p.walk, g, epl);
