@@ -19,8 +19,8 @@ __device__ __forceinline__ void store_elem(void* p, int bf16, size_t i, float v)
   else ((float*)p)[i] = v;
 }
 
-// One thread per output element; window clipped to the image like `boundsOf` (conv.zig:152-161); the average
-// divides by the number of in-bounds taps (`windowCount`, :183-186).
+// Window clipped to the image like `boundsOf` (conv.zig:152-161); the average divides by the number of
+// in-bounds taps (`windowCount`, :183-186).  One thread per output element.
 __global__ void pool2d_kernel(const void* x, void* y, int bf16, int is_max, uint32_t n, uint32_t h, uint32_t w, uint32_t c, uint32_t k,
                               uint32_t stride, uint32_t pad, uint32_t oh, uint32_t ow) {
   const size_t total = (size_t)n * oh * ow * c;
@@ -38,6 +38,45 @@ __global__ void pool2d_kernel(const void* x, void* y, int bf16, int is_max, uint
       }
     const float count = (float)((y1 - y0) * (x1 - x0));
     store_elem(y, bf16, t, is_max ? best : sum / count);
+  }
+}
+
+// The same pooling for bf16 tensors whose channel count is a multiple of 8: one thread per output pixel and
+// group of 8 channels, 16-byte loads and stores, 32-bit index arithmetic.  (The scalar kernel above moved two
+// bytes per thread behind four 64-bit divisions and reached an eighth of the memory bandwidth: 0.8 ms for
+// the 537 MB activation of a 4096-image ResNet stage.)
+__global__ void __launch_bounds__(256) pool2d_bf16x8_kernel(const uint4* x, uint4* y, int is_max, uint32_t n, uint32_t h, uint32_t w, uint32_t c8,
+                                                            uint32_t k, uint32_t stride, uint32_t pad, uint32_t oh, uint32_t ow) {
+  const uint32_t total = n * oh * ow * c8;   // the caller keeps this below 2^32
+  for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gridDim.x * blockDim.x) {
+    const uint32_t pix = t / c8, cg = t - pix * c8;
+    const uint32_t row = pix / ow, ox = pix - row * ow;
+    const uint32_t img = row / oh, oy = row - img * oh;
+    const uint32_t top = oy * stride, left = ox * stride;
+    const uint32_t y0 = top < pad ? 0 : top - pad, y1 = min(top + k - pad, h);
+    const uint32_t x0 = left < pad ? 0 : left - pad, x1 = min(left + k - pad, w);
+    float acc[8];
+#pragma unroll
+    for (uint32_t e = 0; e < 8; ++e) acc[e] = is_max ? -INFINITY : 0.0f;
+    for (uint32_t yy = y0; yy < y1; ++yy) {
+      const uint4* line = x + ((size_t)(img * h + yy) * w) * c8 + cg;
+      for (uint32_t xx = x0; xx < x1; ++xx) {
+        const uint4 q = line[(size_t)xx * c8];
+        const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (uint32_t e = 0; e < 4; ++e) {
+          const float lo = __uint_as_float(wd[e] << 16), hi = __uint_as_float(wd[e] & 0xFFFF0000u);
+          acc[2 * e] = is_max ? fmaxf(acc[2 * e], lo) : acc[2 * e] + lo;
+          acc[2 * e + 1] = is_max ? fmaxf(acc[2 * e + 1], hi) : acc[2 * e + 1] + hi;
+        }
+      }
+    }
+    if (!is_max) {
+      const float count = (float)((y1 - y0) * (x1 - x0));
+#pragma unroll
+      for (uint32_t e = 0; e < 8; ++e) acc[e] = acc[e] / count;
+    }
+    y[t] = make_uint4(gb::pack_bf16x2(acc[0], acc[1]), gb::pack_bf16x2(acc[2], acc[3]), gb::pack_bf16x2(acc[4], acc[5]), gb::pack_bf16x2(acc[6], acc[7]));
   }
 }
 
@@ -111,6 +150,13 @@ int gb_pool2d(void* stream, int is_max, int dtype, const void* x, void* y, uint3
   const uint32_t oh = (h + 2 * pad - k) / stride + 1, ow = (w + 2 * pad - k) / stride + 1;
   const size_t total = (size_t)n * oh * ow * c;
   if (total == 0) return GB_OK;
+  if (dtype == GB_BF16 && c % 8 == 0 && total / 8 < 0xFFFFFFFFull && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0) {
+    const size_t groups = total / 8;
+    const size_t want = (groups + 255) / 256;
+    pool2d_bf16x8_kernel<<<(unsigned)(want < 148 * 16 ? want : 148 * 16), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)y, is_max, n, h, w, c / 8,
+                                                                                                          k, stride, pad, oh, ow);
+    return finish();
+  }
   pool2d_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(x, y, dtype == GB_BF16, is_max, n, h, w, c, k, stride, pad, oh, ow);
   return finish();
 }

@@ -89,3 +89,41 @@ def test_full_width_model_runs_at_batch_100(gpu):
     b = Executor(model, gpu, "bf16").run({"input": x})["logits"]
     assert a.shape == (100, 10) and np.isfinite(a).all()
     assert rel_fro(b, a) <= TOL_BF16
+
+
+@pytest.mark.parametrize("is_max", [0, 1])
+@pytest.mark.parametrize("shape", [(3, 8, 8, 64, 2, 2, 0), (2, 9, 7, 24, 3, 2, 1), (2, 8, 8, 12, 2, 2, 0), (1, 4, 4, 256, 4, 4, 0)])
+def test_pool2d_vector_and_scalar_kernels_agree_with_the_window_definition(gpu, is_max, shape):
+    """`gb_pool2d` on NHWC: clipped windows, the average over in-bounds taps only (src/gpu/math/conv.zig:152-186).
+    bf16 tensors with a multiple of 8 channels take the 16-byte kernel, everything else the scalar one; both
+    must reproduce a plain numpy evaluation of the definition on the same bf16 values, bit for bit."""
+    import ctypes as C
+    import torch
+
+    n, h, w, c, k, stride, pad = shape
+    x = torch.from_numpy(seeded(77, n, h, w, c)).cuda().bfloat16()
+    oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+    xf = x.float().cpu().numpy()
+    want = np.empty((n, oh, ow, c), dtype=np.float32)
+    for oy in range(oh):
+        for ox in range(ow):
+            y0, y1 = max(oy * stride - pad, 0), min(oy * stride + k - pad, h)
+            x0, x1 = max(ox * stride - pad, 0), min(ox * stride + k - pad, w)
+            win = xf[:, y0:y1, x0:x1, :].reshape(n, -1, c)
+            if is_max:
+                want[:, oy, ox, :] = win.max(axis=1)
+            else:
+                acc = np.zeros((n, c), dtype=np.float32)
+                for t in range(win.shape[1]):      # the kernels add the taps in row-major window order
+                    acc += win[:, t, :]
+                want[:, oy, ox, :] = acc / np.float32(win.shape[1])
+    want_bf16 = torch.from_numpy(want).bfloat16().float().numpy()
+    for dtype, code in ((torch.bfloat16, 1), (torch.float32, 0)):
+        xin = x.to(dtype).contiguous()
+        y = torch.empty((n, oh, ow, c), dtype=dtype, device="cuda")
+        rc = gpu.lib.gb_pool2d(C.c_void_p(torch.cuda.current_stream().cuda_stream), is_max, code, C.c_void_p(xin.data_ptr()),
+                               C.c_void_p(y.data_ptr()), n, h, w, c, k, stride, pad)
+        assert rc == 0
+        torch.cuda.synchronize()
+        got = y.float().cpu().numpy()
+        assert np.array_equal(got, want_bf16 if dtype == torch.bfloat16 else want), (shape, is_max, dtype)
