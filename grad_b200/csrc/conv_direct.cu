@@ -2,7 +2,7 @@
 // Such a layer is no tensor-core shape: K fills less than half of one 64-wide K block, its input rows are 6 bytes
 // apart (no TMA box can start there), and the gather warps of the contraction kernel spent ~12 us per 128-row
 // tile building a mostly-zero operand tile -- a fifth of a whole ResNet-14 inference pass.  Here one thread
-// owns one output position and accumulates 32 output channels at a time in registers with FMAs; the filters
+// owns four consecutive output positions and accumulates 16 output channels of each at a time with FMAs; the filters
 // sit in shared memory as f32 and every lane reads the same 16 bytes of them (a broadcast).  The products are
 // those of the tensor path: operands rounded to bf16 (GB_MATH_BF16) or to TF32 (GB_MATH_TF32), f32
 // accumulation, then the same epilogue (old value, bias, residual, ReLU, rounding).  Follows the per-position
@@ -17,13 +17,17 @@ namespace gb {
 
 namespace {
 
-constexpr uint32_t kCoChunk = 32;   // output channels a thread accumulates at a time
+constexpr uint32_t kCoChunk = 16;   // output channels a thread accumulates at a time ...
+constexpr uint32_t kPos = 4;        // ... for this many consecutive output positions
 
 __device__ __forceinline__ float round_operand(float v, uint32_t tf32) {
   return tf32 ? round_tf32(v) : bf16_to_f32((uint16_t)bf16_bits(v));
 }
 
-// Dynamic shared memory: filters as f32 [taps * c][c_out], already rounded to the operand type.
+// Dynamic shared memory: filters as f32 [taps * c][c_out], already rounded to the operand type.  A thread
+// reads 16 bytes of them per four FMAs of ONE position; with one position per thread the kernel was bound
+// by those shared-memory reads (0.8 ms for 4096 images), so a thread keeps four positions and every filter
+// read feeds 16 FMAs.
 __global__ void __launch_bounds__(128) conv_direct_kernel(const GemmParams p) {
   extern __shared__ float w_s[];
   const ConvGeo& g = p.geo;
@@ -36,80 +40,103 @@ __global__ void __launch_bounds__(128) conv_direct_kernel(const GemmParams p) {
   }
   __syncthreads();
   const uint32_t per_image = g.out_h * g.out_w;
-  for (uint32_t pos = blockIdx.x * blockDim.x + threadIdx.x; pos < p.m; pos += gridDim.x * blockDim.x) {
-    const uint32_t img = pos / per_image, rem = pos - img * per_image;
-    const uint32_t oy = rem / g.out_w, ox = rem - oy * g.out_w;
-    const uint64_t out_off = (uint64_t)pos * p.ldc;
-    for (uint32_t co0 = 0; co0 < g.c_out; co0 += kCoChunk) {
-      float acc[kCoChunk];
+  const uint32_t groups = (p.m + kPos - 1) / kPos;
+  for (uint32_t grp = blockIdx.x * blockDim.x + threadIdx.x; grp < groups; grp += gridDim.x * blockDim.x) {
+    // top-left input pixel (before padding is subtracted) and image of each of the thread's positions
+    uint32_t base_y[kPos], base_x[kPos], image[kPos];
 #pragma unroll
-      for (uint32_t j = 0; j < kCoChunk; ++j) acc[j] = 0.0f;
-      for (uint32_t ky = 0; ky < g.k; ++ky) {
-        const uint32_t py = oy * g.stride + ky * g.dilation;
-        if (py < g.pad || py - g.pad >= g.h) continue;
+    for (uint32_t q = 0; q < kPos; ++q) {
+      const uint32_t pos = min(grp * kPos + q, p.m - 1);   // a position past the end repeats the last one and is not stored
+      const uint32_t img = pos / per_image, rem = pos - img * per_image;
+      const uint32_t oy = rem / g.out_w;
+      image[q] = img; base_y[q] = oy * g.stride; base_x[q] = (rem - oy * g.out_w) * g.stride;
+    }
+    for (uint32_t co0 = 0; co0 < g.c_out; co0 += kCoChunk) {
+      float acc[kPos][kCoChunk];
+#pragma unroll
+      for (uint32_t q = 0; q < kPos; ++q)
+#pragma unroll
+        for (uint32_t j = 0; j < kCoChunk; ++j) acc[q][j] = 0.0f;
+      for (uint32_t ky = 0; ky < g.k; ++ky)
         for (uint32_t kx = 0; kx < g.k; ++kx) {
-          const uint32_t px = ox * g.stride + kx * g.dilation;
-          if (px < g.pad || px - g.pad >= g.w) continue;
-          const uint64_t src = ((uint64_t)(img * g.h + py - g.pad) * g.w + px - g.pad) * g.c_step;
+          int64_t src[kPos];
+#pragma unroll
+          for (uint32_t q = 0; q < kPos; ++q) {
+            const uint32_t py = base_y[q] + ky * g.dilation, px = base_x[q] + kx * g.dilation;
+            const bool inside = py >= g.pad && py - g.pad < g.h && px >= g.pad && px - g.pad < g.w;
+            src[q] = inside ? (int64_t)(((uint64_t)(image[q] * g.h + py - g.pad) * g.w + px - g.pad) * g.c_step) : -1;
+          }
           const float* wrow = w_s + (uint64_t)((ky * g.k + kx) * g.c) * g.c_out + co0;
           for (uint32_t ci = 0; ci < g.c; ++ci) {
-            const float raw = p.ga.src_is_bf16 ? bf16_to_f32(((const uint16_t*)p.ga.base)[src + ci]) : ((const float*)p.ga.base)[src + ci];
-            const float xv = p.ga.src_is_bf16 ? raw : round_operand(raw, p.tf32);
+            float xv[kPos];
+#pragma unroll
+            for (uint32_t q = 0; q < kPos; ++q) {
+              float raw = 0.0f;
+              if (src[q] >= 0) raw = p.ga.src_is_bf16 ? bf16_to_f32(((const uint16_t*)p.ga.base)[src[q] + ci]) : ((const float*)p.ga.base)[src[q] + ci];
+              xv[q] = p.ga.src_is_bf16 ? raw : round_operand(raw, p.tf32);
+            }
             const float4* w4 = (const float4*)(wrow + (uint64_t)ci * g.c_out);
 #pragma unroll
             for (uint32_t j = 0; j < kCoChunk / 4; ++j) {
               const float4 wv = w4[j];
-              acc[4 * j] = fmaf(xv, wv.x, acc[4 * j]);
-              acc[4 * j + 1] = fmaf(xv, wv.y, acc[4 * j + 1]);
-              acc[4 * j + 2] = fmaf(xv, wv.z, acc[4 * j + 2]);
-              acc[4 * j + 3] = fmaf(xv, wv.w, acc[4 * j + 3]);
+#pragma unroll
+              for (uint32_t q = 0; q < kPos; ++q) {
+                acc[q][4 * j] = fmaf(xv[q], wv.x, acc[q][4 * j]);
+                acc[q][4 * j + 1] = fmaf(xv[q], wv.y, acc[q][4 * j + 1]);
+                acc[q][4 * j + 2] = fmaf(xv[q], wv.z, acc[q][4 * j + 2]);
+                acc[q][4 * j + 3] = fmaf(xv[q], wv.w, acc[q][4 * j + 3]);
+              }
             }
           }
         }
-      }
       // epilogue on 8 channels at a time: 16 bytes of bf16 or two 16-byte halves of f32
 #pragma unroll
-      for (uint32_t j = 0; j < kCoChunk; j += 8) {
-        const uint64_t off = out_off + co0 + j;
-        float v[8];
+      for (uint32_t q = 0; q < kPos; ++q) {
+        const uint32_t pos = grp * kPos + q;
+        if (pos >= p.m) continue;
 #pragma unroll
-        for (uint32_t e = 0; e < 8; ++e) v[e] = acc[j + e];
-        if (p.accumulate) {
-          if (p.c_is_bf16) {
-            const uint4 q = *(const uint4*)((const uint16_t*)p.c + off);
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        for (uint32_t j = 0; j < kCoChunk; j += 8) {
+          const uint64_t off = (uint64_t)pos * p.ldc + co0 + j;
+          float v[8];
 #pragma unroll
-            for (uint32_t e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(w[e] << 16); v[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u); }
-          } else {
+          for (uint32_t e = 0; e < 8; ++e) v[e] = acc[q][j + e];
+          if (p.accumulate) {
+            if (p.c_is_bf16) {
+              const uint4 qq = *(const uint4*)((const uint16_t*)p.c + off);
+              const uint32_t w[4] = {qq.x, qq.y, qq.z, qq.w};
 #pragma unroll
-            for (uint32_t e = 0; e < 8; ++e) v[e] += ((const float*)p.c)[off + e];
+              for (uint32_t e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(w[e] << 16); v[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u); }
+            } else {
+#pragma unroll
+              for (uint32_t e = 0; e < 8; ++e) v[e] += ((const float*)p.c)[off + e];
+            }
           }
-        }
-        if (p.bias) {
+          if (p.bias) {
 #pragma unroll
-          for (uint32_t e = 0; e < 8; ++e) v[e] += p.bias[co0 + j + e];
-        }
-        if (p.residual) {
-          if (p.c_is_bf16) {
-            const uint4 q = *(const uint4*)((const uint16_t*)p.residual + off);
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-            for (uint32_t e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(w[e] << 16); v[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u); }
-          } else {
-#pragma unroll
-            for (uint32_t e = 0; e < 8; ++e) v[e] += ((const float*)p.residual)[off + e];
+            for (uint32_t e = 0; e < 8; ++e) v[e] += p.bias[co0 + j + e];
           }
-        }
+          if (p.residual) {
+            if (p.c_is_bf16) {
+              const uint4 qq = *(const uint4*)((const uint16_t*)p.residual + off);
+              const uint32_t w[4] = {qq.x, qq.y, qq.z, qq.w};
 #pragma unroll
-        for (uint32_t e = 0; e < 8; ++e) {
-          if (p.relu) v[e] = fmaxf(v[e], 0.0f);
-          if (p.round_tf32) v[e] = round_tf32(v[e]);
-        }
-        if (p.c_is_bf16) {
-          *(uint4*)((uint16_t*)p.c + off) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-        } else {
-          *(float4*)((float*)p.c + off) = make_float4(v[0], v[1], v[2], v[3]);
-          *(float4*)((float*)p.c + off + 4) = make_float4(v[4], v[5], v[6], v[7]);
+              for (uint32_t e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(w[e] << 16); v[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u); }
+            } else {
+#pragma unroll
+              for (uint32_t e = 0; e < 8; ++e) v[e] += ((const float*)p.residual)[off + e];
+            }
+          }
+#pragma unroll
+          for (uint32_t e = 0; e < 8; ++e) {
+            if (p.relu) v[e] = fmaxf(v[e], 0.0f);
+            if (p.round_tf32) v[e] = round_tf32(v[e]);
+          }
+          if (p.c_is_bf16) {
+            *(uint4*)((uint16_t*)p.c + off) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+          } else {
+            *(float4*)((float*)p.c + off) = make_float4(v[0], v[1], v[2], v[3]);
+            *(float4*)((float*)p.c + off + 4) = make_float4(v[4], v[5], v[6], v[7]);
+          }
         }
       }
     }
@@ -130,7 +157,7 @@ cudaError_t launch_conv_direct(const GemmParams& p, int sm_count, cudaStream_t s
   if (p.m == 0) return cudaSuccess;
   const ConvGeo& g = p.geo;
   const size_t smem = (size_t)g.k * g.k * g.c * g.c_out * 4;
-  const uint32_t want = (p.m + 127) / 128, cap = (uint32_t)sm_count * 8;
+  const uint32_t want = ((p.m + kPos - 1) / kPos + 127) / 128, cap = (uint32_t)sm_count * 8;
   conv_direct_kernel<<<want < cap ? want : cap, 128, smem, stream>>>(p);
   return cudaGetLastError();
 }
