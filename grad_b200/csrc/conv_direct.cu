@@ -40,8 +40,13 @@ __global__ void __launch_bounds__(128) conv_direct_kernel(const GemmParams p) {
   }
   __syncthreads();
   const uint32_t per_image = g.out_h * g.out_w;
-  const uint32_t groups = (p.m + kPos - 1) / kPos;
-  for (uint32_t grp = blockIdx.x * blockDim.x + threadIdx.x; grp < groups; grp += gridDim.x * blockDim.x) {
+  // Work item = (group of kPos positions, chunk of kCoChunk channels), chunk fastest: neighbouring lanes hold
+  // the chunks of one position group, so together they store whole 128-byte lines of the result and share
+  // their input reads, and a small batch still yields enough threads to fill the machine.
+  const uint32_t groups = (p.m + kPos - 1) / kPos, chunks = g.c_out / kCoChunk;
+  const uint64_t items = (uint64_t)groups * chunks;
+  for (uint64_t item = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; item < items; item += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t grp = (uint32_t)(item / chunks), co0 = (uint32_t)(item - (uint64_t)grp * chunks) * kCoChunk;
     // top-left input pixel (before padding is subtracted) and image of each of the thread's positions
     uint32_t base_y[kPos], base_x[kPos], image[kPos];
 #pragma unroll
@@ -51,7 +56,7 @@ __global__ void __launch_bounds__(128) conv_direct_kernel(const GemmParams p) {
       const uint32_t oy = rem / g.out_w;
       image[q] = img; base_y[q] = oy * g.stride; base_x[q] = (rem - oy * g.out_w) * g.stride;
     }
-    for (uint32_t co0 = 0; co0 < g.c_out; co0 += kCoChunk) {
+    {
       float acc[kPos][kCoChunk];
 #pragma unroll
       for (uint32_t q = 0; q < kPos; ++q)
@@ -157,7 +162,9 @@ cudaError_t launch_conv_direct(const GemmParams& p, int sm_count, cudaStream_t s
   if (p.m == 0) return cudaSuccess;
   const ConvGeo& g = p.geo;
   const size_t smem = (size_t)g.k * g.k * g.c * g.c_out * 4;
-  const uint32_t want = ((p.m + kPos - 1) / kPos + 127) / 128, cap = (uint32_t)sm_count * 8;
+  const uint64_t items = (uint64_t)((p.m + kPos - 1) / kPos) * (g.c_out / kCoChunk);
+  const uint64_t want64 = (items + 127) / 128;
+  const uint32_t cap = (uint32_t)sm_count * 16, want = (uint32_t)(want64 < cap ? want64 : cap);
   conv_direct_kernel<<<want < cap ? want : cap, 128, smem, stream>>>(p);
   return cudaGetLastError();
 }

@@ -116,6 +116,18 @@ class Executor:
             self.derived[key] = self._constant(name).to(self.act_dtype).contiguous()
         return self.derived[key]
 
+    def _padded(self, name: str, cols: int, vector: bool) -> torch.Tensor:
+        """A constant matrix (or bias vector) with zero columns appended up to `cols`, made once.  A product whose
+        column count is not a multiple of 8 (the 10 logits) can use neither TMA boxes nor 16-byte stores: the
+        classifier took 50 us through the gather warps and the scalar epilogue, a ninth of a batch-100 pass."""
+        key = f"{name}/pad{cols}/{self.mode}"
+        if key not in self.derived:
+            src = self._constant(name) if vector else self._matrix(name)
+            out = torch.zeros(src.shape[:-1] + (cols,), dtype=src.dtype, device=src.device)
+            out[..., : src.shape[-1]] = src
+            self.derived[key] = out
+        return self.derived[key]
+
     def _value(self, values, name: str) -> torch.Tensor:
         if name in values:
             return values[name]
@@ -210,11 +222,17 @@ class Executor:
             if other in self.model.initializers and self.model.initializers[other].shape == (n,):
                 bias, result, consumed = self._constant(other), nxt.outputs[0], 2
         out_dtype = torch.float32 if result in self.model.outputs else self.act_dtype
-        y = torch.empty(tuple(x.shape[:-1]) + (n,), dtype=out_dtype, device=self.gpu.device)
+        cols = n
+        if n % 8 != 0 and node.inputs[1] in self.model.initializers:
+            cols = (n + 7) // 8 * 8
+            w = self._padded(node.inputs[1], cols, False)
+            if bias is not None:
+                bias = self._padded(other, cols, True)
+        y = torch.empty(tuple(x.shape[:-1]) + (cols,), dtype=out_dtype, device=self.gpu.device)
         before = self.gpu.launches
-        self.gpu.matmul(x.contiguous(), w, y, MatmulShape(rows, n, k), MatmulOpts(), epilogue=Epilogue(bias, None, False), math=self.math)
+        self.gpu.matmul(x.contiguous(), w, y, MatmulShape(rows, cols, k), MatmulOpts(), epilogue=Epilogue(bias, None, False), math=self.math)
         self.stats.launches += self.gpu.launches - before
-        values[result] = y
+        values[result] = y if cols == n else y[..., :n]
         self.stats.device_nodes += consumed
         return consumed
 
