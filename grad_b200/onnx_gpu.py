@@ -125,7 +125,8 @@ class Executor:
             src = self._constant(name) if vector else self._matrix(name)
             out = torch.zeros(src.shape[:-1] + (cols,), dtype=src.dtype, device=src.device)
             out[..., : src.shape[-1]] = src
-            self.derived[key] = out
+            # the matrix is kept as (cols, K) rows: a K-major B operand that TMA fetches whatever `cols` is
+            self.derived[key] = out if vector else out.t().contiguous()
         return self.derived[key]
 
     def _value(self, values, name: str) -> torch.Tensor:
@@ -230,7 +231,7 @@ class Executor:
                 bias = self._padded(other, cols, True)
         y = torch.empty(tuple(x.shape[:-1]) + (cols,), dtype=out_dtype, device=self.gpu.device)
         before = self.gpu.launches
-        self.gpu.matmul(x.contiguous(), w, y, MatmulShape(rows, cols, k), MatmulOpts(), epilogue=Epilogue(bias, None, False), math=self.math)
+        self.gpu.matmul(x.contiguous(), w, y, MatmulShape(rows, cols, k), MatmulOpts(False, cols != n), epilogue=Epilogue(bias, None, False), math=self.math)
         self.stats.launches += self.gpu.launches - before
         values[result] = y if cols == n else y[..., :n]
         self.stats.device_nodes += consumed
