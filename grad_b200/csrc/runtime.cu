@@ -143,14 +143,14 @@ double tile_cost(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint
   // One tcgen05.mma never takes less than about 215 cycles here whatever its N (measured 115-125 ns per
   // instruction for N = 32..128), so narrow tiles are issue-bound, not math-bound.
   const double fill = (16384.0 + b_lines * 128.0) / 48.0, mma = 4.0 * std::max(bn / 2.0, 215.0);
-  const double per_tile = k_blocks * std::max(fill, mma) + (bn > 256 ? 6000.0 : 1200.0);
+  const double per_tile = k_blocks * std::max(fill, mma) + (bn > 256 ? 11000.0 : 1200.0);
   const double waves = (double)((tiles + units - 1) / units);
   return waves * per_tile + 3000.0;
 }
 
 // Tile width and K split for an m x n x k_blocks product on `sms` multiprocessors: the width with the
 // lowest estimated time; when it leaves SMs idle, K is split so that about one work item per SM exists,
-// each at least four K blocks long (the role of `splits` in src/gpu/gpu.zig:664, 1000, 1041).
+// each at least sixteen K blocks long (the role of `splits` in src/gpu/gpu.zig:664, 1000, 1041).
 void pick_tiling(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint32_t min_bn, uint32_t sms, bool allow_split,
                  uint32_t& bn, uint32_t& splits, uint32_t& kbps) {
   const uint32_t n_cap = std::max(min_bn, ceil_div(n, min_bn) * min_bn);   // n rounded up to the narrowest tile
@@ -164,7 +164,8 @@ void pick_tiling(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint
   if (bn == 0) bn = min_bn;
   const uint32_t tiles = ceil_div(m, 128) * batch * ceil_div(n, bn);
   splits = 1;
-  if (allow_split && tiles > 0 && tiles * 2 <= sms && k_blocks >= 8) splits = std::max(1u, std::min(sms / tiles, k_blocks / 4));
+  // A split costs a second launch (~5 us) and a pass over the partials: only worth it when every part keeps >= 16 K blocks.
+  if (allow_split && tiles > 0 && tiles * 2 <= sms && k_blocks >= 32) splits = std::max(1u, std::min(sms / tiles, k_blocks / 16));
   kbps = std::max(1u, ceil_div(k_blocks, splits));
   splits = std::max(1u, ceil_div(k_blocks, kbps));
 }
