@@ -121,11 +121,135 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmParams p) {
   }
 }
 
+// ---- dense operands: the matmul family ----------------------------------------------------------------------
+// Both operands are plain matrices, so nothing needs the per-element accessor above (a switch, 64-bit index
+// arithmetic and bounds per element: ~2000 cycles per 16-deep K step, 16-18 TFLOP/s at best and 25-50 us for
+// the MLP's one-tile products).  Each thread keeps pointers to its elements of the next K step and bumps them;
+// the next step's elements are fetched into registers while the current step is multiplied out of shared
+// memory.  TM x TN tile, 256 threads, (TM/16) x (TN/16) accumulators per thread.
+template <int TM, int TN>
+__global__ void __launch_bounds__(256) gemm_f32_dense_kernel(const GemmParams p) {
+  constexpr int RM = TM / 16, RN = TN / 16, EA = TM * 16 / 256, EB = TN * 16 / 256;
+  __shared__ __align__(16) float As[kTK][TM + 4];
+  __shared__ __align__(16) float Bs[kTK][TN + 4];
+  const uint32_t tid = threadIdx.x;
+  const uint32_t split = blockIdx.z % p.splits, batch = blockIdx.z / p.splits;
+  const uint32_t m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  const uint32_t k_begin = split * p.k_blocks_per_split * kTK;
+  const uint32_t k_end = min(p.k, k_begin + p.k_blocks_per_split * kTK);
+  // this thread's elements of a K step: (mn index within the tile, k index within the step), source pointer, row validity
+  uint32_t a_r[EA], a_k[EA], b_c[EB], b_k[EB];
+  int64_t a_off[EA], b_off[EB];
+  bool a_ok[EA], b_ok[EB];
+  const int64_t a_step = p.ga.mn_major ? (int64_t)kTK * p.ga.ld : kTK, b_step = p.gbsrc.mn_major ? (int64_t)kTK * p.gbsrc.ld : kTK;
+#pragma unroll
+  for (int i = 0; i < EA; ++i) {
+    const uint32_t e = tid + i * 256;
+    if (p.ga.mn_major) { a_r[i] = e % TM; a_k[i] = e / TM; } else { a_k[i] = e % kTK; a_r[i] = e / kTK; }
+    const uint32_t row = m0 + a_r[i], kk = k_begin + a_k[i];
+    a_ok[i] = row < p.m;
+    a_off[i] = (int64_t)batch * p.ga.batch_stride + (p.ga.mn_major ? (int64_t)kk * p.ga.ld + row : (int64_t)row * p.ga.ld + kk);
+  }
+#pragma unroll
+  for (int i = 0; i < EB; ++i) {
+    const uint32_t e = tid + i * 256;
+    if (p.gbsrc.mn_major) { b_c[i] = e % TN; b_k[i] = e / TN; } else { b_k[i] = e % kTK; b_c[i] = e / kTK; }
+    const uint32_t col = n0 + b_c[i], kk = k_begin + b_k[i];
+    b_ok[i] = col < p.n;
+    b_off[i] = (int64_t)batch * p.gbsrc.batch_stride + (p.gbsrc.mn_major ? (int64_t)kk * p.gbsrc.ld + col : (int64_t)col * p.gbsrc.ld + kk);
+  }
+  auto fetch = [&](const GatherDesc& d, int64_t off) {
+    return d.src_is_bf16 ? bf16_to_f32(((const uint16_t*)d.base)[off]) : ((const float*)d.base)[off];
+  };
+  float a_next[EA], b_next[EB];
+  auto load_step = [&](uint32_t k0) {
+#pragma unroll
+    for (int i = 0; i < EA; ++i) {
+      a_next[i] = (a_ok[i] && k0 + a_k[i] < k_end) ? fetch(p.ga, a_off[i]) : 0.0f;
+      a_off[i] += a_step;
+    }
+#pragma unroll
+    for (int i = 0; i < EB; ++i) {
+      b_next[i] = (b_ok[i] && k0 + b_k[i] < k_end) ? fetch(p.gbsrc, b_off[i]) : 0.0f;
+      b_off[i] += b_step;
+    }
+  };
+  const uint32_t tr = tid / 16, tc = tid % 16;
+  float acc[RM][RN];
+#pragma unroll
+  for (int i = 0; i < RM; ++i)
+#pragma unroll
+    for (int j = 0; j < RN; ++j) acc[i][j] = 0.0f;
+  if (k_begin < k_end) load_step(k_begin);
+  for (uint32_t k0 = k_begin; k0 < k_end; k0 += kTK) {
+#pragma unroll
+    for (int i = 0; i < EA; ++i) As[a_k[i]][a_r[i]] = a_next[i];
+#pragma unroll
+    for (int i = 0; i < EB; ++i) Bs[b_k[i]][b_c[i]] = b_next[i];
+    __syncthreads();
+    if (k0 + kTK < k_end) load_step(k0 + kTK);
+#pragma unroll
+    for (uint32_t kk = 0; kk < kTK; ++kk) {
+      float a[RM], b[RN];
+#pragma unroll
+      for (int i = 0; i < RM; i += 4) {
+        const float4 v = *(const float4*)&As[kk][tr * RM + i];
+        a[i] = v.x; a[i + 1] = v.y; a[i + 2] = v.z; a[i + 3] = v.w;
+      }
+#pragma unroll
+      for (int j = 0; j < RN; j += 4) {
+        const float4 v = *(const float4*)&Bs[kk][tc * RN + j];
+        b[j] = v.x; b[j + 1] = v.y; b[j + 2] = v.z; b[j + 3] = v.w;
+      }
+#pragma unroll
+      for (int i = 0; i < RM; ++i)
+#pragma unroll
+        for (int j = 0; j < RN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < RM; ++i) {
+    const uint32_t row = m0 + tr * RM + i;
+    if (row >= p.m) continue;
+#pragma unroll
+    for (int j = 0; j < RN; ++j) {
+      const uint32_t col = n0 + tc * RN + j;
+      if (col >= p.n) continue;
+      float x = acc[i][j];
+      if (p.splits > 1) {
+        p.partial[(((uint64_t)split * p.batch + batch) * p.m + row) * p.n + col] = x;
+        continue;
+      }
+      const uint64_t idx = (uint64_t)batch * p.stride_c + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
+      if (p.accumulate) x += p.c_is_bf16 ? bf16_to_f32(((const uint16_t*)p.c)[idx]) : ((const float*)p.c)[idx];
+      if (p.bias) x += p.bias[col];
+      if (p.residual) x += p.c_is_bf16 ? bf16_to_f32(((const uint16_t*)p.residual)[idx]) : ((const float*)p.residual)[idx];
+      if (p.relu) x = fmaxf(x, 0.0f);
+      if (p.round_tf32) x = round_tf32(x);
+      if (p.c_is_bf16) ((uint16_t*)p.c)[idx] = (uint16_t)bf16_bits(x);
+      else ((float*)p.c)[idx] = x;
+    }
+  }
+}
+
 }  // namespace
 
 // p.k_blocks_per_split counts blocks of 16 K values here; p.tiles_* are 64-wide.
 cudaError_t launch_gemm_f32(const GemmParams& p, cudaStream_t stream) {
   if (p.m == 0 || p.n == 0 || p.batch == 0) return cudaSuccess;
+  if (p.ga.source == kSrcDense && p.gbsrc.source == kSrcDense) {
+    // 128 x 128 tiles once they fill the machine, 64 x 64 below that (more blocks, less work per block)
+    const uint64_t big = (uint64_t)((p.m + 127) / 128) * ((p.n + 127) / 128) * p.batch * p.splits;
+    if (big >= 148) {
+      const dim3 grid((p.n + 127) / 128, (p.m + 127) / 128, p.batch * p.splits);
+      gemm_f32_dense_kernel<128, 128><<<grid, 256, 0, stream>>>(p);
+    } else {
+      const dim3 grid((p.n + 63) / 64, (p.m + 63) / 64, p.batch * p.splits);
+      gemm_f32_dense_kernel<64, 64><<<grid, 256, 0, stream>>>(p);
+    }
+    return cudaGetLastError();
+  }
   const dim3 grid((p.n + kTN - 1) / kTN, (p.m + kTM - 1) / kTM, p.batch * p.splits);
   gemm_f32_kernel<<<grid, 256, 0, stream>>>(p);
   return cudaGetLastError();
