@@ -91,41 +91,6 @@ __device__ __forceinline__ Work decode_work(const GemmParams& p, uint32_t w) {
 }
 
 // ---- gather sources ---------------------------------------------------------------------------------
-// Element index (in elements from desc.base) of (line_major, inner), or -1 for an implicit zero.
-__device__ __forceinline__ int64_t gather_index(const GatherDesc& d, const ConvGeo& g, uint32_t line, uint32_t inner) {
-  if (line >= d.lines_total || inner >= d.inner_total) return -1;
-  switch (d.source) {
-    case kSrcDense:
-      return (int64_t)line * d.ld + inner;
-    case kSrcPatch: {   // src/gpu/math/conv.zig:47-65 `patchOf` + `patchSource`
-      const uint32_t tap = inner / g.c, ci = inner - tap * g.c;
-      const uint32_t ky = tap / g.k, kx = tap - ky * g.k;
-      const uint32_t per_image = g.out_h * g.out_w;
-      const uint32_t n = line / per_image, rem = line - n * per_image;
-      const uint32_t oy = rem / g.out_w, ox = rem - oy * g.out_w;
-      const uint32_t py = oy * g.stride + ky * g.dilation, px = ox * g.stride + kx * g.dilation;
-      if (py < g.pad || px < g.pad || py - g.pad >= g.h || px - g.pad >= g.w) return -1;
-      return ((int64_t)(n * g.h + py - g.pad) * g.w + px - g.pad) * g.c_step + ci;
-    }
-    case kSrcPatchT: {  // the adjoint gather: which dy element input pixel `line` sees through tap `inner / c_out`
-      const uint32_t tap = inner / g.c_out, co = inner - tap * g.c_out;
-      const uint32_t ky = tap / g.k, kx = tap - ky * g.k;
-      const uint32_t per_image = g.h * g.w;
-      const uint32_t n = line / per_image, rem = line - n * per_image;
-      const uint32_t y = rem / g.w, x = rem - y * g.w;
-      const int32_t ty = (int32_t)(y + g.pad) - (int32_t)(ky * g.dilation);
-      const int32_t tx = (int32_t)(x + g.pad) - (int32_t)(kx * g.dilation);
-      if (ty < 0 || tx < 0) return -1;
-      const uint32_t oy = (uint32_t)ty / g.stride, ox = (uint32_t)tx / g.stride;
-      if (oy * g.stride != (uint32_t)ty || ox * g.stride != (uint32_t)tx || oy >= g.out_h || ox >= g.out_w) return -1;
-      return ((int64_t)(n * g.out_h + oy) * g.out_w + ox) * g.c_out + co;
-    }
-    default: {          // kSrcWeightT: w[(tap, ci), co] read as [ci][(tap, co)]
-      const uint32_t tap = inner / g.c_out, co = inner - tap * g.c_out;
-      return ((int64_t)tap * g.c + line) * g.c_out + co;
-    }
-  }
-}
 
 __device__ __forceinline__ float load_as_f32(const GatherDesc& d, int64_t idx) {
   if (idx < 0) return 0.0f;

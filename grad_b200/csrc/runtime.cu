@@ -49,6 +49,32 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Tuning knobs, read from the environment once per process.  Each one switches a plan back to the plan it
+// replaced, which is how the two were compared on the device; none is needed in normal use.
+struct Knobs {
+  int group_m = 0;               // GB_GROUP_M=n: height of the tile rasterisation band (default 8)
+  bool no_pair = false;          // GB_NO_PAIR: single-CTA tiles only
+  bool no_tma_store = false;     // GB_NO_TMA_STORE: results leave by per-lane stores
+  bool no_column_stages = false; // GB_NO_COLUMN_STAGES: one stage per tap instead of one per tap column
+  bool no_direct_conv = false;   // GB_NO_DIRECT_CONV: the stem goes through the gathered tensor plan
+  bool no_strided_tma = false;   // GB_NO_STRIDED_TMA: strided forward / weight-gradient patches are gathered
+  bool no_dgrad_classes = false; // GB_NO_DGRAD_CLASSES: a strided input gradient is one gathered product
+};
+const Knobs& knobs() {
+  static const Knobs k = [] {
+    Knobs v;
+    if (const char* g = getenv("GB_GROUP_M")) v.group_m = std::max(1, atoi(g));
+    v.no_pair = getenv("GB_NO_PAIR") != nullptr;
+    v.no_tma_store = getenv("GB_NO_TMA_STORE") != nullptr;
+    v.no_column_stages = getenv("GB_NO_COLUMN_STAGES") != nullptr;
+    v.no_direct_conv = getenv("GB_NO_DIRECT_CONV") != nullptr;
+    v.no_strided_tma = getenv("GB_NO_STRIDED_TMA") != nullptr;
+    v.no_dgrad_classes = getenv("GB_NO_DGRAD_CLASSES") != nullptr;
+    return v;
+  }();
+  return k;
+}
+
 int cuda_fail(gb_handle* h, cudaError_t e) {
   if (h) h->last_cuda = (int)e;
   return GB_ERR_CUDA;
@@ -179,7 +205,7 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
   p.status = h->status;
   p.epi_groups = 2;
   p.group_m = 8;
-  if (const char* v = getenv("GB_GROUP_M")) p.group_m = (uint32_t)std::max(1, atoi(v));
+  if (knobs().group_m) p.group_m = (uint32_t)knobs().group_m;
   if (plan.tensor) {
     const uint32_t epl = p.tf32 ? 32 : 64;
     p.k_blocks_total = ceil_div(p.k, epl);
@@ -216,7 +242,7 @@ template <class EncodeB>
 bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b) {
   GemmParams& p = plan.p;
   if (!plan.tensor || p.a_kind == gb::kGather || p.b_kind == gb::kGather || p.m <= 128 || p.splits > 1) return false;
-  if (getenv("GB_NO_PAIR")) return false;   // tuning knob: keep the single-CTA plan
+  if (knobs().no_pair) return false;
   const uint32_t sms = (uint32_t)h->sm_count;
   const uint32_t n_cap = std::max(min_bn, ceil_div(p.n, min_bn) * min_bn);
   double best = tile_cost(p.m, p.n, p.batch, p.k_blocks_total, p.bn, false, sms);
@@ -345,7 +371,7 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
   p.tma_store = 0;
   std::memset(&plan.tmap_c, 0, sizeof(plan.tmap_c));
   if (plan.tensor && p.k != 0 && p.vec_store && !p.transpose_out && !p.rowmap.enabled && p.epi_groups == 2 &&
-      !getenv("GB_NO_TMA_STORE")) {
+      !knobs().no_tma_store) {
     const uint32_t es = p.c_is_bf16 ? 2 : 4;
     const uint64_t dims[3] = {p.n, p.m, p.batch};
     const uint64_t strides[2] = {(uint64_t)p.ldc * es, p.batch > 1 ? p.stride_c * es : (uint64_t)p.ldc * es * p.m};
@@ -466,7 +492,7 @@ void walk_dgrad_unit(gb::TapWalk& wk, const gb::ConvGeo& g, uint32_t epl) {
 template <class EncodeA>
 void try_column_stages(Plan& plan, EncodeA encode_a) {
   GemmParams& p = plan.p;
-  if (getenv("GB_NO_COLUMN_STAGES")) return;
+  if (knobs().no_column_stages) return;
   const gb::TapWalk& wk = p.walk;
   if (!plan.tensor || p.a_kind != gb::kPatchK || p.b_kind == gb::kGather || p.splits != 1 || p.box_n != 1 || p.bn > 256) return;
   if (wk.n2 < 2 || wk.n2 > 7 || wk.row_scale != 1 || wk.z_step == 0) return;
@@ -524,7 +550,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     set_output(p, out, d->dtype_y, g.c_out, 0, false, d->accumulate, ep);
     int rc = finish_plan(h, plan, true, min_bn, ep);
     if (rc != GB_OK) return rc;
-    if (plan.tensor && gb::conv_direct_applies(p) && !getenv("GB_NO_DIRECT_CONV")) {
+    if (plan.tensor && gb::conv_direct_applies(p) && !knobs().no_direct_conv) {
       plan.direct = true;
       plan.workspace = 0;
       return GB_OK;
@@ -532,7 +558,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     if (plan.tensor) {
       p.a_kind = gb::kGather;
       walk_forward(p.walk, g, epl);
-      if ((g.stride == 1 || !getenv("GB_NO_STRIDED_TMA")) && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+      if ((g.stride == 1 || !knobs().no_strided_tma) && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
           nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, false, g.stride))
         p.a_kind = gb::kPatchK;
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? (w_rows ? gb::kDenseK : gb::kDenseMN) : gb::kGather;
@@ -594,7 +620,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     if (rc != GB_OK) return rc;
     if (plan.tensor) {
       p.a_kind = gb::kGather;
-      if ((g.stride == 1 || !getenv("GB_NO_STRIDED_TMA")) && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+      if ((g.stride == 1 || !knobs().no_strided_tma) && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
           nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, true, g.stride))
         p.a_kind = gb::kPatchMN;
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
@@ -615,7 +641,7 @@ int run_dgrad_classes(gb_handle* h, cudaStream_t stream, const gb_conv_desc* d, 
   const uint32_t s = g.stride, dil = g.dilation;
   uint32_t math = d->math;
   if (math == GB_MATH_F32 && (d->dtype_x == GB_BF16 || d->dtype_y == GB_BF16)) math = GB_MATH_BF16;
-  if (math == GB_MATH_F32 || s < 2 || s > 4 || getenv("GB_NO_DGRAD_CLASSES")) return GB_ERR_UNSUPPORTED;
+  if (math == GB_MATH_F32 || s < 2 || s > 4 || knobs().no_dgrad_classes) return GB_ERR_UNSUPPORTED;
   const bool tf32 = math == GB_MATH_TF32, smem_bf16 = !tf32;
   const uint32_t epl = tf32 ? 32 : 64, es = smem_bf16 ? 2 : 4;
   if ((d->dtype_y == GB_BF16) != smem_bf16 || (d->dtype_w == GB_BF16) != smem_bf16) return GB_ERR_UNSUPPORTED;

@@ -143,13 +143,16 @@ def test_bf16_conv_agrees_with_f32_conv_within_reference_bounds(gpu):
     assert np.all(np.abs(wide_dw - to_host(gw)) <= 0.6 + 0.03 * np.abs(wide_dw))
 
 
+@pytest.mark.parametrize("case", [(3, 16, 16, 64, 3, 128, 1, 1, 1),     # TMA patch boxes, column-patch stages, TMA stores
+                                  (3, 32, 32, 3, 3, 64, 1, 1, 1),       # the stem: direct FMA kernel
+                                  (2, 9, 9, 3, 3, 32, 2, 1, 1),         # strided stem-like layer, odd image
+                                  (2, 16, 16, 64, 3, 72, 1, 1, 1)])     # a ragged last 32-column chunk beside TMA-stored ones
 @pytest.mark.parametrize("math,tol,half", [(0, TOL_F32, False), (1, TOL_TF32, False), (2, TOL_BF16, True)])
-def test_fused_bias_residual_relu_epilogue(gpu, math, tol, half):
+def test_fused_bias_residual_relu_epilogue(gpu, case, math, tol, half):
     """Conv + bias -> Add(residual) -> Relu in one launch == the executor's separate nodes (src/onnx/gpu.zig:608, 372-377)."""
     import torch
     from oracle import binding as orc
 
-    case = (3, 16, 16, 64, 3, 128, 1, 1, 1)
     d, x, w, _ = _inputs(case, 300)
     geo = _geo(case)
     bias = seeded(303, d.c_out) * np.float32(0.1)
