@@ -32,6 +32,9 @@ RESNET = [
     (4, 32, 32, 64, 3, 128, 2, 1, 1),    # strided transition
     (4, 32, 32, 64, 1, 128, 2, 0, 1),    # strided shortcut
     (3, 16, 16, 128, 3, 256, 2, 1, 1),
+    (2, 16, 16, 64, 3, 64, 1, 2, 2),     # dilation 2: column-patch stages step two image rows per tap
+    (2, 16, 16, 64, 5, 64, 1, 2, 1),     # 5x5: five taps per column-patch stage
+    (2, 32, 32, 128, 3, 32, 1, 1, 1),    # two channel blocks per tap, narrow output
 ]
 
 
