@@ -629,6 +629,38 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
   return GB_OK;
 }
 
+// bf16 math over f32 master filters (the reference packs them to bf16 on every call: `packMatrix` in
+// `convImplicitForward`, src/gpu/gpu.zig:926-960).  Read as f32 they could only be gathered -- 185 us instead of
+// 27 us for a 64-channel layer -- so the forward pass and the input gradient first round them into the head of
+// the caller's workspace (one cast launch over a few hundred KB) and then run as if bf16 filters had been
+// passed.  Without a workspace that large the gathered plan runs as before.
+bool wants_filter_shadow(const gb_conv_desc* d) {
+  uint32_t math = d->math;
+  if (math == GB_MATH_F32 && (d->dtype_x == GB_BF16 || d->dtype_y == GB_BF16)) math = GB_MATH_BF16;
+  return math == GB_MATH_BF16 && d->dtype_w == GB_F32;
+}
+size_t filter_shadow_bytes(const gb_conv_desc* d) {
+  const size_t elems = (size_t)d->geo.k * d->geo.k * d->geo.c * d->geo.c_out;
+  return (elems * 2 + 255) & ~(size_t)255;
+}
+// Returns the descriptor / filter pointer / workspace to continue with; `shadow` receives the patched descriptor.
+int make_filter_shadow(gb_handle* h, cudaStream_t stream, const gb_conv_desc*& desc, gb_conv_desc& shadow, const void*& w, void*& workspace,
+                       size_t& workspace_bytes) {
+  if (!wants_filter_shadow(desc)) return GB_OK;
+  const size_t need = filter_shadow_bytes(desc);
+  if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return GB_OK;
+  const size_t elems = (size_t)desc->geo.k * desc->geo.k * desc->geo.c * desc->geo.c_out;
+  const int rc = gb_cast(stream, GB_F32, GB_BF16, w, workspace, elems);
+  if (rc != GB_OK) return rc == GB_ERR_CUDA ? cuda_fail(h, cudaGetLastError()) : rc;
+  shadow = *desc;
+  shadow.dtype_w = GB_BF16;
+  desc = &shadow;
+  w = workspace;
+  workspace = (char*)workspace + need;
+  workspace_bytes -= need;
+  return GB_OK;
+}
+
 // Input gradient of a strided convolution as up to stride^2 products, one per parity class of input pixels.
 // Pixel (s*i + py, s*j + px) only receives taps ky with (py + pad - ky*dil) divisible by s (likewise kx), and
 // through such a tap it reads dy at (i + (py + pad - ky*dil)/s, j + ...): a stride-1 walk over dy.  So each
@@ -824,9 +856,17 @@ int gb_conv_workspace(const gb_handle* h, int pass, const gb_conv_desc* desc, si
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
   Plan plan;
+  gb_conv_desc shadow;
+  size_t head = 0;
+  if (pass != 2 && wants_filter_shadow(desc)) {
+    shadow = *desc;
+    shadow.dtype_w = GB_BF16;
+    desc = &shadow;
+    head = filter_shadow_bytes(desc);
+  }
   rc = plan_conv(h, pass, desc, nullptr, nullptr, nullptr, nullptr, plan);
   if (rc != GB_OK) return rc;
-  *bytes = plan.workspace;
+  *bytes = head + plan.workspace;
   return GB_OK;
 }
 
@@ -835,10 +875,15 @@ int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   if (!h || !x || !w || !y) return GB_ERR_INVALID;
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
+  gb_conv_desc shadow;
+  rc = make_filter_shadow(h, (cudaStream_t)stream, desc, shadow, w, workspace, workspace_bytes);
+  if (rc != GB_OK) return rc;
   Plan plan;
   rc = plan_conv(h, 0, desc, x, w, y, epilogue, plan);
   if (rc != GB_OK) return rc;
-  return run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+  rc = run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+  if (desc == &shadow) h->last_plan.kernel_launches += 1;   // the cast of the filters
+  return rc;
 }
 
 int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* w, void* dx,
@@ -847,14 +892,23 @@ int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
   if (desc->w_layout != 0) return GB_ERR_UNSUPPORTED;   // the prepared filter copy is a forward-only format
+  gb_conv_desc shadow;
+  rc = make_filter_shadow(h, (cudaStream_t)stream, desc, shadow, w, workspace, workspace_bytes);
+  if (rc != GB_OK) return rc;
+  const uint32_t extra = desc == &shadow ? 1u : 0u;   // the cast of the filters
   if (desc->geo.stride > 1) {
     rc = run_dgrad_classes(h, (cudaStream_t)stream, desc, dy, w, dx);
-    if (rc != GB_ERR_UNSUPPORTED) return rc;
+    if (rc != GB_ERR_UNSUPPORTED) {
+      if (rc == GB_OK) h->last_plan.kernel_launches += extra;
+      return rc;
+    }
   }
   Plan plan;
   rc = plan_conv(h, 1, desc, dy, w, dx, nullptr, plan);
   if (rc != GB_OK) return rc;
-  return run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+  rc = run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+  h->last_plan.kernel_launches += extra;
+  return rc;
 }
 
 int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* x, void* dw,
