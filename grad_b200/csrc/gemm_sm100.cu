@@ -65,24 +65,22 @@ __device__ __forceinline__ Work decode_work(const GemmParams& p, uint32_t w) {
   uint32_t t = w;
   out.split = 0;
   if (p.splits > 1) {
-    out.split = w % p.splits;
-    t = w / p.splits;
+    t = fast_div(w, p.div_splits);
+    out.split = w - t * p.splits;
   }
   out.batch = 0;
   if (p.batch > 1) {
-    const uint32_t per_batch = p.tiles_m * p.tiles_n;
-    out.batch = t / per_batch;
-    t -= out.batch * per_batch;
+    out.batch = fast_div(t, p.div_per_batch);
+    t -= out.batch * p.div_per_batch.d;
   }
   if (p.tiles_n == 1) {
     out.m_tile = t;
     out.n_tile = 0;
   } else {
-    const uint32_t band_size = p.group_m * p.tiles_n;
-    const uint32_t band = t / band_size;
-    const uint32_t within = t - band * band_size;
+    const uint32_t band = fast_div(t, p.div_band);
+    const uint32_t within = t - band * p.div_band.d;
     const uint32_t rows_in_band = min(p.group_m, p.tiles_m - band * p.group_m);
-    out.n_tile = within / rows_in_band;
+    out.n_tile = rows_in_band == p.group_m ? fast_div(within, p.div_group) : within / rows_in_band;   // only the last band is shorter
     out.m_tile = band * p.group_m + within - out.n_tile * rows_in_band;
   }
   out.kb_begin = out.split * p.k_blocks_per_split;
@@ -256,7 +254,7 @@ constexpr uint32_t kNever = 0xFFFFFFFFu;
 
 __device__ __forceinline__ uint32_t boxes_of(uint32_t kind, uint32_t lines, uint32_t epl) {
   if (kind == kGather) return 0;
-  return (kind == kDenseMN || kind == kPatchMN) ? lines / epl : 1u;
+  return (kind == kDenseMN || kind == kPatchMN) ? (epl == 64 ? lines >> 6 : lines >> 5) : 1u;   // epl is 64 or 32
 }
 
 // Once per kernel: which box this lane owns and how its coordinates step along K.
@@ -271,7 +269,7 @@ __device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint3
   kind = is_b ? p.b_kind : p.a_kind;
   b.tmap = is_b ? tmap_b : tmap_a;
   const uint32_t a_bytes = p.a_stage_bytes ? p.a_stage_bytes : kATileBytes;
-  const uint32_t b_tap = p.col_taps ? index / max(nb_tap, 1u) : 0u;           // which tap's B tile this box fills
+  const uint32_t b_tap = !p.col_taps ? 0u : (nb_tap <= 1 ? index : index / nb_tap);   // which tap's B tile this box fills
   b.tap = b_tap;
   if (p.col_taps && is_b) index -= b_tap * nb_tap;
   b.smem_off = (is_b ? a_bytes + b_tap * b_lines * kLineBytes : 0u) + index * epl * kLineBytes;

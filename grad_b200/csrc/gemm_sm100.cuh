@@ -78,6 +78,7 @@ struct GemmParams {
   uint32_t a_kind, b_kind;  // OperandKind
   uint32_t a_mn_major, b_mn_major;
   uint32_t group_m;         // tile rasterisation band height
+  FastDiv div_splits, div_per_batch, div_band, div_group;   // dividers of the work decode: splits, tiles_m * tiles_n, group_m * tiles_n, group_m
   uint32_t cta_pair;        // 1: two CTAs share a 256 x bn tile (tiles_m counts 256-row tiles)
   // TMA patch boxes (conv): positions per box and its decomposition
   uint32_t box_w, box_h, box_n;

@@ -366,6 +366,10 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
   info.k_blocks = p.k_blocks_total;
   info.work_items = p.tiles_m * p.tiles_n * p.batch * p.splits;
   info.kernel_launches = p.k == 0 ? 1 : (p.splits > 1 ? 2 : 1);
+  p.div_splits = gb::make_fastdiv_host(p.splits);
+  p.div_per_batch = gb::make_fastdiv_host(p.tiles_m * p.tiles_n);
+  p.div_band = gb::make_fastdiv_host(p.group_m * p.tiles_n);
+  p.div_group = gb::make_fastdiv_host(p.group_m);
   // Row-major results whose rows start on 16-byte boundaries leave through a TMA store: a map of C as
   // {n, m, batch} with a box of 64 bytes x 32 rows, the block one epilogue warp stages per chunk.
   p.tma_store = 0;
