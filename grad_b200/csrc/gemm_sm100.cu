@@ -268,11 +268,12 @@ __device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint3
   index = is_b ? lane - na : lane;
   kind = is_b ? p.b_kind : p.a_kind;
   b.tmap = is_b ? tmap_b : tmap_a;
-  const uint32_t a_bytes = p.a_stage_bytes ? p.a_stage_bytes : kATileBytes;
+  const uint32_t kmul = max(p.k_mul, 1u);
+  const uint32_t a_bytes = p.a_stage_bytes ? p.a_stage_bytes : kATileBytes * kmul;
   const uint32_t b_tap = !p.col_taps ? 0u : (nb_tap <= 1 ? index : index / nb_tap);   // which tap's B tile this box fills
   b.tap = b_tap;
   if (p.col_taps && is_b) index -= b_tap * nb_tap;
-  b.smem_off = (is_b ? a_bytes + b_tap * b_lines * kLineBytes : 0u) + index * epl * kLineBytes;
+  b.smem_off = (is_b ? a_bytes + b_tap * b_lines * kLineBytes : 0u) + index * epl * kLineBytes * kmul;
   b.n0 = b.n1 = kNever;
   b.i0 = b.i1 = 0;
   b.ax = b.ay = b.az = b.aw = b.bx = b.by = b.bz = b.bw = b.cx = b.cy = b.cz = b.cw = 0;
@@ -295,7 +296,7 @@ __device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint3
   }
   switch (kind) {
     case kDenseK: b.ax = epl; break;
-    case kDenseMN: b.ay = epl; break;
+    case kDenseMN: b.ay = epl * (int32_t)kmul; break;
     case kPatchK: {
       const int32_t cblocks = (int32_t)p.walk.cblocks;
       b.n0 = p.walk.cblocks; b.n1 = p.walk.n1;
@@ -333,7 +334,7 @@ __device__ __forceinline__ void box_start(const GemmParams& p, BoxLane& b, uint3
   if (!b.active) return;
   const uint32_t epl = p.tf32 ? 32u : 64u;
   const uint32_t mn0 = is_b ? n0 : m0;
-  const uint32_t k0 = work.kb_begin;
+  const uint32_t k0 = work.kb_begin * max(p.k_mul, 1u);   // in 64- (32-) wide K blocks
   b.i0 = b.i1 = 0;
   b.w = 0;
   if (p.col_taps) {   // column-patch plans never split K: every tile starts at the first tap column
@@ -787,8 +788,9 @@ __device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t
   // K-major: the four K slices of a stage sit 32 bytes apart inside each line.  MN-major: a slice is 16
   // (bf16) or 8 (tf32) whole lines, and 64-/32-wide MN blocks follow each other every epl lines.
   const uint32_t slice_lines = p.tf32 ? 8u : 16u;
-  const uint32_t a_lbo = p.a_mn_major ? epl * kLineBytes : 16u, a_step = p.a_mn_major ? slice_lines * kLineBytes : 32u;
-  const uint32_t b_lbo = p.b_mn_major ? epl * kLineBytes : 16u, b_step = p.b_mn_major ? slice_lines * kLineBytes : 32u;
+  const uint32_t kmul = max(p.k_mul, 1u);
+  const uint32_t a_lbo = p.a_mn_major ? epl * kLineBytes * kmul : 16u, a_step = p.a_mn_major ? slice_lines * kLineBytes : 32u;
+  const uint32_t b_lbo = p.b_mn_major ? epl * kLineBytes * kmul : 16u, b_step = p.b_mn_major ? slice_lines * kLineBytes : 32u;
   // MN-major tf32 tiles use the 32-byte-chunk swizzle whose atom is four lines (512 bytes).
   const uint32_t a_mode = (p.tf32 && p.a_mn_major) ? kSwizzle128Base32 : kSwizzle128, a_sbo = (p.tf32 && p.a_mn_major) ? 512u : 1024u;
   const uint32_t b_mode = (p.tf32 && p.b_mn_major) ? kSwizzle128Base32 : kSwizzle128, b_sbo = (p.tf32 && p.b_mn_major) ? 512u : 1024u;
@@ -813,6 +815,16 @@ __device__ __forceinline__ void mma_stage(const MmaSetup& s, uint32_t tmem_d, ui
   mma_issue<kPair, kTf32>(tmem_d, da + 2 * s.a_step16, db + 2 * s.b_step16, s.idesc, 1u);
   mma_issue<kPair, kTf32>(tmem_d, da + 3 * s.a_step16, db + 3 * s.b_step16, s.idesc, 1u);
 }
+// The further K blocks of a stage that holds several (MN-major tiles: the next block is the next 64 / 32 lines).
+template <bool kPair, bool kTf32>
+__device__ __forceinline__ void mma_stage_more(const MmaSetup& s, uint32_t tmem_d, uint32_t stage, uint32_t kmul) {
+  for (uint32_t t = 1; t < kmul; ++t) {
+    const uint64_t da = s.a_desc0 + (uint64_t)(stage * s.stage16 + 4 * t * s.a_step16);
+    const uint64_t db = s.b_desc0 + (uint64_t)(stage * s.stage16 + 4 * t * s.b_step16);
+#pragma unroll
+    for (uint32_t q = 0; q < 4; ++q) mma_issue<kPair, kTf32>(tmem_d, da + q * s.a_step16, db + q * s.b_step16, s.idesc, 1u);
+  }
+}
 
 // ---- the kernel ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(448, 1)
@@ -822,8 +834,9 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   SmemHeader* hdr = (SmemHeader*)smem;
   uint8_t* tiles = smem + kHeaderBytes;
-  const uint32_t b_tile_bytes = p.bn * kLineBytes;
-  const uint32_t a_bytes = p.a_stage_bytes ? p.a_stage_bytes : kATileBytes, b_tiles = max(p.col_taps, 1u);
+  const uint32_t kmul = max(p.k_mul, 1u);
+  const uint32_t b_tile_bytes = p.bn * kLineBytes * kmul;
+  const uint32_t a_bytes = p.a_stage_bytes ? p.a_stage_bytes : kATileBytes * kmul, b_tiles = max(p.col_taps, 1u);
   const uint32_t stage_bytes = a_bytes + b_tiles * b_tile_bytes;
   volatile uint32_t* abort_flag = &hdr->abort_flag;
 
@@ -860,7 +873,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 
   if (warp == 0) {
     // ===== TMA producer: one lane per box =====
-    const uint32_t tx_bytes = (p.a_kind != kGather ? (p.col_taps ? p.a_box_bytes : kATileBytes) : 0u) + (p.b_kind != kGather ? b_tiles * b_tile_bytes : 0u);
+    const uint32_t tx_bytes = (p.a_kind != kGather ? (p.col_taps ? p.a_box_bytes : kATileBytes * kmul) : 0u) + (p.b_kind != kGather ? b_tiles * b_tile_bytes : 0u);
     const uint32_t n_boxes = boxes_of(p.a_kind, kBM, epl) + b_tiles * boxes_of(p.b_kind, p.bn, epl);
     if (lane < max(n_boxes, 1u)) {
       uint32_t stage = 0, phase = 0;
@@ -914,8 +927,13 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
               if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, (kb > work.kb_begin) | (t > 0), b16, a16);
               else mma_stage<false, false>(ms, tmem_d, stage, (kb > work.kb_begin) | (t > 0), b16, a16);
             }
-          } else if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, kb > work.kb_begin);
-          else mma_stage<false, false>(ms, tmem_d, stage, kb > work.kb_begin);
+          } else if (p.tf32) {
+            mma_stage<false, true>(ms, tmem_d, stage, kb > work.kb_begin);
+            mma_stage_more<false, true>(ms, tmem_d, stage, kmul);
+          } else {
+            mma_stage<false, false>(ms, tmem_d, stage, kb > work.kb_begin);
+            mma_stage_more<false, false>(ms, tmem_d, stage, kmul);
+          }
           mma_commit(&hdr->empty[stage]);
           stage = next_stage;
           phase = next_phase;
@@ -1199,7 +1217,8 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
 size_t gemm_smem_bytes(const GemmParams& p) {
   const size_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
   return 1024 /* alignment slack */ + kHeaderBytes +
-         (size_t)p.stages * ((p.a_stage_bytes ? p.a_stage_bytes : kATileBytes) + (p.col_taps ? p.col_taps : 1u) * b_lines * kLineBytes) +
+         (size_t)p.stages * ((p.a_stage_bytes ? p.a_stage_bytes : kATileBytes * (p.k_mul ? p.k_mul : 1u)) +
+                             (p.col_taps ? p.col_taps : 1u) * b_lines * kLineBytes * (p.k_mul ? p.k_mul : 1u)) +
          (p.tma_store ? kStoreSmemBytes : 0);
 }
 

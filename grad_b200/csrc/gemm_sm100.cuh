@@ -74,6 +74,7 @@ struct GemmParams {
   uint32_t tiles_m, tiles_n, splits, k_blocks_per_split, k_blocks_total;
   uint32_t bn;              // tile columns (multiple of 32, <= 256)
   uint32_t stages;
+  uint32_t k_mul;           // > 1: both operands are MN-major TMA tiles and a stage holds k_mul K blocks (boxes of k_mul times as many lines)
   uint32_t tf32;            // 1: kind::tf32 on f32 tiles (32 elements per line), 0: kind::f16 on bf16 tiles (64 per line)
   uint32_t a_kind, b_kind;  // OperandKind
   uint32_t a_mn_major, b_mn_major;

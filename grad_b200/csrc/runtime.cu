@@ -59,6 +59,7 @@ struct Knobs {
   bool no_direct_conv = false;   // GB_NO_DIRECT_CONV: the stem goes through the gathered tensor plan
   bool no_strided_tma = false;   // GB_NO_STRIDED_TMA: strided forward / weight-gradient patches are gathered
   bool no_dgrad_classes = false; // GB_NO_DGRAD_CLASSES: a strided input gradient is one gathered product
+  bool no_wide_stages = false;   // GB_NO_WIDE_STAGES: weight gradients keep one K block per stage
 };
 const Knobs& knobs() {
   static const Knobs k = [] {
@@ -70,6 +71,7 @@ const Knobs& knobs() {
     v.no_direct_conv = getenv("GB_NO_DIRECT_CONV") != nullptr;
     v.no_strided_tma = getenv("GB_NO_STRIDED_TMA") != nullptr;
     v.no_dgrad_classes = getenv("GB_NO_DGRAD_CLASSES") != nullptr;
+    v.no_wide_stages = getenv("GB_NO_WIDE_STAGES") != nullptr;
     return v;
   }();
   return k;
@@ -135,7 +137,7 @@ void fill_dense_gather(gb::GatherDesc& g, const DenseOperand& o) {
 }
 
 // Tries to describe a dense operand by a TMA map {inner, lines, batch, 1}; false means "gather it".
-bool dense_tma(CUtensorMap* map, const DenseOperand& o, bool smem_bf16, uint32_t batch, uint32_t tile_mn, uint32_t epl) {
+bool dense_tma(CUtensorMap* map, const DenseOperand& o, bool smem_bf16, uint32_t batch, uint32_t tile_mn, uint32_t epl, uint32_t k_mul = 1) {
   const uint32_t es = smem_bf16 ? 2 : 4;
   if ((o.dtype == GB_BF16) != smem_bf16) return false;
   if (!aligned16(o.base) || ((uint64_t)o.ld * es) % 16 != 0) return false;
@@ -145,7 +147,7 @@ bool dense_tma(CUtensorMap* map, const DenseOperand& o, bool smem_bf16, uint32_t
   const uint64_t batch_bytes = batch > 1 ? o.batch_stride * es : (uint64_t)o.ld * es * std::max<uint64_t>(o.lines, 1);
   const uint64_t strides[3] = {(uint64_t)o.ld * es, batch_bytes, batch_bytes * batch};
   // K-major: box = 128 bytes of K x tile_mn lines.  MN-major: box = 128 bytes of MN x epl K lines.
-  const uint32_t box[4] = {epl, o.mn_major ? epl : tile_mn, 1, 1};
+  const uint32_t box[4] = {epl, o.mn_major ? epl * k_mul : tile_mn, 1, 1};
   if (box[1] > 256) return false;
   // MN-major 32-bit tiles must use the 32-byte-chunk flavour of the 128-byte swizzle.
   return encode_map(map, smem_bf16, o.base, 4, dims, strides, box, !smem_bf16 && o.mn_major);
@@ -385,7 +387,8 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
   if (plan.tensor) {
     // The stage ring takes what the epilogue's own shared memory leaves of the 227 KB a CTA can have.
     const uint32_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
-    const size_t stage = (p.a_stage_bytes ? p.a_stage_bytes : 128 * 128) + (size_t)std::max(p.col_taps, 1u) * b_lines * 128;
+    const size_t stage = (p.a_stage_bytes ? p.a_stage_bytes : 128 * 128 * std::max(p.k_mul, 1u)) +
+                         (size_t)std::max(p.col_taps, 1u) * b_lines * 128 * std::max(p.k_mul, 1u);
     const size_t fixed = gb::gemm_smem_bytes(p) - (size_t)p.stages * stage;
     const uint32_t fit = (uint32_t)((227 * 1024 - fixed) / stage);
     p.stages = std::max(2u, std::min(p.stages, fit));
@@ -628,6 +631,24 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
           nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, true, g.stride))
         p.a_kind = gb::kPatchMN;
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
+      // Both operands are MN-major (one line per position), so two K blocks per stage are simply boxes of twice
+      // as many lines: half the stages, barrier round trips and producer iterations for the same MMAs.  (The K
+      // loop of a weight gradient is producer-bound: ~570 cycles per stage against 256 of MMA time.)
+      uint32_t bw2, bh2, bn2;
+      CUtensorMap a2, b2;
+      if (p.a_kind == gb::kPatchMN && p.b_kind == gb::kDenseMN && !knobs().no_wide_stages && p.k_blocks_total >= 8 &&
+          patch_box(2 * epl, g.out_h, g.out_w, bw2, bh2, bn2) &&
+          nhwc_tma(&a2, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, bw2, bh2, bn2, true, g.stride) &&
+          dense_tma(&b2, ob, smem_bf16, 1, p.bn, epl, 2)) {
+        plan.tmap_a = a2; plan.tmap_b = b2;
+        p.box_w = bw2; p.box_h = bh2; p.box_n = bn2;
+        p.k_mul = 2;
+        p.k_blocks_total = ceil_div(p.k_blocks_total, 2);
+        p.k_blocks_per_split = std::max(1u, ceil_div(p.k_blocks_total, p.splits));
+        p.splits = std::max(1u, ceil_div(p.k_blocks_total, p.k_blocks_per_split));
+        plan.workspace = p.splits > 1 ? (size_t)p.splits * p.batch * p.m * p.n * sizeof(float) : 0;
+        p.stages = std::min<uint32_t>(8, (227 * 1024 - 2048) / (2 * (128 * 128 + p.bn * 128)));
+      }
     }
   }
   return GB_OK;
