@@ -868,6 +868,10 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  // Everything above touched only this CTA's shared and tensor memory, so it may overlap the tail of the previous
+  // kernel in the stream; from here on global memory is read and written.
+  grid_launch_dependents();
+  grid_dependency_wait();
   const uint32_t tmem_base = hdr->tmem_base;
   const uint32_t epl = p.tf32 ? 32u : 64u;
 
@@ -1066,6 +1070,8 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
   __syncthreads();
   cluster_sync_all();                   // the partner's barriers are initialised before anyone signals them
   tc_fence_after_sync();
+  grid_launch_dependents();             // see the single-CTA kernel
+  grid_dependency_wait();
   const uint32_t tmem_base = hdr->tmem_base;
   const uint32_t epl = p.tf32 ? 32u : 64u;
 
@@ -1262,6 +1268,26 @@ cudaError_t gemm_sm100_configure() {
   return cudaFuncSetAttribute(gemm_sm100_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
+// Launch with programmatic stream serialization: the kernel's prologue (barriers, TMEM, cluster sync) may run
+// while the previous kernel of the stream drains; the kernel itself waits (griddepcontrol.wait) before its first
+// global access.  GB_NO_OVERLAPPED_LAUNCH=1 falls back to plain stream order.
+template <class Kernel>
+static cudaError_t launch_overlapped(Kernel kernel, uint32_t grid, uint32_t block, size_t smem, cudaStream_t stream, const GemmParams& p,
+                                     const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c) {
+  static const bool plain = getenv("GB_NO_OVERLAPPED_LAUNCH") != nullptr;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = plain ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p, tmap_a, tmap_b, tmap_c);
+}
+
 cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c, int sm_count,
                               cudaStream_t stream) {
   const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
@@ -1272,13 +1298,11 @@ cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, co
     // co-resident 2-CTA clusters can be below sm_count / 2 (SMs are paired within a GPC), and a cluster
     // left waiting would run its whole share of tiles after the others have finished.
     const uint32_t pairs = std::min<uint32_t>(total_work, max_resident_pairs(gemm_smem_bytes(p), sm_count));
-    gemm_sm100_pair_kernel<<<2 * pairs, 64 + 128 * p.epi_groups, gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b, tmap_c);
-    return cudaGetLastError();
+    return launch_overlapped(gemm_sm100_pair_kernel, 2 * pairs, 64 + 128 * p.epi_groups, gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
   }
   const bool gather = p.a_kind == kGather || p.b_kind == kGather;
   const uint32_t grid = total_work < (uint32_t)sm_count ? total_work : (uint32_t)sm_count;
-  gemm_sm100_kernel<<<grid, 64 + 128 * p.epi_groups + (gather ? 128 : 0), gemm_smem_bytes(p), stream>>>(p, tmap_a, tmap_b, tmap_c);
-  return cudaGetLastError();
+  return launch_overlapped(gemm_sm100_kernel, grid, 64 + 128 * p.epi_groups + (gather ? 128 : 0), gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
 }
 
 cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream) {

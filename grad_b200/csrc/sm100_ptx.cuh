@@ -96,6 +96,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in the stream
+// is still running; `grid_dependency_wait` returns once every predecessor has completed and its memory is
+// visible, `grid_launch_dependents` lets the successor start being scheduled.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- proxies and fences -------------------------------------------------------------------------
 // Generic-proxy shared-memory writes (st.shared) become visible to the async proxy (TMA, tcgen05.mma).
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
