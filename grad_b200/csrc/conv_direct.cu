@@ -30,6 +30,8 @@ __device__ __forceinline__ float round_operand(float v, uint32_t tf32) {
 // read feeds 16 FMAs.
 __global__ void __launch_bounds__(128) conv_direct_kernel(const GemmParams p) {
   extern __shared__ float w_s[];
+  grid_launch_dependents();   // launched with programmatic stream serialization: wait for the stream's earlier work
+  grid_dependency_wait();
   const ConvGeo& g = p.geo;
   const uint32_t kk = g.k * g.k * g.c;
   for (uint32_t i = threadIdx.x; i < kk * g.c_out; i += blockDim.x) {
@@ -165,8 +167,7 @@ cudaError_t launch_conv_direct(const GemmParams& p, int sm_count, cudaStream_t s
   const uint64_t items = (uint64_t)((p.m + kPos - 1) / kPos) * (g.c_out / kCoChunk);
   const uint64_t want64 = (items + 127) / 128;
   const uint32_t cap = (uint32_t)sm_count * 16, want = (uint32_t)(want64 < cap ? want64 : cap);
-  conv_direct_kernel<<<want < cap ? want : cap, 128, smem, stream>>>(p);
-  return cudaGetLastError();
+  return launch_overlapped(conv_direct_kernel, dim3(want < cap ? want : cap), dim3(128), smem, stream, p);
 }
 
 }  // namespace gb

@@ -1200,6 +1200,8 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
 // Ordered combine of split-K partials followed by the epilogue; one thread per output element.
 // Takes the place of grad's `splitCombine` (src/gpu/device.zig:664-670), which only deterministic runs use.
 __global__ void splitk_reduce_kernel(const GemmParams p) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const uint64_t per_batch = (uint64_t)p.m * p.n;
   const uint64_t total = per_batch * p.batch;
   for (uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (uint64_t)gridDim.x * blockDim.x) {
@@ -1268,26 +1270,6 @@ cudaError_t gemm_sm100_configure() {
   return cudaFuncSetAttribute(gemm_sm100_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
-// Launch with programmatic stream serialization: the kernel's prologue (barriers, TMEM, cluster sync) may run
-// while the previous kernel of the stream drains; the kernel itself waits (griddepcontrol.wait) before its first
-// global access.  GB_NO_OVERLAPPED_LAUNCH=1 falls back to plain stream order.
-template <class Kernel>
-static cudaError_t launch_overlapped(Kernel kernel, uint32_t grid, uint32_t block, size_t smem, cudaStream_t stream, const GemmParams& p,
-                                     const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c) {
-  static const bool plain = getenv("GB_NO_OVERLAPPED_LAUNCH") != nullptr;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(block, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = plain ? 0 : 1;
-  return cudaLaunchKernelEx(&cfg, kernel, p, tmap_a, tmap_b, tmap_c);
-}
-
 cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c, int sm_count,
                               cudaStream_t stream) {
   const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
@@ -1298,19 +1280,18 @@ cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, co
     // co-resident 2-CTA clusters can be below sm_count / 2 (SMs are paired within a GPC), and a cluster
     // left waiting would run its whole share of tiles after the others have finished.
     const uint32_t pairs = std::min<uint32_t>(total_work, max_resident_pairs(gemm_smem_bytes(p), sm_count));
-    return launch_overlapped(gemm_sm100_pair_kernel, 2 * pairs, 64 + 128 * p.epi_groups, gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
+    return launch_overlapped(gemm_sm100_pair_kernel, dim3(2 * pairs), dim3(64 + 128 * p.epi_groups), gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
   }
   const bool gather = p.a_kind == kGather || p.b_kind == kGather;
   const uint32_t grid = total_work < (uint32_t)sm_count ? total_work : (uint32_t)sm_count;
-  return launch_overlapped(gemm_sm100_kernel, grid, 64 + 128 * p.epi_groups + (gather ? 128 : 0), gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
+  return launch_overlapped(gemm_sm100_kernel, dim3(grid), dim3(64 + 128 * p.epi_groups + (gather ? 128 : 0)), gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
 }
 
 cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream) {
   const uint64_t total = (uint64_t)p.m * p.n * p.batch;
   if (total == 0) return cudaSuccess;
   const uint32_t blocks = (uint32_t)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p);
-  return cudaGetLastError();
+  return launch_overlapped(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, p);
 }
 
 }  // namespace gb

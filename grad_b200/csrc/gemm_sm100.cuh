@@ -2,6 +2,8 @@
 #pragma once
 
 #include <cuda.h>
+#include <cstdlib>
+#include <utility>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -116,6 +118,24 @@ struct GemmParams {
 constexpr uint32_t kStoreStageBytesPerWarp = 2048;
 constexpr uint32_t kStoreBiasBytesPerWarp = 1024;
 constexpr uint32_t kStoreSmemBytes = 8 * (kStoreStageBytesPerWarp + kStoreBiasBytesPerWarp);
+// Launch with programmatic stream serialization (the kernel must execute griddepcontrol.wait before its first
+// global access).  GB_NO_OVERLAPPED_LAUNCH=1 falls back to plain stream order.
+template <class... KernelArgs, class... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  static const bool plain = getenv("GB_NO_OVERLAPPED_LAUNCH") != nullptr;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = plain ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 size_t gemm_smem_bytes(const GemmParams& p);
 cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c, int sm_count,
                               cudaStream_t stream);

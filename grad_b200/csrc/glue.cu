@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include "../../include/gradb200.h"
+#include "gemm_sm100.cuh"
 #include "sm100_ptx.cuh"
 
 namespace {
@@ -47,6 +48,8 @@ __global__ void pool2d_kernel(const void* x, void* y, int bf16, int is_max, uint
 // the 537 MB activation of a 4096-image ResNet stage.)
 __global__ void __launch_bounds__(256) pool2d_bf16x8_kernel(const uint4* x, uint4* y, int is_max, uint32_t n, uint32_t h, uint32_t w, uint32_t c8,
                                                             uint32_t k, uint32_t stride, uint32_t pad, uint32_t oh, uint32_t ow) {
+  gb::grid_launch_dependents();   // launched with programmatic stream serialization: wait for the stream's earlier work
+  gb::grid_dependency_wait();
   const uint32_t total = n * oh * ow * c8;   // the caller keeps this below 2^32
   for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gridDim.x * blockDim.x) {
     const uint32_t pix = t / c8, cg = t - pix * c8;
@@ -153,9 +156,9 @@ int gb_pool2d(void* stream, int is_max, int dtype, const void* x, void* y, uint3
   if (dtype == GB_BF16 && c % 8 == 0 && total / 8 < 0xFFFFFFFFull && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0) {
     const size_t groups = total / 8;
     const size_t want = (groups + 255) / 256;
-    pool2d_bf16x8_kernel<<<(unsigned)(want < 148 * 16 ? want : 148 * 16), 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)y, is_max, n, h, w, c / 8,
-                                                                                                          k, stride, pad, oh, ow);
-    return finish();
+    const cudaError_t e = gb::launch_overlapped(pool2d_bf16x8_kernel, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, (cudaStream_t)stream,
+                                                (const uint4*)x, (uint4*)y, is_max, n, h, w, c / 8, k, stride, pad, oh, ow);
+    return e == cudaSuccess ? GB_OK : GB_ERR_CUDA;
   }
   pool2d_kernel<<<blocks_for(total), 256, 0, (cudaStream_t)stream>>>(x, y, dtype == GB_BF16, is_max, n, h, w, c, k, stride, pad, oh, ow);
   return finish();
