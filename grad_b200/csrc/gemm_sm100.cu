@@ -47,6 +47,7 @@ struct SmemHeader {
 
 struct Work {
   uint32_t batch, m_tile, n_tile, split, kb_begin, kb_end;
+  uint32_t empty;   // fused classes: this tile lies past the rows of its class; every role skips it
 };
 
 __device__ __forceinline__ uint32_t fast_div(uint32_t a, const FastDiv& f) {
@@ -85,6 +86,11 @@ __device__ __forceinline__ Work decode_work(const GemmParams& p, uint32_t w) {
   }
   out.kb_begin = out.split * p.k_blocks_per_split;
   out.kb_end = min(out.kb_begin + p.k_blocks_per_split, p.k_blocks_total);
+  out.empty = 0;
+  if (p.n_classes) {
+    out.kb_end = p.cls[out.batch].k_blocks;
+    out.empty = out.m_tile * (p.cta_pair ? 2 * kBM : kBM) >= p.cls[out.batch].m;
+  }
   return out;
 }
 
@@ -258,8 +264,8 @@ __device__ __forceinline__ uint32_t boxes_of(uint32_t kind, uint32_t lines, uint
 }
 
 // Once per kernel: which box this lane owns and how its coordinates step along K.
-__device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint32_t lane, const CUtensorMap* tmap_a, const CUtensorMap* tmap_b,
-                                          uint32_t b_lines, uint32_t& kind, uint32_t& index) {
+__device__ __forceinline__ void box_setup(const GemmParams& p, const TapWalk& walk, BoxLane& b, uint32_t lane, const CUtensorMap* tmap_a,
+                                          const CUtensorMap* tmap_b, uint32_t b_lines, uint32_t& kind, uint32_t& index) {
   const int32_t epl = p.tf32 ? 32 : 64;
   const uint32_t nb_tap = boxes_of(p.b_kind, b_lines, epl);                   // B boxes of one tap
   const uint32_t na = boxes_of(p.a_kind, kBM, epl), nb = nb_tap * max(p.col_taps, 1u);
@@ -281,36 +287,36 @@ __device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint3
   b.per_image = b.grid_w = FastDiv{1, 0};
   if (!b.active) return;
   if (kind == kPatchK) {
-    b.per_image = p.walk.div_image;
-    b.grid_w = p.walk.div_w;
+    b.per_image = walk.div_image;
+    b.grid_w = walk.div_w;
   }
   if (p.col_taps && is_b) {
     // B of a column-patch plan: channel blocks innermost, then the next tap column; the tap along y is fixed.
-    const int32_t cblocks = (int32_t)p.walk.cblocks, chan = cblocks * epl;
-    b.n0 = p.walk.cblocks;
-    const int32_t next_col = p.walk.tap_x * chan - (cblocks - 1) * epl;
+    const int32_t cblocks = (int32_t)walk.cblocks, chan = cblocks * epl;
+    b.n0 = walk.cblocks;
+    const int32_t next_col = walk.tap_x * chan - (cblocks - 1) * epl;
     if (kind == kDenseK) { b.ax = epl; b.bx = next_col; }
     if (kind == kDenseMN) { b.ay = epl; b.by = next_col; }
-    if (kind == kWeightK) { b.ax = epl; b.bx = -(cblocks - 1) * epl; b.bz = p.walk.tap_x; }
+    if (kind == kWeightK) { b.ax = epl; b.bx = -(cblocks - 1) * epl; b.bz = walk.tap_x; }
     return;
   }
   switch (kind) {
     case kDenseK: b.ax = epl; break;
     case kDenseMN: b.ay = epl * (int32_t)kmul; break;
     case kPatchK: {
-      const int32_t cblocks = (int32_t)p.walk.cblocks;
-      b.n0 = p.walk.cblocks; b.n1 = p.walk.n1;
+      const int32_t cblocks = (int32_t)walk.cblocks;
+      b.n0 = walk.cblocks; b.n1 = walk.n1;
       b.ax = epl;
-      b.bx = -(cblocks - 1) * epl; b.by = p.walk.y_step;
-      b.cx = b.bx; b.cy = -((int32_t)p.walk.n1 - 1) * p.walk.y_step; b.cz = p.walk.z_step;
+      b.bx = -(cblocks - 1) * epl; b.by = walk.y_step;
+      b.cx = b.bx; b.cy = -((int32_t)walk.n1 - 1) * walk.y_step; b.cz = walk.z_step;
       break;
     }
     case kWeightK: {
-      const int32_t cblocks = (int32_t)p.walk.cblocks;
-      b.n0 = p.walk.cblocks; b.n1 = p.walk.n1;
+      const int32_t cblocks = (int32_t)walk.cblocks;
+      b.n0 = walk.cblocks; b.n1 = walk.n1;
       b.ax = epl;
-      b.bx = -(cblocks - 1) * epl; b.bz = p.walk.tap_x;
-      b.cx = b.bx; b.cz = p.walk.tap_y - ((int32_t)p.walk.n1 - 1) * p.walk.tap_x;
+      b.bx = -(cblocks - 1) * epl; b.bz = walk.tap_x;
+      b.cx = b.bx; b.cz = walk.tap_y - ((int32_t)walk.n1 - 1) * walk.tap_x;
       break;
     }
     case kPatchMN:
@@ -329,8 +335,8 @@ __device__ __forceinline__ void box_setup(const GemmParams& p, BoxLane& b, uint3
 
 // Once per tile: the box's coordinates and counters at K block work.kb_begin of a tile whose A rows start at m0
 // and B lines at n0.
-__device__ __forceinline__ void box_start(const GemmParams& p, BoxLane& b, uint32_t kind, uint32_t index, const Work& work, uint32_t m0,
-                                          uint32_t n0, bool is_b) {
+__device__ __forceinline__ void box_start(const GemmParams& p, const TapWalk& walk, BoxLane& b, uint32_t kind, uint32_t index, const Work& work,
+                                          uint32_t m0, uint32_t n0, bool is_b) {
   if (!b.active) return;
   const uint32_t epl = p.tf32 ? 32u : 64u;
   const uint32_t mn0 = is_b ? n0 : m0;
@@ -338,12 +344,12 @@ __device__ __forceinline__ void box_start(const GemmParams& p, BoxLane& b, uint3
   b.i0 = b.i1 = 0;
   b.w = 0;
   if (p.col_taps) {   // column-patch plans never split K: every tile starts at the first tap column
-    const int32_t tap = p.walk.tap0 + (int32_t)b.tap * p.walk.tap_y, chan = (int32_t)(p.walk.cblocks * epl);
+    const int32_t tap = walk.tap0 + (int32_t)b.tap * walk.tap_y, chan = (int32_t)(walk.cblocks * epl);
     if (!is_b) {
       const uint32_t img = fast_div(mn0, b.per_image);
       const int32_t row0 = (int32_t)fast_div(mn0 - img * b.per_image.d, b.grid_w);
-      const int32_t top = p.walk.z_step < 0 ? p.walk.z0 + ((int32_t)p.col_taps - 1) * p.walk.z_step : p.walk.z0;
-      b.x = 0; b.y = p.walk.y0; b.z = row0 + top; b.w = (int32_t)img;
+      const int32_t top = walk.z_step < 0 ? walk.z0 + ((int32_t)p.col_taps - 1) * walk.z_step : walk.z0;
+      b.x = 0; b.y = walk.y0; b.z = row0 + top; b.w = (int32_t)img;
     } else if (kind == kDenseK) {
       b.x = tap * chan; b.y = (int32_t)mn0; b.z = 0;
     } else if (kind == kDenseMN) {
@@ -369,11 +375,11 @@ __device__ __forceinline__ void box_start(const GemmParams& p, BoxLane& b, uint3
         tx = tap - ty * b.n1;
       }
       const uint32_t img = fast_div(mn0, b.per_image);
-      const int32_t row0 = p.box_n > 1 ? 0 : (int32_t)(fast_div(mn0 - img * b.per_image.d, b.grid_w) * p.walk.row_scale);
+      const int32_t row0 = p.box_n > 1 ? 0 : (int32_t)(fast_div(mn0 - img * b.per_image.d, b.grid_w) * walk.row_scale);
       b.i0 = cb; b.i1 = tx;
       b.x = (int32_t)(cb * epl);
-      b.y = p.walk.y0 + (int32_t)tx * p.walk.y_step;
-      b.z = row0 + p.walk.z0 + (int32_t)ty * p.walk.z_step;
+      b.y = walk.y0 + (int32_t)tx * walk.y_step;
+      b.z = row0 + walk.z0 + (int32_t)ty * walk.z_step;
       b.w = (int32_t)img;
       break;
     }
@@ -387,7 +393,7 @@ __device__ __forceinline__ void box_start(const GemmParams& p, BoxLane& b, uint3
       }
       b.i0 = cb; b.i1 = tx;
       b.x = (int32_t)(cb * epl); b.y = (int32_t)mn0;
-      b.z = p.walk.tap0 + (int32_t)tx * p.walk.tap_x + (int32_t)ty * p.walk.tap_y;
+      b.z = walk.tap0 + (int32_t)tx * walk.tap_x + (int32_t)ty * walk.tap_y;
       break;
     }
     case kPatchMN: {
@@ -442,19 +448,19 @@ __device__ __forceinline__ void store_out(void* base, uint32_t is_bf16, uint64_t
 // (one coalesced load per warp, fetched a chunk ahead by the caller); lanes trade it with shuffles, so every
 // lane runs the arithmetic and only the memory accesses are guarded by `live`.
 // Element offset of the start of product row `row` within one batch entry of C.
-__device__ __forceinline__ uint64_t out_row_offset(const GemmParams& p, uint32_t row) {
-  if (!p.rowmap.enabled) return (uint64_t)row * p.ldc;
-  const uint32_t img = fast_div(row, p.rowmap.per_image);
-  const uint32_t rem = row - img * p.rowmap.per_image.d;
-  const uint32_t i = fast_div(rem, p.rowmap.grid_w), j = rem - i * p.rowmap.grid_w.d;
-  const uint64_t pixel = ((uint64_t)img * p.rowmap.h + i * p.rowmap.scale + p.rowmap.off_y) * p.rowmap.w + j * p.rowmap.scale + p.rowmap.off_x;
+__device__ __forceinline__ uint64_t out_row_offset(const GemmParams& p, const RowMap& rm, uint32_t row) {
+  if (!rm.enabled) return (uint64_t)row * p.ldc;
+  const uint32_t img = fast_div(row, rm.per_image);
+  const uint32_t rem = row - img * rm.per_image.d;
+  const uint32_t i = fast_div(rem, rm.grid_w), j = rem - i * rm.grid_w.d;
+  const uint64_t pixel = ((uint64_t)img * rm.h + i * rm.scale + rm.off_y) * rm.w + j * rm.scale + rm.off_x;
   return pixel * p.ldc;
 }
 
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&acc)[32], uint32_t batch, uint32_t split,
-                                               uint32_t row, uint32_t col0, float bias_lane, uint64_t row_off) {
+                                               uint32_t row, uint32_t col0, float bias_lane, uint64_t row_off, uint32_t m_limit) {
   if (col0 >= p.n) return;
-  const bool live = row < p.m;
+  const bool live = row < m_limit;
   const uint32_t cols = min(32u, p.n - col0);
   if (p.splits > 1) {
     if (!live) return;
@@ -563,7 +569,7 @@ __device__ __noinline__ void epilogue_chunk_ragged(const GemmParams& p, const ui
   uint32_t copy[32];
 #pragma unroll
   for (uint32_t i = 0; i < 32; ++i) copy[i] = vals[i];
-  epilogue_chunk(p, copy, batch, split, row, col0, bias_lane, (uint64_t)row * p.ldc);
+  epilogue_chunk(p, copy, batch, split, row, col0, bias_lane, (uint64_t)row * p.ldc, p.m);
 }
 __device__ __forceinline__ void epilogue_chunk_copy(const GemmParams& p, const uint32_t (&acc)[32], uint32_t batch, uint32_t split, uint32_t row,
                                                     uint32_t col0, float bias_lane) {
@@ -708,6 +714,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
                                               uint32_t row, uint32_t col_base, bool wide, uint32_t lane,
                                               uint32_t first, uint32_t step, const CUtensorMap* tmap_c, uint8_t* store_stage, const float* sbias,
                                               Release release) {
+  // a fused class product places its rows by its own map and ends at its own row count
+  const RowMap& rowmap = p.n_classes ? p.cls[batch].rowmap : p.rowmap;
+  const uint32_t m_limit = p.n_classes ? p.cls[batch].m : p.m;
+  if (p.n_classes) batch = 0;   // the classes share one C: no batch stride
   if (first >= ncols) {
     release();
     return;
@@ -746,7 +756,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     return (p.bias != nullptr && c < ncols && col < p.n) ? p.bias[col] : 0.0f;
   };
   // This warp drains the 32-column chunks first, first + step, ...; two chunks are in flight (A and B registers).
-  const uint64_t row_off = out_row_offset(p, row);
+  const uint64_t row_off = out_row_offset(p, rowmap, row);
   uint32_t acc_a[32], acc_b[32];
   float bias_next = bias_at(first);
   tmem_ld_32x32(taddr + first, acc_a);
@@ -757,14 +767,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     else release();
     float bias_cur = bias_next;
     bias_next = bias_at(c + step);
-    epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur, row_off);
+    epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur, row_off, m_limit);
     if (has_b) {
       tmem_ld_wait();
       if (c + 2 * step < ncols) tmem_ld_32x32(taddr + c + 2 * step, acc_a);
       else release();
       bias_cur = bias_next;
       bias_next = bias_at(c + 2 * step);
-      epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur, row_off);
+      epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur, row_off, m_limit);
     }
   }
 }
@@ -884,12 +894,18 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       bool ok = true;
       BoxLane box;
       uint32_t box_kind, box_index;
-      box_setup(p, box, lane, &tmap_a, &tmap_b, p.bn, box_kind, box_index);
+      box_setup(p, p.walk, box, lane, &tmap_a, &tmap_b, p.bn, box_kind, box_index);
+      uint32_t cur_class = 0xFFFFFFFFu;
       const bool box_is_b = lane >= boxes_of(p.a_kind, kBM, epl);
       uint32_t ready = 1;   // the first pass over the ring finds every stage free
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const Work work = decode_work(p, w);
-        box_start(p, box, box_kind, box_index, work, work.m_tile * kBM, work.n_tile * p.bn, box_is_b);
+        if (work.empty) continue;
+        if (p.n_classes && work.batch != cur_class) {   // a new class: its own K walk
+          box_setup(p, p.cls[work.batch].walk, box, lane, &tmap_a, &tmap_b, p.bn, box_kind, box_index);
+          cur_class = work.batch;
+        }
+        box_start(p, p.n_classes ? p.cls[work.batch].walk : p.walk, box, box_kind, box_index, work, work.m_tile * kBM, work.n_tile * p.bn, box_is_b);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_peeked(&hdr->empty[stage], phase ^ 1, ready, abort_flag, kStatusProducerTimeout))) break;
           uint32_t next_stage = stage + 1, next_phase = phase;
@@ -915,6 +931,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       uint32_t ready = 0;   // the first stage is waited for in the ordinary way
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const Work work = decode_work(p, w);
+        if (work.empty) continue;
         if (!(ok = mbar_wait_fast(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * p.bn;
@@ -960,6 +977,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     uint32_t bias_tile = 0xFFFFFFFFu;   // the column tile whose bias values sit in shared memory
     for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       const Work work = decode_work(p, w);
+      if (work.empty) continue;
       if (tma_out && bias_tile != work.n_tile) {
         stage_bias(p, sbias, p.bn, work.n_tile * p.bn, false, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
         bias_tile = work.n_tile;
@@ -986,6 +1004,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     bool ok = true;
     for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       const Work work = decode_work(p, w);
+      if (work.empty) continue;
       for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
         ok = mbar_wait(&hdr->empty[stage], phase ^ 1, abort_flag, kStatusProducerTimeout);
         ok = __all_sync(0xFFFFFFFFu, ok);
@@ -1088,12 +1107,19 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       bool ok = true;
       BoxLane box;
       uint32_t box_kind, box_index;
-      box_setup(p, box, lane, &tmap_a, &tmap_b, b_lines, box_kind, box_index);
+      box_setup(p, p.walk, box, lane, &tmap_a, &tmap_b, b_lines, box_kind, box_index);
+      uint32_t cur_class = 0xFFFFFFFFu;
       const bool box_is_b = lane >= boxes_of(p.a_kind, kBM, epl);
       uint32_t ready = 1;   // the first pass over the ring finds every stage free
       for (uint32_t w = pair; ok && w < total_work; w += pairs) {
         const Work work = decode_work(p, w);
-        box_start(p, box, box_kind, box_index, work, work.m_tile * 2 * kBM + rank * kBM, work.n_tile * p.bn + rank * b_lines, box_is_b);
+        if (work.empty) continue;
+        if (p.n_classes && work.batch != cur_class) {   // a new class: its own K walk
+          box_setup(p, p.cls[work.batch].walk, box, lane, &tmap_a, &tmap_b, b_lines, box_kind, box_index);
+          cur_class = work.batch;
+        }
+        box_start(p, p.n_classes ? p.cls[work.batch].walk : p.walk, box, box_kind, box_index, work, work.m_tile * 2 * kBM + rank * kBM,
+                  work.n_tile * p.bn + rank * b_lines, box_is_b);
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_peeked(&hdr->empty[stage], phase ^ 1, ready, abort_flag, kStatusProducerTimeout))) break;
           uint32_t next_stage = stage + 1, next_phase = phase;
@@ -1118,6 +1144,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       uint32_t ready = 0;
       for (uint32_t w = pair; ok && w < total_work; w += pairs) {
         const Work work = decode_work(p, w);
+        if (work.empty) continue;
         if (!(ok = mbar_wait_fast(&hdr->acc_empty[buf], buf_phase ^ 1, abort_flag, kStatusMmaTimeout))) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * acc_stride;
@@ -1163,6 +1190,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     uint32_t bias_tile = 0xFFFFFFFFu;   // the column tile whose bias values sit in shared memory
     for (uint32_t w = pair; ok && w < total_work; w += pairs) {
       const Work work = decode_work(p, w);
+      if (work.empty) continue;
       if (tma_out && bias_tile != work.n_tile) {
         stage_bias(p, sbias, p.bn, work.n_tile * p.bn, halves == 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
         bias_tile = work.n_tile;

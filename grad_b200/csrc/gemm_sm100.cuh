@@ -70,6 +70,14 @@ struct RowMap {
   uint32_t h, w, scale, off_y, off_x;
 };
 
+// One parity class of a fused strided input gradient (see `GemmParams::n_classes`).
+struct ClassSlot {
+  TapWalk walk;
+  RowMap rowmap;
+  uint32_t m, k_blocks;   // rows and K blocks of this class's product
+};
+constexpr uint32_t kMaxClasses = 4;
+
 struct GemmParams {
   // problem
   uint32_t m, n, k, batch;
@@ -97,6 +105,10 @@ struct GemmParams {
   uint32_t a_box_bytes;     // bytes the A box really delivers
   int32_t col_a_first16, col_a_step16;
   RowMap rowmap;            // output row placement (disabled: row m of C)
+  // > 0: the batch index selects one of `n_classes` products that share operands, tile shape and C but have their
+  // own tap walk, row map, row count and K length (the parity classes of a strided input gradient in one launch)
+  uint32_t n_classes;
+  ClassSlot cls[kMaxClasses];
   // gather sources
   GatherDesc ga, gbsrc;
   // output

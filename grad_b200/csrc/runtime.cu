@@ -60,6 +60,7 @@ struct Knobs {
   bool no_strided_tma = false;   // GB_NO_STRIDED_TMA: strided forward / weight-gradient patches are gathered
   bool no_dgrad_classes = false; // GB_NO_DGRAD_CLASSES: a strided input gradient is one gathered product
   bool no_wide_stages = false;   // GB_NO_WIDE_STAGES: weight gradients keep one K block per stage
+  bool no_fused_classes = false; // GB_NO_FUSED_CLASSES: one launch per parity class of a strided input gradient
 };
 const Knobs& knobs() {
   static const Knobs k = [] {
@@ -72,6 +73,7 @@ const Knobs& knobs() {
     v.no_strided_tma = getenv("GB_NO_STRIDED_TMA") != nullptr;
     v.no_dgrad_classes = getenv("GB_NO_DGRAD_CLASSES") != nullptr;
     v.no_wide_stages = getenv("GB_NO_WIDE_STAGES") != nullptr;
+    v.no_fused_classes = getenv("GB_NO_FUSED_CLASSES") != nullptr;
     return v;
   }();
   return k;
@@ -768,6 +770,34 @@ int run_dgrad_classes(gb_handle* h, cudaStream_t stream, const gb_conv_desc* d, 
     if (g.c_step != g.c) return GB_ERR_UNSUPPORTED;
     const cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)g.n * g.h * g.w * g.c * elem_size(d->dtype_x), stream);
     if (e != cudaSuccess) return cuda_fail(h, e);
+  }
+  // Classes that agree on tile shape, pair mode and patch box run as ONE launch: the class is the batch index of
+  // the work decode, and its tap walk, row map, row count and K length sit in a slot of the parameters.  (Four
+  // launches of a strided ResNet layer cost ~13 us each, mostly fixed cost.)
+  if (plans.size() >= 2 && plans.size() <= gb::kMaxClasses && !knobs().no_fused_classes) {
+    size_t lead = 0;
+    bool same = true;
+    for (size_t i = 0; i < plans.size(); ++i) {
+      const GemmParams &a = plans[i].p, &b = plans[0].p;
+      same = same && a.bn == b.bn && a.cta_pair == b.cta_pair && a.box_w == b.box_w && a.box_h == b.box_h && a.box_n == b.box_n &&
+             a.walk.grid_h == b.walk.grid_h && a.walk.grid_w == b.walk.grid_w && a.splits == 1 && a.col_taps == 0 && a.k_mul <= 1;
+      if (a.k_blocks_total > plans[lead].p.k_blocks_total) lead = i;
+    }
+    if (same) {
+      Plan fused = plans[lead];
+      GemmParams& f = fused.p;
+      f.n_classes = (uint32_t)plans.size();
+      f.batch = f.n_classes;
+      f.stride_c = 0;
+      for (size_t i = 0; i < plans.size(); ++i) {
+        const GemmParams& c = plans[i].p;
+        f.cls[i].walk = c.walk; f.cls[i].rowmap = c.rowmap; f.cls[i].m = c.m; f.cls[i].k_blocks = c.k_blocks_total;
+        f.m = std::max(f.m, c.m);
+        f.tiles_m = std::max(f.tiles_m, c.tiles_m);
+      }
+      f.k_blocks_per_split = f.k_blocks_total;
+      return run_plan(h, stream, fused, nullptr, 0);
+    }
   }
   uint32_t launches = 0, items = 0;
   for (Plan& plan : plans) {
