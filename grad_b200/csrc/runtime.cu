@@ -170,9 +170,8 @@ double tile_cost(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint
   const uint64_t tiles = (uint64_t)ceil_div(m, rows) * ceil_div(n, bn) * batch;
   if (tiles == 0 || units == 0) return 0.0;
   const double b_lines = pair ? bn / 2.0 : bn;
-  // One tcgen05.mma never takes less than about 215 cycles here whatever its N (measured 115-125 ns per
-  // instruction for N = 32..128), so narrow tiles are issue-bound, not math-bound.
-  const double fill = (16384.0 + b_lines * 128.0) / 48.0, mma = 4.0 * std::max(bn / 2.0, 215.0);
+  // One tcgen05.mma costs its issuing thread 45-65 cycles whatever its N, so narrow tiles are issue-bound.
+  const double fill = (16384.0 + b_lines * 128.0) / 48.0, mma = 4.0 * std::max(bn / 2.0, 60.0);
   const double per_tile = k_blocks * std::max(fill, mma) + (bn > 256 ? 11000.0 : 1200.0);
   const double waves = (double)((tiles + units - 1) / units);
   return waves * per_tile + 3000.0;
@@ -252,7 +251,8 @@ bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b)
   double best = tile_cost(p.m, p.n, p.batch, p.k_blocks_total, p.bn, false, sms);
   uint32_t pick = 0;
   for (uint32_t cand : {512u, 256u, 128u, 64u}) {
-    if (cand / 2 < min_bn || cand > n_cap) continue;
+    // a pair tile may overhang n as long as the second CTA's half still holds columns (192 columns: one 256-wide tile)
+    if (cand / 2 < min_bn || (cand > n_cap && cand / 2 >= p.n)) continue;
     const double cost = tile_cost(p.m, p.n, p.batch, p.k_blocks_total, cand, true, sms);
     if (cost <= best) { best = cost; pick = cand; }   // a tie goes to the pair: half as many MMA instructions per row
   }
@@ -987,7 +987,7 @@ int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
 // arena that hands out nothing after start-up, or a process with a fixed device-memory budget.  gb_gemm needs two things such a caller cannot provide: a
 // handle (gb_create allocates a status word) and, when K is split, a workspace for the partial sums.  This
 // entry point needs neither.  Its split-K partials live in the array below, which is part of the library
-// image: every GPU that loads the library carries these 8 MiB until the process exits.
+// image: every GPU that loads the library carries these 4 MiB until the process exits.
 //
 // The array's name is only a stand-in on the host; the kernels need its device address, which is looked up
 // once per device with cudaGetSymbolAddress while that device is current.  That look-up happens on the

@@ -148,7 +148,7 @@ int gb_gemm(gb_handle* h, void* stream, const gb_gemm_desc* desc, const void* a,
  * stream capture.  A product whose partials exceed the array returns GB_ERR_WORKSPACE.  All calls share
  * the array: calls that overlap on the GPU (two streams, two threads) race and must be serialised.
  * Device-side wait time-outs are not reported (there is no status word to report them into). */
-#define GB_STATIC_SCRATCH_BYTES (8u << 20)
+#define GB_STATIC_SCRATCH_BYTES (4u << 20)
 int gb_gemm_static_scratch(void* stream, const gb_gemm_desc* desc, const void* a, const void* b, void* c,
                            const gb_epilogue* epilogue);
 

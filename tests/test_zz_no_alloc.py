@@ -67,7 +67,15 @@ def test_static_scratch_rejects_partials_beyond_the_fixed_array():
 
     lib = grad_b200.library()
     torch.cuda.set_device(0)
-    m, n, k = 1024, 1152, 8192          # 72 tiles, K split in three: 3 * 1024 * 1152 * 4 bytes > 8 MiB
+    # 74 row tiles of 128 x 64 (B is stored (K, N), so 64 is the narrowest tile) leave half of the 148 SMs idle, and
+    # the planner splits K in two: 2 * 9472 * 64 * 4 bytes = 4.6 MiB of partials, more than the 4 MiB array.  The
+    # ordinary entry point states that need, so the case stays honest when the planner changes.
+    m, n, k = 9472, 64, 8192
+    gpu = grad_b200.Gpu(0)
+    need = C.c_size_t(0)
+    assert lib.gb_gemm_workspace(gpu.handle, C.byref(_desc(abi, m, n, k)), C.byref(need)) == 0
+    gpu.close()
+    assert need.value > 4 << 20, need.value
     a = torch.zeros((m, k), dtype=torch.bfloat16, device="cuda")
     b = torch.zeros((k, n), dtype=torch.bfloat16, device="cuda")
     c = torch.zeros((m, n), device="cuda")
