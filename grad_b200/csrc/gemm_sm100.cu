@@ -1,19 +1,26 @@
 // The tcgen05 contraction kernel: one persistent, warp-specialised CTA per SM computes 128 x BN output
 // tiles of C = A * B with f32 accumulators in tensor memory.
 //
-//   warp 0      TMA producer: every box of a stage has its own lane, which keeps the box's coordinates in
-//               registers and steps them from K block to K block; the stage's "full" mbarrier counts the bytes.
-//   warp 1      MMA issuer: owns the TMEM allocation; one thread issues four tcgen05.mma per stage
-//               (K = 16 bf16 or 8 tf32 each) from descriptors built once per kernel, and commits the
-//               stage's "empty" barrier; after the last K block of a tile it commits the accumulator's
-//               "full" barrier.
+//   warp 0      TMA producer: every box of a stage has its own lane, which keeps the box's four coordinates in
+//               registers and steps them from K block to K block with the same instructions in every lane; the
+//               stage's "full" mbarrier counts the bytes.
+//   warp 1      MMA issuer: owns the TMEM allocation; one thread (chosen by elect.sync) issues four tcgen05.mma
+//               per K block (K = 16 bf16 or 8 tf32 each) from descriptors built once per kernel -- several K
+//               blocks per stage for column-patch convolution stages and weight gradients -- and commits the
+//               stage's "empty" barrier; after the last K block of a tile it commits the accumulator's "full"
+//               barrier.  Both loops poll the next stage's barrier one iteration ahead of its use.
 //   warps 2-9   epilogue, two warps per 32-lane quarter of TMEM (they split the column chunks): tcgen05.ld
-//               double-buffered in registers, (+C) (+bias) (+residual) (ReLU), rounding to the output type,
-//               16-byte stores.  Two accumulator buffers let the epilogue of tile i overlap the mainloop of
-//               tile i+1.
+//               double-buffered in registers, accumulator handed back as soon as the last read has landed,
+//               (+C) (+bias from shared memory) (+residual) (ReLU), rounding to the output type, then a 32 x 64
+//               byte block staged in shared memory and written by a TMA store (per-lane 16-byte stores for
+//               transposed, ragged, mapped or split-K results).  Two accumulator buffers let the epilogue of
+//               tile i overlap the mainloop of tile i+1.
 //   warps 10-13 (only when an operand cannot be fetched by TMA) gather warps fill the stage with plain
 //               loads: any pitch, f32 -> bf16 conversion on the fly, implicit im2col of NHWC activations
 //               for any stride / dilation / padding / channel count.
+//
+// The prologue (barriers, TMEM, cluster sync) touches no global memory and is followed by griddepcontrol.wait:
+// launched with programmatic stream serialization it overlaps the tail of the previous kernel in the stream.
 //
 // The same kernel serves the dense matmul family (NN / NT / TN through K-major or MN-major shared-memory
 // descriptors, no packed or transposed copies) and the implicit-GEMM convolutions (forward, input
