@@ -330,7 +330,7 @@ __device__ __forceinline__ void box_setup(const GemmParams& p, const TapWalk& wa
       if (p.box_n > 1) {
         b.aw = (int32_t)p.box_n;
       } else {
-        const int32_t rows = (int32_t)(p.box_h * p.geo.stride);
+        const int32_t rows = (int32_t)(p.box_h * (p.patch_view ? 1u : p.geo.stride));
         b.n0 = p.geo.out_h / p.box_h;
         b.az = rows;
         b.bz = -((int32_t)b.n0 - 1) * rows; b.bw = 1;
@@ -413,7 +413,7 @@ __device__ __forceinline__ void box_start(const GemmParams& p, const TapWalk& wa
       const uint32_t row = p.box_n > 1 ? 0u : (p0 - img * per_image) / p.geo.out_w;
       b.x = kk0 >= taps * p.geo.c ? 0 : (int32_t)(kk0 - tap * p.geo.c);
       b.y = (int32_t)(kx * p.geo.dilation) - (int32_t)p.geo.pad;
-      b.z = (int32_t)(row * p.geo.stride) + (int32_t)(ky * p.geo.dilation) - (int32_t)p.geo.pad;
+      b.z = (int32_t)(row * (p.patch_view ? 1u : p.geo.stride)) + (int32_t)(ky * p.geo.dilation) - (int32_t)p.geo.pad;
       b.w = (int32_t)img;
       b.i0 = p.box_n > 1 ? 0u : row / p.box_h;
       break;

@@ -95,6 +95,7 @@ struct GemmParams {
   uint32_t box_w, box_h, box_n;
   ConvGeo geo;
   uint32_t dgrad;           // 1: patches are taken from dy with flipped taps (input gradient)
+  uint32_t patch_view;      // 1: the activation map is already a strided view of x (1x1 strided layer): MN-major patch boxes step rows by 1
   TapWalk walk;             // K walk of patch / filter-tap boxes
   // Column-patch stages (col_taps > 0): one stage holds, for one (tap column, channel block), the activation
   // rows that ALL col_taps taps of that column read -- box_h + (col_taps - 1) * |row step| image rows in one

@@ -492,6 +492,22 @@ void walk_dgrad_unit(gb::TapWalk& wk, const gb::ConvGeo& g, uint32_t epl) {
   wk.tap0 = 0; wk.tap_x = 1; wk.tap_y = (int32_t)g.k;
 }
 
+// A strided 1x1 convolution without padding reads every s-th pixel of every s-th row and nothing else: the
+// patch tensor is a VIEW of x with doubled (s-fold) pixel and row pitch.  Boxes of that view fetch only the
+// pixels that are used; the traversal-stride boxes of `nhwc_tma` span all s*s of them (0.56 ms for the 64->192
+// shortcut of a 4096-image ResNet pass, four times its useful bytes).
+bool nhwc_view_tma(CUtensorMap* map, const void* base, bool smem_bf16, uint32_t dtype, const gb::ConvGeo& g, uint32_t epl, uint32_t bw,
+                   uint32_t bh, uint32_t bn, bool mn_major) {
+  const uint32_t es = smem_bf16 ? 2 : 4;
+  if ((dtype == GB_BF16) != smem_bf16) return false;
+  if (g.c % epl != 0 || !aligned16(base) || ((uint64_t)g.c_step * es) % 16 != 0) return false;
+  const uint64_t dims[4] = {g.c, g.out_w, g.out_h, g.n};
+  const uint64_t strides[3] = {(uint64_t)g.c_step * es * g.stride, (uint64_t)g.c_step * es * g.w * g.stride, (uint64_t)g.c_step * es * g.w * g.h};
+  const uint32_t box[4] = {epl, bw, bh, bn};
+  if (box[1] > 256 || box[2] > 256) return false;
+  return encode_map(map, smem_bf16, base, 4, dims, strides, box, !smem_bf16 && mn_major);
+}
+
 // Switches a planned patch product to column-patch stages when its geometry allows: the tile is whole rows of
 // one image, patch rows step one image row per output row, every operand arrives by TMA, K is not split, and
 // a tap's row offset keeps the 1024-byte swizzle atoms of the A part aligned (box width x row step a multiple of
@@ -567,8 +583,13 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     if (plan.tensor) {
       p.a_kind = gb::kGather;
       walk_forward(p.walk, g, epl);
-      if ((g.stride == 1 || !knobs().no_strided_tma) && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
-          nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, false, g.stride))
+      const bool view = g.k == 1 && g.pad == 0 && g.stride > 1 && !knobs().no_strided_tma;
+      if (view && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+          nhwc_view_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g, epl, p.box_w, p.box_h, p.box_n, false)) {
+        p.a_kind = gb::kPatchK;
+        p.walk.row_scale = 1;   // rows of the view, not of x
+      } else if ((g.stride == 1 || !knobs().no_strided_tma) && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+                 nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, false, g.stride))
         p.a_kind = gb::kPatchK;
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? (w_rows ? gb::kDenseK : gb::kDenseMN) : gb::kGather;
       CUtensorMap single = plan.tmap_b;
@@ -629,8 +650,13 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     if (rc != GB_OK) return rc;
     if (plan.tensor) {
       p.a_kind = gb::kGather;
-      if ((g.stride == 1 || !knobs().no_strided_tma) && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
-          nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, true, g.stride))
+      const bool view = g.k == 1 && g.pad == 0 && g.stride > 1 && !knobs().no_strided_tma;
+      if (view && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+          nhwc_view_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g, epl, p.box_w, p.box_h, p.box_n, true)) {
+        p.a_kind = gb::kPatchMN;
+        p.patch_view = 1;
+      } else if ((g.stride == 1 || !knobs().no_strided_tma) && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+                 nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, true, g.stride))
         p.a_kind = gb::kPatchMN;
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
       // Both operands are MN-major (one line per position), so two K blocks per stage are simply boxes of twice
@@ -640,7 +666,8 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       CUtensorMap a2, b2;
       if (p.a_kind == gb::kPatchMN && p.b_kind == gb::kDenseMN && !knobs().no_wide_stages && p.k_blocks_total >= 8 &&
           patch_box(2 * epl, g.out_h, g.out_w, bw2, bh2, bn2) &&
-          nhwc_tma(&a2, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, bw2, bh2, bn2, true, g.stride) &&
+          (p.patch_view ? nhwc_view_tma(&a2, other, smem_bf16, d->dtype_x, g, epl, bw2, bh2, bn2, true)
+                        : nhwc_tma(&a2, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, bw2, bh2, bn2, true, g.stride)) &&
           dense_tma(&b2, ob, smem_bf16, 1, p.bn, epl, 2)) {
         plan.tmap_a = a2; plan.tmap_b = b2;
         p.box_w = bw2; p.box_h = bh2; p.box_n = bn2;
