@@ -225,7 +225,7 @@ class Executor:
         out_dtype = torch.float32 if result in self.model.outputs else self.act_dtype
         cols = n
         if n % 8 != 0 and node.inputs[1] in self.model.initializers:
-            cols = (n + 7) // 8 * 8
+            cols = (n + 31) // 32 * 32   # whole 32-column chunks: the epilogue's staged TMA stores, no ragged tail
             w = self._padded(node.inputs[1], cols, False)
             if bias is not None:
                 bias = self._padded(other, cols, True)
