@@ -224,6 +224,61 @@ def test_full_size_adjoint_identity(gpu, case):
     assert abs(a - b) <= 1e-4 * scale and abs(a - c_) <= 1e-4 * scale, (a, b, c_, scale)
 
 
+# Every convolution layer of the two benchmark networks at the benchmark's batch of 128: the ResNet-14 64-128-256
+# stack (examples/cifar/main.zig:15-34: stem, residual 3x3 layers, the widening 3x3 layers applied after the pool,
+# the 1x1 shortcuts) with the strided variants of the four transition convolutions, and the 64-192-384 widths of the
+# ONNX inference graph (192 columns take a 256-wide pair tile that overhangs n; 192 channels are three channel
+# blocks per tap).  The CPU oracle finishes a batch-128 layer in a fraction of a second, so all three passes are
+# compared in full, not by the adjoint identity alone.
+FULL_BATCH = [
+    (128, 32, 32, 3, 3, 64, 1, 1, 1), (128, 32, 32, 64, 3, 64, 1, 1, 1),
+    (128, 16, 16, 64, 3, 128, 1, 1, 1), (128, 16, 16, 128, 3, 128, 1, 1, 1), (128, 16, 16, 64, 1, 128, 1, 0, 1),
+    (128, 8, 8, 128, 3, 256, 1, 1, 1), (128, 8, 8, 256, 3, 256, 1, 1, 1), (128, 8, 8, 128, 1, 256, 1, 0, 1),
+    (128, 32, 32, 64, 3, 128, 2, 1, 1), (128, 32, 32, 64, 1, 128, 2, 0, 1),
+    (128, 16, 16, 128, 3, 256, 2, 1, 1), (128, 16, 16, 128, 1, 256, 2, 0, 1),
+    (128, 16, 16, 64, 3, 192, 1, 1, 1), (128, 16, 16, 192, 3, 192, 1, 1, 1), (128, 16, 16, 64, 1, 192, 1, 0, 1),
+    (128, 8, 8, 192, 3, 384, 1, 1, 1), (128, 8, 8, 384, 3, 384, 1, 1, 1), (128, 8, 8, 192, 1, 384, 1, 0, 1),
+    (128, 32, 32, 64, 3, 192, 2, 1, 1), (128, 32, 32, 64, 1, 192, 2, 0, 1),
+    (128, 16, 16, 192, 3, 384, 2, 1, 1), (128, 16, 16, 192, 1, 384, 2, 0, 1),
+]
+
+
+@pytest.mark.parametrize("case", FULL_BATCH)
+@pytest.mark.parametrize("math,tol,half", [(1, TOL_TF32, False), (2, TOL_BF16, True)])
+def test_benchmark_layers_at_batch_128_against_the_oracle(gpu, case, math, tol, half):
+    """All three passes of every benchmark layer at batch 128, bf16 storage and TF32, every element; the filters are
+    passed in the activations' type (the bench's configuration), so every operand takes its TMA path."""
+    import torch
+    from oracle import binding as orc
+
+    d, x, w, dy = _inputs(case, 900)
+    geo = _geo(case)
+    if half:
+        x, w, dy = orc.bf16_round(x), orc.bf16_round(w), orc.bf16_round(dy)
+    threads = orc.host_threads()
+    want_y = orc.conv_forward(x, w, d, threads)
+    want_dx = orc.conv_input_grad(dy, w, d, threads)
+    want_dw = orc.conv_weight_grad(x, dy, d, threads)
+    act = torch.bfloat16 if half else torch.float32
+    tx, tw, tdy = to_dev(x, half), to_dev(w, half), to_dev(dy, half)
+    y = torch.full((d.n, d.out_h, d.out_w, d.c_out), 5.0, dtype=act, device="cuda")
+    gx = torch.full((d.n, d.h, d.w, d.c), 5.0, dtype=act, device="cuda")
+    gw = torch.zeros((d.taps, d.c_out), dtype=torch.float32, device="cuda")
+    gpu.convForward(tx, tw, y, geo, math=math)
+    gpu.convInputGrad(tdy, tw, gx, geo, accumulate=False, math=math)
+    gpu.convWeightGrad(tdy, tx, gw, geo, math=math)
+    torch.cuda.synchronize()
+    errs = (rel_fro(to_host(y), want_y), rel_fro(to_host(gx), want_dx), rel_fro(to_host(gw), want_dw))
+    assert max(errs) <= tol, (case, math, errs)
+    # per image, so that one mis-addressed image cannot hide in the norm of the other 127
+    gy, wy = to_host(y).reshape(d.n, -1), want_y.reshape(d.n, -1)
+    per_image = np.linalg.norm(gy - wy, axis=1) / np.maximum(np.linalg.norm(wy, axis=1), 1e-30)
+    assert per_image.max() <= tol, (case, math, int(per_image.argmax()), float(per_image.max()))
+    gxi, wxi = to_host(gx).reshape(d.n, -1), want_dx.reshape(d.n, -1)
+    per_image = np.linalg.norm(gxi - wxi, axis=1) / np.maximum(np.linalg.norm(wxi, axis=1), 1e-30)
+    assert per_image.max() <= tol, (case, math, int(per_image.argmax()), float(per_image.max()))
+
+
 @pytest.mark.parametrize("case", [RESNET[1], RESNET[2], RESNET[0], RESNET[7], SMALL[7]])
 @pytest.mark.parametrize("math,tol,half", [(0, TOL_F32, False), (1, TOL_TF32, False), (2, TOL_BF16, True)])
 def test_forward_with_prepared_filter_rows(gpu, case, math, tol, half):

@@ -79,6 +79,25 @@ def test_graph_replay_equals_eager_run(gpu, small_case):
     assert torch.equal(want, got)
 
 
+@pytest.mark.parametrize("mode,tol", [("tf32", TOL_TF32), ("bf16", TOL_BF16)])
+def test_full_width_model_matches_cpu_walk(gpu, mode, tol):
+    """The benchmark's own graph (ResNet-14 64-192-384, batch norm folded) against the CPU walk (`Model.run`,
+    src/onnx/runtime.zig:560-620) on the same seeded images: logits within the mode's tolerance, argmax identical
+    wherever the CPU's own top-2 margin exceeds the error bound."""
+    from grad_b200.onnx_gpu import Executor, resnet14_model
+    from oracle import onnx_cpu
+
+    model = resnet14_model(64, 192, 384)
+    x = seeded(1241, 16, 3072)
+    want = onnx_cpu.run(model, {"input": x})["logits"]
+    got = Executor(model, gpu, mode=mode).run({"input": x})["logits"]
+    assert got.shape == want.shape == (16, 10)
+    assert rel_fro(got, want) <= tol, rel_fro(got, want)
+    top2 = np.sort(want, axis=1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 4 * tol * np.abs(want).max()
+    assert clear.sum() >= 8 and np.array_equal(got.argmax(1)[clear], want.argmax(1)[clear])
+
+
 def test_full_width_model_runs_at_batch_100(gpu):
     """The benchmark's graph (64-192-384) at batch 100: shape, finiteness, and bf16 vs tf32 agreement."""
     from grad_b200.onnx_gpu import Executor, resnet14_model
