@@ -89,6 +89,8 @@ SIGNATURES = {
     "gb_comm_unique_id": ([C.c_void_p], C.c_int),
     "gb_comm_create": ([C.c_int, C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)], C.c_int),
     "gb_allreduce_mean": ([C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t], C.c_int),
+    "gb_comm_set_timeout": ([C.c_void_p, C.c_uint32], C.c_int),
+    "gb_comm_finish": ([C.c_void_p, C.c_void_p], C.c_int),
     "gb_comm_abort": ([C.c_void_p], C.c_int),
     "gb_comm_destroy": ([C.c_void_p], None),
 }

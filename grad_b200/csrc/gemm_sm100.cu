@@ -50,6 +50,7 @@ struct SmemHeader {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
+  uint32_t spin_limit;   // directly behind abort_flag: the bounded waits read it as abort_flag[1]
 };
 
 struct Work {
@@ -465,11 +466,12 @@ __device__ __forceinline__ uint64_t out_row_offset(const GemmParams& p, const Ro
 }
 
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&acc)[32], uint32_t batch, uint32_t split,
-                                               uint32_t row, uint32_t col0, float bias_lane, uint64_t row_off, uint32_t m_limit) {
+                                               uint32_t row, uint32_t col0, float bias_lane, uint64_t row_off, uint32_t m_limit,
+                                               bool as_partial) {
   if (col0 >= p.n) return;
   const bool live = row < m_limit;
   const uint32_t cols = min(32u, p.n - col0);
-  if (p.splits > 1) {
+  if (as_partial) {
     if (!live) return;
     float* dst = p.partial + (((uint64_t)split * p.batch + batch) * p.m + row) * p.n + col0;
     if (cols == 32 && (p.n & 3) == 0) {
@@ -576,7 +578,7 @@ __device__ __noinline__ void epilogue_chunk_ragged(const GemmParams& p, const ui
   uint32_t copy[32];
 #pragma unroll
   for (uint32_t i = 0; i < 32; ++i) copy[i] = vals[i];
-  epilogue_chunk(p, copy, batch, split, row, col0, bias_lane, (uint64_t)row * p.ldc, p.m);
+  epilogue_chunk(p, copy, batch, split, row, col0, bias_lane, (uint64_t)row * p.ldc, p.m, p.splits > 1);
 }
 __device__ __forceinline__ void epilogue_chunk_copy(const GemmParams& p, const uint32_t (&acc)[32], uint32_t batch, uint32_t split, uint32_t row,
                                                     uint32_t col0, float bias_lane) {
@@ -774,14 +776,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     else release();
     float bias_cur = bias_next;
     bias_next = bias_at(c + step);
-    epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur, row_off, m_limit);
+    epilogue_chunk(p, acc_a, batch, split, row, col_base + tile_col(c), bias_cur, row_off, m_limit, p.splits > 1);
     if (has_b) {
       tmem_ld_wait();
       if (c + 2 * step < ncols) tmem_ld_32x32(taddr + c + 2 * step, acc_a);
       else release();
       bias_cur = bias_next;
       bias_next = bias_at(c + 2 * step);
-      epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur, row_off, m_limit);
+      epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur, row_off, m_limit, p.splits > 1);
     }
   }
 }
@@ -874,6 +876,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       mbar_init(&hdr->acc_empty[b], 4 * p.epi_groups);
     }
     hdr->abort_flag = 0;
+    hdr->spin_limit = p.spin_limit ? p.spin_limit : kSpinLimit;
     fence_barrier_init();
     if (p.a_kind != kGather) prefetch_tmap(&tmap_a);
     if (p.b_kind != kGather) prefetch_tmap(&tmap_b);
@@ -905,6 +908,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       uint32_t cur_class = 0xFFFFFFFFu;
       const bool box_is_b = lane >= boxes_of(p.a_kind, kBM, epl);
       uint32_t ready = 1;   // the first pass over the ring finds every stage free
+      uint32_t issued = 0;
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const Work work = decode_work(p, w);
         if (work.empty) continue;
@@ -919,8 +923,12 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           if (next_stage == p.stages) { next_stage = 0; next_phase ^= 1; }
           const bool more = kb + 1 < work.kb_end || w + gridDim.x < total_work;
           ready = more ? mbar_try_wait(&hdr->empty[next_stage], next_phase ^ 1) : 0u;
-          if (lane == 0) mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
-          if (box.active) box_issue<false>(box, tiles + stage * stage_bytes, &hdr->full[stage], 0);
+          // Failure injection asked for by the host (a test of the time-out path): CTA 0 leaves out one K block's
+          // copies, so the stage's "full" barrier never completes and the bounded waits downstream run out.
+          const bool dropped = p.test_drop_kblock != 0 && blockIdx.x == 0 && issued == p.test_drop_kblock - 1;
+          ++issued;
+          if (lane == 0 && !dropped) mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
+          if (box.active && !dropped) box_issue<false>(box, tiles + stage * stage_bytes, &hdr->full[stage], 0);
           box_step(box);
           stage = next_stage;
           phase = next_phase;
@@ -1084,6 +1092,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       mbar_init(&hdr->acc_empty[b], 8 * p.epi_groups); // every epilogue warp of both CTAs (used on the leader only)
     }
     hdr->abort_flag = 0;
+    hdr->spin_limit = p.spin_limit ? p.spin_limit : kSpinLimit;
     fence_barrier_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);

@@ -124,6 +124,8 @@ struct GemmParams {
   uint32_t round_tf32;      // round the stored f32 result to TF32 (nearest, ties away)
   uint32_t tma_store;       // full 32-column chunks leave through shared memory and a TMA store (map of C passed to the kernel)
   uint32_t* status;
+  uint32_t spin_limit;      // failed polls after which a bounded wait gives up (0 = the default, about a second)
+  uint32_t test_drop_kblock;   // fault injection on the host's request: the producer leaves out this K block's copies (+1; 0 = off)
 };
 
 // Shared memory the epilogue warps own when p.tma_store is set: per warp a 2 KB staging block (32 rows x 64

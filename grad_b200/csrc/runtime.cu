@@ -27,8 +27,10 @@ struct gb_handle {
   int sm_count = 0;
   int last_cuda = 0;
   uint32_t* status = nullptr;   // device word the kernels report bounded-wait failures into
+  uint32_t test_drops_left = 0; // fault injection requested through the environment: calls that still drop a K block
   gb_plan_info last_plan = {};
 };
+
 
 namespace {
 
@@ -61,6 +63,12 @@ struct Knobs {
   bool no_dgrad_classes = false; // GB_NO_DGRAD_CLASSES: a strided input gradient is one gathered product
   bool no_wide_stages = false;   // GB_NO_WIDE_STAGES: weight gradients keep one K block per stage
   bool no_fused_classes = false; // GB_NO_FUSED_CLASSES: one launch per parity class of a strided input gradient
+  int force_bn = 0;              // GB_FORCE_BN=n: tile width of a dense single-CTA product (with GB_FORCE_SPLITS: its K split)
+  int force_splits = 0;
+  // Host-requested failure injection for the time-out path (tests only): the first GB_TEST_DROP_CALLS (default 1)
+  // single-CTA tensor launches of each handle leave out the copies of K block GB_TEST_DROP_KBLOCK, and bounded waits
+  // give up after GB_TEST_SPIN_LIMIT polls instead of about a second's worth.
+  uint32_t test_spin_limit = 0, test_drop_kblock = 0, test_drop_calls = 0;
 };
 const Knobs& knobs() {
   static const Knobs k = [] {
@@ -74,6 +82,14 @@ const Knobs& knobs() {
     v.no_dgrad_classes = getenv("GB_NO_DGRAD_CLASSES") != nullptr;
     v.no_wide_stages = getenv("GB_NO_WIDE_STAGES") != nullptr;
     v.no_fused_classes = getenv("GB_NO_FUSED_CLASSES") != nullptr;
+    if (const char* g = getenv("GB_FORCE_BN")) v.force_bn = atoi(g);
+    if (const char* g = getenv("GB_FORCE_SPLITS")) v.force_splits = atoi(g);
+    if (const char* g = getenv("GB_TEST_SPIN_LIMIT")) v.test_spin_limit = (uint32_t)std::max(1, atoi(g));
+    if (const char* g = getenv("GB_TEST_DROP_KBLOCK")) {
+      v.test_drop_kblock = (uint32_t)std::max(0, atoi(g)) + 1;
+      v.test_drop_calls = 1;
+      if (const char* c = getenv("GB_TEST_DROP_CALLS")) v.test_drop_calls = (uint32_t)std::max(0, atoi(c));
+    }
     return v;
   }();
   return k;
@@ -191,10 +207,12 @@ void pick_tiling(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint
     if (bn == 0 || cost < best) { bn = cand; best = cost; }
   }
   if (bn == 0) bn = min_bn;
+  if (knobs().force_bn >= (int)min_bn && knobs().force_bn <= 256 && knobs().force_bn % 32 == 0) bn = (uint32_t)knobs().force_bn;
   const uint32_t tiles = ceil_div(m, 128) * batch * ceil_div(n, bn);
   splits = 1;
   // A split costs a second launch (~5 us) and a pass over the partials: only worth it when every part keeps >= 16 K blocks.
   if (allow_split && tiles > 0 && tiles * 2 <= sms && k_blocks >= 32) splits = std::max(1u, std::min(sms / tiles, k_blocks / 16));
+  if (allow_split && knobs().force_splits > 0) splits = std::min<uint32_t>((uint32_t)knobs().force_splits, std::max(1u, k_blocks));
   kbps = std::max(1u, ceil_div(k_blocks, splits));
   splits = std::max(1u, ceil_div(k_blocks, kbps));
 }
@@ -358,6 +376,11 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
     } else {
       p.partial = (float*)workspace;
     }
+  }
+  p.spin_limit = knobs().test_spin_limit;
+  if (plan.tensor && !p.cta_pair && h->test_drops_left > 0 && knobs().test_drop_kblock) {
+    p.test_drop_kblock = knobs().test_drop_kblock;
+    --h->test_drops_left;
   }
   gb_plan_info& info = h->last_plan;
   info.tensor_path = plan.tensor;
@@ -873,6 +896,7 @@ int gb_create(int device_ordinal, gb_handle** out) {
   h->sm_count = prop.multiProcessorCount;
   cudaError_t e = cudaMalloc(&h->status, sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(h->status, 0, sizeof(uint32_t));
+  h->test_drops_left = knobs().test_drop_calls;
   if (e == cudaSuccess) e = gb::gemm_sm100_configure();
   if (e != cudaSuccess || encode_tiled_fn() == nullptr) {
     if (h->status) cudaFree(h->status);

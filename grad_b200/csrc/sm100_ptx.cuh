@@ -56,14 +56,16 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
   return done;
 }
 
-// Every wait in these kernels is bounded: after kSpinLimit failed polls (about a second at worst) the
-// waiter raises the shared abort flag, records a status code and returns false; every other waiter
+// Every wait in these kernels is bounded: after a limit of failed polls (kSpinLimit, about a second at worst)
+// the waiter raises the shared abort flag, records a status code and returns false; every other waiter
 // sees the flag within one poll and leaves its loop too, so a broken pipeline ends the kernel with an
-// error status instead of hanging the device.
+// error status instead of hanging the device.  The limit sits in shared memory in the word after the abort
+// flag (the kernels set it up with the flag), so a caller may shorten it per launch.
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+  const uint32_t limit = abort_flag[1];
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag != 0) return false;
     if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
@@ -87,7 +89,8 @@ __device__ __forceinline__ bool mbar_wait_peeked(uint64_t* bar, uint32_t parity,
 }
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t code) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+  const uint32_t limit = abort_flag[1];
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag != 0) return false;
     if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);

@@ -1,16 +1,16 @@
 """Host-side mirror of `Replicas` (src/nn/replicas.zig): the data-parallel group of one training or inference job.
 
 One process per GPU (the reference runs one thread per replica, src/nn/trainer.zig:603-612).  The mean of
-the gradients goes over NCCL on the device buffers (`gb_allreduce_mean`) instead of through host memory;
-the barrier with a stop flag that releases waiting replicas when one of them fails (`wait` / `stop`,
-replicas.zig:36-53) lives on the rendezvous store, so it works without a GPU.  torch.distributed is only the
-plumbing that hands rank 0's NCCL id to the others.
+the gradients is ONE NCCL allreduce over the flat gradient vector on the device (`gb_allreduce_mean`) instead of
+two trips through host memory; the barrier with a stop flag that releases waiting replicas when one of them
+fails (`wait` / `stop`, replicas.zig:36-53) lives on the rendezvous store, so it works without a GPU.
+torch.distributed is only the plumbing that hands rank 0's NCCL id to the others.
 """
 from __future__ import annotations
 
 import ctypes as C
 import time
-from typing import Optional, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple, Union
 
 import torch
 import torch.distributed as dist
@@ -26,6 +26,28 @@ def shard(total: int, count: int, index: int) -> Tuple[int, int]:
     """The slice of `total` items replica `index` of `count` owns: [total*index/count, total*(index+1)/count)
     (replicas.zig:71-72); also how an inference batch is split across GPUs."""
     return total * index // count, total * (index + 1) // count
+
+
+def flat_grads(shapes: Sequence[Sequence[int]], device, align: int = 4) -> Tuple[torch.Tensor, List[torch.Tensor]]:
+    """One flat f32 gradient vector with a view per parameter, the layout `gradLen` describes (replicas.zig:95-99):
+    the whole model's gradients are then averaged by ONE collective.  Every view starts on a multiple of `align`
+    elements (16 bytes), so the contraction kernels can store into it with their vector / TMA stores."""
+    offsets, total = [], 0
+    for shape in shapes:
+        total = (total + align - 1) // align * align
+        offsets.append(total)
+        n = 1
+        for d in shape:
+            n *= int(d)
+        total += n
+    flat = torch.zeros(total, dtype=torch.float32, device=device)
+    views = []
+    for shape, off in zip(shapes, offsets):
+        n = 1
+        for d in shape:
+            n *= int(d)
+        views.append(flat[off:off + n].view(*shape))
+    return flat, views
 
 
 class Replicas:
@@ -47,11 +69,15 @@ class Replicas:
             comm = C.c_void_p()
             abi.check(self.lib.gb_comm_create(count, index, ident, device, C.byref(comm)), "gb_comm_create")
             self.comm = comm
+            abi.check(self.lib.gb_comm_set_timeout(comm, max(1, int(timeout_s * 1000))), "gb_comm_set_timeout")
 
     # ---- barrier with a stop flag (replicas.zig:36-53) ---------------------------------------------------
     def stop(self):
         if self.store is not None:
             self.store.set("gb_replicas_stopped", "1")
+        self._abort()
+
+    def _abort(self):
         if self.comm is not None:
             self.lib.gb_comm_abort(self.comm)
 
@@ -62,10 +88,13 @@ class Replicas:
             return False
 
     def wait(self):
-        """Blocks until every replica has called it; raises Stopped if one has called stop()."""
+        """Blocks until every replica has called it; raises Stopped if one has called stop().  A replica released by
+        the stop flag or by the deadline also aborts its own communicator, so nothing it enqueues later can wait on
+        the device for the replica that failed."""
         if self.count == 1:
             return
         if self._stopped():
+            self._abort()
             raise Stopped()
         self.generation += 1
         key = f"gb_replicas_gen_{self.generation}"
@@ -73,26 +102,60 @@ class Replicas:
         deadline = time.monotonic() + self.timeout_s
         while arrived < self.count:
             if self._stopped():
+                self._abort()
                 raise Stopped()
             if time.monotonic() > deadline:
+                self._abort()
                 raise TimeoutError(f"replica barrier {self.generation}: {arrived} of {self.count} arrived")
             time.sleep(0.001)
             arrived = self.store.add(key, 0)
 
     # ---- the gradient mean (replicas.zig:57-91) ------------------------------------------------------------
-    def averageGrads(self, grads: Sequence[torch.Tensor]):
+    @staticmethod
+    def _span(grads: Sequence[torch.Tensor]) -> Optional[torch.Tensor]:
+        """The one contiguous f32 range that covers `grads` when they are views into one flat buffer (in order,
+        gaps of alignment padding allowed), else None."""
+        first = grads[0]
+        storage = first.untyped_storage().data_ptr()
+        end = first.data_ptr()
+        for g in grads:
+            if g.untyped_storage().data_ptr() != storage or g.data_ptr() < end or g.data_ptr() - end > 64:
+                return None
+            end = g.data_ptr() + g.numel() * 4
+        count = (end - first.data_ptr()) // 4
+        return torch.as_strided(first, (count,), (1,))
+
+    def averageGrads(self, grads: Union[torch.Tensor, Sequence[torch.Tensor]], finish: bool = False):
         """Replaces every gradient, in every replica, by the mean over the replicas; identical bits everywhere.
-        One flat f32 device tensor is reduced in place; several tensors are reduced one after the other."""
+        The replicas first meet at the barrier (replicas.zig:67), so a replica that has failed releases the others
+        with `Stopped` before any of them has enqueued the collective.  A flat f32 tensor, or views into one flat
+        buffer (`flat_grads`), are reduced by ONE call like the reference's single flat vector; tensors that live
+        in separate allocations are reduced one after the other.  `finish` waits for the result on the host with
+        the group's deadline (the bounded form of the barrier after the reduction, replicas.zig:81)."""
         if self.count == 1:
             return
         if self.comm is None:
             raise RuntimeError("averageGrads needs a CUDA device: the mean runs over NCCL, there is no host path")
-        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self.wait()
+        if isinstance(grads, torch.Tensor):
+            grads = [grads]
         for g in grads:
-            assert g.is_cuda and g.dtype == torch.float32 and g.is_contiguous()
-            rc = self.lib.gb_allreduce_mean(self.comm, stream, C.c_void_p(g.data_ptr()), g.numel())
-            if rc != 0:
-                raise Stopped() if rc == 6 else abi.GbError(rc, "gb_allreduce_mean")
+            assert g.dtype == torch.float32 and g.is_contiguous()
+        span = self._span(grads) if len(grads) > 1 else grads[0].view(-1)
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream) if grads[0].is_cuda else None
+        for g in ([span] if span is not None else grads):
+            self._check(self.lib.gb_allreduce_mean(self.comm, stream, C.c_void_p(g.data_ptr()), g.numel()), "gb_allreduce_mean")
+        if finish:
+            self._check(self.lib.gb_comm_finish(self.comm, stream), "gb_comm_finish")
+
+    def _check(self, rc: int, where: str):
+        if rc == 0:
+            return
+        if rc in (5, 6):   # GB_ERR_TIMEOUT / GB_ERR_NCCL: the communicator is gone; tell the others
+            if self.store is not None:
+                self.store.set("gb_replicas_stopped", "1")
+            raise Stopped(f"{where}: {abi.STATUS_NAMES.get(rc, rc)}")
+        raise abi.GbError(rc, where)
 
     def close(self):
         if self.comm is not None:

@@ -34,9 +34,11 @@ typedef enum {
   GB_OK = 0,
   GB_ERR_INVALID = 1,       /* bad argument (null pointer, zero stride, trans_a and trans_b both set, ...) */
   GB_ERR_CUDA = 2,          /* a CUDA call failed; gb_last_cuda_error() has the code (maps to error.CudaFailed) */
-  GB_ERR_WORKSPACE = 3,     /* workspace pointer null or too small (maps to error.OutOfMemory) */
+  GB_ERR_WORKSPACE = 3,     /* only gb_gemm_static_scratch: the partial sums exceed the fixed array (error.OutOfMemory).  gb_gemm
+                             * and gb_conv_* never return it: with a workspace that is null, misaligned or smaller than the
+                             * *_workspace query said, they run the product unsplit (and gather f32 master filters) instead */
   GB_ERR_UNSUPPORTED = 4,   /* shape / dtype combination outside what the kernels cover (error.NoAlgorithm) */
-  GB_ERR_TIMEOUT = 5,       /* a bounded device-side wait gave up; see gb_last_status */
+  GB_ERR_TIMEOUT = 5,       /* a bounded wait gave up: on the device (see gb_last_status) or for a peer replica (gb_comm_*) */
   GB_ERR_NCCL = 6,          /* NCCL missing or a collective failed */
   GB_ERR_NO_DEVICE = 7      /* no CUDA device / not an sm_100 part (error.NoSuchDevice) */
 } gb_status;
@@ -192,12 +194,24 @@ int gb_reorder_oihw_rows(void* stream, int dst_dtype, const float* w, void* wt, 
 int gb_permute_layout(void* stream, int dtype, int to_nhwc, const void* src, void* dst, uint32_t n, uint32_t c, uint32_t h, uint32_t w);
 
 /* ---- data-parallel gradient mean -------------------------------------------------------------- */
-/* Replaces `Replicas.averageGrads` (src/nn/replicas.zig:57-91): the mean over replicas of one flat
- * f32 gradient vector, in place, identical bits on every rank -- over NCCL (NVLink) instead of host
- * memory.  unique_id is 128 bytes from gb_comm_unique_id on rank 0, shared by the caller. */
+/* Replaces `Replicas.averageGrads` (src/nn/replicas.zig:57-91): the mean over replicas of ONE flat f32
+ * gradient vector (`gradLen`, replicas.zig:95-99), in place, identical bits on every rank -- one NCCL
+ * allreduce over NVLink instead of two trips through host memory.  unique_id is 128 bytes from
+ * gb_comm_unique_id on rank 0, shared by the caller.  device_ordinal < 0 keeps the current device.
+ * The communicator is non-blocking and every wait has a host deadline (gb_comm_set_timeout, default 60 s or
+ * GB_COMM_TIMEOUT_MS): a replica that never joins makes gb_comm_create / gb_allreduce_mean / gb_comm_finish
+ * abort the communicator and return GB_ERR_TIMEOUT, the counterpart of `Replicas.stop` releasing the waiters
+ * with error.Stopped (replicas.zig:36-53).  After an abort every call on the communicator returns GB_ERR_NCCL. */
 int gb_comm_unique_id(void* out128);
 int gb_comm_create(int nranks, int rank, const void* unique_id128, int device_ordinal, gb_comm** out);
+int gb_comm_set_timeout(gb_comm* comm, uint32_t timeout_ms);
+/* Enqueues the mean on `stream` and returns (capture-safe once the communicator exists). */
 int gb_allreduce_mean(gb_comm* comm, void* stream, float* grads, size_t count);
+/* Host-side wait for `stream` with the communicator's deadline: GB_OK when the work on the stream has finished;
+ * when the deadline passes first, the communicator is aborted (which ends a collective still waiting for a peer
+ * on the device) and GB_ERR_TIMEOUT is returned.  The bounded form of the barrier after the reduction
+ * (replicas.zig:81). */
+int gb_comm_finish(gb_comm* comm, void* stream);
 int gb_comm_abort(gb_comm* comm);     /* the analogue of `Replicas.stop` (replicas.zig:36-38) */
 void gb_comm_destroy(gb_comm* comm);
 

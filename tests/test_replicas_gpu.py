@@ -17,15 +17,20 @@ def _worker(rank, world, port, queue):
         import torch
         import torch.distributed as dist
 
-        from grad_b200.replicas import Replicas
+        from grad_b200.replicas import Replicas, flat_grads
 
         torch.cuda.set_device(rank)
         dist.init_process_group("gloo", rank=rank, world_size=world)   # plumbing only: the mean itself runs through gb_allreduce_mean
         group = Replicas(world, rank, device=rank)
         gen = torch.Generator(device="cuda").manual_seed(100 + rank)
-        grads = [torch.randn(101770, generator=gen, device="cuda"), torch.randn((784, 128), generator=gen, device="cuda")]
+        # the MLP's gradients as views of one flat vector (one collective) and one tensor in its own allocation
+        flat, views = flat_grads([(784, 128), (128,), (128, 10), (10,)], "cuda")
+        flat.copy_(torch.randn(flat.numel(), generator=gen, device="cuda"))
+        lone = torch.randn(3228737, generator=gen, device="cuda")      # the character Transformer's gradient length
+        grads = [flat, lone]
         before = [g.cpu().numpy().copy() for g in grads]
-        group.averageGrads(grads)
+        group.averageGrads(views)
+        group.averageGrads(lone, finish=True)
         torch.cuda.synchronize()
         group.wait()
         queue.put((rank, "ok", before, [g.cpu().numpy() for g in grads]))
