@@ -73,6 +73,7 @@ SIGNATURES = {
     "gb_gemm": ([C.c_void_p, C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Epilogue), C.c_void_p,
                  C.c_size_t], C.c_int),
     "gb_gemm_static_scratch": ([C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Epilogue)], C.c_int),
+    "gb_static_last_status": ([C.c_void_p, C.POINTER(C.c_uint32)], C.c_int),
     "gb_conv_workspace": ([C.c_void_p, C.c_int, C.POINTER(ConvDesc), C.POINTER(C.c_size_t)], C.c_int),
     "gb_conv_fprop": ([C.c_void_p, C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Epilogue),
                        C.c_void_p, C.c_size_t], C.c_int),

@@ -53,13 +53,30 @@ __device__ __forceinline__ float f32_operand(const GatherDesc& d, const ConvGeo&
   return d.src_is_bf16 ? bf16_to_f32(((const uint16_t*)d.base)[batch_off + idx]) : ((const float*)d.base)[batch_off + idx];
 }
 
-// grid: (tiles_n, tiles_m, batch * splits); 256 threads, each a 4 x 4 block of the 64 x 64 tile.
+// Which tile a block owns.  The grid is one-dimensional, column tiles innermost, then row tiles, then (batch, K
+// part): grid.y and grid.z stop at 65535, which a convolution over 4096 images of 32 x 32 outputs (65536 row
+// tiles) already exceeds; grid.x does not.
+struct TileIndex {
+  uint32_t m0, n0, split, batch;
+};
+template <uint32_t TM, uint32_t TN>
+__device__ __forceinline__ TileIndex f32_tile_index(const GemmParams& p) {
+  const uint32_t tiles_n = (p.n + TN - 1) / TN, tiles_m = (p.m + TM - 1) / TM;
+  uint32_t w = blockIdx.x;
+  const uint32_t tn = w % tiles_n;
+  w /= tiles_n;
+  const uint32_t tm = w % tiles_m, z = w / tiles_m;
+  return TileIndex{tm * TM, tn * TN, z % p.splits, z / p.splits};
+}
+
+// 256 threads, each a 4 x 4 block of the 64 x 64 tile.
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmParams p) {
   __shared__ float As[kTK][kTM + 4];
   __shared__ float Bs[kTK][kTN + 4];
   const uint32_t tid = threadIdx.x;
-  const uint32_t split = blockIdx.z % p.splits, batch = blockIdx.z / p.splits;
-  const uint32_t m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
+  const TileIndex tile = f32_tile_index<kTM, kTN>(p);
+  const uint32_t split = tile.split, batch = tile.batch;
+  const uint32_t m0 = tile.m0, n0 = tile.n0;
   const uint32_t k_begin = split * p.k_blocks_per_split * kTK;
   const uint32_t k_end = min(p.k, k_begin + p.k_blocks_per_split * kTK);
   const uint64_t a_off = (uint64_t)batch * p.ga.batch_stride, b_off = (uint64_t)batch * p.gbsrc.batch_stride;
@@ -133,8 +150,9 @@ __global__ void __launch_bounds__(256) gemm_f32_dense_kernel(const GemmParams p)
   __shared__ __align__(16) float As[kTK][TM + 4];
   __shared__ __align__(16) float Bs[kTK][TN + 4];
   const uint32_t tid = threadIdx.x;
-  const uint32_t split = blockIdx.z % p.splits, batch = blockIdx.z / p.splits;
-  const uint32_t m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  const TileIndex tile = f32_tile_index<TM, TN>(p);
+  const uint32_t split = tile.split, batch = tile.batch;
+  const uint32_t m0 = tile.m0, n0 = tile.n0;
   const uint32_t k_begin = split * p.k_blocks_per_split * kTK;
   const uint32_t k_end = min(p.k, k_begin + p.k_blocks_per_split * kTK);
   // this thread's elements of a K step: (mn index within the tile, k index within the step), source pointer, row validity
@@ -235,23 +253,30 @@ __global__ void __launch_bounds__(256) gemm_f32_dense_kernel(const GemmParams p)
 
 }  // namespace
 
-// p.k_blocks_per_split counts blocks of 16 K values here; p.tiles_* are 64-wide.
+// Blocks of a strict-f32 launch with TM x TN tiles; 0 when the product is empty or does not fit grid.x.
+uint32_t f32_grid_blocks(const GemmParams& p, uint32_t tm, uint32_t tn) {
+  const uint64_t blocks = (uint64_t)((p.m + tm - 1) / tm) * ((p.n + tn - 1) / tn) * p.batch * p.splits;
+  return blocks > 0x7FFFFFFFull ? 0u : (uint32_t)blocks;
+}
+
+// p.k_blocks_per_split counts blocks of 16 K values here.
 cudaError_t launch_gemm_f32(const GemmParams& p, cudaStream_t stream) {
   if (p.m == 0 || p.n == 0 || p.batch == 0) return cudaSuccess;
   if (p.ga.source == kSrcDense && p.gbsrc.source == kSrcDense) {
     // 128 x 128 tiles once they fill the machine, 64 x 64 below that (more blocks, less work per block)
-    const uint64_t big = (uint64_t)((p.m + 127) / 128) * ((p.n + 127) / 128) * p.batch * p.splits;
+    const uint32_t big = f32_grid_blocks(p, 128, 128);
     if (big >= 148) {
-      const dim3 grid((p.n + 127) / 128, (p.m + 127) / 128, p.batch * p.splits);
-      gemm_f32_dense_kernel<128, 128><<<grid, 256, 0, stream>>>(p);
+      gemm_f32_dense_kernel<128, 128><<<big, 256, 0, stream>>>(p);
     } else {
-      const dim3 grid((p.n + 63) / 64, (p.m + 63) / 64, p.batch * p.splits);
-      gemm_f32_dense_kernel<64, 64><<<grid, 256, 0, stream>>>(p);
+      const uint32_t small = f32_grid_blocks(p, 64, 64);
+      if (small == 0) return cudaErrorInvalidConfiguration;
+      gemm_f32_dense_kernel<64, 64><<<small, 256, 0, stream>>>(p);
     }
     return cudaGetLastError();
   }
-  const dim3 grid((p.n + kTN - 1) / kTN, (p.m + kTM - 1) / kTM, p.batch * p.splits);
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(p);
+  const uint32_t blocks = f32_grid_blocks(p, kTM, kTN);
+  if (blocks == 0) return cudaErrorInvalidConfiguration;
+  gemm_f32_kernel<<<blocks, 256, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -29,6 +29,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 
 #include "gemm_sm100.cuh"
 #include "sm100_ptx.cuh"
@@ -1276,6 +1277,8 @@ size_t gemm_smem_bytes(const GemmParams& p) {
 
 // Co-resident 2-CTA clusters of the pair kernel for a given dynamic shared-memory size (cached per size).
 static uint32_t max_resident_pairs(size_t smem_bytes, int sm_count) {
+  static std::mutex guard;   // one handle per host thread, but this cache is shared by all of them
+  std::lock_guard<std::mutex> lock(guard);
   static size_t cached_smem[8] = {};
   static int cached_pairs[8] = {};
   static int cached_device[8] = {-1, -1, -1, -1, -1, -1, -1, -1};

@@ -156,5 +156,6 @@ cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, co
                               cudaStream_t stream);
 cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream);
 cudaError_t gemm_sm100_configure();
+uint32_t f32_grid_blocks(const GemmParams& p, uint32_t tm, uint32_t tn);
 
 }  // namespace gb

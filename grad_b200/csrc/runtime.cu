@@ -1046,18 +1046,23 @@ int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
 // All calls share the one array and it keeps whatever the previous call left: every element a call reads
 // is written by the same call first (each K part stores its whole partial tile), so nothing has to be
 // cleared, but two calls that overlap on the GPU -- different streams, or different host threads -- race on
-// it.  Serialise them.
+// it.  Serialise them.  A bounded device-side wait that gives up is reported into a status word that also lives in
+// the library image; gb_static_last_status reads and clears it.
 namespace {
 
 __device__ __align__(256) unsigned char g_static_scratch[GB_STATIC_SCRATCH_BYTES];
+// The word a kernel launched by this entry point reports a bounded wait that gave up into (0 = none); read and
+// cleared by gb_static_last_status.  Like the array it belongs to the library image, one copy per GPU.
+__device__ uint32_t g_static_status;
 
 constexpr int kMaxStaticDevices = 64;
 std::mutex g_static_mutex;
 void* g_static_scratch_ptr[kMaxStaticDevices] = {};
+uint32_t* g_static_status_ptr[kMaxStaticDevices] = {};
 int g_static_sm_count[kMaxStaticDevices] = {};
 
-// Resolves the device address of the scratch array for the current device (once), without allocating.
-int static_setup(int device, void** scratch, int* sm_count) {
+// Resolves the device addresses of the scratch array and the status word for the current device (once), without allocating.
+int static_setup(int device, void** scratch, uint32_t** status, int* sm_count) {
   std::lock_guard<std::mutex> lock(g_static_mutex);
   if (device < 0 || device >= kMaxStaticDevices) return GB_ERR_NO_DEVICE;
   if (g_static_scratch_ptr[device] == nullptr) {
@@ -1066,11 +1071,15 @@ int static_setup(int device, void** scratch, int* sm_count) {
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return GB_ERR_CUDA;
     void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return GB_ERR_CUDA;
+    void* word = nullptr;
+    if (cudaGetSymbolAddress(&word, g_static_status) != cudaSuccess || word == nullptr) return GB_ERR_CUDA;
     if (gb::gemm_sm100_configure() != cudaSuccess || encode_tiled_fn() == nullptr) return GB_ERR_CUDA;
     g_static_sm_count[device] = sms;
+    g_static_status_ptr[device] = (uint32_t*)word;
     g_static_scratch_ptr[device] = ptr;
   }
   *scratch = g_static_scratch_ptr[device];
+  *status = g_static_status_ptr[device];
   *sm_count = g_static_sm_count[device];
   return GB_OK;
 }
@@ -1085,9 +1094,9 @@ extern "C" int gb_gemm_static_scratch(void* stream, const gb_gemm_desc* desc, co
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return GB_ERR_NO_DEVICE;
   void* scratch = nullptr;
-  gb_handle local;            // lives on the host stack: no status word, so bounded-wait failures go unreported here
+  gb_handle local;            // lives on the host stack; its status word is the one inside the library image
   local.device = device;
-  rc = static_setup(device, &scratch, &local.sm_count);
+  rc = static_setup(device, &scratch, &local.status, &local.sm_count);
   if (rc != GB_OK) return rc;
   Plan plan;
   rc = plan_gemm(&local, desc, a, b, c, epilogue, plan);
@@ -1095,4 +1104,21 @@ extern "C" int gb_gemm_static_scratch(void* stream, const gb_gemm_desc* desc, co
   // A product whose partial sums do not fit the fixed array is refused, not silently run another way.
   if (plan.workspace > (size_t)GB_STATIC_SCRATCH_BYTES) return GB_ERR_WORKSPACE;
   return run_plan(&local, (cudaStream_t)stream, plan, scratch, GB_STATIC_SCRATCH_BYTES);
+}
+
+extern "C" int gb_static_last_status(void* stream, uint32_t* device_status) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return GB_ERR_NO_DEVICE;
+  void* scratch = nullptr;
+  uint32_t* status = nullptr;
+  int sms = 0;
+  int rc = static_setup(device, &scratch, &status, &sms);
+  if (rc != GB_OK) return rc;
+  uint32_t word = 0;
+  cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaMemcpy(&word, status, sizeof(word), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && word != 0) e = cudaMemset(status, 0, sizeof(word));
+  if (e != cudaSuccess) return GB_ERR_CUDA;
+  if (device_status) *device_status = word;
+  return word == 0 ? GB_OK : GB_ERR_TIMEOUT;
 }

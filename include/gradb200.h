@@ -149,10 +149,13 @@ int gb_gemm(gb_handle* h, void* stream, const gb_gemm_desc* desc, const void* a,
  * first call with a given device current resolves the array's device address; make that call outside
  * stream capture.  A product whose partials exceed the array returns GB_ERR_WORKSPACE.  All calls share
  * the array: calls that overlap on the GPU (two streams, two threads) race and must be serialised.
- * Device-side wait time-outs are not reported (there is no status word to report them into). */
+ * A bounded device-side wait that gave up leaves C partly written; gb_static_last_status (the handle-free
+ * gb_last_status: synchronises the stream, reads and clears a status word that also lives in the library image)
+ * then returns GB_ERR_TIMEOUT.  It allocates nothing either. */
 #define GB_STATIC_SCRATCH_BYTES (4u << 20)
 int gb_gemm_static_scratch(void* stream, const gb_gemm_desc* desc, const void* a, const void* b, void* c,
                            const gb_epilogue* epilogue);
+int gb_static_last_status(void* stream, uint32_t* device_status);
 
 /* ---- implicit-GEMM convolution ---------------------------------------------------------------- */
 /* Forward: replaces `Gpu.convImplicitForward` (src/gpu/gpu.zig:926-929), `Gpu.convF32Forward`

@@ -332,3 +332,24 @@ def test_strided_input_gradient_by_parity_classes(gpu, case, by_classes, math, t
         gpu.convInputGrad(to_dev(dy, half), to_dev(w, half), gx32, geo, accumulate=True, math=math)
         torch.cuda.synchronize()
         assert rel_fro(to_host(gx32) - 1.0, want) <= tol
+
+
+def test_strict_f32_convolution_with_more_than_65535_row_tiles(gpu):
+    """4096 images of 32 x 32 outputs are 65536 row tiles of 64 positions: the strict-f32 kernels index their tiles
+    on grid.x (grid.y and grid.z stop at 65535).  First, middle and last image against the oracle."""
+    import torch
+    from oracle import binding as orc
+
+    n, hw, c, co = 4096, 32, 8, 8
+    geo = _geo((n, hw, hw, c, 3, co, 1, 1, 1))
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    x = torch.randn((n, hw, hw, c), generator=gen, device="cuda")
+    w = torch.randn((9 * c, co), generator=gen, device="cuda") * (2.0 / (9 * c)) ** 0.5
+    y = torch.full((n, hw, hw, co), 3.0, device="cuda")
+    gpu.convForward(x, w, y, geo, math=0)
+    torch.cuda.synchronize()
+    assert gpu.last_plan()["tensor_path"] == 0
+    for img in (0, n // 2 - 1, n - 1):
+        d = _dims((1, hw, hw, c, 3, co, 1, 1, 1))
+        want = orc.conv_forward(to_host(x[img:img + 1]), to_host(w), d)
+        assert rel_fro(to_host(y[img:img + 1]), want) <= TOL_F32, img

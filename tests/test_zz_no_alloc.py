@@ -46,15 +46,54 @@ def test_static_scratch_matches_workspace_gemm_on_two_calls_in_a_row():
         d = _desc(abi, m, n, k)
         ep = abi.Epilogue(bias.data_ptr(), None, abi.ACT_RELU, 0)
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
+        # Free bytes as the driver counts them (cudaMemGetInfo): a cudaMalloc inside the library would lower this,
+        # whereas torch's own counters only see torch's caching allocator.  The first call may make the driver load
+        # the kernels lazily, so the comparison brackets the second call.
+        before = torch.cuda.mem_get_info()[0]
         rc = lib.gb_gemm_static_scratch(stream, C.byref(d), C.c_void_p(a.data_ptr()), C.c_void_p(b.data_ptr()),
                                         C.c_void_p(got.data_ptr()), C.byref(ep))
         assert rc == 0, abi.error_string(rc)
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        if call == 1:
+            assert torch.cuda.mem_get_info()[0] == before
+        word = C.c_uint32(7)
+        assert lib.gb_static_last_status(stream, C.byref(word)) == 0 and word.value == 0
         assert torch.equal(got, want), f"call {call}: max abs diff {(got - want).abs().max().item()}"
         ref = torch.relu(a.float() @ b.float() + bias)
         assert ((got - ref).norm() / ref.norm()).item() <= 2e-2
+    gpu.check_status()
+    gpu.close()
+
+
+def test_static_scratch_on_the_strict_f32_split_path():
+    """The strict-f32 kernels split K too (few tiles, long K) and their partial sums use the same fixed array."""
+    import torch
+
+    import grad_b200
+    from grad_b200 import MatmulOpts, MatmulShape, abi
+
+    gpu = grad_b200.Gpu(0)
+    lib = gpu.lib
+    m, n, k = 64, 128, 784              # the MLP's first product: two 64 x 64 tiles, K split three ways
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    for call in range(2):
+        a = torch.randn((m, k), generator=gen, device="cuda")
+        b = torch.randn((k, n), generator=gen, device="cuda")
+        want = torch.empty((m, n), device="cuda")
+        gpu.matmul(a, b, want, MatmulShape(m, n, k), MatmulOpts(), math=abi.MATH_F32)
+        plan = gpu.last_plan()
+        assert plan["tensor_path"] == 0 and plan["splits"] > 1, plan
+        got = torch.full((m, n), -1.0, device="cuda")
+        d = _desc(abi, m, n, k)
+        d.dtype_a = d.dtype_b = abi.F32
+        d.math = abi.MATH_F32
+        rc = lib.gb_gemm_static_scratch(stream, C.byref(d), C.c_void_p(a.data_ptr()), C.c_void_p(b.data_ptr()), C.c_void_p(got.data_ptr()), None)
+        assert rc == 0, abi.error_string(rc)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"call {call}: max abs diff {(got - want).abs().max().item()}"
+        ref = a.double() @ b.double()
+        assert ((got.double() - ref).norm() / ref.norm()).item() <= 1e-5
     gpu.check_status()
     gpu.close()
 
