@@ -125,18 +125,21 @@ class Replicas:
         count = (end - first.data_ptr()) // 4
         return torch.as_strided(first, (count,), (1,))
 
-    def averageGrads(self, grads: Union[torch.Tensor, Sequence[torch.Tensor]], finish: bool = False):
+    def averageGrads(self, grads: Union[torch.Tensor, Sequence[torch.Tensor]], finish: bool = False, barrier: bool = True):
         """Replaces every gradient, in every replica, by the mean over the replicas; identical bits everywhere.
         The replicas first meet at the barrier (replicas.zig:67), so a replica that has failed releases the others
         with `Stopped` before any of them has enqueued the collective.  A flat f32 tensor, or views into one flat
         buffer (`flat_grads`), are reduced by ONE call like the reference's single flat vector; tensors that live
         in separate allocations are reduced one after the other.  `finish` waits for the result on the host with
-        the group's deadline (the bounded form of the barrier after the reduction, replicas.zig:81)."""
+        the group's deadline (the bounded form of the barrier after the reduction, replicas.zig:81).  `barrier=False`
+        skips the host barrier in front (a store round trip per step) for callers that rely on `finish` and the
+        communicator's deadline alone to be released from a replica that failed."""
         if self.count == 1:
             return
         if self.comm is None:
             raise RuntimeError("averageGrads needs a CUDA device: the mean runs over NCCL, there is no host path")
-        self.wait()
+        if barrier:
+            self.wait()
         if isinstance(grads, torch.Tensor):
             grads = [grads]
         for g in grads:
