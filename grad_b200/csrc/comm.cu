@@ -95,13 +95,17 @@ void abort_comm(gb_comm* c) {
 // Polls the communicator until the call that answered `first` has settled; aborts it when the deadline passes.
 int settle(gb_comm* c, ncclResult_t first) {
   ncclResult_t state = first;
-  const auto deadline = Clock::now() + std::chrono::milliseconds(c->timeout_ms);
+  const auto start = Clock::now();
+  const auto deadline = start + std::chrono::milliseconds(c->timeout_ms);
   while (state == ncclInProgress) {
-    if (Clock::now() > deadline) {
+    const auto now = Clock::now();
+    if (now > deadline) {
       abort_comm(c);
       return GB_ERR_TIMEOUT;
     }
-    std::this_thread::sleep_for(std::chrono::microseconds(50));
+    // an enqueue settles within microseconds: poll without sleeping at first, so that back-to-back collectives are
+    // not spaced by the poll interval; back off once the wait is clearly a wait for a peer
+    if (now - start > std::chrono::microseconds(500)) std::this_thread::sleep_for(std::chrono::microseconds(50));
     if (nccl().ncclCommGetAsyncError(c->comm, &state) != ncclSuccess) state = ncclInternalError;
   }
   if (state != ncclSuccess) {

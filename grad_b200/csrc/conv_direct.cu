@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
+
 #include "gemm_sm100.cuh"
 #include "sm100_ptx.cuh"
 
@@ -150,7 +152,153 @@ __global__ void __launch_bounds__(128) conv_direct_kernel(const GemmParams p) {
   }
 }
 
+// ---- weight gradient of the same kind of layer --------------------------------------------------------------
+// dw[(tap, ci), co] += sum over positions of patch(x)[pos, (tap, ci)] * dy[pos, co] with taps * c <= 36 rows (the stem:
+// 27).  As a tensor-core product this has one 128-row tile that is four fifths padding, an A operand that only the
+// gather warps can build, and K = all positions: 181 us for the stem at batch 128, a third of the whole network's
+// weight-gradient time.  Here a block owns a contiguous range of positions and stages the patch values of 64 positions
+// at a time in shared memory, with their dy rows (both rounded to the operand type like the tensor path; every global
+// load of a tile is issued in that one staging phase, so their latencies overlap).  A thread keeps a 9-row x 4-channel
+// block of partial sums in registers: its lanes split into (position, channel quad), its warp into a group of nine
+// rows, so one 4-byte shared-memory read (two addresses per warp, different banks) feeds four FMAs.  (With one
+// channel per thread every patch value was read once per FMA and the kernel was bound by those reads: 67 us.)
+// Blocks write their partial matrices to the workspace and the split-K reduce kernel adds them in a fixed order, so
+// the result does not depend on scheduling.
+constexpr uint32_t kWgRows = 36;        // most (tap, channel) rows: four row groups of nine
+constexpr uint32_t kWgRowsPerGroup = 9;
+constexpr uint32_t kWgTile = 64;        // positions staged per round
+constexpr uint32_t kWgThreads = 256;
+
+__global__ void __launch_bounds__(kWgThreads) conv_direct_wgrad_kernel(const GemmParams p, uint32_t chunk) {
+  __shared__ __align__(16) float patch_s[kWgTile][kWgRows];
+  __shared__ float sum_s[kWgRows][64];
+  __shared__ __align__(16) float dy_s[kWgTile][64];
+  __shared__ int32_t row_dy[kWgRows], row_dx[kWgRows], row_ci[kWgRows];   // (tap, channel) row -> input offset and channel
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const ConvGeo& g = p.geo;
+  const uint32_t rows = g.k * g.k * g.c, positions = p.k;
+  const uint32_t span = min(g.c_out, 64u);             // output channels handled per pass
+  const uint32_t quads = span / 4;                     // lanes per position: 4, 8, 16 or 32
+  const uint32_t per_warp = 32 / quads;                // positions one warp instruction covers
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rg = warp & 3, pset = warp >> 2;      // row group; which half of the position slots
+  const uint32_t quad = lane % quads, slot = pset * per_warp + lane / quads, slots = 2 * per_warp;
+  const uint32_t per_image = g.out_h * g.out_w;
+  const uint32_t begin = blockIdx.x * chunk, end = min(positions, begin + chunk);
+  const bool dy_bf16 = p.gbsrc.src_is_bf16, x_bf16 = p.ga.src_is_bf16;
+  if (threadIdx.x < kWgRows) {
+    const uint32_t r = threadIdx.x, tap = r / g.c, ky = tap / g.k, kx = tap - ky * g.k;
+    row_dy[r] = r < rows ? (int32_t)(ky * g.dilation) - (int32_t)g.pad : -(1 << 20);   // rows past the layer's read nothing
+    row_dx[r] = (int32_t)(kx * g.dilation) - (int32_t)g.pad;
+    row_ci[r] = (int32_t)(r - tap * g.c);
+  }
+  // staging role of this thread: one position of the tile, every fourth row of it
+  const uint32_t st_pos = threadIdx.x % kWgTile, st_row0 = threadIdx.x / kWgTile;
+  constexpr uint32_t kRowStep = kWgThreads / kWgTile;
+  for (uint32_t co0 = 0; co0 < g.c_out; co0 += span) {
+    const uint32_t co = co0 + quad * 4;
+    float acc[kWgRowsPerGroup][4];
+#pragma unroll
+    for (uint32_t r = 0; r < kWgRowsPerGroup; ++r)
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) acc[r][j] = 0.0f;
+    for (uint32_t t0 = begin; t0 < end; t0 += kWgTile) {
+      __syncthreads();
+      {
+        // patch(x) of the tile's positions: this thread's position, every fourth row
+        const uint32_t pos = t0 + st_pos;
+        const bool valid = pos < end;
+        const uint32_t img = pos / per_image, rem = pos - img * per_image, oy = rem / g.out_w, ox = rem - oy * g.out_w;
+        const int32_t y0 = (int32_t)(oy * g.stride), x0 = (int32_t)(ox * g.stride);
+#pragma unroll
+        for (uint32_t r = st_row0; r < kWgRows; r += kRowStep) {
+          const int32_t py = y0 + row_dy[r], px = x0 + row_dx[r];
+          float v = 0.0f;
+          if (valid && py >= 0 && px >= 0 && py < (int32_t)g.h && px < (int32_t)g.w) {
+            const uint64_t idx = ((uint64_t)(img * g.h + py) * g.w + px) * g.c_step + row_ci[r];
+            v = x_bf16 ? bf16_to_f32(((const uint16_t*)p.ga.base)[idx]) : round_operand(((const float*)p.ga.base)[idx], p.tf32);
+          }
+          patch_s[st_pos][r] = v;
+        }
+        // dy of the tile's positions x this pass's channels, as f32: coalesced 16-byte loads, all in flight together
+        const uint32_t quads_per_row = span / 4;
+        for (uint32_t e = threadIdx.x; e < kWgTile * quads_per_row; e += kWgThreads) {
+          const uint32_t lp = e / quads_per_row, q4 = e - lp * quads_per_row, dpos = t0 + lp;
+          float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (dpos < end) {
+            const uint64_t idx = (uint64_t)dpos * p.gbsrc.ld + co0 + q4 * 4;
+            if (dy_bf16) {
+              const uint2 raw = *(const uint2*)((const uint16_t*)p.gbsrc.base + idx);
+              v = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u), __uint_as_float(raw.y << 16),
+                              __uint_as_float(raw.y & 0xFFFF0000u));
+            } else {
+              const float4 raw = *(const float4*)((const float*)p.gbsrc.base + idx);
+              v = make_float4(round_operand(raw.x, p.tf32), round_operand(raw.y, p.tf32), round_operand(raw.z, p.tf32), round_operand(raw.w, p.tf32));
+            }
+          }
+          *(float4*)&dy_s[lp][q4 * 4] = v;
+        }
+      }
+      __syncthreads();
+      const uint32_t steps = kWgTile / slots;
+#pragma unroll 4
+      for (uint32_t st = 0; st < steps; ++st) {
+        const uint32_t lp = st * slots + slot;
+        const float4 dq = *(const float4*)&dy_s[lp][quad * 4];
+        const float d[4] = {dq.x, dq.y, dq.z, dq.w};
+        const float* prow = &patch_s[lp][rg * kWgRowsPerGroup];
+#pragma unroll
+        for (uint32_t r = 0; r < kWgRowsPerGroup; ++r) {
+          const float v = prow[r];
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) acc[r][j] = fmaf(v, d[j], acc[r][j]);
+        }
+      }
+    }
+    // combine the position slots in slot order, then write this block's partial matrix [rows][c_out]
+    for (uint32_t turn = 0; turn < slots; ++turn) {
+      __syncthreads();
+      if (slot == turn) {
+#pragma unroll
+        for (uint32_t r = 0; r < kWgRowsPerGroup; ++r)
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            float* cell = &sum_s[rg * kWgRowsPerGroup + r][quad * 4 + j];
+            *cell = turn == 0 ? acc[r][j] : *cell + acc[r][j];
+          }
+      }
+    }
+    __syncthreads();
+    float* dst = p.partial + (uint64_t)blockIdx.x * rows * g.c_out;
+    for (uint32_t e = threadIdx.x; e < rows * span; e += kWgThreads) {
+      const uint32_t r = e / span, c = e - r * span;
+      dst[(uint64_t)r * g.c_out + co0 + c] = sum_s[r][c];
+    }
+  }
+}
+
 }  // namespace
+
+// Weight gradients this kernel takes: at most 36 (tap, channel) rows, 16, 32 or a multiple of 64 output channels,
+// dy read as stored with 8-byte (bf16) or 16-byte (f32) aligned channel quads.
+bool conv_direct_wgrad_applies(const GemmParams& p) {
+  const ConvGeo& g = p.geo;
+  const uint32_t rows = g.k * g.k * g.c;
+  const bool lanes_ok = g.c_out == 16 || g.c_out == 32 || g.c_out % 64 == 0;
+  const bool aligned = ((uintptr_t)p.gbsrc.base & 15) == 0 && p.gbsrc.ld % 4 == 0;
+  return g.c <= 4 && rows <= kWgRows && lanes_ok && aligned && p.gbsrc.source == kSrcDense && p.ga.source == kSrcPatch && !p.transpose_out;
+}
+uint32_t conv_direct_wgrad_blocks(const GemmParams& p, int sm_count) {
+  const uint32_t want = (p.k + 2 * kWgTile - 1) / (2 * kWgTile);      // at least two staged tiles per block
+  return std::max(1u, std::min<uint32_t>(want, (uint32_t)sm_count * 4));
+}
+// `p.partial` holds blocks * rows * c_out floats; `p.splits` is set to the block count for the reduce launch that follows.
+cudaError_t launch_conv_direct_wgrad(const GemmParams& p, uint32_t blocks, cudaStream_t stream) {
+  if (p.k == 0) return cudaSuccess;
+  const uint32_t chunk = (p.k + blocks - 1) / blocks;
+  return launch_overlapped(conv_direct_wgrad_kernel, dim3(blocks), dim3(kWgThreads), 0, stream, p, chunk);
+}
 
 // The shapes this kernel takes: a forward pass whose whole filter fits 48 KB of shared memory as f32, output
 // channels in whole chunks, and a result that can be stored 16 bytes at a time.

@@ -612,7 +612,21 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* tmap_c, uint8
 }
 
 __device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
-                                                   const float* sbias, uint32_t batch, uint32_t row, uint32_t col0, uint32_t lane) {
+                                                   const float* sbias, uint32_t batch, uint32_t split, uint32_t row, uint32_t col0, uint32_t lane) {
+  if (p.splits > 1) {
+    // A K part's partial tile: the raw f32 accumulators, into the map of the partial buffer {n, m, split * batch}.
+    // (Stored straight from the accumulator layout a lane owns a row and a warp-wide store half-fills 32 sectors:
+    // with 29 parts of a weight gradient in flight those stores were most of the kernel.)
+    const int32_t y = (int32_t)(row - lane), z = (int32_t)(split * p.batch + batch);
+#pragma unroll
+    for (uint32_t half = 0; half < 2; ++half) {
+      uint4 q[4];
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) q[j] = make_uint4(acc[16 * half + 4 * j], acc[16 * half + 4 * j + 1], acc[16 * half + 4 * j + 2], acc[16 * half + 4 * j + 3]);
+      stage_and_store(tmap_c, stage, q, lane, (int32_t)(col0 + 16 * half), y, z);
+    }
+    return;
+  }
   const bool live = row < p.m;
   const uint64_t off = (uint64_t)batch * p.stride_c + (uint64_t)row * p.ldc + col0;
   float v[32];
@@ -732,7 +746,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     release();
     return;
   }
-  if (p.tma_store && p.splits == 1) {
+  if (p.tma_store) {
     // Chunks that lie wholly inside C and rows that begin inside it go through the TMA store; a ragged last
     // chunk takes the guarded scalar path with its bias read back from the staged values.
     auto tile_col = [&](uint32_t c) { return wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c; };
@@ -746,7 +760,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
       else release();
       {
         const uint32_t col0 = col_base + tile_col(c);
-        if (col0 + 32 <= p.n && row - lane < p.m) epilogue_chunk_tma(p, tmap_c, acc_a, store_stage, sbias + 32 * i, batch, row, col0, lane);
+        if (col0 + 32 <= p.n && row - lane < p.m) epilogue_chunk_tma(p, tmap_c, acc_a, store_stage, sbias + 32 * i, batch, split, row, col0, lane);
         else epilogue_chunk_copy(p, acc_a, batch, split, row, col0, p.bias ? sbias[32 * i + lane] : 0.0f);
       }
       if (has_b) {
@@ -754,7 +768,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
         if (c + 2 * step < ncols) tmem_ld_32x32(taddr + c + 2 * step, acc_a);
         else release();
         const uint32_t col0 = col_base + tile_col(c + step);
-        if (col0 + 32 <= p.n && row - lane < p.m) epilogue_chunk_tma(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), batch, row, col0, lane);
+        if (col0 + 32 <= p.n && row - lane < p.m) epilogue_chunk_tma(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), batch, split, row, col0, lane);
         else epilogue_chunk_copy(p, acc_b, batch, split, row, col0, p.bias ? sbias[32 * (i + 1) + lane] : 0.0f);
       }
     }
@@ -985,7 +999,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     const uint32_t quarter = warp & 3;
     uint32_t buf = 0, buf_phase = 0;
     bool ok = true;
-    const bool tma_out = p.tma_store && p.splits == 1;
+    const bool tma_out = p.tma_store != 0;
     uint8_t* epi_smem = tiles + p.stages * stage_bytes;
     uint8_t* store_stage = epi_smem + (warp - 2) * kStoreStageBytesPerWarp;
     float* sbias = (float*)(epi_smem + 8 * kStoreStageBytesPerWarp + (warp - 2) * kStoreBiasBytesPerWarp);
@@ -994,7 +1008,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       const Work work = decode_work(p, w);
       if (work.empty) continue;
-      if (tma_out && bias_tile != work.n_tile) {
+      if (tma_out && p.splits == 1 && bias_tile != work.n_tile) {
         stage_bias(p, sbias, p.bn, work.n_tile * p.bn, false, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
         bias_tile = work.n_tile;
       }
@@ -1199,7 +1213,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     const uint32_t quarter = warp & 3;
     uint32_t buf = 0, buf_phase = 0;
     bool ok = true;
-    const bool tma_out = p.tma_store && p.splits == 1;
+    const bool tma_out = p.tma_store != 0;
     uint8_t* epi_smem = tiles + p.stages * stage_bytes;
     uint8_t* store_stage = epi_smem + (warp - 2) * kStoreStageBytesPerWarp;
     float* sbias = (float*)(epi_smem + 8 * kStoreStageBytesPerWarp + (warp - 2) * kStoreBiasBytesPerWarp);
@@ -1208,7 +1222,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     for (uint32_t w = pair; ok && w < total_work; w += pairs) {
       const Work work = decode_work(p, w);
       if (work.empty) continue;
-      if (tma_out && bias_tile != work.n_tile) {
+      if (tma_out && p.splits == 1 && bias_tile != work.n_tile) {
         stage_bias(p, sbias, p.bn, work.n_tile * p.bn, halves == 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
         bias_tile = work.n_tile;
       }
@@ -1262,6 +1276,54 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
     if (p.relu) x = fmaxf(x, 0.0f);
     if (p.round_tf32) x = round_tf32(x);
     store_out(p.c, p.c_is_bf16, idx, x);
+  }
+}
+
+// The same combine for MANY parts (a weight gradient splits its positions 14-29 ways, the stem's FMA kernel into one part
+// per block): one thread per element would chain that many dependent-latency loads (29 parts: 9 us for a 576 x 64 matrix,
+// a third of the layer's time).  Here a block is 32 consecutive elements x 8 part groups: warp g sums its eighth of
+// the parts in part order, the eight group sums are added in group order.  The association is fixed by (parts, 8), so
+// the result is reproducible; it is not the left-to-right sum of the kernel above.
+constexpr uint32_t kReduceGroups = 8;
+__global__ void __launch_bounds__(32 * kReduceGroups) splitk_reduce_grouped_kernel(const GemmParams p) {
+  __shared__ float group_sum[kReduceGroups][32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const uint64_t per_batch = (uint64_t)p.m * p.n;
+  const uint64_t total = per_batch * p.batch;
+  const uint32_t lane = threadIdx.x & 31, group = threadIdx.x >> 5;
+  const uint32_t s_begin = (uint32_t)((uint64_t)p.splits * group / kReduceGroups), s_end = (uint32_t)((uint64_t)p.splits * (group + 1) / kReduceGroups);
+  for (uint64_t t0 = (uint64_t)blockIdx.x * 32; t0 < total; t0 += (uint64_t)gridDim.x * 32) {
+    const uint64_t t = t0 + lane;
+    float x = 0.0f;
+    if (t < total) {
+      const float* src = p.partial + t;
+      uint32_t sidx = s_begin;
+      for (; sidx + 4 <= s_end; sidx += 4) {
+        const float v0 = src[(uint64_t)sidx * total], v1 = src[(uint64_t)(sidx + 1) * total], v2 = src[(uint64_t)(sidx + 2) * total],
+                    v3 = src[(uint64_t)(sidx + 3) * total];
+        x += v0; x += v1; x += v2; x += v3;
+      }
+      for (; sidx < s_end; ++sidx) x += src[(uint64_t)sidx * total];
+    }
+    __syncthreads();
+    group_sum[group][lane] = x;
+    __syncthreads();
+    if (group == 0 && t < total) {
+      x = group_sum[0][lane];
+#pragma unroll
+      for (uint32_t gi = 1; gi < kReduceGroups; ++gi) x += group_sum[gi][lane];
+      const uint32_t batch = (uint32_t)(t / per_batch);
+      const uint64_t r = t - (uint64_t)batch * per_batch;
+      const uint32_t row = (uint32_t)(r / p.n), col = (uint32_t)(r - (uint64_t)row * p.n);
+      const uint64_t idx = (uint64_t)batch * p.stride_c + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
+      if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx);
+      if (p.bias) x += p.bias[col];
+      if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
+      if (p.relu) x = fmaxf(x, 0.0f);
+      if (p.round_tf32) x = round_tf32(x);
+      store_out(p.c, p.c_is_bf16, idx, x);
+    }
   }
 }
 
@@ -1337,6 +1399,10 @@ cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, co
 cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream) {
   const uint64_t total = (uint64_t)p.m * p.n * p.batch;
   if (total == 0) return cudaSuccess;
+  if (p.splits >= 3 * kReduceGroups) {
+    const uint32_t blocks = (uint32_t)((total + 31) / 32 < 148 * 32 ? (total + 31) / 32 : 148 * 32);
+    return launch_overlapped(splitk_reduce_grouped_kernel, dim3(blocks), dim3(32 * kReduceGroups), 0, stream, p);
+  }
   const uint32_t blocks = (uint32_t)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   return launch_overlapped(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, p);
 }

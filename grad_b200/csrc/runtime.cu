@@ -20,6 +20,9 @@ namespace gb {
 cudaError_t launch_gemm_f32(const GemmParams& p, cudaStream_t stream);
 bool conv_direct_applies(const GemmParams& p);
 cudaError_t launch_conv_direct(const GemmParams& p, int sm_count, cudaStream_t stream);
+bool conv_direct_wgrad_applies(const GemmParams& p);
+uint32_t conv_direct_wgrad_blocks(const GemmParams& p, int sm_count);
+cudaError_t launch_conv_direct_wgrad(const GemmParams& p, uint32_t blocks, cudaStream_t stream);
 }
 
 struct gb_handle {
@@ -131,6 +134,8 @@ struct Plan {
   GemmParams p;
   CUtensorMap tmap_a, tmap_b, tmap_c;
   bool direct = false;      // forward convolution with very few input channels: the FMA kernel of conv_direct.cu
+  uint32_t direct_wgrad_blocks = 0;   // > 0: weight gradient of such a layer by the FMA kernel, this many position ranges
+  size_t direct_wgrad_bytes = 0;      // ... when the workspace holds their partial matrices
   bool tensor = false;      // tcgen05 path, else strict-f32
   size_t workspace = 0;     // bytes of split-K partials
 };
@@ -368,6 +373,18 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
     const cudaError_t de = gb::launch_conv_direct(p, h->sm_count, stream);
     return de == cudaSuccess ? GB_OK : cuda_fail(h, de);
   }
+  if (plan.direct_wgrad_blocks > 0 && workspace != nullptr && workspace_bytes >= plan.direct_wgrad_bytes && aligned16(workspace)) {
+    p.partial = (float*)workspace;
+    p.splits = plan.direct_wgrad_blocks;
+    gb_plan_info& di = h->last_plan;
+    di = gb_plan_info{};
+    di.tensor_path = 0; di.a_kind = di.b_kind = (uint32_t)gb::kGather;
+    di.tile_m = p.m; di.tile_n = p.n; di.stages = 1; di.splits = p.splits; di.k_blocks = 1;
+    di.work_items = p.splits; di.kernel_launches = 2;
+    cudaError_t de = gb::launch_conv_direct_wgrad(p, plan.direct_wgrad_blocks, stream);
+    if (de == cudaSuccess) de = gb::launch_splitk_reduce(p, stream);
+    return de == cudaSuccess ? GB_OK : cuda_fail(h, de);
+  }
   if (p.splits > 1) {
     if (workspace == nullptr || workspace_bytes < plan.workspace || !aligned16(workspace)) {
       // Without room for partials the product runs unsplit rather than failing.
@@ -401,7 +418,13 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
   // {n, m, batch} with a box of 64 bytes x 32 rows, the block one epilogue warp stages per chunk.
   p.tma_store = 0;
   std::memset(&plan.tmap_c, 0, sizeof(plan.tmap_c));
-  if (plan.tensor && p.k != 0 && p.vec_store && !p.transpose_out && !p.rowmap.enabled && p.epi_groups == 2 &&
+  if (plan.tensor && p.k != 0 && p.splits > 1 && p.epi_groups == 2 && (p.n & 3) == 0 && !knobs().no_tma_store) {
+    // K parts leave their partial tiles the same way, through a map of the partial buffer {n, m, split * batch}
+    const uint64_t dims[3] = {p.n, p.m, (uint64_t)p.splits * p.batch};
+    const uint64_t strides[2] = {(uint64_t)p.n * 4, (uint64_t)p.n * 4 * p.m};
+    const uint32_t box[3] = {16, 32, 1};
+    p.tma_store = encode_map(&plan.tmap_c, false, p.partial, 3, dims, strides, box, false, nullptr, true) ? 1 : 0;
+  } else if (plan.tensor && p.k != 0 && p.splits == 1 && p.vec_store && !p.transpose_out && !p.rowmap.enabled && p.epi_groups == 2 &&
       !knobs().no_tma_store) {
     const uint32_t es = p.c_is_bf16 ? 2 : 4;
     const uint64_t dims[3] = {p.n, p.m, p.batch};
@@ -671,6 +694,10 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     set_output(p, out, d->dtype_w, g.c_out, 0, false, d->accumulate, nullptr);
     int rc = finish_plan(h, plan, true, min_bn, nullptr);
     if (rc != GB_OK) return rc;
+    if (plan.tensor && gb::conv_direct_wgrad_applies(p) && !knobs().no_direct_conv) {
+      plan.direct_wgrad_blocks = gb::conv_direct_wgrad_blocks(p, h->sm_count);
+      plan.direct_wgrad_bytes = (size_t)plan.direct_wgrad_blocks * p.m * p.n * sizeof(float);
+    }
     if (plan.tensor) {
       p.a_kind = gb::kGather;
       const bool view = g.k == 1 && g.pad == 0 && g.stride > 1 && !knobs().no_strided_tma;
@@ -702,6 +729,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
         p.stages = std::min<uint32_t>(8, (227 * 1024 - 2048) / (2 * (128 * 128 + p.bn * 128)));
       }
     }
+    plan.workspace = std::max(plan.workspace, plan.direct_wgrad_bytes);
   }
   return GB_OK;
 }
