@@ -7,7 +7,7 @@ compute call goes through the C ABI and fails loudly when the CUDA library is mi
 """
 from .abi import (ACT_NONE, ACT_RELU, BF16, F32, MATH_BF16, MATH_F32, MATH_TF32, GbError, abi_version, error_string, library,
                   library_path)
-from .gpu import ConvGeometry, Epilogue, Gpu, MatmulOpts, MatmulShape, conv_geometry
+from .gpu import ConvGeometry, Epilogue, Gpu, MatmulOpts, MatmulShape, PreparedWeights, conv_geometry
 
 __all__ = ["ACT_NONE", "ACT_RELU", "BF16", "F32", "MATH_BF16", "MATH_F32", "MATH_TF32", "GbError", "abi_version", "error_string",
-           "library", "library_path", "ConvGeometry", "Epilogue", "Gpu", "MatmulOpts", "MatmulShape", "conv_geometry"]
+           "library", "library_path", "ConvGeometry", "Epilogue", "Gpu", "MatmulOpts", "MatmulShape", "PreparedWeights", "conv_geometry"]

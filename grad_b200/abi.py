@@ -16,6 +16,7 @@ MATH_F32, MATH_TF32, MATH_BF16 = 0, 1, 2
 ACT_NONE, ACT_RELU = 0, 1
 EPILOGUE_ROUND_TF32 = 1
 PASS_FPROP, PASS_DGRAD, PASS_WGRAD = 0, 1, 2
+WEIGHTS_PLAIN, WEIGHTS_ROWS = 0, 1
 
 STATUS_NAMES = {0: "GB_OK", 1: "GB_ERR_INVALID", 2: "GB_ERR_CUDA", 3: "GB_ERR_WORKSPACE", 4: "GB_ERR_UNSUPPORTED",
                 5: "GB_ERR_TIMEOUT", 6: "GB_ERR_NCCL", 7: "GB_ERR_NO_DEVICE"}
@@ -69,6 +70,12 @@ SIGNATURES = {
     "gb_last_status": ([C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)], C.c_int),
     "gb_sm_count": ([C.c_void_p], C.c_int),
     "gb_last_plan": ([C.c_void_p, C.POINTER(PlanInfo)], C.c_int),
+    "gb_plan_cache_hits": ([C.c_void_p], C.c_uint64),
+    "gb_weights_bytes": ([C.c_uint32, C.c_uint32, C.c_int], C.c_size_t),
+    "gb_prepare_weights": ([C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)], C.c_int),
+    "gb_refresh_weights": ([C.c_void_p, C.c_void_p], C.c_int),
+    "gb_weights_data": ([C.c_void_p], C.c_void_p),
+    "gb_weights_destroy": ([C.c_void_p], None),
     "gb_gemm_workspace": ([C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_size_t)], C.c_int),
     "gb_gemm": ([C.c_void_p, C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Epilogue), C.c_void_p,
                  C.c_size_t], C.c_int),

@@ -143,9 +143,69 @@ unsigned blocks_for(size_t total) {
 
 int finish() { return cudaGetLastError() == cudaSuccess ? GB_OK : GB_ERR_CUDA; }
 
+
+
+// (rows, cols) f32 -> (cols, rows) in the destination type through a 32 x 33 shared-memory tile: both sides coalesced.
+__global__ void transpose_cast_kernel(const float* src, void* dst, int dst_bf16, uint32_t rows, uint32_t cols) {
+  __shared__ float tile[32][33];
+  const uint32_t r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+  for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
+    const uint32_t r = r0 + i, c = c0 + threadIdx.x;
+    tile[i][threadIdx.x] = (r < rows && c < cols) ? src[(size_t)r * cols + c] : 0.0f;
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
+    const uint32_t c = c0 + i, r = r0 + threadIdx.x;
+    if (c < cols && r < rows) store_elem(dst, dst_bf16, (size_t)c * rows + r, tile[threadIdx.x][i]);
+  }
+}
+
+}  // namespace
+
+// A prepared copy of one f32 master weight matrix: where it came from, where the copy lives, how to remake it.
+struct gb_weights {
+  const float* master;
+  void* data;
+  uint32_t rows, cols;
+  int kind, dtype;
+};
+
+namespace {
+
+int convert_weights(const gb_weights* w, cudaStream_t stream) {
+  const size_t total = (size_t)w->rows * w->cols;
+  if (total == 0) return GB_OK;
+  if (w->kind == GB_WEIGHTS_PLAIN) return gb_cast(stream, GB_F32, w->dtype, w->master, w->data, total);
+  const dim3 grid((w->cols + 31) / 32, (w->rows + 31) / 32), block(32, 8);
+  transpose_cast_kernel<<<grid, block, 0, stream>>>(w->master, w->data, w->dtype == GB_BF16, w->rows, w->cols);
+  return cudaGetLastError() == cudaSuccess ? GB_OK : GB_ERR_CUDA;
+}
+
 }  // namespace
 
 extern "C" {
+
+size_t gb_weights_bytes(uint32_t rows, uint32_t cols, int dtype) { return (size_t)rows * cols * (dtype == GB_BF16 ? 2 : 4); }
+
+int gb_prepare_weights(void* stream, const float* master, uint32_t rows, uint32_t cols, int kind, int dtype, void* storage, size_t storage_bytes,
+                       gb_weights** out) {
+  if (!out) return GB_ERR_INVALID;
+  *out = nullptr;
+  if (!master || !storage || (kind != GB_WEIGHTS_PLAIN && kind != GB_WEIGHTS_ROWS) || (dtype != GB_F32 && dtype != GB_BF16)) return GB_ERR_INVALID;
+  if (storage_bytes < gb_weights_bytes(rows, cols, dtype) || ((uintptr_t)storage & 15) != 0) return GB_ERR_INVALID;
+  gb_weights* w = new gb_weights{master, storage, rows, cols, kind, dtype};
+  const int rc = convert_weights(w, (cudaStream_t)stream);
+  if (rc != GB_OK) {
+    delete w;
+    return rc;
+  }
+  *out = w;
+  return GB_OK;
+}
+
+int gb_refresh_weights(const gb_weights* weights, void* stream) { return weights ? convert_weights(weights, (cudaStream_t)stream) : GB_ERR_INVALID; }
+const void* gb_weights_data(const gb_weights* weights) { return weights ? weights->data : nullptr; }
+void gb_weights_destroy(gb_weights* weights) { delete weights; }
 
 int gb_pool2d(void* stream, int is_max, int dtype, const void* x, void* y, uint32_t n, uint32_t h, uint32_t w, uint32_t c, uint32_t k,
               uint32_t stride, uint32_t pad) {

@@ -25,15 +25,7 @@ uint32_t conv_direct_wgrad_blocks(const GemmParams& p, int sm_count);
 cudaError_t launch_conv_direct_wgrad(const GemmParams& p, uint32_t blocks, cudaStream_t stream);
 }
 
-struct gb_handle {
-  int device = 0;
-  int sm_count = 0;
-  int last_cuda = 0;
-  uint32_t* status = nullptr;   // device word the kernels report bounded-wait failures into
-  uint32_t test_drops_left = 0; // fault injection requested through the environment: calls that still drop a K block
-  gb_plan_info last_plan = {};
-};
-
+struct gb_handle;
 
 namespace {
 
@@ -66,6 +58,7 @@ struct Knobs {
   bool no_dgrad_classes = false; // GB_NO_DGRAD_CLASSES: a strided input gradient is one gathered product
   bool no_wide_stages = false;   // GB_NO_WIDE_STAGES: weight gradients keep one K block per stage
   bool no_fused_classes = false; // GB_NO_FUSED_CLASSES: one launch per parity class of a strided input gradient
+  bool no_plan_cache = false;    // GB_NO_PLAN_CACHE: every call plans from scratch
   int force_bn = 0;              // GB_FORCE_BN=n: tile width of a dense single-CTA product (with GB_FORCE_SPLITS: its K split)
   int force_splits = 0;
   // Host-requested failure injection for the time-out path (tests only): the first GB_TEST_DROP_CALLS (default 1)
@@ -85,6 +78,7 @@ const Knobs& knobs() {
     v.no_dgrad_classes = getenv("GB_NO_DGRAD_CLASSES") != nullptr;
     v.no_wide_stages = getenv("GB_NO_WIDE_STAGES") != nullptr;
     v.no_fused_classes = getenv("GB_NO_FUSED_CLASSES") != nullptr;
+    v.no_plan_cache = getenv("GB_NO_PLAN_CACHE") != nullptr;
     if (const char* g = getenv("GB_FORCE_BN")) v.force_bn = atoi(g);
     if (const char* g = getenv("GB_FORCE_SPLITS")) v.force_splits = atoi(g);
     if (const char* g = getenv("GB_TEST_SPIN_LIMIT")) v.test_spin_limit = (uint32_t)std::max(1, atoi(g));
@@ -96,11 +90,6 @@ const Knobs& knobs() {
     return v;
   }();
   return k;
-}
-
-int cuda_fail(gb_handle* h, cudaError_t e) {
-  if (h) h->last_cuda = (int)e;
-  return GB_ERR_CUDA;
 }
 
 uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
@@ -130,15 +119,52 @@ bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, co
   return r == CUDA_SUCCESS;
 }
 
+enum LaunchKind : uint32_t { kLaunchNone, kLaunchDirect, kLaunchDirectWgrad, kLaunchEmptyK, kLaunchTensor, kLaunchF32 };
+
 struct Plan {
   GemmParams p;
   CUtensorMap tmap_a, tmap_b, tmap_c;
+  LaunchKind launch = kLaunchNone;   // set by prepare_plan: which kernel runs ...
+  bool reduce = false;               // ... and whether the split-K reduce follows it
+  gb_plan_info info = {};            // what gb_last_plan reports after the launch
   bool direct = false;      // forward convolution with very few input channels: the FMA kernel of conv_direct.cu
   uint32_t direct_wgrad_blocks = 0;   // > 0: weight gradient of such a layer by the FMA kernel, this many position ranges
   size_t direct_wgrad_bytes = 0;      // ... when the workspace holds their partial matrices
   bool tensor = false;      // tcgen05 path, else strict-f32
   size_t workspace = 0;     // bytes of split-K partials
 };
+
+struct PlanKey {
+  uint32_t kind, pad;
+  unsigned char desc[72];
+  uint64_t ptr[8];
+  uint64_t hash;     // over the bytes before it
+};
+struct CachedPlan {
+  PlanKey key;
+  Plan plan;
+  uint64_t stamp;
+};
+
+}  // namespace
+
+struct gb_handle {
+  int device = 0;
+  int sm_count = 0;
+  int last_cuda = 0;
+  uint32_t* status = nullptr;   // device word the kernels report bounded-wait failures into
+  uint32_t test_drops_left = 0; // fault injection requested through the environment: calls that still drop a K block
+  gb_plan_info last_plan = {};
+  std::vector<CachedPlan> cache;   // prepared plans of recent calls
+  uint64_t cache_clock = 0, cache_hits = 0;
+};
+
+namespace {
+
+int cuda_fail(gb_handle* h, cudaError_t e) {
+  if (h) h->last_cuda = (int)e;
+  return GB_ERR_CUDA;
+}
 
 // Dense operand stored as `lines` rows of `inner` contiguous elements with pitch ld.
 struct DenseOperand {
@@ -361,29 +387,33 @@ int plan_gemm(const gb_handle* h, const gb_gemm_desc* d, const void* a, const vo
   return GB_OK;
 }
 
-int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, size_t workspace_bytes) {
+// Everything a call decides before it launches: workspace use, the result's TMA map, stage count, what to launch.
+// No CUDA launch happens here, so a prepared plan can be kept and launched again (the plan cache below).
+int prepare_plan(const gb_handle* h, Plan& plan, void* workspace, size_t workspace_bytes) {
   GemmParams& p = plan.p;
-  if (p.m == 0 || p.n == 0 || p.batch == 0) return GB_OK;   // an empty grid is a no-op (src/gpu/gpu.zig:612)
+  gb_plan_info& info = plan.info;
+  info = gb_plan_info{};
+  plan.reduce = false;
+  if (p.m == 0 || p.n == 0 || p.batch == 0) {   // an empty grid is a no-op (src/gpu/gpu.zig:612)
+    plan.launch = kLaunchNone;
+    return GB_OK;
+  }
   if (plan.direct) {
-    gb_plan_info& di = h->last_plan;
-    di = gb_plan_info{};
-    di.tensor_path = 0; di.a_kind = di.b_kind = (uint32_t)gb::kGather;
-    di.tile_m = 128; di.tile_n = 32; di.stages = 1; di.splits = 1; di.k_blocks = 1;
-    di.work_items = (p.m + 127) / 128; di.kernel_launches = 1;
-    const cudaError_t de = gb::launch_conv_direct(p, h->sm_count, stream);
-    return de == cudaSuccess ? GB_OK : cuda_fail(h, de);
+    plan.launch = kLaunchDirect;
+    info.tensor_path = 0; info.a_kind = info.b_kind = (uint32_t)gb::kGather;
+    info.tile_m = 128; info.tile_n = 32; info.stages = 1; info.splits = 1; info.k_blocks = 1;
+    info.work_items = (p.m + 127) / 128; info.kernel_launches = 1;
+    return GB_OK;
   }
   if (plan.direct_wgrad_blocks > 0 && workspace != nullptr && workspace_bytes >= plan.direct_wgrad_bytes && aligned16(workspace)) {
+    plan.launch = kLaunchDirectWgrad;
+    plan.reduce = true;
     p.partial = (float*)workspace;
     p.splits = plan.direct_wgrad_blocks;
-    gb_plan_info& di = h->last_plan;
-    di = gb_plan_info{};
-    di.tensor_path = 0; di.a_kind = di.b_kind = (uint32_t)gb::kGather;
-    di.tile_m = p.m; di.tile_n = p.n; di.stages = 1; di.splits = p.splits; di.k_blocks = 1;
-    di.work_items = p.splits; di.kernel_launches = 2;
-    cudaError_t de = gb::launch_conv_direct_wgrad(p, plan.direct_wgrad_blocks, stream);
-    if (de == cudaSuccess) de = gb::launch_splitk_reduce(p, stream);
-    return de == cudaSuccess ? GB_OK : cuda_fail(h, de);
+    info.tensor_path = 0; info.a_kind = info.b_kind = (uint32_t)gb::kGather;
+    info.tile_m = p.m; info.tile_n = p.n; info.stages = 1; info.splits = p.splits; info.k_blocks = 1;
+    info.work_items = p.splits; info.kernel_launches = 2;
+    return GB_OK;
   }
   if (p.splits > 1) {
     if (workspace == nullptr || workspace_bytes < plan.workspace || !aligned16(workspace)) {
@@ -395,17 +425,11 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
     }
   }
   p.spin_limit = knobs().test_spin_limit;
-  if (plan.tensor && !p.cta_pair && h->test_drops_left > 0 && knobs().test_drop_kblock) {
-    p.test_drop_kblock = knobs().test_drop_kblock;
-    --h->test_drops_left;
-  }
-  gb_plan_info& info = h->last_plan;
   info.tensor_path = plan.tensor;
   info.a_kind = plan.tensor ? p.a_kind : (uint32_t)gb::kGather;
   info.b_kind = plan.tensor ? p.b_kind : (uint32_t)gb::kGather;
   info.tile_m = plan.tensor ? (p.cta_pair ? 256 : 128) : 64;
   info.tile_n = p.bn;
-  info.stages = p.stages;
   info.splits = p.splits;
   info.k_blocks = p.k_blocks_total;
   info.work_items = p.tiles_m * p.tiles_n * p.batch * p.splits;
@@ -442,21 +466,96 @@ int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, siz
     p.stages = std::max(2u, std::min(p.stages, fit));
   }
   info.stages = p.stages;
-  cudaError_t e;
   if (p.k == 0) {
     // An empty contraction is a zero product: only the epilogue runs (through the reduce kernel, zero parts).
     p.splits = 0;
     p.partial = nullptr;
-    e = gb::launch_splitk_reduce(p, stream);
-    return e == cudaSuccess ? GB_OK : cuda_fail(h, e);
+    plan.launch = kLaunchEmptyK;
+    plan.reduce = true;
+    return GB_OK;
   }
-  e = plan.tensor ? gb::launch_gemm_sm100(p, plan.tmap_a, plan.tmap_b, plan.tmap_c, h->sm_count, stream) : gb::launch_gemm_f32(p, stream);
-  if (e != cudaSuccess) return cuda_fail(h, e);
-  if (p.splits > 1) {
-    e = gb::launch_splitk_reduce(p, stream);
-    if (e != cudaSuccess) return cuda_fail(h, e);
-  }
+  plan.launch = plan.tensor ? kLaunchTensor : kLaunchF32;
+  plan.reduce = p.splits > 1;
   return GB_OK;
+}
+
+// Launches a prepared plan on `stream`.
+int launch_plan(gb_handle* h, cudaStream_t stream, const Plan& plan) {
+  h->last_plan = plan.info;
+  cudaError_t e = cudaSuccess;
+  switch (plan.launch) {
+    case kLaunchNone: return GB_OK;
+    case kLaunchDirect: e = gb::launch_conv_direct(plan.p, h->sm_count, stream); break;
+    case kLaunchDirectWgrad: e = gb::launch_conv_direct_wgrad(plan.p, plan.direct_wgrad_blocks, stream); break;
+    case kLaunchEmptyK: break;
+    case kLaunchF32: e = gb::launch_gemm_f32(plan.p, stream); break;
+    case kLaunchTensor:
+      if (!plan.p.cta_pair && h->test_drops_left > 0 && knobs().test_drop_kblock) {
+        GemmParams injected = plan.p;   // host-requested failure injection (tests): this launch leaves out one K block's copies
+        injected.test_drop_kblock = knobs().test_drop_kblock;
+        --h->test_drops_left;
+        e = gb::launch_gemm_sm100(injected, plan.tmap_a, plan.tmap_b, plan.tmap_c, h->sm_count, stream);
+      } else {
+        e = gb::launch_gemm_sm100(plan.p, plan.tmap_a, plan.tmap_b, plan.tmap_c, h->sm_count, stream);
+      }
+      break;
+  }
+  if (e == cudaSuccess && plan.reduce) e = gb::launch_splitk_reduce(plan.p, stream);
+  return e == cudaSuccess ? GB_OK : cuda_fail(h, e);
+}
+
+int run_plan(gb_handle* h, cudaStream_t stream, Plan& plan, void* workspace, size_t workspace_bytes) {
+  const int rc = prepare_plan(h, plan, workspace, workspace_bytes);
+  return rc == GB_OK ? launch_plan(h, stream, plan) : rc;
+}
+
+// ---- plan cache -------------------------------------------------------------------------------------
+// Planning a call costs the host ~15 us (the cost model and up to three cuTensorMapEncodeTiled calls), more than
+// most ResNet layers take on the device, and a training step or an executor pass issues the same calls again and
+// again.  A handle therefore keeps the prepared plans of its last calls, keyed by everything that went into them
+// (descriptor, operand and result addresses, epilogue, workspace): a repeated call is a key compare and a launch.
+// Tensor maps hold addresses and shapes only, so a cached plan stays valid whatever the buffers contain.
+PlanKey make_key(uint32_t kind, const void* desc, size_t desc_bytes, const void* a, const void* b, const void* c, const gb_epilogue* ep,
+                 const void* workspace, size_t workspace_bytes) {
+  PlanKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.kind = kind;
+  std::memcpy(key.desc, desc, std::min(desc_bytes, sizeof(key.desc)));
+  key.ptr[0] = (uint64_t)(uintptr_t)a; key.ptr[1] = (uint64_t)(uintptr_t)b; key.ptr[2] = (uint64_t)(uintptr_t)c;
+  key.ptr[3] = (uint64_t)(uintptr_t)workspace; key.ptr[4] = (uint64_t)workspace_bytes;
+  if (ep) {
+    key.ptr[5] = (uint64_t)(uintptr_t)ep->bias; key.ptr[6] = (uint64_t)(uintptr_t)ep->residual;
+    key.ptr[7] = ((uint64_t)(uint32_t)ep->activation << 32) | (uint32_t)ep->flags;
+  }
+  uint64_t hash = 1469598103934665603ull;
+  const unsigned char* bytes = (const unsigned char*)&key;
+  for (size_t i = 0; i < offsetof(PlanKey, hash); ++i) hash = (hash ^ bytes[i]) * 1099511628211ull;
+  key.hash = hash;
+  return key;
+}
+
+Plan* cache_find(gb_handle* h, const PlanKey& key) {
+  if (knobs().no_plan_cache) return nullptr;
+  for (CachedPlan& e : h->cache)
+    if (e.key.hash == key.hash && std::memcmp(&e.key, &key, sizeof(key)) == 0) {
+      e.stamp = ++h->cache_clock;
+      ++h->cache_hits;
+      return &e.plan;
+    }
+  return nullptr;
+}
+
+void cache_store(gb_handle* h, const PlanKey& key, const Plan& plan) {
+  if (knobs().no_plan_cache) return;
+  constexpr size_t kMaxPlans = 256;
+  if (h->cache.size() < kMaxPlans) {
+    h->cache.push_back(CachedPlan{key, plan, ++h->cache_clock});
+    return;
+  }
+  CachedPlan* oldest = &h->cache[0];
+  for (CachedPlan& e : h->cache)
+    if (e.stamp < oldest->stamp) oldest = &e;
+  *oldest = CachedPlan{key, plan, ++h->cache_clock};
 }
 
 // ---- convolution planning ---------------------------------------------------------------------------
@@ -956,6 +1055,8 @@ int gb_last_status(gb_handle* h, void* stream, uint32_t* device_status) {
   return word == 0 ? GB_OK : GB_ERR_TIMEOUT;
 }
 
+uint64_t gb_plan_cache_hits(const gb_handle* h) { return h ? h->cache_hits : 0; }
+
 int gb_last_plan(const gb_handle* h, gb_plan_info* out) {
   if (!h || !out) return GB_ERR_INVALID;
   *out = h->last_plan;
@@ -966,9 +1067,16 @@ int gb_gemm_workspace(const gb_handle* h, const gb_gemm_desc* desc, size_t* byte
   if (!h || !bytes) return GB_ERR_INVALID;
   int rc = validate_gemm(desc);
   if (rc != GB_OK) return rc;
+  gb_handle* hm = const_cast<gb_handle*>(h);   // the cache is bookkeeping, not state a caller can observe
+  const PlanKey key = make_key(0x10, desc, sizeof(*desc), nullptr, nullptr, nullptr, nullptr, nullptr, 0);
+  if (const Plan* cached = cache_find(hm, key)) {
+    *bytes = cached->workspace;
+    return GB_OK;
+  }
   Plan plan;
   rc = plan_gemm(h, desc, nullptr, nullptr, nullptr, nullptr, plan);
   if (rc != GB_OK) return rc;
+  cache_store(hm, key, plan);
   *bytes = plan.workspace;
   return GB_OK;
 }
@@ -979,10 +1087,14 @@ int gb_gemm(gb_handle* h, void* stream, const gb_gemm_desc* desc, const void* a,
   int rc = validate_gemm(desc);
   if (rc != GB_OK) return rc;
   if (desc->m != 0 && desc->n != 0 && (!c || (desc->k != 0 && (!a || !b)))) return GB_ERR_INVALID;
+  const PlanKey key = make_key(0, desc, sizeof(*desc), a, b, c, epilogue, workspace, workspace_bytes);
+  if (const Plan* cached = cache_find(h, key)) return launch_plan(h, (cudaStream_t)stream, *cached);
   Plan plan;
   rc = plan_gemm(h, desc, a, b, c, epilogue, plan);
+  if (rc == GB_OK) rc = prepare_plan(h, plan, workspace, workspace_bytes);
   if (rc != GB_OK) return rc;
-  return run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+  cache_store(h, key, plan);
+  return launch_plan(h, (cudaStream_t)stream, plan);
 }
 
 int gb_conv_workspace(const gb_handle* h, int pass, const gb_conv_desc* desc, size_t* bytes) {
@@ -998,8 +1110,15 @@ int gb_conv_workspace(const gb_handle* h, int pass, const gb_conv_desc* desc, si
     desc = &shadow;
     head = filter_shadow_bytes(desc);
   }
+  gb_handle* hm = const_cast<gb_handle*>(h);
+  const PlanKey key = make_key(0x11 + (uint32_t)pass, desc, sizeof(*desc), nullptr, nullptr, nullptr, nullptr, nullptr, 0);
+  if (const Plan* cached = cache_find(hm, key)) {
+    *bytes = head + cached->workspace;
+    return GB_OK;
+  }
   rc = plan_conv(h, pass, desc, nullptr, nullptr, nullptr, nullptr, plan);
   if (rc != GB_OK) return rc;
+  cache_store(hm, key, plan);
   *bytes = head + plan.workspace;
   return GB_OK;
 }
@@ -1012,10 +1131,17 @@ int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   gb_conv_desc shadow;
   rc = make_filter_shadow(h, (cudaStream_t)stream, desc, shadow, w, workspace, workspace_bytes);
   if (rc != GB_OK) return rc;
+  const PlanKey key = make_key(1, desc, sizeof(*desc), x, w, y, epilogue, workspace, workspace_bytes);
+  const Plan* cached = cache_find(h, key);
   Plan plan;
-  rc = plan_conv(h, 0, desc, x, w, y, epilogue, plan);
-  if (rc != GB_OK) return rc;
-  rc = run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+  if (!cached) {
+    rc = plan_conv(h, 0, desc, x, w, y, epilogue, plan);
+    if (rc == GB_OK) rc = prepare_plan(h, plan, workspace, workspace_bytes);
+    if (rc != GB_OK) return rc;
+    cache_store(h, key, plan);
+    cached = &plan;
+  }
+  rc = launch_plan(h, (cudaStream_t)stream, *cached);
   if (desc == &shadow) h->last_plan.kernel_launches += 1;   // the cast of the filters
   return rc;
 }
@@ -1037,10 +1163,17 @@ int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
       return rc;
     }
   }
+  const PlanKey key = make_key(2, desc, sizeof(*desc), dy, w, dx, nullptr, workspace, workspace_bytes);
+  const Plan* cached = cache_find(h, key);
   Plan plan;
-  rc = plan_conv(h, 1, desc, dy, w, dx, nullptr, plan);
-  if (rc != GB_OK) return rc;
-  rc = run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+  if (!cached) {
+    rc = plan_conv(h, 1, desc, dy, w, dx, nullptr, plan);
+    if (rc == GB_OK) rc = prepare_plan(h, plan, workspace, workspace_bytes);
+    if (rc != GB_OK) return rc;
+    cache_store(h, key, plan);
+    cached = &plan;
+  }
+  rc = launch_plan(h, (cudaStream_t)stream, *cached);
   h->last_plan.kernel_launches += extra;
   return rc;
 }
@@ -1051,10 +1184,14 @@ int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
   if (desc->dtype_w != GB_F32 || desc->w_layout != 0) return GB_ERR_UNSUPPORTED;   // weight gradients accumulate in f32 (gpu.zig:983)
+  const PlanKey key = make_key(3, desc, sizeof(*desc), dy, x, dw, nullptr, workspace, workspace_bytes);
+  if (const Plan* cached = cache_find(h, key)) return launch_plan(h, (cudaStream_t)stream, *cached);
   Plan plan;
   rc = plan_conv(h, 2, desc, dy, x, dw, nullptr, plan);
+  if (rc == GB_OK) rc = prepare_plan(h, plan, workspace, workspace_bytes);
   if (rc != GB_OK) return rc;
-  return run_plan(h, (cudaStream_t)stream, plan, workspace, workspace_bytes);
+  cache_store(h, key, plan);
+  return launch_plan(h, (cudaStream_t)stream, plan);
 }
 
 }  // extern "C"
@@ -1122,7 +1259,7 @@ extern "C" int gb_gemm_static_scratch(void* stream, const gb_gemm_desc* desc, co
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return GB_ERR_NO_DEVICE;
   void* scratch = nullptr;
-  gb_handle local;            // lives on the host stack; its status word is the one inside the library image
+  gb_handle local;            // lives on the host stack (so nothing is cached); its status word is the one inside the library image
   local.device = device;
   rc = static_setup(device, &scratch, &local.status, &local.sm_count);
   if (rc != GB_OK) return rc;

@@ -87,6 +87,39 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else C.c_void_p(t.data_ptr())
 
 
+class PreparedWeights:
+    """A bf16 (or f32) copy of one f32 master weight matrix, made once and refreshed after the optimizer step
+    (`gb_prepare_weights` / `gb_refresh_weights`): the reference converts the master on every use (`packMatrix`,
+    src/autograd/autograd.zig:955, 1226, 1345).  `tensor` is the copy -- `(rows, cols)` for the plain kind,
+    `(cols, rows)` for the rows kind -- to pass as `w` / `b` to the contraction calls."""
+
+    def __init__(self, lib, stream, master: torch.Tensor, kind: int, dtype: torch.dtype):
+        assert master.dtype == torch.float32 and master.dim() == 2 and master.is_contiguous()
+        rows, cols = master.shape
+        self.lib, self.master, self.kind = lib, master, kind
+        self.tensor = torch.empty((cols, rows) if kind == abi.WEIGHTS_ROWS else (rows, cols), dtype=dtype, device=master.device)
+        handle = C.c_void_p()
+        abi.check(lib.gb_prepare_weights(stream, C.c_void_p(master.data_ptr()), rows, cols, kind, _dtype_code(self.tensor),
+                                         C.c_void_p(self.tensor.data_ptr()), self.tensor.numel() * self.tensor.element_size(), C.byref(handle)),
+                  "gb_prepare_weights")
+        self.handle = handle
+        assert lib.gb_weights_data(handle) == self.tensor.data_ptr()
+
+    def refresh(self, stream):
+        abi.check(self.lib.gb_refresh_weights(self.handle, stream), "gb_refresh_weights")
+
+    def close(self):
+        if self.handle:
+            self.lib.gb_weights_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class Gpu:
     """One per device and host thread, like the reference's `Gpu` (src/gpu/gpu.zig:247-477).
 
@@ -110,6 +143,7 @@ class Gpu:
         self.handle = handle
         self.multiprocessors = int(self.lib.gb_sm_count(handle))
         self._scratch: Optional[torch.Tensor] = None
+        self._needs = {}    # descriptor bytes -> workspace bytes (the query is a pure function of the descriptor)
         self.launches = 0   # calls into compute entry points (each is one or two kernel launches)
 
     def close(self):
@@ -134,6 +168,13 @@ class Gpu:
 
     def _stream(self):
         return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def prepareWeights(self, master: torch.Tensor, rows_layout: bool = False, dtype: torch.dtype = torch.bfloat16) -> PreparedWeights:
+        """The prepared copy of an f32 master weight matrix; call `.refresh(gpu._stream())` after the optimizer step."""
+        return PreparedWeights(self.lib, self._stream(), master, abi.WEIGHTS_ROWS if rows_layout else abi.WEIGHTS_PLAIN, dtype)
+
+    def plan_cache_hits(self) -> int:
+        return int(self.lib.gb_plan_cache_hits(self.handle))
 
     def check_status(self) -> int:
         """Synchronises and raises GB_ERR_TIMEOUT if a bounded device wait gave up."""
@@ -191,11 +232,15 @@ class Gpu:
         d.dtype_a, d.dtype_b, d.dtype_c = _dtype_code(a), _dtype_code(b), _dtype_code(out)
         d.math = self._gemm_math(a, b, out, shape, math)
         d.deterministic = self.deterministic
-        need = C.c_size_t(0)
-        abi.check(self.lib.gb_gemm_workspace(self.handle, C.byref(d), C.byref(need)), "gb_gemm_workspace")
-        ws = self.scratch(need.value)
+        key = bytes(d)
+        need = self._needs.get(key)
+        if need is None:
+            size = C.c_size_t(0)
+            abi.check(self.lib.gb_gemm_workspace(self.handle, C.byref(d), C.byref(size)), "gb_gemm_workspace")
+            need = self._needs[key] = size.value
+        ws = self.scratch(need)
         rc = self.lib.gb_gemm(self.handle, self._stream(), C.byref(d), _ptr(a), _ptr(b), _ptr(out), self._epilogue(epilogue),
-                              _ptr(ws), need.value)
+                              _ptr(ws), need)
         abi.check(rc, "gb_gemm")
         self.launches += self._count()
 
@@ -214,9 +259,13 @@ class Gpu:
         return d
 
     def _conv_ws(self, which: int, d: abi.ConvDesc):
-        need = C.c_size_t(0)
-        abi.check(self.lib.gb_conv_workspace(self.handle, which, C.byref(d), C.byref(need)), "gb_conv_workspace")
-        return self.scratch(need.value), need.value
+        key = (which, bytes(d))
+        need = self._needs.get(key)
+        if need is None:
+            size = C.c_size_t(0)
+            abi.check(self.lib.gb_conv_workspace(self.handle, which, C.byref(d), C.byref(size)), "gb_conv_workspace")
+            need = self._needs[key] = size.value
+        return self.scratch(need), need
 
     def convForward(self, x, w, out, geo: ConvGeometry, accumulate: bool = False, epilogue: Optional[Epilogue] = None,
                     math: Optional[int] = None, w_rows: bool = False):

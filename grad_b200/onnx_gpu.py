@@ -78,6 +78,7 @@ class Executor:
                 self.uses[name] = self.uses.get(name, 0) + 1
         for name in model.outputs:
             self.uses[name] = self.uses.get(name, 0) + 1
+        self.peak_live = 0    # most values alive at once during the last walk
         self._graph = None
         self._static_in: Dict[str, torch.Tensor] = {}
         self._static_out: Dict[str, torch.Tensor] = {}
@@ -239,6 +240,47 @@ class Executor:
         self.stats.device_nodes += consumed
         return consumed
 
+    def _gemm(self, values, at: int) -> int:
+        """`Executor.gemm` (gpu.zig:500-521): Y = op(A) * op(B) + C for alpha = beta = 1 and at most one transposed
+        operand (anything else is a host node in the reference and outside this path).  C broadcasts over the rows
+        (a bias vector: folded into the epilogue) or has the result's shape (added as the epilogue's residual); a
+        following Relu is folded in as well."""
+        node = self.model.nodes[at]
+        ta, tb = int(node.attrs.get("transA", 0)) != 0, int(node.attrs.get("transB", 0)) != 0
+        if (ta and tb) or float(node.attrs.get("alpha", 1.0)) != 1.0 or float(node.attrs.get("beta", 1.0)) != 1.0:
+            raise NotImplementedError("Gemm with alpha/beta != 1 or both operands transposed runs on the host in the reference (gpu.zig:503)")
+        x = self._value(values, node.inputs[0]).contiguous()
+        w = self._matrix(node.inputs[1]) if node.inputs[1] in self.model.initializers else self._value(values, node.inputs[1]).contiguous()
+        if x.dim() != 2 or w.dim() != 2:
+            raise NotImplementedError("Gemm operands must be matrices (gpu.zig:506)")
+        m, k = (x.shape[1], x.shape[0]) if ta else (x.shape[0], x.shape[1])
+        n = w.shape[0] if tb else w.shape[1]
+        if (w.shape[1] if tb else w.shape[0]) != k:
+            raise ValueError("Gemm: inner dimensions differ (error.ShapeMismatch)")
+        bias, residual = None, None
+        if len(node.inputs) > 2 and node.inputs[2]:
+            c = self._constant(node.inputs[2]) if node.inputs[2] in self.model.initializers else self._value(values, node.inputs[2])
+            if tuple(c.shape) in ((n,), (1, n)):
+                bias = c.reshape(n).float().contiguous()
+            elif tuple(c.shape) == (m, n):
+                residual = c.to(torch.float32 if node.outputs[0] in self.model.outputs else self.act_dtype).contiguous()
+            else:
+                raise NotImplementedError("Gemm: C must broadcast over the rows or have the result's shape (gpu.zig:512-516)")
+        result, relu, consumed = node.outputs[0], False, 1
+        nxt = self.model.nodes[at + 1] if at + 1 < len(self.model.nodes) else None
+        if self.fuse and nxt is not None and nxt.op == "Relu" and nxt.inputs[0] == result and self._single_use(result):
+            relu, result, consumed = True, nxt.outputs[0], 2
+        out_dtype = torch.float32 if result in self.model.outputs else self.act_dtype
+        if residual is not None and residual.dtype != out_dtype:
+            residual = residual.to(out_dtype)
+        y = torch.empty((m, n), dtype=out_dtype, device=self.gpu.device)
+        before = self.gpu.launches
+        self.gpu.matmul(x, w, y, MatmulShape(m, n, k), MatmulOpts(ta, tb), epilogue=Epilogue(bias, residual, relu), math=self.math)
+        self.stats.launches += self.gpu.launches - before
+        values[result] = y
+        self.stats.device_nodes += consumed
+        return consumed
+
     # ---- the walk -------------------------------------------------------------------------------------
     def _step(self, values, at: int) -> int:
         nodes = self.model.nodes
@@ -253,6 +295,8 @@ class Executor:
             return 3
         if node.op == "MatMul":
             return self._matmul(values, at)
+        if node.op == "Gemm":
+            return self._gemm(values, at)
         if node.op == "Relu":
             values[node.outputs[0]] = self._elementwise(1, self._value(values, node.inputs[0]).contiguous(), None)
         elif node.op == "Add":
@@ -285,16 +329,35 @@ class Executor:
         return 1
 
     def _walk(self, values) -> Dict[str, torch.Tensor]:
+        """Runs the nodes in order.  A value is dropped as soon as its last consumer has run (the reference keeps every
+        activation until the next `run`, its TODO.md:15), so peak memory follows the live set of the graph, not its
+        length: at batch 4096 the ResNet holds three or four activation maps instead of forty."""
+        remaining = dict(self.uses)
+        self.peak_live = 0
         at = 0
         while at < len(self.model.nodes):
-            at += self._step(values, at)
+            done = self._step(values, at)
+            for node in self.model.nodes[at:at + done]:
+                for name in node.inputs:
+                    if name in remaining:
+                        remaining[name] -= 1
+                        if remaining[name] == 0 and name in values and name not in self.model.outputs:
+                            del values[name]
+            self.peak_live = max(self.peak_live, len(values))
+            at += done
         return {name: values[name] for name in self.model.outputs}
 
     def run_device(self, feeds: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
         """Runs the graph on device-resident feeds (f32 or the activation dtype) and returns device outputs."""
         values = {}
         for name, t in feeds.items():
-            values[name] = t if t.dtype == self.act_dtype else t.to(self.act_dtype)
+            if t.dtype != self.act_dtype:
+                src = t.contiguous()
+                t = torch.empty(src.shape, dtype=self.act_dtype, device=src.device)
+                abi.check(self.gpu.lib.gb_cast(self._stream(), self._code(src), self._code(t), C.c_void_p(src.data_ptr()), C.c_void_p(t.data_ptr()),
+                                               src.numel()), "gb_cast")
+                self.stats.launches += 1
+            values[name] = t
         for name in self.model.inputs:
             if name not in values:
                 raise KeyError(f"missing input {name} (error.MissingInput)")

@@ -133,6 +133,11 @@ typedef struct {
   uint32_t tile_m, tile_n, stages, splits, k_blocks, work_items, kernel_launches;
 } gb_plan_info;
 int gb_last_plan(const gb_handle* h, gb_plan_info* out);
+/* A handle keeps the prepared plans (tile choice, tensor maps) of its recent calls, keyed by descriptor, addresses,
+ * epilogue and workspace, so that a repeated call -- every step of a training loop, every pass of the executor --
+ * costs the host a key compare and a launch instead of ~15 us of planning.  Returns how many calls were served from
+ * that cache so far (GB_NO_PLAN_CACHE in the environment turns it off). */
+uint64_t gb_plan_cache_hits(const gb_handle* h);
 
 /* ---- matmul family ---------------------------------------------------------------------------- */
 /* Replaces `Gpu.matmul` (src/gpu/gpu.zig:642-679), `Gpu.matmulTensor` / `packMatrix` / `matmulPacked`
@@ -175,6 +180,28 @@ int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
  * (:775-787, :828-866).  Partials of the split over positions are combined in order. */
 int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* x, void* dw,
                   void* workspace, size_t workspace_bytes);
+
+/* ---- prepared weights -------------------------------------------------------------------------- */
+/* grad keeps f32 master weights and converts them on EVERY use: `packMatrix` before each forward product and
+ * `packRotatedWeights` before each input gradient (src/autograd/autograd.zig:955, 967, 1226, 1272, 1345, 1350, 1401,
+ * 1418; src/gpu/gpu.zig:711-722).  With a prepared copy the conversion happens once per optimizer step instead: the
+ * caller makes the copy after `adam.step` (src/nn/optim.zig:122-150) with gb_refresh_weights and passes
+ * gb_weights_data() as `w` (dtype_w = the copy's dtype) to gb_gemm / gb_conv_fprop / gb_conv_dgrad, which then fetch
+ * every operand by TMA and launch no cast.  No rotated copy exists or is needed: gb_conv_dgrad reads the forward
+ * layout.  The copy lives in caller-owned device memory (`storage`, gb_weights_bytes() bytes, 16-byte aligned): the
+ * library allocates nothing on the device; the gb_weights object is a few host words.
+ *   GB_WEIGHTS_PLAIN  the master's (rows, cols) layout -- (k*k*c_in, c_out) filters, (n_in, n_out) Linear weights
+ *   GB_WEIGHTS_ROWS   transposed to (cols, rows): filters as (c_out, k*k*c_in) for gb_conv_desc.w_layout = 1, or a
+ *                     Linear weight as the K-major B operand of `trans_b` */
+typedef struct gb_weights gb_weights;
+typedef enum { GB_WEIGHTS_PLAIN = 0, GB_WEIGHTS_ROWS = 1 } gb_weights_kind;
+size_t gb_weights_bytes(uint32_t rows, uint32_t cols, int dtype);
+int gb_prepare_weights(void* stream, const float* master_f32, uint32_t rows, uint32_t cols, int kind, int dtype, void* storage,
+                       size_t storage_bytes, gb_weights** out);
+/* Remakes the copy from the master (one launch on `stream`, capture-safe): call it after the optimizer step. */
+int gb_refresh_weights(const gb_weights* weights, void* stream);
+const void* gb_weights_data(const gb_weights* weights);
+void gb_weights_destroy(gb_weights* weights);
 
 /* ---- executor glue (ONNX inference graphs) ------------------------------------------------------ */
 /* The bandwidth-bound node kinds `grad.onnx_gpu.Executor` runs between contractions, so a ResNet graph

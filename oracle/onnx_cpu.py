@@ -66,6 +66,15 @@ def run(model, feeds, threads=None):
             values[node.outputs[0]] = x.reshape(shape)
         elif node.op == "MatMul":
             values[node.outputs[0]] = orc.onnx_matmul(get(node.inputs[0]), get(node.inputs[1]), threads)
+        elif node.op == "Gemm":    # runtime.zig:648-664
+            c = get(node.inputs[2]) if len(node.inputs) > 2 and node.inputs[2] else None
+            row_bias = c is not None and c.size == np.asarray(c).shape[-1]       # broadcast over the rows
+            beta = float(node.attrs.get("beta", 1.0))
+            out = orc.onnx_gemm(get(node.inputs[0]), get(node.inputs[1]), np.asarray(c).reshape(-1) if row_bias else None,
+                                bool(node.attrs.get("transA", 0)), bool(node.attrs.get("transB", 0)), float(node.attrs.get("alpha", 1.0)), beta, threads)
+            if c is not None and not row_bias:                                    # C of the result's shape
+                out = (out + np.float32(beta) * np.asarray(c, np.float32)).astype(np.float32)
+            values[node.outputs[0]] = out
         else:
             raise NotImplementedError(node.op)
         at += 1

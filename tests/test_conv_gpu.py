@@ -353,3 +353,63 @@ def test_strict_f32_convolution_with_more_than_65535_row_tiles(gpu):
         d = _dims((1, hw, hw, c, 3, co, 1, 1, 1))
         want = orc.conv_forward(to_host(x[img:img + 1]), to_host(w), d)
         assert rel_fro(to_host(y[img:img + 1]), want) <= TOL_F32, img
+
+
+def test_prepared_weights_replace_the_per_call_filter_cast(gpu):
+    """`gb_prepare_weights` / `gb_refresh_weights`: a bf16 copy of the f32 master filters made once per optimizer step
+    instead of on every use (the reference's per-call `packMatrix`, src/autograd/autograd.zig:955, 1226, 1345).  The
+    forward pass and the input gradient on the prepared copy launch no cast and give the bits of the per-call path;
+    the rows layout feeds `w_layout = 1`; after the master changes, `refresh` brings the copy up to date."""
+    import torch
+    from oracle import binding as orc
+
+    case = (4, 16, 16, 64, 3, 128, 1, 1, 1)
+    d, x, w, dy = _inputs(case, 1100)
+    geo = _geo(case)
+    tx, tdy, master = to_dev(x, True), to_dev(dy, True), to_dev(w)
+    y_ref = torch.empty((d.n, d.out_h, d.out_w, d.c_out), dtype=torch.bfloat16, device="cuda")
+    gpu.convForward(tx, master, y_ref, geo)                       # f32 masters: cast launch + product
+    assert gpu.last_plan()["kernel_launches"] == 2
+    gx_ref = torch.zeros((d.n, d.h, d.w, d.c), dtype=torch.bfloat16, device="cuda")
+    gpu.convInputGrad(tdy, master, gx_ref, geo, accumulate=False)
+    plain, rows = gpu.prepareWeights(master), gpu.prepareWeights(master, rows_layout=True)
+    assert plain.tensor.shape == (d.taps, d.c_out) and rows.tensor.shape == (d.c_out, d.taps)
+    y, y_rows = torch.empty_like(y_ref), torch.empty_like(y_ref)
+    gpu.convForward(tx, plain.tensor, y, geo)
+    assert gpu.last_plan()["kernel_launches"] == 1
+    gpu.convForward(tx, rows.tensor, y_rows, geo, w_rows=True)
+    gx = torch.zeros_like(gx_ref)
+    gpu.convInputGrad(tdy, plain.tensor, gx, geo, accumulate=False)
+    assert gpu.last_plan()["kernel_launches"] == 1
+    torch.cuda.synchronize()
+    assert torch.equal(y, y_ref) and torch.equal(gx, gx_ref)
+    want = orc.conv_forward(x, w, d, orc.host_threads())
+    assert rel_fro(to_host(y_rows), want) <= TOL_BF16
+    master.mul_(-2.0)                                              # the optimizer step
+    plain.refresh(gpu._stream())
+    gpu.convForward(tx, plain.tensor, y, geo)
+    torch.cuda.synchronize()
+    assert rel_fro(to_host(y), -2.0 * want) <= TOL_BF16
+    plain.close(); rows.close()
+
+
+def test_repeated_calls_are_served_from_the_plan_cache(gpu):
+    """A call with the same descriptor, addresses, epilogue and workspace reuses its prepared plan (tile choice and
+    tensor maps) and must give the same bits; a changed address plans anew."""
+    import torch
+
+    case = (4, 16, 16, 64, 3, 64, 1, 1, 1)
+    d, x, w, dy = _inputs(case, 1200)
+    geo = _geo(case)
+    tx, tw = to_dev(x, True), to_dev(w, True)
+    y1 = torch.empty((d.n, d.out_h, d.out_w, d.c_out), dtype=torch.bfloat16, device="cuda")
+    gpu.convForward(tx, tw, y1, geo)
+    hits = gpu.plan_cache_hits()
+    first = y1.clone()
+    for _ in range(3):
+        gpu.convForward(tx, tw, y1, geo)
+    assert gpu.plan_cache_hits() >= hits + 3
+    y2 = torch.empty_like(y1)
+    gpu.convForward(tx, tw, y2, geo)                               # another result buffer: a new plan, same values
+    torch.cuda.synchronize()
+    assert torch.equal(y1, first) and torch.equal(y2, first)

@@ -110,6 +110,45 @@ def test_full_width_model_runs_at_batch_100(gpu):
     assert rel_fro(b, a) <= TOL_BF16
 
 
+@pytest.mark.parametrize("mode,tol", [("f32", 1e-5), ("tf32", TOL_TF32), ("bf16", TOL_BF16)])
+def test_gemm_nodes_match_cpu_walk(gpu, mode, tol):
+    """ONNX `Gemm` (src/onnx/gpu.zig:500-521, CPU: src/onnx/runtime.zig:648-664): transB with a bias vector and a
+    following Relu (one launch), transA with a C of the result's shape, and a plain product; against the CPU walk."""
+    from grad_b200.onnx_gpu import Executor, Model, Node
+    from oracle import onnx_cpu
+
+    rng = np.random.default_rng(77)
+    init = {"w1": rng.standard_normal((160, 96)).astype(np.float32) * 0.1, "b1": rng.standard_normal(160).astype(np.float32),
+            "w2": rng.standard_normal((160, 64)).astype(np.float32) * 0.1, "c2": rng.standard_normal((48, 64)).astype(np.float32),
+            "w3": rng.standard_normal((48, 40)).astype(np.float32) * 0.1}
+    nodes = [Node("Gemm", ["input", "w1", "b1"], ["h1"], {"transB": 1}), Node("Relu", ["h1"], ["a1"]),
+             Node("Gemm", ["a1", "w2", "c2"], ["h2"], {}),                       # (48,160) x (160,64) + C (48,64)
+             Node("Gemm", ["h2", "w3"], ["out"], {"transA": 1})]                 # h2 stored (k=48, m=64): (64,48) x (48,40)
+    model = Model(nodes, init, ["input"], ["out"])
+    x = seeded(78, 48, 96)
+    want = onnx_cpu.run(model, {"input": x})["out"]
+    ex = Executor(model, gpu, mode=mode)
+    got = ex.run({"input": x})["out"]
+    assert got.shape == want.shape == (64, 40)
+    assert rel_fro(got, want) <= tol, rel_fro(got, want)
+    assert ex.stats.host_nodes == 0 and ex.stats.device_nodes == 4
+    with pytest.raises(NotImplementedError):
+        Executor(Model([Node("Gemm", ["input", "w1"], ["out"], {"transB": 1, "alpha": 0.5})], init, ["input"], ["out"]), gpu, mode).run({"input": x})
+
+
+def test_activations_are_released_after_their_last_use(gpu, small_case):
+    """The walk drops a value once its last consumer has run: far fewer values are alive at once than the graph
+    produces, and the logits do not change."""
+    from grad_b200.onnx_gpu import Executor
+
+    model, x, want = small_case
+    ex = Executor(model, gpu, "tf32")
+    got = ex.run({"input": x})["logits"]
+    assert rel_fro(got, want) <= TOL_TF32
+    produced = sum(len(n.outputs) for n in model.nodes)
+    assert 0 < ex.peak_live <= 4 and produced > 40, (ex.peak_live, produced)
+
+
 @pytest.mark.parametrize("is_max", [0, 1])
 @pytest.mark.parametrize("shape", [(3, 8, 8, 64, 2, 2, 0), (2, 9, 7, 24, 3, 2, 1), (2, 8, 8, 12, 2, 2, 0), (1, 4, 4, 256, 4, 4, 0)])
 def test_pool2d_vector_and_scalar_kernels_agree_with_the_window_definition(gpu, is_max, shape):
