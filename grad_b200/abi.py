@@ -30,8 +30,12 @@ class GbError(RuntimeError):
         super().__init__(f"{where}: {STATUS_NAMES.get(status, status)} ({error_string(status)})")
 
 
+class BnStats(C.Structure):
+    _fields_ = [("shift", C.c_void_p), ("sums", C.c_void_p), ("ordered", C.c_uint32), ("reserved", C.c_uint32)]
+
+
 class Epilogue(C.Structure):
-    _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("activation", C.c_int32), ("flags", C.c_int32)]
+    _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("activation", C.c_int32), ("flags", C.c_int32), ("bn_stats", C.POINTER(BnStats))]
 
 
 class GemmDesc(C.Structure):

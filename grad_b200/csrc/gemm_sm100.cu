@@ -611,8 +611,50 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* tmap_c, uint8
   }
 }
 
-__device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
-                                                   const float* sbias, uint32_t batch, uint32_t split, uint32_t row, uint32_t col0, uint32_t lane) {
+// ---- batch-norm statistics in the epilogue ------------------------------------------------------------------
+// Per-channel sums of (v - shift) and (v - shift)^2 over the values the tile stores, the role of `statsTile`
+// (src/gpu/device.zig:1505-1535).  In the accumulator layout a lane owns a ROW of the chunk, so the 32 column sums of
+// the warp's 32 rows are formed by a transposing butterfly: in the step of distance d a lane keeps the half of its
+// columns that its bit d selects and adds the partner's values for them; after five steps lane l holds column l's sum
+// over the 32 rows (31 shuffles per quantity instead of 160).  The order of the additions is fixed by the layout.
+__device__ __forceinline__ float column_sums(float (&t)[32], uint32_t lane) {
+#pragma unroll
+  for (uint32_t d = 16; d >= 1; d >>= 1) {
+    const bool upper = (lane & d) != 0;
+#pragma unroll
+    for (uint32_t j = 0; j < d; ++j) {
+      const float keep = upper ? t[j + d] : t[j], give = upper ? t[j] : t[j + d];
+      t[j] = keep + __shfl_xor_sync(0xFFFFFFFFu, give, d);
+    }
+  }
+  return t[0];
+}
+
+struct ChunkStats {
+  float sum, squares;
+};
+// `v` = the values as stored (already rounded to the output type), `shift` = this chunk's 32 shift values in shared memory.
+__device__ __forceinline__ ChunkStats chunk_stats(const float* v, const float* shift, bool live, uint32_t lane) {
+  float t[32], q[32];
+#pragma unroll
+  for (uint32_t i = 0; i < 32; i += 4) {
+    const float4 sh = *(const float4*)(shift + i);
+    t[i] = live ? v[i] - sh.x : 0.0f; t[i + 1] = live ? v[i + 1] - sh.y : 0.0f;
+    t[i + 2] = live ? v[i + 2] - sh.z : 0.0f; t[i + 3] = live ? v[i + 3] - sh.w : 0.0f;
+  }
+#pragma unroll
+  for (uint32_t i = 0; i < 32; ++i) q[i] = t[i] * t[i];
+  ChunkStats out;
+  out.sum = column_sums(t, lane);
+  out.squares = column_sums(q, lane);
+  return out;
+}
+
+template <bool kStats>
+__device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
+                                                              const float* sbias, const float* sshift, uint32_t batch, uint32_t split, uint32_t row,
+                                                              uint32_t col0, uint32_t lane) {
+  ChunkStats stats = {0.0f, 0.0f};
   if (p.splits > 1) {
     // A K part's partial tile: the raw f32 accumulators, into the map of the partial buffer {n, m, split * batch}.
     // (Stored straight from the accumulator layout a lane owns a row and a warp-wide store half-fills 32 sectors:
@@ -625,7 +667,7 @@ __device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CU
       for (uint32_t j = 0; j < 4; ++j) q[j] = make_uint4(acc[16 * half + 4 * j], acc[16 * half + 4 * j + 1], acc[16 * half + 4 * j + 2], acc[16 * half + 4 * j + 3]);
       stage_and_store(tmap_c, stage, q, lane, (int32_t)(col0 + 16 * half), y, z);
     }
-    return;
+    return stats;
   }
   const bool live = row < p.m;
   const uint64_t off = (uint64_t)batch * p.stride_c + (uint64_t)row * p.ldc + col0;
@@ -694,8 +736,18 @@ __device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CU
     for (uint32_t j = 0; j < 4; ++j)
       q[j] = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]), pack_bf16x2(v[8 * j + 4], v[8 * j + 5]),
                         pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+    if constexpr (kStats) {   // over the values as stored: the bf16-rounded ones (device.zig:1524)
+      const uint32_t w[16] = {q[0].x, q[0].y, q[0].z, q[0].w, q[1].x, q[1].y, q[1].z, q[1].w, q[2].x, q[2].y, q[2].z, q[2].w, q[3].x, q[3].y, q[3].z, q[3].w};
+#pragma unroll
+      for (uint32_t j = 0; j < 16; ++j) {
+        v[2 * j] = __uint_as_float(w[j] << 16);
+        v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+      }
+      stats = chunk_stats(v, sshift, live, lane);
+    }
     stage_and_store(tmap_c, stage, q, lane, (int32_t)col0, y, (int32_t)batch);
   } else {
+    if constexpr (kStats) stats = chunk_stats(v, sshift, live, lane);
 #pragma unroll
     for (uint32_t half = 0; half < 2; ++half) {   // 16 f32 columns = 64 bytes per row and store
       uint4 q[4];
@@ -706,7 +758,39 @@ __device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CU
       stage_and_store(tmap_c, stage, q, lane, (int32_t)(col0 + 16 * half), y, (int32_t)batch);
     }
   }
+  return stats;
 }
+
+__device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
+                                                   const float* sbias, uint32_t batch, uint32_t split, uint32_t row, uint32_t col0, uint32_t lane) {
+  epilogue_chunk_tma_impl<false>(p, tmap_c, acc, stage, sbias, nullptr, batch, split, row, col0, lane);
+}
+// The chunk epilogue of a statistics plan.  Kept out of line on its own copy of the chunk: inlined, its 64 temporaries
+// raised the register pressure (and the spills) of every plan's epilogue, with or without statistics.
+// `sstat` is the warp's statistics block in shared memory: the 128 shift values of its four column chunks, then per
+// chunk and lane the running (sum, sum of squares) of that lane's column over every row the warp has drained.
+__device__ __noinline__ void epilogue_chunk_tma_stats(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t* vals, uint8_t* stage,
+                                                      const float* sbias, float* sstat, uint32_t slot, uint32_t batch, uint32_t row, uint32_t col0,
+                                                      uint32_t lane) {
+  uint32_t copy[32];
+#pragma unroll
+  for (uint32_t i = 0; i < 32; ++i) copy[i] = vals[i];
+  const ChunkStats c = epilogue_chunk_tma_impl<true>(p, tmap_c, copy, stage, sbias, sstat + 32 * slot, batch, 0, row, col0, lane);
+  float2* cell = (float2*)(sstat + 128) + slot * 32 + lane;   // only this lane ever touches its cell
+  float2 v = *cell;
+  v.x += c.sum;
+  v.y += c.squares;
+  *cell = v;
+}
+__device__ __forceinline__ void epilogue_chunk_tma_stats_call(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
+                                                           const float* sbias, float* sstat, uint32_t slot, uint32_t batch, uint32_t row, uint32_t col0,
+                                                           uint32_t lane) {
+  uint32_t spill[32];
+#pragma unroll
+  for (uint32_t i = 0; i < 32; ++i) spill[i] = acc[i];
+  epilogue_chunk_tma_stats(p, tmap_c, spill, stage, sbias, sstat, slot, batch, row, col0, lane);
+}
+
 
 // The bias values of every chunk this warp will drain from the next accumulator, fetched into the warp's own
 // shared memory before it waits for that accumulator: chunk i's 32 values sit at sbias[32 * i].  (Fetched
@@ -737,7 +821,7 @@ template <class Release>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, uint32_t ncols, uint32_t batch, uint32_t split,
                                               uint32_t row, uint32_t col_base, bool wide, uint32_t lane,
                                               uint32_t first, uint32_t step, const CUtensorMap* tmap_c, uint8_t* store_stage, const float* sbias,
-                                              Release release) {
+                                              float* sstat, Release release) {
   // a fused class product places its rows by its own map and ends at its own row count
   const RowMap& rowmap = p.n_classes ? p.cls[batch].rowmap : p.rowmap;
   const uint32_t m_limit = p.n_classes ? p.cls[batch].m : p.m;
@@ -760,16 +844,20 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
       else release();
       {
         const uint32_t col0 = col_base + tile_col(c);
-        if (col0 + 32 <= p.n && row - lane < p.m) epilogue_chunk_tma(p, tmap_c, acc_a, store_stage, sbias + 32 * i, batch, split, row, col0, lane);
-        else epilogue_chunk_copy(p, acc_a, batch, split, row, col0, p.bias ? sbias[32 * i + lane] : 0.0f);
+        if (col0 + 32 <= p.n && row - lane < p.m) {
+          if (p.stats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_a, store_stage, sbias + 32 * i, sstat, i, batch, row, col0, lane);
+          else epilogue_chunk_tma(p, tmap_c, acc_a, store_stage, sbias + 32 * i, batch, split, row, col0, lane);
+        } else epilogue_chunk_copy(p, acc_a, batch, split, row, col0, p.bias ? sbias[32 * i + lane] : 0.0f);
       }
       if (has_b) {
         tmem_ld_wait();
         if (c + 2 * step < ncols) tmem_ld_32x32(taddr + c + 2 * step, acc_a);
         else release();
         const uint32_t col0 = col_base + tile_col(c + step);
-        if (col0 + 32 <= p.n && row - lane < p.m) epilogue_chunk_tma(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), batch, split, row, col0, lane);
-        else epilogue_chunk_copy(p, acc_b, batch, split, row, col0, p.bias ? sbias[32 * (i + 1) + lane] : 0.0f);
+        if (col0 + 32 <= p.n && row - lane < p.m) {
+          if (p.stats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), sstat, i + 1, batch, row, col0, lane);
+          else epilogue_chunk_tma(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), batch, split, row, col0, lane);
+        } else epilogue_chunk_copy(p, acc_b, batch, split, row, col0, p.bias ? sbias[32 * (i + 1) + lane] : 0.0f);
       }
     }
     return;
@@ -799,6 +887,25 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
       bias_cur = bias_next;
       bias_next = bias_at(c + 2 * step);
       epilogue_chunk(p, acc_b, batch, split, row, col_base + tile_col(c + step), bias_cur, row_off, m_limit, p.splits > 1);
+    }
+  }
+}
+
+// Hands a warp's statistics over at the end of the kernel: added to sums[col] and sums[n + col] with atomics, or, for
+// an ordered (reproducible) run, written to this warp's slot of the partial buffer that `stats_combine_kernel` adds
+// up in CTA and warp order.
+__device__ __noinline__ void flush_stats(const GemmParams& p, const float* sstat, uint32_t epi_warp, uint32_t lane, uint32_t first, uint32_t step) {
+  for (uint32_t i = 0; i < 4; ++i) {
+    const uint32_t col = first + i * step + lane;
+    if (first + i * step >= p.bn || col >= p.n) continue;
+    const float2 v = ((const float2*)(sstat + 128))[i * 32 + lane];
+    if (p.stat_partial != nullptr) {
+      float* dst = p.stat_partial + (((uint64_t)blockIdx.x * 8 + epi_warp) * 4 + i) * 64 + lane * 2;
+      dst[0] = v.x;
+      dst[1] = v.y;
+    } else {
+      atomicAdd(p.stat_sums + col, v.x);
+      atomicAdd(p.stat_sums + p.n + col, v.y);
     }
   }
 }
@@ -1005,6 +1112,17 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     float* sbias = (float*)(epi_smem + 8 * kStoreStageBytesPerWarp + (warp - 2) * kStoreBiasBytesPerWarp);
     if (tma_out && warp == 2 && lane == 0) prefetch_tmap(&tmap_c);
     uint32_t bias_tile = 0xFFFFFFFFu;   // the column tile whose bias values sit in shared memory
+    // statistics plans have one column tile, so a warp's shift values are staged once (chunk i's 32 values at sstat[32 * i])
+    // and its running sums sit behind them
+    float* sstat = (float*)(epi_smem + kStoreSmemBytes + (warp - 2) * kStatBytesPerWarp);
+    if (p.stats) {
+      for (uint32_t i = 0; i < 4; ++i) {
+        const uint32_t col = ((warp - 2) >> 2) * 32 + i * 32 * p.epi_groups + lane;
+        sstat[32 * i + lane] = col < p.n ? p.stat_shift[col] : 0.0f;
+        ((float2*)(sstat + 128))[32 * i + lane] = make_float2(0.0f, 0.0f);
+      }
+      __syncwarp();
+    }
     for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       const Work work = decode_work(p, w);
       if (work.empty) continue;
@@ -1019,13 +1137,14 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       const uint32_t row = work.m_tile * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
       epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane,
-                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, [&] {
+                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, sstat, [&] {
                                                  tc_fence_before_sync();
                                                  __syncwarp();
                                                  if (lane == 0) mbar_arrive(&hdr->acc_empty[buf]);
                                                });
       if ((buf ^= 1) == 0) buf_phase ^= 1;
     }
+    if (p.stats && ok) flush_stats(p, sstat, warp - 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
     if (tma_out && lane == 0) bulk_wait_all();   // the staging block must outlive its last store
   } else {
     // ===== gather warps =====
@@ -1219,6 +1338,15 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     float* sbias = (float*)(epi_smem + 8 * kStoreStageBytesPerWarp + (warp - 2) * kStoreBiasBytesPerWarp);
     if (tma_out && warp == 2 && lane == 0) prefetch_tmap(&tmap_c);
     uint32_t bias_tile = 0xFFFFFFFFu;   // the column tile whose bias values sit in shared memory
+    float* sstat = (float*)(epi_smem + kStoreSmemBytes + (warp - 2) * kStatBytesPerWarp);   // see the single-CTA kernel
+    if (p.stats) {
+      for (uint32_t i = 0; i < 4; ++i) {
+        const uint32_t col = ((warp - 2) >> 2) * 32 + i * 32 * p.epi_groups + lane;
+        sstat[32 * i + lane] = col < p.n ? p.stat_shift[col] : 0.0f;
+        ((float2*)(sstat + 128))[32 * i + lane] = make_float2(0.0f, 0.0f);
+      }
+      __syncwarp();
+    }
     for (uint32_t w = pair; ok && w < total_work; w += pairs) {
       const Work work = decode_work(p, w);
       if (work.empty) continue;
@@ -1233,13 +1361,14 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       const uint32_t row = work.m_tile * 2 * kBM + rank * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * (p.bn / halves);
       epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane,
-                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, [&] {
+                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, sstat, [&] {
                                                  tc_fence_before_sync();
                                                  __syncwarp();
                                                  if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->acc_empty[buf]), 0));
                                                });
       if (++buf == bufs) { buf = 0; buf_phase ^= 1; }
     }
+    if (p.stats && ok) flush_stats(p, sstat, warp - 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
     if (tma_out && lane == 0) bulk_wait_all();   // the staging block must outlive its last store
   }
 
@@ -1327,14 +1456,40 @@ __global__ void __launch_bounds__(32 * kReduceGroups) splitk_reduce_grouped_kern
   }
 }
 
+// Ordered combine of the statistics partials (the role of `columnCombine`, src/gpu/device.zig:672-678): one thread per
+// column adds the slots of every CTA and of the four row quarters in a fixed order, then adds the total into sums.
+__global__ void stats_combine_kernel(const float* partial, float* sums, uint32_t ctas, uint32_t n, uint32_t epi_groups) {
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const uint32_t col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= n) return;
+  const uint32_t chunk = col >> 5, lane = col & 31, group = chunk % epi_groups, slot = chunk / epi_groups;
+  float s = 0.0f, q = 0.0f;
+  for (uint32_t cta = 0; cta < ctas; ++cta)
+    for (uint32_t quarter = 0; quarter < 4; ++quarter) {
+      const float* src = partial + (((uint64_t)cta * 8 + group * 4 + quarter) * 4 + slot) * 64 + lane * 2;
+      s += src[0];
+      q += src[1];
+    }
+  sums[col] += s;
+  sums[n + col] += q;
+}
+
 }  // namespace
+
+uint32_t gemm_grid_ctas(const GemmParams& p, int sm_count);
+
+cudaError_t launch_stats_combine(const GemmParams& p, uint32_t ctas, cudaStream_t stream) {
+  return launch_overlapped(stats_combine_kernel, dim3((p.n + 127) / 128), dim3(128), 0, stream, (const float*)p.stat_partial, p.stat_sums, ctas, p.n,
+                           p.epi_groups);
+}
 
 size_t gemm_smem_bytes(const GemmParams& p) {
   const size_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
   return 1024 /* alignment slack */ + kHeaderBytes +
          (size_t)p.stages * ((p.a_stage_bytes ? p.a_stage_bytes : kATileBytes * (p.k_mul ? p.k_mul : 1u)) +
                              (p.col_taps ? p.col_taps : 1u) * b_lines * kLineBytes * (p.k_mul ? p.k_mul : 1u)) +
-         (p.tma_store ? kStoreSmemBytes : 0);
+         (p.tma_store ? kStoreSmemBytes : 0) + (p.stats ? 8 * kStatBytesPerWarp : 0);
 }
 
 // Co-resident 2-CTA clusters of the pair kernel for a given dynamic shared-memory size (cached per size).
@@ -1377,6 +1532,13 @@ cudaError_t gemm_sm100_configure() {
   cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e != cudaSuccess) return e;
   return cudaFuncSetAttribute(gemm_sm100_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+}
+
+// CTAs the launch below uses (what the statistics partial buffer is sized by).
+uint32_t gemm_grid_ctas(const GemmParams& p, int sm_count) {
+  const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
+  if (p.cta_pair) return 2 * std::min<uint32_t>(total_work, max_resident_pairs(gemm_smem_bytes(p), sm_count));
+  return total_work < (uint32_t)sm_count ? total_work : (uint32_t)sm_count;
 }
 
 cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c, int sm_count,

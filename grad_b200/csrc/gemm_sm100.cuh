@@ -123,6 +123,11 @@ struct GemmParams {
   uint32_t epi_groups;      // epilogue warps = 4 * epi_groups; group g drains column chunks g, g + groups, ...
   uint32_t round_tf32;      // round the stored f32 result to TF32 (nearest, ties away)
   uint32_t tma_store;       // full 32-column chunks leave through shared memory and a TMA store (map of C passed to the kernel)
+  // batch-norm statistics of the stored result, summed in the epilogue (stats != 0): see `chunk_stats`
+  uint32_t stats;
+  const float* stat_shift;  // f32[n]: the values are centred by it before they are summed
+  float* stat_sums;         // f32[2n]: += sum(v - shift), += sum((v - shift)^2)
+  float* stat_partial;      // ordered runs: [cta][8 warps][4 chunks][32 lanes][2], combined by `stats_combine_kernel`; else null
   uint32_t* status;
   uint32_t spin_limit;      // failed polls after which a bounded wait gives up (0 = the default, about a second)
   uint32_t test_drop_kblock;   // fault injection on the host's request: the producer leaves out this K block's copies (+1; 0 = off)
@@ -133,6 +138,8 @@ struct GemmParams {
 constexpr uint32_t kStoreStageBytesPerWarp = 2048;
 constexpr uint32_t kStoreBiasBytesPerWarp = 1024;
 constexpr uint32_t kStoreSmemBytes = 8 * (kStoreStageBytesPerWarp + kStoreBiasBytesPerWarp);
+// statistics plans: per epilogue warp the shift values of its four column chunks (512 B) and its running sums (1 KB), behind the block above
+constexpr uint32_t kStatBytesPerWarp = 512 + 1024;
 // Launch with programmatic stream serialization (the kernel must execute griddepcontrol.wait before its first
 // global access).  GB_NO_OVERLAPPED_LAUNCH=1 falls back to plain stream order.
 template <class... KernelArgs, class... Args>
@@ -155,6 +162,8 @@ size_t gemm_smem_bytes(const GemmParams& p);
 cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_c, int sm_count,
                               cudaStream_t stream);
 cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream);
+uint32_t gemm_grid_ctas(const GemmParams& p, int sm_count);
+cudaError_t launch_stats_combine(const GemmParams& p, uint32_t ctas, cudaStream_t stream);
 cudaError_t gemm_sm100_configure();
 uint32_t f32_grid_blocks(const GemmParams& p, uint32_t tm, uint32_t tn);
 

@@ -119,6 +119,9 @@ bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, co
   return r == CUDA_SUCCESS;
 }
 
+// Ordered batch-norm statistics: 8 epilogue warps x 4 chunks x 32 lanes x (sum, squares) floats per CTA.
+constexpr size_t kStatsPartialBytesPerCta = 8 * 4 * 64 * sizeof(float);
+
 enum LaunchKind : uint32_t { kLaunchNone, kLaunchDirect, kLaunchDirectWgrad, kLaunchEmptyK, kLaunchTensor, kLaunchF32 };
 
 struct Plan {
@@ -128,6 +131,8 @@ struct Plan {
   bool reduce = false;               // ... and whether the split-K reduce follows it
   gb_plan_info info = {};            // what gb_last_plan reports after the launch
   bool direct = false;      // forward convolution with very few input channels: the FMA kernel of conv_direct.cu
+  bool stats_ordered = false;         // statistics through per-CTA partials in the workspace and an ordered combine
+  uint32_t stats_ctas = 0;
   uint32_t direct_wgrad_blocks = 0;   // > 0: weight gradient of such a layer by the FMA kernel, this many position ranges
   size_t direct_wgrad_bytes = 0;      // ... when the workspace holds their partial matrices
   bool tensor = false;      // tcgen05 path, else strict-f32
@@ -137,7 +142,7 @@ struct Plan {
 struct PlanKey {
   uint32_t kind, pad;
   unsigned char desc[72];
-  uint64_t ptr[8];
+  uint64_t ptr[11];
   uint64_t hash;     // over the bytes before it
 };
 struct CachedPlan {
@@ -255,6 +260,18 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
   p.relu = ep && ep->activation == GB_ACT_RELU;
   p.round_tf32 = ep && (ep->flags & GB_EPILOGUE_ROUND_TF32) && !p.c_is_bf16;
   p.status = h->status;
+  const gb_bn_stats* st = ep ? ep->bn_stats : nullptr;
+  if (st) {
+    // statistics are summed per warp over ONE column tile and over the final values: tensor path, whole 32-column chunks,
+    // at most 256 columns, no K split
+    if (!st->shift || !st->sums || !plan.tensor || p.n > 256 || p.n % 32 != 0 || p.batch != 1) return GB_ERR_UNSUPPORTED;
+    p.stats = 1;
+    p.stat_shift = st->shift;
+    p.stat_sums = st->sums;
+    plan.stats_ordered = st->ordered != 0;
+    allow_split = false;
+    min_bn = std::max<uint32_t>(min_bn, p.n <= 32 ? 32 : (p.n <= 64 ? 64 : (p.n <= 128 ? 128 : 256)));
+  }
   p.epi_groups = 2;
   p.group_m = 8;
   if (knobs().group_m) p.group_m = (uint32_t)knobs().group_m;
@@ -302,6 +319,7 @@ bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b)
   for (uint32_t cand : {512u, 256u, 128u, 64u}) {
     // a pair tile may overhang n as long as the second CTA's half still holds columns (192 columns: one 256-wide tile)
     if (cand / 2 < min_bn || (cand > n_cap && cand / 2 >= p.n)) continue;
+    if (p.stats && (cand > 256 || cand < p.n)) continue;   // statistics: one column tile of at most 256 columns
     const double cost = tile_cost(p.m, p.n, p.batch, p.k_blocks_total, cand, true, sms);
     if (cost <= best) { best = cost; pick = cand; }   // a tie goes to the pair: half as many MMA instructions per row
   }
@@ -466,6 +484,18 @@ int prepare_plan(const gb_handle* h, Plan& plan, void* workspace, size_t workspa
     p.stages = std::max(2u, std::min(p.stages, fit));
   }
   info.stages = p.stages;
+  if (p.stats) {
+    if (!p.tma_store || p.k == 0 || p.splits != 1 || p.tiles_n != 1) return GB_ERR_UNSUPPORTED;
+    p.stat_partial = nullptr;
+    if (plan.stats_ordered) {
+      // every CTA leaves its warps' partial sums in the workspace (8 KB each) for the ordered combine
+      plan.stats_ctas = gb::gemm_grid_ctas(p, h->sm_count);
+      const size_t need = (size_t)plan.stats_ctas * kStatsPartialBytesPerCta;
+      if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return GB_ERR_WORKSPACE;
+      p.stat_partial = (float*)workspace;
+      info.kernel_launches += 1;
+    }
+  }
   if (p.k == 0) {
     // An empty contraction is a zero product: only the epilogue runs (through the reduce kernel, zero parts).
     p.splits = 0;
@@ -501,6 +531,7 @@ int launch_plan(gb_handle* h, cudaStream_t stream, const Plan& plan) {
       break;
   }
   if (e == cudaSuccess && plan.reduce) e = gb::launch_splitk_reduce(plan.p, stream);
+  if (e == cudaSuccess && plan.p.stats && plan.p.stat_partial != nullptr) e = gb::launch_stats_combine(plan.p, plan.stats_ctas, stream);
   return e == cudaSuccess ? GB_OK : cuda_fail(h, e);
 }
 
@@ -526,6 +557,10 @@ PlanKey make_key(uint32_t kind, const void* desc, size_t desc_bytes, const void*
   if (ep) {
     key.ptr[5] = (uint64_t)(uintptr_t)ep->bias; key.ptr[6] = (uint64_t)(uintptr_t)ep->residual;
     key.ptr[7] = ((uint64_t)(uint32_t)ep->activation << 32) | (uint32_t)ep->flags;
+    if (ep->bn_stats) {
+      key.ptr[8] = (uint64_t)(uintptr_t)ep->bn_stats->shift; key.ptr[9] = (uint64_t)(uintptr_t)ep->bn_stats->sums;
+      key.ptr[10] = 1 + (uint64_t)ep->bn_stats->ordered;
+    }
   }
   uint64_t hash = 1469598103934665603ull;
   const unsigned char* bytes = (const unsigned char*)&key;
@@ -720,7 +755,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     set_output(p, out, d->dtype_y, g.c_out, 0, false, d->accumulate, ep);
     int rc = finish_plan(h, plan, true, min_bn, ep);
     if (rc != GB_OK) return rc;
-    if (plan.tensor && gb::conv_direct_applies(p) && !knobs().no_direct_conv) {
+    if (plan.tensor && gb::conv_direct_applies(p) && !knobs().no_direct_conv && !p.stats) {
       plan.direct = true;
       plan.workspace = 0;
       return GB_OK;
@@ -1076,6 +1111,8 @@ int gb_gemm_workspace(const gb_handle* h, const gb_gemm_desc* desc, size_t* byte
   Plan plan;
   rc = plan_gemm(h, desc, nullptr, nullptr, nullptr, nullptr, plan);
   if (rc != GB_OK) return rc;
+  // room for the ordered batch-norm statistics of a call whose epilogue asks for them (the query does not see the epilogue)
+  plan.workspace = std::max(plan.workspace, (size_t)h->sm_count * kStatsPartialBytesPerCta);
   cache_store(hm, key, plan);
   *bytes = plan.workspace;
   return GB_OK;
@@ -1118,6 +1155,7 @@ int gb_conv_workspace(const gb_handle* h, int pass, const gb_conv_desc* desc, si
   }
   rc = plan_conv(h, pass, desc, nullptr, nullptr, nullptr, nullptr, plan);
   if (rc != GB_OK) return rc;
+  if (pass == 0) plan.workspace = std::max(plan.workspace, (size_t)h->sm_count * kStatsPartialBytesPerCta);   // ordered statistics, if asked for
   cache_store(hm, key, plan);
   *bytes = head + plan.workspace;
   return GB_OK;

@@ -42,6 +42,9 @@ class Epilogue:
     residual: Optional[torch.Tensor] = None    # same shape / dtype as the output
     relu: bool = False
     round_tf32: bool = False                   # store the f32 result rounded to TF32 (nearest, ties away)
+    stats_shift: Optional[torch.Tensor] = None # f32[n]: with stats_sums, batch-norm statistics of the stored result
+    stats_sums: Optional[torch.Tensor] = None  # f32[2n], += sum(v - shift) and sum((v - shift)^2) per column
+    stats_ordered: bool = False                # reproducible sums (ordered partials) instead of atomics
 
 
 @dataclass
@@ -204,7 +207,11 @@ class Gpu:
     def _epilogue(self, ep: Optional[Epilogue]):
         if ep is None:
             return None
-        e = abi.Epilogue(_ptr(ep.bias), _ptr(ep.residual), ACT_RELU if ep.relu else ACT_NONE, abi.EPILOGUE_ROUND_TF32 if ep.round_tf32 else 0)
+        stats = None
+        if ep.stats_sums is not None:
+            self._stats = abi.BnStats(_ptr(ep.stats_shift), _ptr(ep.stats_sums), int(ep.stats_ordered), 0)   # kept alive for the call
+            stats = C.pointer(self._stats)
+        e = abi.Epilogue(_ptr(ep.bias), _ptr(ep.residual), ACT_RELU if ep.relu else ACT_NONE, abi.EPILOGUE_ROUND_TF32 if ep.round_tf32 else 0, stats)
         return C.byref(e)
 
     # ---- matmul family ----------------------------------------------------------------------------

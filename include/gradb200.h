@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define GB_ABI_VERSION 1
+#define GB_ABI_VERSION 2
 
 typedef struct gb_handle gb_handle;   /* per-device state; one per host thread, like one `Gpu` per thread */
 typedef struct gb_comm gb_comm;       /* one rank of a gradient-averaging group */
@@ -34,9 +34,10 @@ typedef enum {
   GB_OK = 0,
   GB_ERR_INVALID = 1,       /* bad argument (null pointer, zero stride, trans_a and trans_b both set, ...) */
   GB_ERR_CUDA = 2,          /* a CUDA call failed; gb_last_cuda_error() has the code (maps to error.CudaFailed) */
-  GB_ERR_WORKSPACE = 3,     /* only gb_gemm_static_scratch: the partial sums exceed the fixed array (error.OutOfMemory).  gb_gemm
-                             * and gb_conv_* never return it: with a workspace that is null, misaligned or smaller than the
-                             * *_workspace query said, they run the product unsplit (and gather f32 master filters) instead */
+  GB_ERR_WORKSPACE = 3,     /* gb_gemm_static_scratch: the partial sums exceed the fixed array; ordered batch-norm statistics
+                             * without room for their partials (error.OutOfMemory).  Otherwise gb_gemm and gb_conv_* do not
+                             * return it: with a workspace that is null, misaligned or smaller than the *_workspace query said,
+                             * they run the product unsplit (and gather f32 master filters) instead */
   GB_ERR_UNSUPPORTED = 4,   /* shape / dtype combination outside what the kernels cover (error.NoAlgorithm) */
   GB_ERR_TIMEOUT = 5,       /* a bounded wait gave up: on the device (see gb_last_status) or for a peer replica (gb_comm_*) */
   GB_ERR_NCCL = 6,          /* NCCL missing or a collective failed */
@@ -57,11 +58,28 @@ typedef enum { GB_ACT_NONE = 0, GB_ACT_RELU = 1 } gb_activation;
  * (src/autograd/autograd.zig:449-468) and the ONNX executor adds bias and applies Relu with two more
  * (src/onnx/gpu.zig:518-519, 372-377).  The fused result is defined as that unfused sequence in f32:
  *   v = acc (+ old C when accumulate) ; v += bias[col] ; v += residual[row][col] ; v = act(v) ; store. */
+/* Batch-norm statistics summed in the epilogue, the role of `BnStats` / `statsTile` (src/gpu/device.zig:1447, 1505-1535;
+ * host side `Gpu.convImplicitForwardStats`, src/gpu/gpu.zig:915-923): for every output column (channel) the sums of
+ * (v - shift[col]) and of (v - shift[col])^2 over all rows (positions), taken over the values AS STORED (rounded to bf16
+ * when the result is bf16), are ADDED to sums[col] and sums[n + col]; the caller zeroes `sums` (`scratchZeroed`).  shift is
+ * the running mean, a close estimate that keeps the squared sums precise.  The stored result is bit-identical to the
+ * same call without statistics (tests/gpu.zig:205).  ordered = 1 is the reference's deterministic mode: every CTA writes
+ * its partial sums to the workspace and a second launch adds them in a fixed order, so repeated runs give identical
+ * bits; ordered = 0 adds with atomics.  Needs n <= 256, n a multiple of 32 and a 16-byte aligned row-major result
+ * (every ResNet training layer); otherwise the call returns GB_ERR_UNSUPPORTED and nothing is launched. */
+typedef struct {
+  const float* shift;       /* f32[n] */
+  float* sums;              /* f32[2 * n]: += */
+  uint32_t ordered;
+  uint32_t reserved;
+} gb_bn_stats;
+
 typedef struct {
   const float* bias;        /* f32[n] (per output column / output channel) or NULL */
   const void* residual;     /* same shape, pitch and dtype as the output, or NULL (ONNX Add before Relu) */
   int32_t activation;       /* gb_activation */
   int32_t flags;            /* GB_EPILOGUE_* bits */
+  const gb_bn_stats* bn_stats;   /* NULL, or per-column statistics of the stored result (see gb_bn_stats) */
 } gb_epilogue;
 /* Round the stored f32 result to TF32 (nearest, ties away: cvt.rna.tf32.f32, src/gpu/device.zig:1888-1893).
  * The tensor core reads TF32 operands by dropping the low mantissa bits; a chain of TF32 layers whose

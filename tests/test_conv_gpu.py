@@ -413,3 +413,67 @@ def test_repeated_calls_are_served_from_the_plan_cache(gpu):
     gpu.convForward(tx, tw, y2, geo)                               # another result buffer: a new plan, same values
     torch.cuda.synchronize()
     assert torch.equal(y1, first) and torch.equal(y2, first)
+
+
+@pytest.mark.parametrize("n,side,c_in,c_out,seed", [(5, 16, 64, 96, 51), (12, 32, 64, 128, 52), (6, 8, 128, 256, 53), (3, 16, 64, 32, 54)])
+def test_forward_epilogue_accumulates_batch_norm_sums(gpu, n, side, c_in, c_out, seed):
+    """tests/gpu.zig:170-241 (`runEpilogueStats`): the forward pass with statistics in its epilogue stores the very bits
+    of the plain forward pass, and its sums of (v - shift) and (v - shift)^2 per channel match a host reduction (f64) of
+    the stored output within the reference's bounds; the ordered mode gives identical bits on repeated runs and stays
+    close to the atomic sums."""
+    import torch
+    from grad_b200 import Epilogue
+
+    geo = _geo((n, side, side, c_in, 3, c_out, 1, 1, 1))
+    rng = np.random.default_rng(seed)
+    x = (rng.standard_normal((n, side, side, c_in), dtype=np.float32) * 2 + 0.5).astype(np.float32)
+    w = (rng.standard_normal((9 * c_in, c_out), dtype=np.float32) * 0.05).astype(np.float32)
+    shift = (rng.standard_normal(c_out, dtype=np.float32) * 0.4).astype(np.float32)
+    tx, tw, tshift = to_dev(x, True), to_dev(w, True), to_dev(shift)
+    plain = torch.empty((n, side, side, c_out), dtype=torch.bfloat16, device="cuda")
+    gpu.convForward(tx, tw, plain, geo)
+    out = torch.empty_like(plain)
+    sums = torch.zeros(2 * c_out, device="cuda")
+    gpu.convForward(tx, tw, out, geo, epilogue=Epilogue(stats_shift=tshift, stats_sums=sums))
+    torch.cuda.synchronize()
+    assert gpu.last_plan()["tile_n"] >= c_out
+    assert torch.equal(plain, out)                                   # tests/gpu.zig:205
+    stored = out.double().cpu().numpy().reshape(-1, c_out) - shift.astype(np.float64)
+    want_s, want_q = stored.sum(0), (stored * stored).sum(0)
+    got = sums.cpu().numpy()
+    assert np.all(np.abs(got[:c_out] - want_s) <= 0.05 + 1e-5 * np.abs(want_s)), float(np.abs(got[:c_out] - want_s).max())
+    assert np.all(np.abs(got[c_out:] - want_q) <= 0.05 + 1e-4 * want_q), float(np.abs(got[c_out:] - want_q).max())
+    det = []
+    for _ in range(2):
+        s2 = torch.zeros(2 * c_out, device="cuda")
+        gpu.convForward(tx, tw, out, geo, epilogue=Epilogue(stats_shift=tshift, stats_sums=s2, stats_ordered=True))
+        torch.cuda.synchronize()
+        det.append(s2.cpu().numpy())
+    assert np.array_equal(det[0], det[1])
+    assert np.all(np.abs(det[0] - got) <= 0.05 + 1e-4 * np.abs(got))
+    assert torch.equal(plain, out)
+
+
+def test_statistics_accumulate_and_reject_what_the_epilogue_cannot_sum(gpu):
+    """`sums` is added to (two calls double it); f32 results are summed unrounded; a product wider than one 256-column
+    tile, or with a ragged last chunk, is refused with GB_ERR_UNSUPPORTED before anything is launched."""
+    import torch
+    from grad_b200 import Epilogue, GbError, MatmulOpts, MatmulShape
+
+    m, n, k = 300, 64, 192
+    a, b = seeded(61, m, k), seeded(62, k, n)
+    out = torch.empty((m, n), device="cuda")
+    sums = torch.zeros(2 * n, device="cuda")
+    shift = to_dev(np.zeros(n, np.float32))
+    for _ in range(2):
+        gpu.matmul(to_dev(a, True), to_dev(b, True), out, MatmulShape(m, n, k), MatmulOpts(), epilogue=Epilogue(stats_shift=shift, stats_sums=sums))
+    torch.cuda.synchronize()
+    stored = out.double().cpu().numpy()
+    got = sums.cpu().numpy()
+    assert np.allclose(got[:n], 2 * stored.sum(0), rtol=1e-4, atol=0.05) and np.allclose(got[n:], 2 * (stored * stored).sum(0), rtol=1e-4, atol=0.05)
+    for bad_n in (320, 72):
+        wide = torch.empty((m, bad_n), device="cuda")
+        with pytest.raises(GbError) as err:
+            gpu.matmul(to_dev(a, True), to_dev(seeded(63, k, bad_n), True), wide, MatmulShape(m, bad_n, k), MatmulOpts(),
+                       epilogue=Epilogue(stats_shift=to_dev(np.zeros(bad_n, np.float32)), stats_sums=torch.zeros(2 * bad_n, device="cuda")))
+        assert err.value.status == 4
