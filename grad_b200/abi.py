@@ -34,6 +34,11 @@ class BnStats(C.Structure):
     _fields_ = [("shift", C.c_void_p), ("sums", C.c_void_p), ("ordered", C.c_uint32), ("reserved", C.c_uint32)]
 
 
+class DxStats(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("mean", C.c_void_p), ("inv_std", C.c_void_p), ("gamma", C.c_void_p), ("beta", C.c_void_p),
+                ("sums", C.c_void_p), ("ordered", C.c_uint32), ("reserved", C.c_uint32)]
+
+
 class Epilogue(C.Structure):
     _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("activation", C.c_int32), ("flags", C.c_int32), ("bn_stats", C.POINTER(BnStats))]
 
@@ -90,6 +95,8 @@ SIGNATURES = {
                        C.c_void_p, C.c_size_t], C.c_int),
     "gb_conv_dgrad": ([C.c_void_p, C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t],
                       C.c_int),
+    "gb_conv_dgrad_stats": ([C.c_void_p, C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(DxStats), C.c_void_p,
+                             C.c_size_t], C.c_int),
     "gb_conv_wgrad": ([C.c_void_p, C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t],
                       C.c_int),
     "gb_pool2d": ([C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p] + [C.c_uint32] * 7, C.c_int),

@@ -650,10 +650,40 @@ __device__ __forceinline__ ChunkStats chunk_stats(const float* v, const float* s
   return out;
 }
 
+// The sums a batch-norm BACKWARD needs from the epilogue of the input-gradient product that feeds it, the role of
+// `dxStatsTile` (src/gpu/device.zig:1537-1580): v = the stored gradient with respect to a normalised-and-rectified map
+// that was never written, x = the raw map the norm ran on.  x_hat = (x - mean) * inv_std rebuilds the normalised value,
+// gamma * x_hat + beta > 0 the ReLU mask; the masked gradient g and g * x_hat are summed per column.  The products and
+// sums are rounded one by one (no fused multiply-add), like the reference's separate operations.
+__device__ __forceinline__ ChunkStats chunk_dx_stats(const GemmParams& p, const float* v, const float* sstat, uint32_t slot, uint64_t off, bool live,
+                                                     uint32_t lane) {
+  const float *mean = sstat + 32 * slot, *inv_std = sstat + 384 + 32 * slot, *gamma = sstat + 512 + 32 * slot, *beta = sstat + 640 + 32 * slot;
+  float t[32], q[32];
+#pragma unroll
+  for (uint32_t i = 0; i < 32; i += 8) {
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (live) raw = *(const uint4*)((const uint16_t*)p.stat_x + off + i);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (uint32_t j = 0; j < 8; ++j) {
+      const uint32_t c = i + j;
+      const float x = __uint_as_float((j & 1) ? (w[j >> 1] & 0xFFFF0000u) : (w[j >> 1] << 16));
+      const float xh = __fmul_rn(__fsub_rn(x, mean[c]), inv_std[c]);
+      const bool on = live && __fadd_rn(__fmul_rn(gamma[c], xh), beta[c]) > 0.0f;
+      t[c] = on ? v[c] : 0.0f;
+      q[c] = on ? __fmul_rn(v[c], xh) : 0.0f;
+    }
+  }
+  ChunkStats out;
+  out.sum = column_sums(t, lane);
+  out.squares = column_sums(q, lane);
+  return out;
+}
+
 template <bool kStats>
 __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
-                                                              const float* sbias, const float* sshift, uint32_t batch, uint32_t split, uint32_t row,
-                                                              uint32_t col0, uint32_t lane) {
+                                                              const float* sbias, const float* sstat, uint32_t slot, uint32_t batch, uint32_t split,
+                                                              uint32_t row, uint32_t col0, uint32_t lane) {
   ChunkStats stats = {0.0f, 0.0f};
   if (p.splits > 1) {
     // A K part's partial tile: the raw f32 accumulators, into the map of the partial buffer {n, m, split * batch}.
@@ -743,11 +773,11 @@ __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& 
         v[2 * j] = __uint_as_float(w[j] << 16);
         v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
       }
-      stats = chunk_stats(v, sshift, live, lane);
+      stats = p.stats == 2 ? chunk_dx_stats(p, v, sstat, slot, off, live, lane) : chunk_stats(v, sstat + 32 * slot, live, lane);
     }
     stage_and_store(tmap_c, stage, q, lane, (int32_t)col0, y, (int32_t)batch);
   } else {
-    if constexpr (kStats) stats = chunk_stats(v, sshift, live, lane);
+    if constexpr (kStats) stats = chunk_stats(v, sstat + 32 * slot, live, lane);   // the backward sums exist for bf16 maps only
 #pragma unroll
     for (uint32_t half = 0; half < 2; ++half) {   // 16 f32 columns = 64 bytes per row and store
       uint4 q[4];
@@ -763,19 +793,20 @@ __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& 
 
 __device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
                                                    const float* sbias, uint32_t batch, uint32_t split, uint32_t row, uint32_t col0, uint32_t lane) {
-  epilogue_chunk_tma_impl<false>(p, tmap_c, acc, stage, sbias, nullptr, batch, split, row, col0, lane);
+  epilogue_chunk_tma_impl<false>(p, tmap_c, acc, stage, sbias, nullptr, 0, batch, split, row, col0, lane);
 }
 // The chunk epilogue of a statistics plan.  Kept out of line on its own copy of the chunk: inlined, its 64 temporaries
 // raised the register pressure (and the spills) of every plan's epilogue, with or without statistics.
-// `sstat` is the warp's statistics block in shared memory: the 128 shift values of its four column chunks, then per
-// chunk and lane the running (sum, sum of squares) of that lane's column over every row the warp has drained.
+// `sstat` is the warp's statistics block in shared memory (floats): [0, 128) the shift (or mean) values of its four
+// column chunks, [128, 384) per chunk and lane the running (sum, sum of squares) of that lane's column over every row the
+// warp has drained, and for the backward sums [384, 512) inv_std, [512, 640) gamma, [640, 768) beta.
 __device__ __noinline__ void epilogue_chunk_tma_stats(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t* vals, uint8_t* stage,
                                                       const float* sbias, float* sstat, uint32_t slot, uint32_t batch, uint32_t row, uint32_t col0,
                                                       uint32_t lane) {
   uint32_t copy[32];
 #pragma unroll
   for (uint32_t i = 0; i < 32; ++i) copy[i] = vals[i];
-  const ChunkStats c = epilogue_chunk_tma_impl<true>(p, tmap_c, copy, stage, sbias, sstat + 32 * slot, batch, 0, row, col0, lane);
+  const ChunkStats c = epilogue_chunk_tma_impl<true>(p, tmap_c, copy, stage, sbias, sstat, slot, batch, 0, row, col0, lane);
   float2* cell = (float2*)(sstat + 128) + slot * 32 + lane;   // only this lane ever touches its cell
   float2 v = *cell;
   v.x += c.sum;
@@ -1120,6 +1151,11 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         const uint32_t col = ((warp - 2) >> 2) * 32 + i * 32 * p.epi_groups + lane;
         sstat[32 * i + lane] = col < p.n ? p.stat_shift[col] : 0.0f;
         ((float2*)(sstat + 128))[32 * i + lane] = make_float2(0.0f, 0.0f);
+        if (p.stats == 2) {
+          sstat[384 + 32 * i + lane] = col < p.n ? p.stat_inv_std[col] : 0.0f;
+          sstat[512 + 32 * i + lane] = col < p.n ? p.stat_gamma[col] : 0.0f;
+          sstat[640 + 32 * i + lane] = col < p.n ? p.stat_beta[col] : 0.0f;
+        }
       }
       __syncwarp();
     }
@@ -1344,6 +1380,11 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
         const uint32_t col = ((warp - 2) >> 2) * 32 + i * 32 * p.epi_groups + lane;
         sstat[32 * i + lane] = col < p.n ? p.stat_shift[col] : 0.0f;
         ((float2*)(sstat + 128))[32 * i + lane] = make_float2(0.0f, 0.0f);
+        if (p.stats == 2) {
+          sstat[384 + 32 * i + lane] = col < p.n ? p.stat_inv_std[col] : 0.0f;
+          sstat[512 + 32 * i + lane] = col < p.n ? p.stat_gamma[col] : 0.0f;
+          sstat[640 + 32 * i + lane] = col < p.n ? p.stat_beta[col] : 0.0f;
+        }
       }
       __syncwarp();
     }

@@ -124,8 +124,10 @@ struct GemmParams {
   uint32_t round_tf32;      // round the stored f32 result to TF32 (nearest, ties away)
   uint32_t tma_store;       // full 32-column chunks leave through shared memory and a TMA store (map of C passed to the kernel)
   // batch-norm statistics of the stored result, summed in the epilogue (stats != 0): see `chunk_stats`
-  uint32_t stats;
-  const float* stat_shift;  // f32[n]: the values are centred by it before they are summed
+  uint32_t stats;           // 1: forward sums of (v - shift), (v - shift)^2; 2: backward sums of the masked gradient g and g * x_hat
+  const float* stat_shift;  // f32[n]: the values are centred by it before they are summed (mode 2: the batch mean)
+  const void* stat_x;       // mode 2: the raw bf16 map the norm ran on, laid out like the result
+  const float *stat_inv_std, *stat_gamma, *stat_beta;   // mode 2: f32[n] each
   float* stat_sums;         // f32[2n]: += sum(v - shift), += sum((v - shift)^2)
   float* stat_partial;      // ordered runs: [cta][8 warps][4 chunks][32 lanes][2], combined by `stats_combine_kernel`; else null
   uint32_t* status;
@@ -138,8 +140,8 @@ struct GemmParams {
 constexpr uint32_t kStoreStageBytesPerWarp = 2048;
 constexpr uint32_t kStoreBiasBytesPerWarp = 1024;
 constexpr uint32_t kStoreSmemBytes = 8 * (kStoreStageBytesPerWarp + kStoreBiasBytesPerWarp);
-// statistics plans: per epilogue warp the shift values of its four column chunks (512 B) and its running sums (1 KB), behind the block above
-constexpr uint32_t kStatBytesPerWarp = 512 + 1024;
+// statistics plans: per epilogue warp the per-column values of its four column chunks (4 x 512 B) and its running sums (1 KB), behind the block above
+constexpr uint32_t kStatBytesPerWarp = 4 * 512 + 1024;
 // Launch with programmatic stream serialization (the kernel must execute griddepcontrol.wait before its first
 // global access).  GB_NO_OVERLAPPED_LAUNCH=1 falls back to plain stream order.
 template <class... KernelArgs, class... Args>

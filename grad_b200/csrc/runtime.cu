@@ -724,7 +724,7 @@ void try_column_stages(Plan& plan, EncodeA encode_a) {
 }
 
 int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* act, const void* other, void* out,
-              const gb_epilogue* ep, Plan& plan) {
+              const gb_epilogue* ep, Plan& plan, const gb_dx_stats* dxs = nullptr) {
   std::memset(&plan.p, 0, sizeof(plan.p));
   GemmParams& p = plan.p;
   const gb::ConvGeo g = to_geo(d->geo);
@@ -790,8 +790,22 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     p.gbsrc.lines_total = g.c; p.gbsrc.inner_total = p.k; p.gbsrc.mn_major = 0;
     p.a_mn_major = 0; p.b_mn_major = 0;
     set_output(p, out, d->dtype_x, g.c_step, 0, false, d->accumulate, nullptr);
-    int rc = finish_plan(h, plan, true, 32, nullptr);
+    gb_bn_stats as_forward = {};
+    gb_epilogue stats_ep = {};
+    if (dxs) {
+      // the backward sums ride on the machinery of the forward statistics: same shape limits, same per-warp sums
+      if (!dxs->x || !dxs->mean || !dxs->inv_std || !dxs->gamma || !dxs->beta || !dxs->sums || d->dtype_x != GB_BF16 || d->accumulate ||
+          g.stride != 1 || g.c_step != g.c || !aligned16(dxs->x))
+        return GB_ERR_UNSUPPORTED;
+      as_forward.shift = dxs->mean; as_forward.sums = dxs->sums; as_forward.ordered = dxs->ordered;
+      stats_ep.bn_stats = &as_forward;
+    }
+    int rc = finish_plan(h, plan, true, 32, dxs ? &stats_ep : nullptr);
     if (rc != GB_OK) return rc;
+    if (dxs) {
+      p.stats = 2;
+      p.stat_x = dxs->x; p.stat_inv_std = dxs->inv_std; p.stat_gamma = dxs->gamma; p.stat_beta = dxs->beta;
+    }
     if (plan.tensor) {
       p.a_kind = gb::kGather;
       walk_dgrad_unit(p.walk, g, epl);
@@ -1155,7 +1169,7 @@ int gb_conv_workspace(const gb_handle* h, int pass, const gb_conv_desc* desc, si
   }
   rc = plan_conv(h, pass, desc, nullptr, nullptr, nullptr, nullptr, plan);
   if (rc != GB_OK) return rc;
-  if (pass == 0) plan.workspace = std::max(plan.workspace, (size_t)h->sm_count * kStatsPartialBytesPerCta);   // ordered statistics, if asked for
+  if (pass != 2) plan.workspace = std::max(plan.workspace, (size_t)h->sm_count * kStatsPartialBytesPerCta);   // ordered statistics, if asked for
   cache_store(hm, key, plan);
   *bytes = head + plan.workspace;
   return GB_OK;
@@ -1213,6 +1227,25 @@ int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   }
   rc = launch_plan(h, (cudaStream_t)stream, *cached);
   h->last_plan.kernel_launches += extra;
+  return rc;
+}
+
+int gb_conv_dgrad_stats(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* w, void* dx,
+                        const gb_dx_stats* stats, void* workspace, size_t workspace_bytes) {
+  if (!stats) return gb_conv_dgrad(h, stream, desc, dy, w, dx, workspace, workspace_bytes);
+  if (!h || !dy || !w || !dx) return GB_ERR_INVALID;
+  int rc = validate_conv(desc);
+  if (rc != GB_OK) return rc;
+  if (desc->w_layout != 0) return GB_ERR_UNSUPPORTED;
+  gb_conv_desc shadow;
+  rc = make_filter_shadow(h, (cudaStream_t)stream, desc, shadow, w, workspace, workspace_bytes);
+  if (rc != GB_OK) return rc;
+  Plan plan;
+  rc = plan_conv(h, 1, desc, dy, w, dx, nullptr, plan, stats);
+  if (rc == GB_OK) rc = prepare_plan(h, plan, workspace, workspace_bytes);
+  if (rc != GB_OK) return rc;
+  rc = launch_plan(h, (cudaStream_t)stream, plan);
+  if (desc == &shadow) h->last_plan.kernel_launches += 1;
   return rc;
 }
 

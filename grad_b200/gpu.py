@@ -298,6 +298,17 @@ class Gpu:
         abi.check(rc, "gb_conv_dgrad")
         self.launches += self._count()
 
+    def convInputGradDxStats(self, dy, w, dx, geo: ConvGeometry, x_bn, mean, inv_std, gamma, beta, sums, ordered: bool = False,
+                             math: Optional[int] = None):
+        """`convImplicitForwardDxStats` (gpu.zig:964-972): the input gradient (stored) whose epilogue also sums the masked
+        batch-norm gradient g and g * x_hat per channel into `sums` (2 * c)."""
+        d = self._conv_desc(geo, dx, w, dy, math, False)
+        ws, n = self._conv_ws(abi.PASS_DGRAD, d)
+        st = abi.DxStats(_ptr(x_bn), _ptr(mean), _ptr(inv_std), _ptr(gamma), _ptr(beta), _ptr(sums), int(ordered), 0)
+        rc = self.lib.gb_conv_dgrad_stats(self.handle, self._stream(), C.byref(d), _ptr(dy), _ptr(w), _ptr(dx), C.byref(st), _ptr(ws), n)
+        abi.check(rc, "gb_conv_dgrad_stats")
+        self.launches += self._count()
+
     def convWeightGrad(self, dy, x, out, geo: ConvGeometry, math: Optional[int] = None, accumulate: bool = True):
         """`convImplicitWeightGrad` (gpu.zig:983-1022) / `convF32WeightGrad` (:828-866): out (taps, c_out) f32 += ...;
         dy is read as stored (positions, c_out), no transposed copy."""

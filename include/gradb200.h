@@ -74,6 +74,20 @@ typedef struct {
   uint32_t reserved;
 } gb_bn_stats;
 
+/* The sums a batch-norm backward needs, from the epilogue of the input-gradient product whose result is the gradient with
+ * respect to a normalised-and-rectified map that was never written (`DxStats` / `dxStatsTile`, src/gpu/device.zig:1452,
+ * 1537-1580; `Gpu.convImplicitForwardDxStats`, src/gpu/gpu.zig:964-972): x is the raw bf16 map the norm ran on, laid out
+ * like dx; x_hat = (x - mean) * inv_std; where gamma * x_hat + beta > 0 the stored gradient g counts, elsewhere it is 0;
+ * sums[col] += sum g, sums[n + col] += sum g * x_hat.  dx itself is stored unmasked.  Same shape limits and `ordered`
+ * meaning as gb_bn_stats; dx must be bf16. */
+typedef struct {
+  const void* x;            /* bf16, same shape and pitch as dx */
+  const float *mean, *inv_std, *gamma, *beta;   /* f32[n] each */
+  float* sums;              /* f32[2 * n]: += */
+  uint32_t ordered;
+  uint32_t reserved;
+} gb_dx_stats;
+
 typedef struct {
   const float* bias;        /* f32[n] (per output column / output channel) or NULL */
   const void* residual;     /* same shape, pitch and dtype as the output, or NULL (ONNX Add before Relu) */
@@ -193,6 +207,10 @@ int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
  * the `*Subsampled` kernels for strided layers (device.zig:1921-1925). */
 int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* w, void* dx,
                   void* workspace, size_t workspace_bytes);
+/* The same product with the batch-norm backward sums of gb_dx_stats in its epilogue (stride-1 layers, dx stored, not
+ * accumulated): `Gpu.convImplicitForwardDxStats`. */
+int gb_conv_dgrad_stats(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* w, void* dx,
+                        const gb_dx_stats* stats, void* workspace, size_t workspace_bytes);
 /* Weight gradient: dw[(tap,ci),co] (+)= sum_positions patch(x)[pos,(tap,ci)] * dy[pos,co], f32 output.
  * Replaces `Gpu.convImplicitWeightGrad` (gpu.zig:983-1022) and `convF32WeightGrad` + `transposeF32`
  * (:775-787, :828-866).  Partials of the split over positions are combined in order. */

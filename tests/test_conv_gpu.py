@@ -477,3 +477,47 @@ def test_statistics_accumulate_and_reject_what_the_epilogue_cannot_sum(gpu):
             gpu.matmul(to_dev(a, True), to_dev(seeded(63, k, bad_n), True), wide, MatmulShape(m, bad_n, k), MatmulOpts(),
                        epilogue=Epilogue(stats_shift=to_dev(np.zeros(bad_n, np.float32)), stats_sums=torch.zeros(2 * bad_n, device="cuda")))
         assert err.value.status == 4
+
+
+@pytest.mark.parametrize("n,side,c_in,c_out,seed", [(6, 16, 64, 128, 71), (5, 8, 128, 128, 72), (3, 32, 64, 64, 73)])
+def test_input_gradient_epilogue_accumulates_batch_norm_backward_sums(gpu, n, side, c_in, c_out, seed):
+    """`convImplicitForwardDxStats` (src/gpu/gpu.zig:964-972, device.zig:1537-1580): the input gradient with the masked
+    batch-norm gradient sums in its epilogue stores the bits of the plain input gradient, and its sums of g and g * x_hat
+    per channel match a host evaluation of the definition on the stored gradient; the ordered mode repeats bit for bit."""
+    import torch
+
+    geo = _geo((n, side, side, c_in, 3, c_out, 1, 1, 1))
+    rng = np.random.default_rng(seed)
+    dy = rng.standard_normal((n, side, side, c_out), dtype=np.float32)
+    w = (rng.standard_normal((9 * c_in, c_out), dtype=np.float32) * 0.05).astype(np.float32)
+    x_bn = (rng.standard_normal((n, side, side, c_in), dtype=np.float32) * 1.5 + 0.3).astype(np.float32)
+    mean = (rng.standard_normal(c_in, dtype=np.float32) * 0.3).astype(np.float32)
+    inv_std = (0.5 + rng.random(c_in, dtype=np.float32)).astype(np.float32)
+    gamma = (0.5 + rng.random(c_in, dtype=np.float32)).astype(np.float32)
+    beta = (rng.standard_normal(c_in, dtype=np.float32) * 0.2).astype(np.float32)
+    tdy, tw, tx = to_dev(dy, True), to_dev(w, True), to_dev(x_bn, True)
+    plain = torch.empty((n, side, side, c_in), dtype=torch.bfloat16, device="cuda")
+    gpu.convInputGrad(tdy, tw, plain, geo, accumulate=False)
+    dx = torch.empty_like(plain)
+    sums = torch.zeros(2 * c_in, device="cuda")
+    args = (tx, to_dev(mean), to_dev(inv_std), to_dev(gamma), to_dev(beta))
+    gpu.convInputGradDxStats(tdy, tw, dx, geo, *args, sums)
+    torch.cuda.synchronize()
+    assert torch.equal(plain, dx)
+    stored = dx.float().cpu().numpy().reshape(-1, c_in)
+    xs = tx.float().cpu().numpy().reshape(-1, c_in)
+    xh = ((xs - mean) * inv_std).astype(np.float32)                    # one rounding per operation, as on the device
+    mask = ((gamma * xh).astype(np.float32) + beta).astype(np.float32) > 0
+    g = np.where(mask, stored, np.float32(0)).astype(np.float64)
+    want_s, want_q = g.sum(0), (np.where(mask, (stored * xh).astype(np.float32), np.float32(0)).astype(np.float64)).sum(0)
+    got = sums.cpu().numpy()
+    assert np.all(np.abs(got[:c_in] - want_s) <= 0.05 + 1e-4 * np.abs(want_s)), float(np.abs(got[:c_in] - want_s).max())
+    assert np.all(np.abs(got[c_in:] - want_q) <= 0.05 + 1e-4 * np.abs(want_q)), float(np.abs(got[c_in:] - want_q).max())
+    det = []
+    for _ in range(2):
+        s2 = torch.zeros(2 * c_in, device="cuda")
+        gpu.convInputGradDxStats(tdy, tw, dx, geo, *args, s2, ordered=True)
+        torch.cuda.synchronize()
+        det.append(s2.cpu().numpy())
+    assert np.array_equal(det[0], det[1])
+    assert np.all(np.abs(det[0] - got) <= 0.05 + 1e-4 * np.abs(got))
