@@ -39,6 +39,10 @@ class DxStats(C.Structure):
                 ("sums", C.c_void_p), ("ordered", C.c_uint32), ("reserved", C.c_uint32)]
 
 
+class AffineInput(C.Structure):
+    _fields_ = [("mean", C.c_void_p), ("inv_std", C.c_void_p), ("gamma", C.c_void_p), ("beta", C.c_void_p)]
+
+
 class Epilogue(C.Structure):
     _fields_ = [("bias", C.c_void_p), ("residual", C.c_void_p), ("activation", C.c_int32), ("flags", C.c_int32), ("bn_stats", C.POINTER(BnStats))]
 
@@ -61,7 +65,7 @@ class ConvGeometryC(C.Structure):
 
 class ConvDesc(C.Structure):
     _fields_ = [("geo", ConvGeometryC), ("dtype_x", C.c_uint8), ("dtype_w", C.c_uint8), ("dtype_y", C.c_uint8), ("math", C.c_uint8),
-                ("accumulate", C.c_uint8), ("deterministic", C.c_uint8), ("w_layout", C.c_uint8), ("reserved", C.c_uint8)]
+                ("accumulate", C.c_uint8), ("deterministic", C.c_uint8), ("w_layout", C.c_uint8), ("reserved", C.c_uint8), ("groups", C.c_uint32)]
 
 
 class PlanInfo(C.Structure):
@@ -95,6 +99,10 @@ SIGNATURES = {
                        C.c_void_p, C.c_size_t], C.c_int),
     "gb_conv_dgrad": ([C.c_void_p, C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t],
                       C.c_int),
+    "gb_conv_fprop_affine": ([C.c_void_p, C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Epilogue),
+                              C.POINTER(AffineInput), C.c_void_p, C.c_size_t], C.c_int),
+    "gb_conv_wgrad_affine": ([C.c_void_p, C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(AffineInput), C.c_void_p,
+                              C.c_size_t], C.c_int),
     "gb_conv_dgrad_stats": ([C.c_void_p, C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(DxStats), C.c_void_p,
                              C.c_size_t], C.c_int),
     "gb_conv_wgrad": ([C.c_void_p, C.c_void_p, C.POINTER(ConvDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t],

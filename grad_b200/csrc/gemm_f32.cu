@@ -38,11 +38,11 @@ __device__ __forceinline__ int64_t f32_gather_index(const GatherDesc& d, const C
       if (ty < 0 || tx < 0) return -1;
       const uint32_t oy = (uint32_t)ty / g.stride, ox = (uint32_t)tx / g.stride;
       if (oy * g.stride != (uint32_t)ty || ox * g.stride != (uint32_t)tx || oy >= g.out_h || ox >= g.out_w) return -1;
-      return ((int64_t)(n * g.out_h + oy) * g.out_w + ox) * g.c_out + co;
+      return ((int64_t)(n * g.out_h + oy) * g.out_w + ox) * g.y_step + co;
     }
     default: {
       const uint32_t tap = inner / g.c_out, co = inner - tap * g.c_out;
-      return ((int64_t)tap * g.c + line) * g.c_out + co;
+      return ((int64_t)tap * g.c + line) * g.w_step + co;
     }
   }
 }

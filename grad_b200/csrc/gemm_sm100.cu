@@ -164,12 +164,12 @@ __device__ __forceinline__ int64_t gather_run(const GatherDesc& d, const ConvGeo
       if (ty < 0 || tx < 0) return -1;
       const uint32_t oy = (uint32_t)ty / g.stride, ox = (uint32_t)tx / g.stride;
       if (oy * g.stride != (uint32_t)ty || ox * g.stride != (uint32_t)tx || oy >= g.out_h || ox >= g.out_w) return -1;
-      return ((int64_t)(c.img * g.out_h + oy) * g.out_w + ox) * g.c_out + co;
+      return ((int64_t)(c.img * g.out_h + oy) * g.out_w + ox) * g.y_step + co;
     }
     default: {
       const uint32_t tap = inner / g.c_out, co = inner - tap * g.c_out;
       run = min(run, g.c_out - co);
-      return ((int64_t)tap * g.c + c.line) * g.c_out + co;
+      return ((int64_t)tap * g.c + c.line) * g.w_step + co;
     }
   }
 }
@@ -203,6 +203,17 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
     lo[chunk] = *(const uint4*)ptr;
     if (convert) hi[chunk] = *(const uint4*)(ptr + 16);
   }
+  // A patch operand that stands for a normalised-and-rectified map: in-bounds values become relu(scale * x + shift) in
+  // bf16 (device.zig:1604-1612); padding stays exactly zero, which is why this cannot be done after a zero-filling copy.
+  const bool affine = p.affine_scale != nullptr && d.source == kSrcPatch && !p.tf32 && src.src_is_bf16;
+  uint32_t inbounds = 0;
+  if (affine) {
+#pragma unroll
+    for (uint32_t chunk = 0; chunk < 8; ++chunk) {
+      uint32_t run;
+      if (gather_run(src, p.geo, ctx, inner0 + chunk * epc, epc, run) >= 0 && run == epc) inbounds |= 1u << chunk;
+    }
+  }
 #pragma unroll
   for (uint32_t chunk = 0; chunk < 8; ++chunk) {
     uint4 out = lo[chunk];
@@ -212,6 +223,10 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
         uint32_t run;
         const int64_t idx = gather_run(src, p.geo, ctx, inner0 + chunk * epc + e, 1, run);
         v[e] = load_as_f32(src, idx);
+        if (affine && idx >= 0) {
+          const uint32_t ci = (inner0 + chunk * epc + e) % p.geo.c;
+          v[e] = bf16_to_f32((uint16_t)affine_relu_bf16x2(bf16_bits(v[e]), p.affine_scale[ci], p.affine_shift[ci]));
+        }
       }
       if (p.tf32) out = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
       else out = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
@@ -219,6 +234,12 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
       const uint4 a = lo[chunk], b2 = hi[chunk];
       out = make_uint4(pack_bf16x2(__uint_as_float(a.x), __uint_as_float(a.y)), pack_bf16x2(__uint_as_float(a.z), __uint_as_float(a.w)),
                        pack_bf16x2(__uint_as_float(b2.x), __uint_as_float(b2.y)), pack_bf16x2(__uint_as_float(b2.z), __uint_as_float(b2.w)));
+    }
+    if (affine && !(slow & (1u << chunk)) && (inbounds & (1u << chunk))) {
+      const uint32_t ci = (inner0 + chunk * epc) % p.geo.c;   // a multiple of 8: the chunk is one aligned run of channels
+      const uint4 sc = *(const uint4*)(p.affine_scale + ci), sh = *(const uint4*)(p.affine_shift + ci);
+      out = make_uint4(affine_relu_bf16x2(out.x, sc.x, sh.x), affine_relu_bf16x2(out.y, sc.y, sh.y), affine_relu_bf16x2(out.z, sc.z, sh.z),
+                       affine_relu_bf16x2(out.w, sc.w, sh.w));
     }
     *(uint4*)(line + ((chunk ^ sw) << 4)) = out;
   }

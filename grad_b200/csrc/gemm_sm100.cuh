@@ -29,6 +29,9 @@ enum GatherSource : uint32_t {
 
 struct ConvGeo {
   uint32_t n, h, w, c, k, stride, pad, dilation, out_h, out_w, c_out, c_step;
+  // Channel pitch of y / dy and column pitch of w / dw in memory: c_out for a dense layer; one group of a grouped layer
+  // is a layer of its own over channel slices of x, w and y, whose pitches stay those of the whole tensors.
+  uint32_t y_step, w_step;
 };
 
 struct GatherDesc {
@@ -112,6 +115,10 @@ struct GemmParams {
   ClassSlot cls[kMaxClasses];
   // gather sources
   GatherDesc ga, gbsrc;
+  // non-null: the patch operand stands for relu(scale[ci] * x + shift[ci]) of the stored bf16 map (a batch norm and ReLU
+  // that were never written out); bf16[c] each, applied by the gather warps to in-bounds taps only (padding stays zero)
+  const uint16_t* affine_scale;
+  const uint16_t* affine_shift;
   // output
   void* c;
   const float* bias;

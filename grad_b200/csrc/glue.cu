@@ -183,6 +183,26 @@ int convert_weights(const gb_weights* w, cudaStream_t stream) {
 
 }  // namespace
 
+namespace {
+// s = gamma * inv_std and t = beta - mean * s per channel, each rounded to bf16 (`affineExpand`, src/gpu/device.zig:1774-1783).
+__global__ void affine_expand_kernel(const float* mean, const float* inv_std, const float* gamma, const float* beta, uint16_t* scale,
+                                     uint16_t* shift, uint32_t c) {
+  const uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= c) return;
+  const float s = __fmul_rn(gamma[ch], inv_std[ch]);
+  scale[ch] = (uint16_t)gb::bf16_bits(s);
+  shift[ch] = (uint16_t)gb::bf16_bits(__fsub_rn(beta[ch], __fmul_rn(mean[ch], s)));
+}
+}  // namespace
+
+namespace gb {
+cudaError_t launch_affine_expand(const float* mean, const float* inv_std, const float* gamma, const float* beta, uint16_t* scale, uint16_t* shift,
+                                 uint32_t c, cudaStream_t stream) {
+  affine_expand_kernel<<<(c + 127) / 128, 128, 0, stream>>>(mean, inv_std, gamma, beta, scale, shift, c);
+  return cudaGetLastError();
+}
+}  // namespace gb
+
 extern "C" {
 
 size_t gb_weights_bytes(uint32_t rows, uint32_t cols, int dtype) { return (size_t)rows * cols * (dtype == GB_BF16 ? 2 : 4); }

@@ -23,6 +23,8 @@ cudaError_t launch_conv_direct(const GemmParams& p, int sm_count, cudaStream_t s
 bool conv_direct_wgrad_applies(const GemmParams& p);
 uint32_t conv_direct_wgrad_blocks(const GemmParams& p, int sm_count);
 cudaError_t launch_conv_direct_wgrad(const GemmParams& p, uint32_t blocks, cudaStream_t stream);
+cudaError_t launch_affine_expand(const float* mean, const float* inv_std, const float* gamma, const float* beta, uint16_t* scale, uint16_t* shift,
+                                 uint32_t c, cudaStream_t stream);
 }
 
 struct gb_handle;
@@ -605,12 +607,15 @@ int validate_conv(const gb_conv_desc* d) {
   if (g.out_h != oh || g.out_w != ow) return GB_ERR_INVALID;
   if ((uint64_t)g.positions != (uint64_t)g.n * oh * ow) return GB_ERR_INVALID;
   if (g.c_step != 0 && g.c_step < g.c) return GB_ERR_INVALID;
+  if (d->groups > 1 && (g.c % d->groups != 0 || g.c_out % d->groups != 0)) return GB_ERR_INVALID;
   if (d->dtype_x > GB_BF16 || d->dtype_w > GB_BF16 || d->dtype_y > GB_BF16 || d->math > GB_MATH_BF16 || d->w_layout > 1) return GB_ERR_INVALID;
   return GB_OK;
 }
 
-gb::ConvGeo to_geo(const gb_conv_geometry& g) {
+gb::ConvGeo to_geo(const gb_conv_geometry& g, uint32_t y_step = 0, uint32_t w_step = 0) {
   gb::ConvGeo o;
+  o.y_step = y_step ? y_step : g.c_out;
+  o.w_step = w_step ? w_step : g.c_out;
   o.n = g.n; o.h = g.h; o.w = g.w; o.c = g.c; o.k = g.k; o.stride = g.stride; o.pad = g.pad;
   o.dilation = g.dilation ? g.dilation : 1;
   o.out_h = g.out_h; o.out_w = g.out_w; o.c_out = g.c_out;
@@ -724,10 +729,15 @@ void try_column_stages(Plan& plan, EncodeA encode_a) {
 }
 
 int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* act, const void* other, void* out,
-              const gb_epilogue* ep, Plan& plan, const gb_dx_stats* dxs = nullptr) {
+              const gb_epilogue* ep, Plan& plan, const gb_dx_stats* dxs = nullptr, const uint16_t* affine_scale = nullptr,
+              const uint16_t* affine_shift = nullptr, uint32_t y_step = 0, uint32_t w_step = 0) {
   std::memset(&plan.p, 0, sizeof(plan.p));
   GemmParams& p = plan.p;
-  const gb::ConvGeo g = to_geo(d->geo);
+  p.affine_scale = affine_scale;
+  p.affine_shift = affine_shift;
+  const bool affine = affine_scale != nullptr;   // the patch operand is transformed while it is gathered: no TMA, no FMA kernel
+  if (affine && (d->dtype_x != GB_BF16 || (d->math != GB_MATH_BF16 && d->math != GB_MATH_F32) || pass == 1)) return GB_ERR_UNSUPPORTED;
+  const gb::ConvGeo g = to_geo(d->geo, y_step, w_step);
   p.geo = g;
   p.batch = 1;
   uint32_t math = d->math;
@@ -738,6 +748,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
   const uint32_t epl = p.tf32 ? 32 : 64;
   const uint32_t taps = g.k * g.k;
   const uint32_t positions = d->geo.positions;
+  if ((g.y_step != g.c_out || g.w_step != g.c_out) && (d->w_layout != 0 || dxs || (ep && ep->bn_stats))) return GB_ERR_UNSUPPORTED;   // group slices: plain layers only
   const uint32_t pixels = g.n * g.h * g.w;
   uint32_t min_bn = 32;
 
@@ -748,14 +759,14 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     p.ga.lines_total = positions; p.ga.inner_total = p.k; p.ga.mn_major = 0;
     // Filters as grad stores them, (K, c_out), are an MN-major B; the prepared (c_out, K) copy is a K-major B.
     const bool w_rows = d->w_layout == 1;
-    DenseOperand ob = w_rows ? DenseOperand{other, d->dtype_w, g.c_out, p.k, p.k, 0, false} : DenseOperand{other, d->dtype_w, p.k, g.c_out, g.c_out, 0, true};
+    DenseOperand ob = w_rows ? DenseOperand{other, d->dtype_w, g.c_out, p.k, p.k, 0, false} : DenseOperand{other, d->dtype_w, p.k, g.c_out, g.w_step, 0, true};
     fill_dense_gather(p.gbsrc, ob);
     p.a_mn_major = 0; p.b_mn_major = w_rows ? 0 : 1;
     min_bn = (plan.tensor && !w_rows) ? epl : 32;
-    set_output(p, out, d->dtype_y, g.c_out, 0, false, d->accumulate, ep);
+    set_output(p, out, d->dtype_y, g.y_step, 0, false, d->accumulate, ep);
     int rc = finish_plan(h, plan, true, min_bn, ep);
     if (rc != GB_OK) return rc;
-    if (plan.tensor && gb::conv_direct_applies(p) && !knobs().no_direct_conv && !p.stats) {
+    if (plan.tensor && gb::conv_direct_applies(p) && !knobs().no_direct_conv && !p.stats && !affine) {
       plan.direct = true;
       plan.workspace = 0;
       return GB_OK;
@@ -764,7 +775,9 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       p.a_kind = gb::kGather;
       walk_forward(p.walk, g, epl);
       const bool view = g.k == 1 && g.pad == 0 && g.stride > 1 && !knobs().no_strided_tma;
-      if (view && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+      if (affine) {
+        // stays gathered
+      } else if (view && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
           nhwc_view_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g, epl, p.box_w, p.box_h, p.box_n, false)) {
         p.a_kind = gb::kPatchK;
         p.walk.row_scale = 1;   // rows of the view, not of x
@@ -810,15 +823,15 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       p.a_kind = gb::kGather;
       walk_dgrad_unit(p.walk, g, epl);
       if (g.stride == 1 && patch_box(128, g.h, g.w, p.box_w, p.box_h, p.box_n) &&
-          nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_y, g.c_out, g.c_out, g.out_w, g.out_h, g.n, epl, p.box_w, p.box_h, p.box_n))
+          nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_y, g.c_out, g.y_step, g.out_w, g.out_h, g.n, epl, p.box_w, p.box_h, p.box_n))
         p.a_kind = gb::kPatchK;
       p.b_kind = gb::kGather;
       const uint32_t es = smem_bf16 ? 2 : 4;
       if ((d->dtype_w == GB_BF16) == smem_bf16 && g.c_out % epl == 0 && aligned16(other) && p.bn <= 256) {
         const uint64_t dims[4] = {g.c_out, g.c, taps, 1};
-        const uint64_t strides[3] = {(uint64_t)g.c_out * es, (uint64_t)g.c_out * es * g.c, (uint64_t)g.c_out * es * g.c * taps};
+        const uint64_t strides[3] = {(uint64_t)g.w_step * es, (uint64_t)g.w_step * es * g.c, (uint64_t)g.w_step * es * g.c * taps};
         const uint32_t box[4] = {epl, p.bn, 1, 1};
-        if (encode_map(&plan.tmap_b, smem_bf16, other, 4, dims, strides, box)) p.b_kind = gb::kWeightK;
+        if (((uint64_t)g.w_step * es) % 16 == 0 && encode_map(&plan.tmap_b, smem_bf16, other, 4, dims, strides, box)) p.b_kind = gb::kWeightK;
         CUtensorMap single = plan.tmap_b;
         if (!try_pair(h, plan, 32, [&](uint32_t rows) {
               const uint32_t half_box[4] = {epl, rows, 1, 1};
@@ -826,7 +839,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
             }))
           plan.tmap_b = single;
         try_column_stages(plan, [&](uint32_t rows) {
-          return nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_y, g.c_out, g.c_out, g.out_w, g.out_h, g.n, epl, p.box_w, rows, 1);
+          return nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_y, g.c_out, g.y_step, g.out_w, g.out_h, g.n, epl, p.box_w, rows, 1);
         });
       }
     }
@@ -835,21 +848,23 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     p.m = taps * g.c; p.n = g.c_out; p.k = positions;
     p.ga.base = other; p.ga.source = gb::kSrcPatch; p.ga.src_is_bf16 = d->dtype_x == GB_BF16;
     p.ga.lines_total = positions; p.ga.inner_total = p.m; p.ga.mn_major = 1;
-    DenseOperand ob{act, d->dtype_y, positions, g.c_out, g.c_out, 0, true};
+    DenseOperand ob{act, d->dtype_y, positions, g.c_out, g.y_step, 0, true};
     fill_dense_gather(p.gbsrc, ob);
     p.a_mn_major = 1; p.b_mn_major = 1;
     min_bn = plan.tensor ? epl : 32;
-    set_output(p, out, d->dtype_w, g.c_out, 0, false, d->accumulate, nullptr);
+    set_output(p, out, d->dtype_w, g.w_step, 0, false, d->accumulate, nullptr);
     int rc = finish_plan(h, plan, true, min_bn, nullptr);
     if (rc != GB_OK) return rc;
-    if (plan.tensor && gb::conv_direct_wgrad_applies(p) && !knobs().no_direct_conv) {
+    if (plan.tensor && gb::conv_direct_wgrad_applies(p) && !knobs().no_direct_conv && !affine) {
       plan.direct_wgrad_blocks = gb::conv_direct_wgrad_blocks(p, h->sm_count);
       plan.direct_wgrad_bytes = (size_t)plan.direct_wgrad_blocks * p.m * p.n * sizeof(float);
     }
     if (plan.tensor) {
       p.a_kind = gb::kGather;
       const bool view = g.k == 1 && g.pad == 0 && g.stride > 1 && !knobs().no_strided_tma;
-      if (view && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+      if (affine) {
+        // stays gathered
+      } else if (view && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
           nhwc_view_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g, epl, p.box_w, p.box_h, p.box_n, true)) {
         p.a_kind = gb::kPatchMN;
         p.patch_view = 1;
@@ -893,7 +908,7 @@ bool wants_filter_shadow(const gb_conv_desc* d) {
   return math == GB_MATH_BF16 && d->dtype_w == GB_F32;
 }
 size_t filter_shadow_bytes(const gb_conv_desc* d) {
-  const size_t elems = (size_t)d->geo.k * d->geo.k * d->geo.c * d->geo.c_out;
+  const size_t elems = (size_t)d->geo.k * d->geo.k * (d->geo.c / std::max<uint32_t>(d->groups, 1)) * d->geo.c_out;
   return (elems * 2 + 255) & ~(size_t)255;
 }
 // Returns the descriptor / filter pointer / workspace to continue with; `shadow` receives the patched descriptor.
@@ -902,7 +917,7 @@ int make_filter_shadow(gb_handle* h, cudaStream_t stream, const gb_conv_desc*& d
   if (!wants_filter_shadow(desc)) return GB_OK;
   const size_t need = filter_shadow_bytes(desc);
   if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return GB_OK;
-  const size_t elems = (size_t)desc->geo.k * desc->geo.k * desc->geo.c * desc->geo.c_out;
+  const size_t elems = (size_t)desc->geo.k * desc->geo.k * (desc->geo.c / std::max<uint32_t>(desc->groups, 1)) * desc->geo.c_out;
   const int rc = gb_cast(stream, GB_F32, GB_BF16, w, workspace, elems);
   if (rc != GB_OK) return rc == GB_ERR_CUDA ? cuda_fail(h, cudaGetLastError()) : rc;
   shadow = *desc;
@@ -1037,6 +1052,62 @@ int run_dgrad_classes(gb_handle* h, cudaStream_t stream, const gb_conv_desc* d, 
   return GB_OK;
 }
 
+// A grouped convolution as one product per group: group g reads input channels [g*cg, (g+1)*cg) of x (a channel slice:
+// same pixel pitch), columns [g*og, (g+1)*og) of w and of y / dy (column slices: same row pitch), the way grad's
+// `grouped_implicit` path launches its kernel once per group with `c_pitch` / `c_offset` (src/autograd/autograd.zig:1041-1050,
+// src/gpu/args.zig:72).  `act`, `other`, `out` are the pass's operands in the order of plan_conv.
+int run_grouped(gb_handle* h, cudaStream_t stream, int pass, const gb_conv_desc* desc, const void* act, const void* other, void* out,
+                const gb_epilogue* ep, void* workspace, size_t workspace_bytes) {
+  if (desc->w_layout != 0 || (ep && ep->bn_stats)) return GB_ERR_UNSUPPORTED;
+  const uint32_t groups = desc->groups, cg = desc->geo.c / groups, og = desc->geo.c_out / groups;
+  const uint32_t c_total = desc->geo.c_step ? desc->geo.c_step : desc->geo.c, o_total = desc->geo.c_out;
+  const void* w = pass == 2 ? nullptr : other;
+  gb_conv_desc whole = *desc;
+  const gb_conv_desc* cast_desc = desc;
+  uint32_t extra = 0;
+  if (pass != 2) {
+    const int rc = make_filter_shadow(h, stream, cast_desc, whole, w, workspace, workspace_bytes);   // the whole filter bank, once
+    if (rc != GB_OK) return rc;
+    extra = cast_desc == &whole ? 1u : 0u;
+  }
+  gb_conv_desc one = *cast_desc;
+  one.groups = 1;
+  one.geo.c = cg;
+  one.geo.c_step = c_total;
+  one.geo.c_out = og;
+  const size_t es_x = elem_size(one.dtype_x), es_w = elem_size(one.dtype_w), es_y = elem_size(one.dtype_y);
+  uint32_t launches = 0, items = 0;
+  for (uint32_t g = 0; g < groups; ++g) {
+    // which operand is what, per pass: fprop (x, w, y); dgrad (dy, w, dx); wgrad (dy, x, dw)
+    const char* a = (const char*)act + (size_t)g * (pass == 0 ? cg * es_x : og * es_y);
+    const char* b = pass == 2 ? (const char*)other + (size_t)g * cg * es_x : (const char*)w + (size_t)g * og * es_w;
+    char* c = (char*)out + (size_t)g * (pass == 0 ? og * es_y : (pass == 1 ? cg * es_x : og * es_w));
+    gb_epilogue slice = {};
+    if (ep) {
+      slice = *ep;
+      if (ep->bias) slice.bias = ep->bias + (size_t)g * og;
+      if (ep->residual) slice.residual = (const char*)ep->residual + (size_t)g * og * es_y;
+    }
+    const PlanKey key = make_key(0x100u + (uint32_t)pass, &one, sizeof(one), a, b, c, ep ? &slice : nullptr, workspace, workspace_bytes);
+    const Plan* cached = cache_find(h, key);
+    Plan plan;
+    if (!cached) {
+      int rc = plan_conv(h, pass, &one, a, b, c, ep ? &slice : nullptr, plan, nullptr, nullptr, nullptr, o_total, o_total);
+      if (rc == GB_OK) rc = prepare_plan(h, plan, workspace, workspace_bytes);
+      if (rc != GB_OK) return rc;
+      cache_store(h, key, plan);
+      cached = &plan;
+    }
+    const int rc = launch_plan(h, stream, *cached);
+    if (rc != GB_OK) return rc;
+    launches += h->last_plan.kernel_launches;
+    items += h->last_plan.work_items;
+  }
+  h->last_plan.kernel_launches = launches + extra;
+  h->last_plan.work_items = items;
+  return GB_OK;
+}
+
 }  // namespace
 
 // =====================================================================================================
@@ -1161,15 +1232,27 @@ int gb_conv_workspace(const gb_handle* h, int pass, const gb_conv_desc* desc, si
     desc = &shadow;
     head = filter_shadow_bytes(desc);
   }
+  gb_conv_desc one;
+  uint32_t y_step = 0;
+  if (desc->groups > 1) {   // every group runs the same plan: one group's need
+    one = *desc;
+    y_step = desc->geo.c_out;
+    one.geo.c_step = desc->geo.c_step ? desc->geo.c_step : desc->geo.c;
+    one.geo.c = desc->geo.c / desc->groups;
+    one.geo.c_out = desc->geo.c_out / desc->groups;
+    one.groups = 1;
+    desc = &one;
+  }
   gb_handle* hm = const_cast<gb_handle*>(h);
   const PlanKey key = make_key(0x11 + (uint32_t)pass, desc, sizeof(*desc), nullptr, nullptr, nullptr, nullptr, nullptr, 0);
   if (const Plan* cached = cache_find(hm, key)) {
     *bytes = head + cached->workspace;
     return GB_OK;
   }
-  rc = plan_conv(h, pass, desc, nullptr, nullptr, nullptr, nullptr, plan);
+  rc = plan_conv(h, pass, desc, nullptr, nullptr, nullptr, nullptr, plan, nullptr, nullptr, nullptr, y_step, y_step);
   if (rc != GB_OK) return rc;
   if (pass != 2) plan.workspace = std::max(plan.workspace, (size_t)h->sm_count * kStatsPartialBytesPerCta);   // ordered statistics, if asked for
+  if (pass != 1) plan.workspace += ((size_t)desc->geo.c * 4 + 255) & ~(size_t)255;                              // the expanded norm of the *_affine entry points
   cache_store(hm, key, plan);
   *bytes = head + plan.workspace;
   return GB_OK;
@@ -1180,6 +1263,7 @@ int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   if (!h || !x || !w || !y) return GB_ERR_INVALID;
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
+  if (desc->groups > 1) return run_grouped(h, (cudaStream_t)stream, 0, desc, x, w, y, epilogue, workspace, workspace_bytes);
   gb_conv_desc shadow;
   rc = make_filter_shadow(h, (cudaStream_t)stream, desc, shadow, w, workspace, workspace_bytes);
   if (rc != GB_OK) return rc;
@@ -1204,6 +1288,7 @@ int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
   if (desc->w_layout != 0) return GB_ERR_UNSUPPORTED;   // the prepared filter copy is a forward-only format
+  if (desc->groups > 1) return run_grouped(h, (cudaStream_t)stream, 1, desc, dy, w, dx, nullptr, workspace, workspace_bytes);
   gb_conv_desc shadow;
   rc = make_filter_shadow(h, (cudaStream_t)stream, desc, shadow, w, workspace, workspace_bytes);
   if (rc != GB_OK) return rc;
@@ -1230,13 +1315,71 @@ int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   return rc;
 }
 
+namespace {
+// Expands the norm into bf16 scale / shift vectors at the head of the workspace; returns what is left of it.
+int expand_affine(gb_handle* h, cudaStream_t stream, const gb_affine_input* affine, uint32_t c, void*& workspace, size_t& workspace_bytes,
+                  const uint16_t*& scale, const uint16_t*& shift) {
+  if (!affine || !affine->mean || !affine->inv_std || !affine->gamma || !affine->beta) return GB_ERR_INVALID;
+  const size_t need = ((size_t)c * 4 + 255) & ~(size_t)255;
+  if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return GB_ERR_WORKSPACE;
+  uint16_t* s = (uint16_t*)workspace;
+  uint16_t* t = s + ((c + 7) & ~7u);
+  const cudaError_t e = gb::launch_affine_expand(affine->mean, affine->inv_std, affine->gamma, affine->beta, s, t, c, stream);
+  if (e != cudaSuccess) return cuda_fail(h, e);
+  scale = s;
+  shift = t;
+  workspace = (char*)workspace + need;
+  workspace_bytes -= need;
+  return GB_OK;
+}
+}  // namespace
+
+int gb_conv_fprop_affine(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* x, const void* w, void* y,
+                         const gb_epilogue* epilogue, const gb_affine_input* affine, void* workspace, size_t workspace_bytes) {
+  if (!h || !x || !w || !y) return GB_ERR_INVALID;
+  int rc = validate_conv(desc);
+  if (rc != GB_OK) return rc;
+  if (desc->groups > 1) return GB_ERR_UNSUPPORTED;
+  const uint16_t *scale = nullptr, *shift = nullptr;
+  rc = expand_affine(h, (cudaStream_t)stream, affine, desc->geo.c, workspace, workspace_bytes, scale, shift);
+  if (rc != GB_OK) return rc;
+  gb_conv_desc shadow;
+  rc = make_filter_shadow(h, (cudaStream_t)stream, desc, shadow, w, workspace, workspace_bytes);
+  if (rc != GB_OK) return rc;
+  Plan plan;
+  rc = plan_conv(h, 0, desc, x, w, y, epilogue, plan, nullptr, scale, shift);
+  if (rc == GB_OK) rc = prepare_plan(h, plan, workspace, workspace_bytes);
+  if (rc != GB_OK) return rc;
+  rc = launch_plan(h, (cudaStream_t)stream, plan);
+  h->last_plan.kernel_launches += 1 + (desc == &shadow ? 1 : 0);
+  return rc;
+}
+
+int gb_conv_wgrad_affine(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* x, void* dw,
+                         const gb_affine_input* affine, void* workspace, size_t workspace_bytes) {
+  if (!h || !dy || !x || !dw) return GB_ERR_INVALID;
+  int rc = validate_conv(desc);
+  if (rc != GB_OK) return rc;
+  if (desc->dtype_w != GB_F32 || desc->w_layout != 0 || desc->groups > 1) return GB_ERR_UNSUPPORTED;
+  const uint16_t *scale = nullptr, *shift = nullptr;
+  rc = expand_affine(h, (cudaStream_t)stream, affine, desc->geo.c, workspace, workspace_bytes, scale, shift);
+  if (rc != GB_OK) return rc;
+  Plan plan;
+  rc = plan_conv(h, 2, desc, dy, x, dw, nullptr, plan, nullptr, scale, shift);
+  if (rc == GB_OK) rc = prepare_plan(h, plan, workspace, workspace_bytes);
+  if (rc != GB_OK) return rc;
+  rc = launch_plan(h, (cudaStream_t)stream, plan);
+  h->last_plan.kernel_launches += 1;
+  return rc;
+}
+
 int gb_conv_dgrad_stats(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* w, void* dx,
                         const gb_dx_stats* stats, void* workspace, size_t workspace_bytes) {
   if (!stats) return gb_conv_dgrad(h, stream, desc, dy, w, dx, workspace, workspace_bytes);
   if (!h || !dy || !w || !dx) return GB_ERR_INVALID;
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
-  if (desc->w_layout != 0) return GB_ERR_UNSUPPORTED;
+  if (desc->w_layout != 0 || desc->groups > 1) return GB_ERR_UNSUPPORTED;
   gb_conv_desc shadow;
   rc = make_filter_shadow(h, (cudaStream_t)stream, desc, shadow, w, workspace, workspace_bytes);
   if (rc != GB_OK) return rc;
@@ -1255,6 +1398,7 @@ int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
   if (desc->dtype_w != GB_F32 || desc->w_layout != 0) return GB_ERR_UNSUPPORTED;   // weight gradients accumulate in f32 (gpu.zig:983)
+  if (desc->groups > 1) return run_grouped(h, (cudaStream_t)stream, 2, desc, dy, x, dw, nullptr, workspace, workspace_bytes);
   const PlanKey key = make_key(3, desc, sizeof(*desc), dy, x, dw, nullptr, workspace, workspace_bytes);
   if (const Plan* cached = cache_find(h, key)) return launch_plan(h, (cudaStream_t)stream, *cached);
   Plan plan;

@@ -355,5 +355,17 @@ __device__ __forceinline__ float round_tf32(float x) {
   return __uint_as_float(r);
 }
 __device__ __forceinline__ float bf16_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+// relu(x * scale + shift) on a pair of bf16 values, each product-and-sum rounded once to bf16: the transform grad applies
+// to an operand that stands for a normalised-and-rectified map (`affinePair`, src/gpu/device.zig:1604-1612).
+__device__ __forceinline__ uint32_t affine_relu_bf16x2(uint32_t x2, uint32_t scale2, uint32_t shift2) {
+  uint32_t out;
+  asm("{\n"
+      "fma.rn.bf16x2 %0, %1, %2, %3;\n"
+      "max.bf16x2 %0, %0, %4;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(x2), "r"(scale2), "r"(shift2), "r"(0u));
+  return out;
+}
 
 }  // namespace gb

@@ -65,17 +65,18 @@ class ConvGeometry:
     dilation: int = 1
     c_step: int = 0
     subsample: int = 1
+    groups: int = 1          # grouped convolution: carried in gb_conv_desc.groups, not in the C geometry struct
 
     def c_struct(self) -> abi.ConvGeometryC:
         return abi.ConvGeometryC(self.n, self.h, self.w, self.c, self.k, self.stride, self.pad, self.out_h, self.out_w,
                                  self.positions, self.c_out, self.dilation, self.c_step, self.subsample)
 
 
-def conv_geometry(n, h, w, c, k, c_out, stride=1, pad=0, dilation=1) -> ConvGeometry:
+def conv_geometry(n, h, w, c, k, c_out, stride=1, pad=0, dilation=1, groups=1) -> ConvGeometry:
     """src/autograd/autograd.zig:99-141 `convGeometry` (forward case) with conv.zig's output-size formula."""
     oh = (h + 2 * pad - dilation * (k - 1) - 1) // stride + 1
     ow = (w + 2 * pad - dilation * (k - 1) - 1) // stride + 1
-    return ConvGeometry(n, h, w, c, k, stride, pad, oh, ow, n * oh * ow, c_out, dilation)
+    return ConvGeometry(n, h, w, c, k, stride, pad, oh, ow, n * oh * ow, c_out, dilation, groups=groups)
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -254,6 +255,7 @@ class Gpu:
     # ---- convolution ------------------------------------------------------------------------------
     def _conv_desc(self, geo: ConvGeometry, x_like, w_like, y_like, math: Optional[int], accumulate: bool, w_layout: int = 0) -> abi.ConvDesc:
         d = abi.ConvDesc()
+        d.groups = getattr(geo, "groups", 1)
         d.geo = geo.c_struct()
         d.dtype_x, d.dtype_w, d.dtype_y = _dtype_code(x_like), _dtype_code(w_like), _dtype_code(y_like)
         if math is None:
@@ -296,6 +298,27 @@ class Gpu:
         ws, n = self._conv_ws(abi.PASS_DGRAD, d)
         rc = self.lib.gb_conv_dgrad(self.handle, self._stream(), C.byref(d), _ptr(dy), _ptr(w), _ptr(dx), _ptr(ws), n)
         abi.check(rc, "gb_conv_dgrad")
+        self.launches += self._count()
+
+    def convForwardAffine(self, x, w, out, geo: ConvGeometry, mean, inv_std, gamma, beta, epilogue: Optional[Epilogue] = None,
+                          math: Optional[int] = None):
+        """`convImplicitForwardAffineStats` (gpu.zig:951-959): the forward pass over relu(batch_norm(x)) that was never
+        written out; the statistics of the result ride in `epilogue.stats_*`."""
+        d = self._conv_desc(geo, x, w, out, math, False)
+        ws, n = self._conv_ws(abi.PASS_FPROP, d)
+        aff = abi.AffineInput(_ptr(mean), _ptr(inv_std), _ptr(gamma), _ptr(beta))
+        rc = self.lib.gb_conv_fprop_affine(self.handle, self._stream(), C.byref(d), _ptr(x), _ptr(w), _ptr(out), self._epilogue(epilogue),
+                                           C.byref(aff), _ptr(ws), n)
+        abi.check(rc, "gb_conv_fprop_affine")
+        self.launches += self._count()
+
+    def convWeightGradAffine(self, dy, x, out, geo: ConvGeometry, mean, inv_std, gamma, beta, math: Optional[int] = None, accumulate: bool = True):
+        """`convImplicitWeightGrad(..., aff)` (gpu.zig:983-1022): the weight gradient over the same virtual input."""
+        d = self._conv_desc(geo, x, out, dy, math, accumulate)
+        ws, n = self._conv_ws(abi.PASS_WGRAD, d)
+        aff = abi.AffineInput(_ptr(mean), _ptr(inv_std), _ptr(gamma), _ptr(beta))
+        rc = self.lib.gb_conv_wgrad_affine(self.handle, self._stream(), C.byref(d), _ptr(dy), _ptr(x), _ptr(out), C.byref(aff), _ptr(ws), n)
+        abi.check(rc, "gb_conv_wgrad_affine")
         self.launches += self._count()
 
     def convInputGradDxStats(self, dy, w, dx, geo: ConvGeometry, x_bn, mean, inv_std, gamma, beta, sums, ordered: bool = False,

@@ -138,6 +138,11 @@ typedef struct {
                               * (src/onnx/gpu.zig:566-574).  With K contiguous per output channel two CTAs can
                               * split even a 64-channel filter bank, so 256 positions share one MMA. */
   uint8_t reserved;
+  uint32_t groups;           /* 0 or 1: dense.  > 1: grouped convolution (src/gpu/math/conv.zig:259-340): input channels
+                              * [g*c/groups, (g+1)*c/groups) feed output channels [g*c_out/groups, ...); w is (k*k*c/groups, c_out)
+                              * with row (ky*k+kx)*(c/groups)+ic.  Runs as one product per group over channel slices of x, w and y,
+                              * the reference's `grouped_implicit` path (src/autograd/autograd.zig:150-155, 1041, 1129); plain
+                              * layers only (w_layout 0, no statistics). */
 } gb_conv_desc;
 
 /* ---- lifetime --------------------------------------------------------------------------------- */
@@ -202,6 +207,19 @@ int gb_static_last_status(void* stream, uint32_t* device_status);
 int gb_conv_workspace(const gb_handle* h, int pass /*0 fprop, 1 dgrad, 2 wgrad*/, const gb_conv_desc* desc, size_t* bytes);
 int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* x, const void* w, void* y,
                   const gb_epilogue* epilogue, void* workspace, size_t workspace_bytes);
+/* Forward pass over an input that stands for a batch norm + ReLU of the stored map x that was never written out:
+ * every in-bounds tap reads relu(s * x + t) with s = gamma * inv_std and t = beta - mean * s per input channel, both
+ * rounded to bf16 and applied as one bf16 fused multiply-add (`affineExpand` / `affinePair`, src/gpu/device.zig:1774-1805,
+ * 1604-1612); padding taps stay exactly zero.  Replaces `Gpu.convImplicitForwardAffineStats` (src/gpu/gpu.zig:951-959;
+ * the statistics part is `epilogue->bn_stats`).  bf16 activations and bf16 math only.  The transform is applied by the
+ * gather warps while they build the operand tile -- a TMA copy zero-fills padding, and relu(s * 0 + t) is not zero -- so
+ * this path runs at the gathered rate, several times slower than gb_conv_fprop; the first 4 * c bytes of the workspace
+ * (rounded up to 256) hold the expanded s and t. */
+typedef struct {
+  const float *mean, *inv_std, *gamma, *beta;   /* f32[c] each: the norm that the input stands for */
+} gb_affine_input;
+int gb_conv_fprop_affine(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* x, const void* w, void* y,
+                         const gb_epilogue* epilogue, const gb_affine_input* affine, void* workspace, size_t workspace_bytes);
 /* Input gradient: dx (+)= conv_transpose(dy, w).  Replaces `convImplicitForward` / `convF32Forward` on
  * the reversed geometry with `packRotatedWeights` / `rotateWeightsF32` (gpu.zig:754-772, 856-866) and
  * the `*Subsampled` kernels for strided layers (device.zig:1921-1925). */
@@ -216,6 +234,10 @@ int gb_conv_dgrad_stats(gb_handle* h, void* stream, const gb_conv_desc* desc, co
  * (:775-787, :828-866).  Partials of the split over positions are combined in order. */
 int gb_conv_wgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* x, void* dw,
                   void* workspace, size_t workspace_bytes);
+/* The weight gradient over the same kind of virtual input (the `...Affine` weight-gradient kernels,
+ * src/gpu/device.zig:1756-1766; `convImplicitWeightGrad(..., aff)`, src/gpu/gpu.zig:983-1022). */
+int gb_conv_wgrad_affine(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* x, void* dw,
+                         const gb_affine_input* affine, void* workspace, size_t workspace_bytes);
 
 /* ---- prepared weights -------------------------------------------------------------------------- */
 /* grad keeps f32 master weights and converts them on EVERY use: `packMatrix` before each forward product and

@@ -521,3 +521,103 @@ def test_input_gradient_epilogue_accumulates_batch_norm_backward_sums(gpu, n, si
         det.append(s2.cpu().numpy())
     assert np.array_equal(det[0], det[1])
     assert np.all(np.abs(det[0] - got) <= 0.05 + 1e-4 * np.abs(got))
+
+
+def _virtual_map(x_bf16, mean, inv_std, gamma, beta):
+    """relu(s * x + t) with s = bf16(gamma * inv_std), t = bf16(beta - mean * (gamma * inv_std)) and ONE rounding of the
+    product-and-sum to bf16 (`affineExpand` / `affinePair`, src/gpu/device.zig:1774-1783, 1604-1612), evaluated in f64."""
+    from oracle import binding as orc
+
+    s32 = (gamma * inv_std).astype(np.float32)
+    s = orc.bf16_round(s32)
+    t = orc.bf16_round((beta - (mean * s32).astype(np.float32)).astype(np.float32))
+    exact = x_bf16.astype(np.float64) * s.astype(np.float64) + t.astype(np.float64)
+    return np.maximum(orc.bf16_round(exact.astype(np.float32)), np.float32(0))
+
+
+@pytest.mark.parametrize("case", [(3, 16, 16, 64, 3, 64, 1, 1, 1), (2, 8, 8, 128, 3, 96, 1, 1, 1), (2, 9, 9, 64, 3, 32, 2, 1, 1)])
+def test_forward_and_weight_gradient_over_a_virtual_normalised_input(gpu, case):
+    """`convImplicitForwardAffineStats` and the `Affine` weight gradient (src/gpu/gpu.zig:951-959, 983-1022): a layer whose
+    input is relu(batch_norm(x)) that was never written out must give what the same layer gives on the written-out map
+    -- padding taps included, where relu(s * 0 + t) would be wrong -- and the statistics of its result ride along."""
+    import torch
+    from grad_b200 import Epilogue
+    from oracle import binding as orc
+
+    d, x, w, dy = _inputs(case, 1300)
+    geo = _geo(case)
+    rng = np.random.default_rng(1301)
+    mean = (rng.standard_normal(d.c, dtype=np.float32) * 0.3).astype(np.float32)
+    inv_std = (0.5 + rng.random(d.c, dtype=np.float32)).astype(np.float32)
+    gamma = (0.5 + rng.random(d.c, dtype=np.float32)).astype(np.float32)
+    beta = (0.3 + rng.standard_normal(d.c, dtype=np.float32) * 0.2).astype(np.float32)      # mostly positive: padding would show
+    xb, wb, dyb = orc.bf16_round(x), orc.bf16_round(w), orc.bf16_round(dy)
+    z = _virtual_map(xb, mean, inv_std, gamma, beta)
+    want_y = orc.conv_forward(z, wb, d, orc.host_threads())
+    want_dw = orc.conv_weight_grad(z, dyb, d, orc.host_threads())
+    norm = tuple(to_dev(v) for v in (mean, inv_std, gamma, beta))
+    tx, tw, tdy = to_dev(xb, True), to_dev(wb, True), to_dev(dyb, True)
+    y = torch.empty((d.n, d.out_h, d.out_w, d.c_out), dtype=torch.bfloat16, device="cuda")
+    sums = torch.zeros(2 * d.c_out, device="cuda")
+    shift = to_dev(np.zeros(d.c_out, np.float32))
+    gpu.convForwardAffine(tx, tw, y, geo, *norm, epilogue=Epilogue(stats_shift=shift, stats_sums=sums))
+    assert gpu.last_plan()["a_kind"] == 5                          # gathered: the transform happens while the tile is built
+    y_written = torch.empty_like(y)
+    gpu.convForward(to_dev(z, True), tw, y_written, geo)           # the same layer on the written-out map
+    gw = torch.zeros((d.taps, d.c_out), device="cuda")
+    gpu.convWeightGradAffine(tdy, tx, gw, geo, *norm)
+    torch.cuda.synchronize()
+    assert rel_fro(to_host(y), want_y) <= 5e-3, rel_fro(to_host(y), want_y)
+    assert rel_fro(to_host(y), to_host(y_written)) <= 5e-3
+    assert rel_fro(to_host(gw), want_dw) <= 1e-3, rel_fro(to_host(gw), want_dw)
+    stored = y.double().cpu().numpy().reshape(-1, d.c_out)
+    got = sums.cpu().numpy()
+    assert np.all(np.abs(got[:d.c_out] - stored.sum(0)) <= 0.05 + 1e-5 * np.abs(stored.sum(0)))
+    assert np.all(np.abs(got[d.c_out:] - (stored * stored).sum(0)) <= 0.05 + 1e-4 * (stored * stored).sum(0))
+
+
+def test_grouped_convolution_known_answer(gpu):
+    """tests/runtime.zig:62-84: 2 groups of one channel, 2x2 filters on a 3x3 image -> [6, 8, 12, 14, 2, 2, 2, 2] (NCHW)."""
+    import torch
+    from grad_b200 import conv_geometry
+
+    x = np.array([1, 2, 3, 4, 5, 6, 7, 8, 9, 1, 0, 1, 0, 1, 0, 1, 0, 1], np.float32).reshape(1, 2, 3, 3).transpose(0, 2, 3, 1)
+    w_oihw = np.array([1, 0, 0, 1, 1, 1, 1, 1], np.float32).reshape(2, 1, 2, 2)
+    w = np.ascontiguousarray(w_oihw.transpose(2, 3, 1, 0).reshape(4, 2))        # (k*k*c/groups, c_out), row (ky*k+kx)*cg+ic
+    geo = conv_geometry(1, 3, 3, 2, 2, 2, groups=2)
+    y = torch.empty((1, 2, 2, 2), device="cuda")
+    gpu.convForward(to_dev(x), to_dev(w), y, geo, math=0)
+    torch.cuda.synchronize()
+    assert to_host(y).transpose(0, 3, 1, 2).ravel().tolist() == [6, 8, 12, 14, 2, 2, 2, 2]
+
+
+@pytest.mark.parametrize("case,groups", [((2, 8, 8, 128, 3, 128, 1, 1, 1), 2), ((2, 8, 8, 64, 3, 96, 1, 1, 1), 4), ((2, 9, 9, 64, 3, 64, 2, 1, 1), 2),
+                                         ((3, 6, 6, 12, 3, 8, 1, 1, 1), 4), ((2, 8, 8, 64, 1, 64, 1, 0, 1), 64)])
+@pytest.mark.parametrize("math,tol,half", [(0, TOL_F32, False), (1, TOL_TF32, False), (2, TOL_BF16, True)])
+def test_grouped_convolution_all_passes(gpu, case, groups, math, tol, half):
+    """`groups > 1` through the ABI (src/autograd/autograd.zig:150-155, per element: src/gpu/math/conv.zig:259-340): one product
+    per group over channel slices of x, w and y, against the oracle's grouped convolution; the last case is depthwise."""
+    import torch
+    from grad_b200 import conv_geometry
+    from oracle.binding import ConvDims
+    from oracle import binding as orc
+
+    n, h, w_, c, k, c_out, s, p, dil = case
+    d = ConvDims(n=n, h=h, w=w_, c=c, k=k, stride=s, pad=p, dilation=dil, groups=groups, c_out=c_out)
+    geo = conv_geometry(n, h, w_, c, k, c_out, s, p, dil, groups=groups)
+    cg = c // groups
+    x = seeded(1400, n, h, w_, c)
+    w = (seeded(1401, k * k * cg, c_out) * np.float32(np.sqrt(2.0 / (k * k * cg)))).astype(np.float32)
+    dy = seeded(1402, n, d.out_h, d.out_w, c_out)
+    want_y, want_dx, want_dw = orc.conv_forward(x, w, d), orc.conv_input_grad(dy, w, d), orc.conv_weight_grad(x, dy, d)
+    act = torch.bfloat16 if half else torch.float32
+    y = torch.full((n, d.out_h, d.out_w, c_out), 5.0, dtype=act, device="cuda")
+    gx = torch.zeros((n, h, w_, c), dtype=act, device="cuda")
+    gw = torch.zeros((k * k * cg, c_out), device="cuda")
+    gpu.convForward(to_dev(x, half), to_dev(w), y, geo, math=math)
+    assert gpu.last_plan()["kernel_launches"] >= groups
+    gpu.convInputGrad(to_dev(dy, half), to_dev(w), gx, geo, accumulate=True, math=math)
+    gpu.convWeightGrad(to_dev(dy, half), to_dev(x, half), gw, geo, math=math)
+    torch.cuda.synchronize()
+    errs = (rel_fro(to_host(y), want_y), rel_fro(to_host(gx), want_dx), rel_fro(to_host(gw), want_dw))
+    assert max(errs) <= tol, (case, groups, math, errs)
