@@ -126,7 +126,8 @@ _lib = None
 
 
 def library_path() -> str:
-    return os.path.join(HERE, "libgradb200.so")
+    """The library next to this file, or the one GB_LIBRARY names (a build with other compile-time options)."""
+    return os.environ.get("GB_LIBRARY") or os.path.join(HERE, "libgradb200.so")
 
 
 def library() -> C.CDLL:

@@ -869,7 +869,7 @@ __device__ __forceinline__ void stage_bias(const GemmParams& p, float* sbias, ui
 // back to the MMA issuer; it is called as soon as this warp's last TMEM read has landed in registers, before
 // that chunk's arithmetic and stores: with short-K tiles (a convolution layer) the time from "accumulator
 // full" to "accumulator free" is what paces the kernel.
-template <class Release>
+template <bool kStats, class Release>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, uint32_t ncols, uint32_t batch, uint32_t split,
                                               uint32_t row, uint32_t col_base, bool wide, uint32_t lane,
                                               uint32_t first, uint32_t step, const CUtensorMap* tmap_c, uint8_t* store_stage, const float* sbias,
@@ -897,7 +897,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
       {
         const uint32_t col0 = col_base + tile_col(c);
         if (col0 + 32 <= p.n && row - lane < p.m) {
-          if (p.stats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_a, store_stage, sbias + 32 * i, sstat, i, batch, row, col0, lane);
+          if constexpr (kStats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_a, store_stage, sbias + 32 * i, sstat, i, batch, row, col0, lane);
           else epilogue_chunk_tma(p, tmap_c, acc_a, store_stage, sbias + 32 * i, batch, split, row, col0, lane);
         } else epilogue_chunk_copy(p, acc_a, batch, split, row, col0, p.bias ? sbias[32 * i + lane] : 0.0f);
       }
@@ -907,7 +907,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
         else release();
         const uint32_t col0 = col_base + tile_col(c + step);
         if (col0 + 32 <= p.n && row - lane < p.m) {
-          if (p.stats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), sstat, i + 1, batch, row, col0, lane);
+          if constexpr (kStats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), sstat, i + 1, batch, row, col0, lane);
           else epilogue_chunk_tma(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), batch, split, row, col0, lane);
         } else epilogue_chunk_copy(p, acc_b, batch, split, row, col0, p.bias ? sbias[32 * (i + 1) + lane] : 0.0f);
       }
@@ -1020,6 +1020,10 @@ __device__ __forceinline__ void mma_stage_more(const MmaSetup& s, uint32_t tmem_
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------------
+// kStats = the instantiation whose epilogue also sums batch-norm statistics.  It is a kernel of its own because the mere
+// presence of the (out-of-line) statistics call in the epilogue cost every other plan registers and spills: convolution
+// layers ran 7-20 % slower with it compiled in, whether or not they asked for statistics.
+template <bool kStats>
 __global__ void __launch_bounds__(448, 1)
 gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c) {
@@ -1167,7 +1171,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     // statistics plans have one column tile, so a warp's shift values are staged once (chunk i's 32 values at sstat[32 * i])
     // and its running sums sit behind them
     float* sstat = (float*)(epi_smem + kStoreSmemBytes + (warp - 2) * kStatBytesPerWarp);
-    if (p.stats) {
+    if constexpr (kStats) {
       for (uint32_t i = 0; i < 4; ++i) {
         const uint32_t col = ((warp - 2) >> 2) * 32 + i * 32 * p.epi_groups + lane;
         sstat[32 * i + lane] = col < p.n ? p.stat_shift[col] : 0.0f;
@@ -1193,7 +1197,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       tc_fence_after_sync();
       const uint32_t row = work.m_tile * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
-      epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane,
+      epilogue_tile<kStats>(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane,
                                                ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, sstat, [&] {
                                                  tc_fence_before_sync();
                                                  __syncwarp();
@@ -1201,7 +1205,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
                                                });
       if ((buf ^= 1) == 0) buf_phase ^= 1;
     }
-    if (p.stats && ok) flush_stats(p, sstat, warp - 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
+    if constexpr (kStats) if (ok) flush_stats(p, sstat, warp - 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
     if (tma_out && lane == 0) bulk_wait_all();   // the staging block must outlive its last store
   } else {
     // ===== gather warps =====
@@ -1248,6 +1252,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 // Both CTAs run their own TMA producer (own tiles only, bytes counted on the leader's "full" barrier)
 // and their own epilogue (own 128 accumulator rows); only the leader issues MMAs and commits, once per
 // CTA, to the "empty" and "accumulator full" barriers of both.
+template <bool kStats>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c) {
@@ -1396,7 +1401,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     if (tma_out && warp == 2 && lane == 0) prefetch_tmap(&tmap_c);
     uint32_t bias_tile = 0xFFFFFFFFu;   // the column tile whose bias values sit in shared memory
     float* sstat = (float*)(epi_smem + kStoreSmemBytes + (warp - 2) * kStatBytesPerWarp);   // see the single-CTA kernel
-    if (p.stats) {
+    if constexpr (kStats) {
       for (uint32_t i = 0; i < 4; ++i) {
         const uint32_t col = ((warp - 2) >> 2) * 32 + i * 32 * p.epi_groups + lane;
         sstat[32 * i + lane] = col < p.n ? p.stat_shift[col] : 0.0f;
@@ -1422,7 +1427,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       tc_fence_after_sync();
       const uint32_t row = work.m_tile * 2 * kBM + rank * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * (p.bn / halves);
-      epilogue_tile(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane,
+      epilogue_tile<kStats>(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane,
                                                ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, sstat, [&] {
                                                  tc_fence_before_sync();
                                                  __syncwarp();
@@ -1430,7 +1435,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
                                                });
       if (++buf == bufs) { buf = 0; buf_phase ^= 1; }
     }
-    if (p.stats && ok) flush_stats(p, sstat, warp - 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
+    if constexpr (kStats) if (ok) flush_stats(p, sstat, warp - 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
     if (tma_out && lane == 0) bulk_wait_all();   // the staging block must outlive its last store
   }
 
@@ -1577,7 +1582,7 @@ static uint32_t max_resident_pairs(size_t smem_bytes, int sm_count) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int clusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&clusters, gemm_sm100_pair_kernel, &cfg) != cudaSuccess || clusters <= 0) {
+  if (cudaOccupancyMaxActiveClusters(&clusters, gemm_sm100_pair_kernel<false>, &cfg) != cudaSuccess || clusters <= 0) {
     cudaGetLastError();
     clusters = sm_count / 2 > 8 ? sm_count / 2 - 8 : 1;   // conservative guess when the query is unavailable
   }
@@ -1591,9 +1596,13 @@ static uint32_t max_resident_pairs(size_t smem_bytes, int sm_count) {
 }
 
 cudaError_t gemm_sm100_configure() {
-  cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(gemm_sm100_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_sm100_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_sm100_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  return e;
 }
 
 // CTAs the launch below uses (what the statistics partial buffer is sized by).
@@ -1613,11 +1622,14 @@ cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, co
     // co-resident 2-CTA clusters can be below sm_count / 2 (SMs are paired within a GPC), and a cluster
     // left waiting would run its whole share of tiles after the others have finished.
     const uint32_t pairs = std::min<uint32_t>(total_work, max_resident_pairs(gemm_smem_bytes(p), sm_count));
-    return launch_overlapped(gemm_sm100_pair_kernel, dim3(2 * pairs), dim3(64 + 128 * p.epi_groups), gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
+    return launch_overlapped(p.stats ? gemm_sm100_pair_kernel<true> : gemm_sm100_pair_kernel<false>, dim3(2 * pairs), dim3(64 + 128 * p.epi_groups),
+                             gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
   }
   const bool gather = p.a_kind == kGather || p.b_kind == kGather;
   const uint32_t grid = total_work < (uint32_t)sm_count ? total_work : (uint32_t)sm_count;
-  return launch_overlapped(gemm_sm100_kernel, dim3(grid), dim3(64 + 128 * p.epi_groups + (gather ? 128 : 0)), gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
+  auto kernel = gather ? (p.stats ? gemm_sm100_kernel<true> : gemm_sm100_kernel<false>)
+                       : (p.stats ? gemm_sm100_kernel<true> : gemm_sm100_kernel<false>);
+  return launch_overlapped(kernel, dim3(grid), dim3(64 + 128 * p.epi_groups + (gather ? 128 : 0)), gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
 }
 
 cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream) {
