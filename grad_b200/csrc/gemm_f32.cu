@@ -73,6 +73,8 @@ __device__ __forceinline__ TileIndex f32_tile_index(const GemmParams& p) {
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmParams p) {
   __shared__ float As[kTK][kTM + 4];
   __shared__ float Bs[kTK][kTN + 4];
+  grid_launch_dependents();   // launched with programmatic stream serialization, like the tensor kernels
+  grid_dependency_wait();
   const uint32_t tid = threadIdx.x;
   const TileIndex tile = f32_tile_index<kTM, kTN>(p);
   const uint32_t split = tile.split, batch = tile.batch;
@@ -149,6 +151,8 @@ __global__ void __launch_bounds__(256) gemm_f32_dense_kernel(const GemmParams p)
   constexpr int RM = TM / 16, RN = TN / 16, EA = TM * 16 / 256, EB = TN * 16 / 256;
   __shared__ __align__(16) float As[kTK][TM + 4];
   __shared__ __align__(16) float Bs[kTK][TN + 4];
+  grid_launch_dependents();
+  grid_dependency_wait();
   const uint32_t tid = threadIdx.x;
   const TileIndex tile = f32_tile_index<TM, TN>(p);
   const uint32_t split = tile.split, batch = tile.batch;
@@ -266,18 +270,16 @@ cudaError_t launch_gemm_f32(const GemmParams& p, cudaStream_t stream) {
     // 128 x 128 tiles once they fill the machine, 64 x 64 below that (more blocks, less work per block)
     const uint32_t big = f32_grid_blocks(p, 128, 128);
     if (big >= 148) {
-      gemm_f32_dense_kernel<128, 128><<<big, 256, 0, stream>>>(p);
+      return launch_overlapped(gemm_f32_dense_kernel<128, 128>, dim3(big), dim3(256), 0, stream, p);
     } else {
       const uint32_t small = f32_grid_blocks(p, 64, 64);
       if (small == 0) return cudaErrorInvalidConfiguration;
-      gemm_f32_dense_kernel<64, 64><<<small, 256, 0, stream>>>(p);
+      return launch_overlapped(gemm_f32_dense_kernel<64, 64>, dim3(small), dim3(256), 0, stream, p);
     }
-    return cudaGetLastError();
   }
   const uint32_t blocks = f32_grid_blocks(p, kTM, kTN);
   if (blocks == 0) return cudaErrorInvalidConfiguration;
-  gemm_f32_kernel<<<blocks, 256, 0, stream>>>(p);
-  return cudaGetLastError();
+  return launch_overlapped(gemm_f32_kernel, dim3(blocks), dim3(256), 0, stream, p);
 }
 
 }  // namespace gb

@@ -1067,9 +1067,11 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   // Everything above touched only this CTA's shared and tensor memory, so it may overlap the tail of the previous
-  // kernel in the stream; from here on global memory is read and written.
+  // kernel in the stream.  Each role goes on with what needs no global memory -- the producer's box set-up and first
+  // tile decode, the issuer's descriptors -- and waits for the stream's earlier work only right before its first
+  // global access: that set-up is a first walk through cold instructions (~2500 cycles) that a product of one or two
+  // tiles cannot hide otherwise.  The MMA issuer touches shared and tensor memory only and never waits.
   grid_launch_dependents();
-  grid_dependency_wait();
   const uint32_t tmem_base = hdr->tmem_base;
   const uint32_t epl = p.tf32 ? 32u : 64u;
 
@@ -1087,6 +1089,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       const bool box_is_b = lane >= boxes_of(p.a_kind, kBM, epl);
       uint32_t ready = 1;   // the first pass over the ring finds every stage free
       uint32_t issued = 0;
+      bool waited = false;
       for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
         const Work work = decode_work(p, w);
         if (work.empty) continue;
@@ -1095,6 +1098,10 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           cur_class = work.batch;
         }
         box_start(p, p.n_classes ? p.cls[work.batch].walk : p.walk, box, box_kind, box_index, work, work.m_tile * kBM, work.n_tile * p.bn, box_is_b);
+        if (!waited) {   // the first copy is this warp's first global access
+          grid_dependency_wait();
+          waited = true;
+        }
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_peeked(&hdr->empty[stage], phase ^ 1, ready, abort_flag, kStatusProducerTimeout))) break;
           uint32_t next_stage = stage + 1, next_phase = phase;
@@ -1159,6 +1166,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     }
   } else if (warp < 2 + 4 * p.epi_groups) {
     // ===== epilogue =====
+    grid_dependency_wait();   // bias, old C and residual are read and C is written from here on
     const uint32_t quarter = warp & 3;
     uint32_t buf = 0, buf_phase = 0;
     bool ok = true;
@@ -1209,6 +1217,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     if (tma_out && lane == 0) bulk_wait_all();   // the staging block must outlive its last store
   } else {
     // ===== gather warps =====
+    grid_dependency_wait();
     const uint32_t tid = threadIdx.x - 64 - epi_threads;
     uint32_t stage = 0, phase = 0;
     bool ok = true;
@@ -1301,8 +1310,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
   __syncthreads();
   cluster_sync_all();                   // the partner's barriers are initialised before anyone signals them
   tc_fence_after_sync();
-  grid_launch_dependents();             // see the single-CTA kernel
-  grid_dependency_wait();
+  grid_launch_dependents();             // see the single-CTA kernel: each role waits before its first global access
   const uint32_t tmem_base = hdr->tmem_base;
   const uint32_t epl = p.tf32 ? 32u : 64u;
 
@@ -1323,6 +1331,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
       uint32_t cur_class = 0xFFFFFFFFu;
       const bool box_is_b = lane >= boxes_of(p.a_kind, kBM, epl);
       uint32_t ready = 1;   // the first pass over the ring finds every stage free
+      bool waited = false;
       for (uint32_t w = pair; ok && w < total_work; w += pairs) {
         const Work work = decode_work(p, w);
         if (work.empty) continue;
@@ -1332,6 +1341,10 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
         }
         box_start(p, p.n_classes ? p.cls[work.batch].walk : p.walk, box, box_kind, box_index, work, work.m_tile * 2 * kBM + rank * kBM,
                   work.n_tile * p.bn + rank * b_lines, box_is_b);
+        if (!waited) {
+          grid_dependency_wait();
+          waited = true;
+        }
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_peeked(&hdr->empty[stage], phase ^ 1, ready, abort_flag, kStatusProducerTimeout))) break;
           uint32_t next_stage = stage + 1, next_phase = phase;
@@ -1391,6 +1404,7 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     }
   } else {
     // ===== epilogue (both CTAs, own 128 rows) =====
+    grid_dependency_wait();
     const uint32_t quarter = warp & 3;
     uint32_t buf = 0, buf_phase = 0;
     bool ok = true;
