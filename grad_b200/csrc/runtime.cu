@@ -231,9 +231,20 @@ double tile_cost(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint
   return waves * per_tile + 3000.0;
 }
 
-// Tile width and K split for an m x n x k_blocks product on `sms` multiprocessors: the width with the
-// lowest estimated time; when it leaves SMs idle, K is split so that about one work item per SM exists,
-// each at least sixteen K blocks long (the role of `splits` in src/gpu/gpu.zig:664, 1000, 1041).
+// K split a tile width would get: when its tiles leave SMs idle, about one work item per SM, each at least sixteen K
+// blocks long (the role of `splits` in src/gpu/gpu.zig:664, 1000, 1041).  A split costs a second launch and a pass over
+// the partials.
+uint32_t split_for_width(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint32_t bn, uint32_t sms, bool allow_split) {
+  const uint32_t tiles = ceil_div(m, 128) * batch * ceil_div(n, bn);
+  if (!allow_split || tiles == 0 || tiles * 2 > sms || k_blocks < 32) return 1;
+  return std::max(1u, std::min(sms / tiles, k_blocks / 16));
+}
+
+// Tile width and K split for an m x n x k_blocks product on `sms` multiprocessors: the (width, split) pair with the
+// lowest estimated time.  The estimate of a split product is that of its longest part plus the reduce launch and its
+// pass over the partial tiles; judged by the unsplit time alone, a product with few tiles and a long K (a weight
+// gradient: 2304 x 256 x 8192) took the narrowest tile -- most tiles, shortest wave -- and then ran issue-bound 64-wide
+// MMAs in every part.
 void pick_tiling(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint32_t min_bn, uint32_t sms, bool allow_split,
                  uint32_t& bn, uint32_t& splits, uint32_t& kbps) {
   const uint32_t n_cap = std::max(min_bn, ceil_div(n, min_bn) * min_bn);   // n rounded up to the narrowest tile
@@ -241,15 +252,14 @@ void pick_tiling(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint
   double best = 0.0;
   for (uint32_t cand : {256u, 128u, 64u, 32u}) {
     if (cand < min_bn || cand > n_cap) continue;
-    const double cost = tile_cost(m, n, batch, k_blocks, cand, false, sms);
+    const uint32_t parts = split_for_width(m, n, batch, k_blocks, cand, sms, allow_split);
+    double cost = tile_cost(m, n, batch * parts, ceil_div(k_blocks, parts), cand, false, sms);
+    if (parts > 1) cost += 4000.0 + (double)m * n * batch * parts * 4.0 / 2000.0;   // reduce launch + its read of the partials
     if (bn == 0 || cost < best) { bn = cand; best = cost; }
   }
   if (bn == 0) bn = min_bn;
   if (knobs().force_bn >= (int)min_bn && knobs().force_bn <= 256 && knobs().force_bn % 32 == 0) bn = (uint32_t)knobs().force_bn;
-  const uint32_t tiles = ceil_div(m, 128) * batch * ceil_div(n, bn);
-  splits = 1;
-  // A split costs a second launch (~5 us) and a pass over the partials: only worth it when every part keeps >= 16 K blocks.
-  if (allow_split && tiles > 0 && tiles * 2 <= sms && k_blocks >= 32) splits = std::max(1u, std::min(sms / tiles, k_blocks / 16));
+  splits = split_for_width(m, n, batch, k_blocks, bn, sms, allow_split);
   if (allow_split && knobs().force_splits > 0) splits = std::min<uint32_t>((uint32_t)knobs().force_splits, std::max(1u, k_blocks));
   kbps = std::max(1u, ceil_div(k_blocks, splits));
   splits = std::max(1u, ceil_div(k_blocks, kbps));
@@ -881,6 +891,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
           patch_box(2 * epl, g.out_h, g.out_w, bw2, bh2, bn2) &&
           (p.patch_view ? nhwc_view_tma(&a2, other, smem_bf16, d->dtype_x, g, epl, bw2, bh2, bn2, true)
                         : nhwc_tma(&a2, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, bw2, bh2, bn2, true, g.stride)) &&
+          (227 * 1024 - 2048 - gb::kStoreSmemBytes) / (2 * (128 * 128 + p.bn * 128)) >= 3 &&   // two-block stages only while three of them fit
           dense_tma(&b2, ob, smem_bf16, 1, p.bn, epl, 2)) {
         plan.tmap_a = a2; plan.tmap_b = b2;
         p.box_w = bw2; p.box_h = bh2; p.box_n = bn2;
