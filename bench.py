@@ -294,7 +294,7 @@ def resnet_inference(gpu, rank, world, dist, torch, cpu_baseline):
         ms_eager = timed(lambda: ex.run_device({"input": x}), iters)
         per_run = (ex.stats.launches - launches0) // (iters + 3)
         out[f"batch_{batch}"] = {"value": round(batch / ms * 1e3, 1), "ms": round(ms, 4), "tflops": round(batch * 1.482e9 / ms / 1e9, 1),
-                                 "frac_of_nominal_2250": round(batch * 1.482e9 / ms / 1e9 / NOMINAL_BF16, 4),
+                                 "frac_of_nominal_2250": round(batch * 1.482e9 / ms / 1e9 / (NOMINAL_BF16 * world), 4),
                                  "e2e": round(batch / ms_e2e * 1e3, 1), "eager": round(batch / ms_eager * 1e3, 1),
                                  "launches_per_run": per_run, "per_gpu_batch": hi - lo}
     if cpu_baseline and rank == 0:

@@ -15,7 +15,7 @@
 //               byte block staged in shared memory and written by a TMA store (per-lane 16-byte stores for
 //               transposed, ragged, mapped or split-K results).  Two accumulator buffers let the epilogue of
 //               tile i overlap the mainloop of tile i+1.
-//   warps 10-13 (only when an operand cannot be fetched by TMA) gather warps fill the stage with plain
+//   warps 10-11 (only when an operand cannot be fetched by TMA) gather warps fill the stage with plain
 //               loads: any pitch, f32 -> bf16 conversion on the fly, implicit im2col of NHWC activations
 //               for any stride / dilation / padding / channel count.
 //
@@ -248,7 +248,7 @@ __device__ __forceinline__ void gather_tile(const GemmParams& p, const GatherDes
                                             uint32_t mn0, uint32_t k0, uint32_t batch, uint32_t tid) {
   const uint32_t epl = p.tf32 ? 32u : 64u;
   const uint64_t batch_off = (uint64_t)batch * d.batch_stride;
-  for (uint32_t l = tid; l < lines_in_tile; l += 128) {
+  for (uint32_t l = tid; l < lines_in_tile; l += kGatherThreads) {
     if (d.mn_major) {
       const uint32_t block = l / epl, kline = l - block * epl;
       gather_line(p, d, tile, l, k0 + kline, mn0 + block * epl, batch_off);
@@ -1024,7 +1024,7 @@ __device__ __forceinline__ void mma_stage_more(const MmaSetup& s, uint32_t tmem_
 // presence of the (out-of-line) statistics call in the epilogue cost every other plan registers and spills: convolution
 // layers ran 7-20 % slower with it compiled in, whether or not they asked for statistics.
 template <bool kStats>
-__global__ void __launch_bounds__(448, 1)
+__global__ void __launch_bounds__(64 + 256 + kGatherThreads, 1)
 gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c) {
   extern __shared__ uint8_t smem_raw[];
@@ -1044,7 +1044,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const uint32_t tmem_cols = p.bn * 2 <= 32 ? 32u : (p.bn * 2 <= 64 ? 64u : (p.bn * 2 <= 128 ? 128u : (p.bn * 2 <= 256 ? 256u : 512u)));
 
   if (threadIdx.x == 0) {
-    const uint32_t full_count = 1 + (has_gather ? 4 : 0);
+    const uint32_t full_count = 1 + (has_gather ? kGatherThreads / 32 : 0);
     for (uint32_t s = 0; s < p.stages; ++s) {
       mbar_init(&hdr->full[s], full_count);
       mbar_init(&hdr->empty[s], 1);
@@ -1611,8 +1611,6 @@ static uint32_t max_resident_pairs(size_t smem_bytes, int sm_count) {
 
 cudaError_t gemm_sm100_configure() {
   cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_sm100_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_sm100_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -1641,9 +1639,8 @@ cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, co
   }
   const bool gather = p.a_kind == kGather || p.b_kind == kGather;
   const uint32_t grid = total_work < (uint32_t)sm_count ? total_work : (uint32_t)sm_count;
-  auto kernel = gather ? (p.stats ? gemm_sm100_kernel<true> : gemm_sm100_kernel<false>)
-                       : (p.stats ? gemm_sm100_kernel<true> : gemm_sm100_kernel<false>);
-  return launch_overlapped(kernel, dim3(grid), dim3(64 + 128 * p.epi_groups + (gather ? 128 : 0)), gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
+  auto kernel = p.stats ? gemm_sm100_kernel<true> : gemm_sm100_kernel<false>;
+  return launch_overlapped(kernel, dim3(grid), dim3(64 + 128 * p.epi_groups + (gather ? kGatherThreads : 0)), gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
 }
 
 cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream) {

@@ -142,6 +142,10 @@ struct GemmParams {
   uint32_t test_drop_kblock;   // fault injection on the host's request: the producer leaves out this K block's copies (+1; 0 = off)
 };
 
+// Threads of the gather warps (single-CTA kernel, plans with a gathered operand).  Two warps: with four the CTA had 14
+// warps, four of them on one scheduler, which caps every thread at 128 registers and spilled the epilogue of EVERY
+// plan of that kernel; 12 warps leave 168.
+constexpr uint32_t kGatherThreads = 64;
 // Shared memory the epilogue warps own when p.tma_store is set: per warp a 2 KB staging block (32 rows x 64
 // bytes, 64-byte swizzle) and 1 KB of bias values (eight 32-column chunks).
 constexpr uint32_t kStoreStageBytesPerWarp = 2048;
