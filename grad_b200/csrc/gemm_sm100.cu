@@ -1043,7 +1043,14 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
   const uint32_t tmem_cols = p.bn * 2 <= 32 ? 32u : (p.bn * 2 <= 64 ? 64u : (p.bn * 2 <= 128 ? 128u : (p.bn * 2 <= 256 ? 256u : 512u)));
 
-  if (threadIdx.x == 0) {
+  // The prologue is spread over three warps so that none of it queues behind another part: warp 2 initialises the
+  // barriers, warp 1 allocates tensor memory, and the producer warp meanwhile works out which box each lane owns (a
+  // first walk through ~150 cold instructions that used to follow the barrier set-up in the same thread).
+  const uint32_t epl = p.tf32 ? 32u : 64u;
+  BoxLane box;
+  uint32_t box_kind = 0, box_index = 0;
+  if (warp == 0) box_setup(p, p.walk, box, lane, &tmap_a, &tmap_b, p.bn, box_kind, box_index);
+  if (threadIdx.x == 64) {
     const uint32_t full_count = 1 + (has_gather ? kGatherThreads / 32 : 0);
     for (uint32_t s = 0; s < p.stages; ++s) {
       mbar_init(&hdr->full[s], full_count);
@@ -1073,7 +1080,6 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   // tiles cannot hide otherwise.  The MMA issuer touches shared and tensor memory only and never waits.
   grid_launch_dependents();
   const uint32_t tmem_base = hdr->tmem_base;
-  const uint32_t epl = p.tf32 ? 32u : 64u;
 
   if (warp == 0) {
     // ===== TMA producer: one lane per box =====
@@ -1082,9 +1088,6 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     if (lane < max(n_boxes, 1u)) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      BoxLane box;
-      uint32_t box_kind, box_index;
-      box_setup(p, p.walk, box, lane, &tmap_a, &tmap_b, p.bn, box_kind, box_index);
       uint32_t cur_class = 0xFFFFFFFFu;
       const bool box_is_b = lane >= boxes_of(p.a_kind, kBM, epl);
       uint32_t ready = 1;   // the first pass over the ring finds every stage free
@@ -1287,7 +1290,11 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
   const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
   const uint32_t tmem_cols = p.bn * 2 <= 32 ? 32u : (p.bn * 2 <= 64 ? 64u : (p.bn * 2 <= 128 ? 128u : (p.bn * 2 <= 256 ? 256u : 512u)));
 
-  if (threadIdx.x == 0) {
+  const uint32_t epl = p.tf32 ? 32u : 64u;
+  BoxLane box;   // see the single-CTA kernel: the producer's box set-up runs beside the barrier and tensor-memory set-up
+  uint32_t box_kind = 0, box_index = 0;
+  if (warp == 0) box_setup(p, p.walk, box, lane, &tmap_a, &tmap_b, b_lines, box_kind, box_index);
+  if (threadIdx.x == 64) {
     for (uint32_t s = 0; s < p.stages; ++s) {
       mbar_init(&hdr->full[s], 1);      // the leader's arrive.expect_tx covers both CTAs' bytes (used on the leader only)
       mbar_init(&hdr->empty[s], 1);     // one commit from the leader
@@ -1312,7 +1319,6 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
   tc_fence_after_sync();
   grid_launch_dependents();             // see the single-CTA kernel: each role waits before its first global access
   const uint32_t tmem_base = hdr->tmem_base;
-  const uint32_t epl = p.tf32 ? 32u : 64u;
 
   if (warp == 0) {
     // ===== TMA producer (both CTAs): one lane per box =====
@@ -1325,9 +1331,6 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
     if (lane < n_boxes) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      BoxLane box;
-      uint32_t box_kind, box_index;
-      box_setup(p, p.walk, box, lane, &tmap_a, &tmap_b, b_lines, box_kind, box_index);
       uint32_t cur_class = 0xFFFFFFFFu;
       const bool box_is_b = lane >= boxes_of(p.a_kind, kBM, epl);
       uint32_t ready = 1;   // the first pass over the ring finds every stage free
