@@ -464,7 +464,9 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
     its weight gradient (TN, `+=` into a slice of ONE flat f32 gradient vector).  `per_head` issues the projections
     the way the reference composes attention (one Linear per head and per Q/K/V: 12 products of 8192x256x64 and 4 of
     8192x64x256 per block, src/nn/nn.zig:421-461); `fused_qkv` issues one 8192x256x768 and one 8192x256x256 product
-    instead.  After the captured contraction step the flat gradient vector (3 228 737 floats, all parameters) is
+    instead; `fused_qkv_two_streams` is the same list of launches captured as a graph with two branches: weight
+    gradients, dV / dK and the attention of every second head go to a side stream (a second handle with its own
+    workspace), so products that are one wave of tiles or less run beside each other instead of one after the other.  After the captured contraction step the flat gradient vector (3 228 737 floats, all parameters) is
     averaged over the replicas by ONE `gb_allreduce_mean`, outside the graph, where `averageGrads` sits in the
     reference (src/nn/trainer.zig:507-508).  Softmax, layer norm, embedding, loss and Adam are not contractions and
     are not part of this path."""
@@ -493,13 +495,44 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
 
     flops = [0.0]
 
-    def mm(a, b, out, m, n, k, ta=False, tb=False, acc=False, batch=1, ep=None, strides=None, ld=(0, 0, 0)):
+    import grad_b200
+
+    gpu_main = gpu
+    side_stream = torch.cuda.Stream()
+    gpu_side = grad_b200.Gpu(torch.cuda.current_device())   # its own workspace: its products run beside the main handle's
+    two_streams = [False]
+
+    class on_side:
+        """Runs the enclosed launches on the side stream after everything the main stream has been given so far."""
+
+        def __enter__(self):
+            self.active = two_streams[0]
+            if self.active:
+                side_stream.wait_stream(torch.cuda.current_stream())
+                self.ctx = torch.cuda.stream(side_stream)
+                self.ctx.__enter__()
+            return gpu_side if self.active else gpu
+
+        def __exit__(self, *exc):
+            if self.active:
+                self.ctx.__exit__(*exc)
+            return False
+
+    def join_side():
+        if two_streams[0]:
+            torch.cuda.current_stream().wait_stream(side_stream)
+
+    def mm(a, b, out, m, n, k, ta=False, tb=False, acc=False, batch=1, ep=None, strides=None, ld=(0, 0, 0), g=None):
         flops[0] += 2.0 * m * n * k * batch
         shape = MatmulShape(m, n, k, batch)
-        gpu.matmul(a, b, out, shape, MatmulOpts(ta, tb, acc), epilogue=ep, math=MATH_BF16, lda=ld[0], ldb=ld[1], ldc=ld[2])
+        (g or gpu).matmul(a, b, out, shape, MatmulOpts(ta, tb, acc), epilogue=ep, math=MATH_BF16, lda=ld[0], ldb=ld[1], ldc=ld[2])
 
-    x0 = randn(rows, d)
-    dy_head = randn(rows, vocab)
+    # Vocabulary 65: a bf16 row of 65 values is 130 bytes, which no TMA copy can step by (strides are multiples of 16
+    # bytes), and such an operand falls to the gather warps (80-250 us per head product instead of ~10).  The head's
+    # weight, logits and logit gradients therefore live in rows of 72 values (144 bytes), passed as lda / ldb / ldc: the
+    # caller pads the pitch once where the reference's packMatrix pads a scratch copy on every call (gpu.zig:711-722).
+    vpitch = (vocab + 7) // 8 * 8
+    dy_head = randn(rows, vpitch)
 
     def build(fused: bool):
         cursor[0] = 0
@@ -528,7 +561,7 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
                 blk["gq"] = [blk["gqkv"].view(-1)[i * d * hd:(i + 1) * d * hd].view(d, hd) for i in range(3 * heads)]
                 blk["goh"] = [blk["go"].view(-1)[i * hd * d:(i + 1) * hd * d].view(hd, d) for i in range(heads)]
             blocks.append(blk)
-        head = {"w": randn(d, vocab, scale=(2.0 / d) ** 0.5), "g": grad_view(d, vocab), "logits": torch.empty((rows, vocab), dtype=bf, device="cuda"),
+        head = {"w": randn(d, vpitch, scale=(2.0 / d) ** 0.5), "g": grad_view(d, vocab), "logits": torch.empty((rows, vpitch), dtype=bf, device="cuda"),
                 "dx": torch.empty((rows, d), dtype=bf, device="cuda")}
         return blocks, head
 
@@ -537,6 +570,7 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
         if fused:
             # (rows, 3*width) activations: head h of Q sits in columns h*hd.. of the first third, row pitch 3*width;
             # one launch per head, the 64 sequences as the batch
+            # with two streams: forward, odd heads run on the side stream; backward, dV and dK do
             for hh in range(heads):
                 q, k_, v = (blk["qkv2"][:, part * d + hh * hd:] for part in range(3))
                 dq, dk, dv = (blk["dqkv2"][:, part * d + hh * hd:] for part in range(3))
@@ -544,13 +578,21 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
                 o, do = blk["o2"][:, hh * hd:], blk["do2"][:, hh * hd:]
                 st = seq * 3 * d
                 if not backward:
-                    batched(q, k_, p, seq, seq, hd, False, True, seqs, (st, st, seq * seq), (3 * d, 3 * d, 0))
-                    batched(p, v, o, seq, hd, seq, False, False, seqs, (seq * seq, st, seq * d), (0, 3 * d, d))
+                    if hh % 2 == 1:
+                        with on_side() as g2:
+                            batched(q, k_, p, seq, seq, hd, False, True, seqs, (st, st, seq * seq), (3 * d, 3 * d, 0), g2)
+                            batched(p, v, o, seq, hd, seq, False, False, seqs, (seq * seq, st, seq * d), (0, 3 * d, d), g2)
+                    else:
+                        batched(q, k_, p, seq, seq, hd, False, True, seqs, (st, st, seq * seq), (3 * d, 3 * d, 0))
+                        batched(p, v, o, seq, hd, seq, False, False, seqs, (seq * seq, st, seq * d), (0, 3 * d, d))
                 else:
+                    with on_side() as g2:
+                        batched(p, do, dv, seq, hd, seq, True, False, seqs, (seq * seq, seq * d, st), (0, d, 3 * d), g2)
                     batched(do, v, dp, seq, seq, hd, False, True, seqs, (seq * d, st, seq * seq), (d, 3 * d, 0))
-                    batched(p, do, dv, seq, hd, seq, True, False, seqs, (seq * seq, seq * d, st), (0, d, 3 * d))
+                    with on_side() as g2:
+                        batched(dp, q, dk, seq, hd, seq, True, False, seqs, (seq * seq, st, st), (0, 3 * d, 3 * d), g2)
                     batched(dp, k_, dq, seq, hd, seq, False, False, seqs, (seq * seq, st, st), (0, 3 * d, 3 * d))
-                    batched(dp, q, dk, seq, hd, seq, True, False, seqs, (seq * seq, st, st), (0, 3 * d, 3 * d))
+            join_side()
             return
         q, k_, v = blk["qkv"][0:heads].view(b, seq, hd), blk["qkv"][heads:2 * heads].view(b, seq, hd), blk["qkv"][2 * heads:].view(b, seq, hd)
         dq, dk, dv = blk["dqkv"][0:heads].view(b, seq, hd), blk["dqkv"][heads:2 * heads].view(b, seq, hd), blk["dqkv"][2 * heads:].view(b, seq, hd)
@@ -564,9 +606,11 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
             mm(blk["dp"], k_, dq, seq, hd, seq, batch=b)                        # dQ = dS K
             mm(blk["dp"], q, dk, seq, hd, seq, True, False, batch=b)           # dK = dS^T Q
 
-    def batched(a, b_, out, m, n, k, ta, tb, batch, strides, ld):
+    def batched(a, b_, out, m, n, k, ta, tb, batch, strides, ld, g=None):
         from grad_b200 import abi as _abi
         import ctypes as C
+
+        gpu = g or gpu_main
 
         flops[0] += 2.0 * m * n * k * batch
         dsc = _abi.GemmDesc()
@@ -584,6 +628,8 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
         gpu.launches += gpu._count()
 
     def step(blocks, head, fused):
+        """Weight gradients are issued before the input gradient that reads the same dy, on the side stream when there is
+        one; the side stream joins before the products that read what it wrote and at the end of the step."""
         flat.zero_()                                                            # zeroGrad is part of the captured step
         for blk in blocks:                                                      # ---- forward
             if fused:
@@ -599,41 +645,48 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
                     mm(blk["o"][hh], blk["woh"][hh], blk["a"], rows, d, hd, acc=hh > 0)
             mm(blk["a"], blk["w1"], blk["h"], rows, ffn, d, ep=Epilogue(blk["b1"], None, True))
             mm(blk["h"], blk["w2"], blk["y"], rows, d, ffn, ep=Epilogue(blk["b2"], None, False))
-        mm(blocks[-1]["y"], head["w"], head["logits"], rows, vocab, d)
-        mm(dy_head, head["w"], head["dx"], rows, d, vocab, False, True)          # ---- backward
-        mm(blocks[-1]["y"], dy_head, head["g"], d, vocab, rows, True, False, acc=True)
+        mm(blocks[-1]["y"], head["w"], head["logits"], rows, vocab, d, ld=(0, vpitch, vpitch))
+        with on_side() as g2:                                                    # ---- backward
+            mm(blocks[-1]["y"], dy_head, head["g"], d, vocab, rows, True, False, acc=True, g=g2, ld=(0, vpitch, 0))
+        mm(dy_head, head["w"], head["dx"], rows, d, vocab, False, True, ld=(vpitch, vpitch, 0))
         for blk in reversed(blocks):
             dy = head["dx"]
+            with on_side() as g2:
+                mm(blk["h"], dy, blk["g2"], ffn, d, rows, True, False, acc=True, g=g2)
             mm(dy, blk["w2"], blk["dh"], rows, ffn, d, False, True)
-            mm(blk["h"], dy, blk["g2"], ffn, d, rows, True, False, acc=True)
+            with on_side() as g2:
+                mm(blk["a"], blk["dh"], blk["g1"], d, ffn, rows, True, False, acc=True, g=g2)
             mm(blk["dh"], blk["w1"], blk["da"], rows, d, ffn, False, True)
-            mm(blk["a"], blk["dh"], blk["g1"], d, ffn, rows, True, False, acc=True)
             if fused:
+                with on_side() as g2:
+                    mm(blk["o2"], blk["da"], blk["go"], d, d, rows, True, False, acc=True, g=g2)
                 mm(blk["da"], blk["wo"], blk["do2"], rows, d, d, False, True)
-                mm(blk["o2"], blk["da"], blk["go"], d, d, rows, True, False, acc=True)
             else:
                 for hh in range(heads):
                     mm(blk["da"], blk["woh"][hh], blk["do"][hh], rows, hd, d, False, True)
                     mm(blk["o"][hh], blk["da"], blk["goh"][hh], hd, d, rows, True, False, acc=True)
             attention(blk, fused, True)
             if fused:
+                with on_side() as g2:
+                    mm(blk["x"], blk["dqkv2"], blk["gqkv"], d, 3 * d, rows, True, False, acc=True, g=g2)
                 mm(blk["dqkv2"], blk["wqkv"], blk["dx"], rows, d, 3 * d, False, True)
-                mm(blk["x"], blk["dqkv2"], blk["gqkv"], d, 3 * d, rows, True, False, acc=True)
             else:
                 for i in range(3 * heads):
                     mm(blk["dqkv"][i], blk["wq"][i], blk["dx"], rows, d, hd, False, True, acc=i > 0)
                     mm(blk["x"], blk["dqkv"][i], blk["gq"][i], d, hd, rows, True, False, acc=True)
+        join_side()
 
     out = {"workload": "character Transformer: vocab 65, width 256, 4 heads, 4 blocks, FFN 1024, context 128, 64 sequences per replica; "
                        "bf16 contractions fwd + dX + dW, one captured step per replica; gradients averaged by one allreduce",
            "replicas": world, "dtype": "bf16", "grad_floats": cfg["grad_len"]}
-    for label, fused in (("per_head", False), ("fused_qkv", True)):
+    for label, fused, forked in (("per_head", False, False), ("fused_qkv", True, False), ("fused_qkv_two_streams", True, True)):
         blocks, head = build(fused)
+        two_streams[0] = forked
         flops[0] = 0.0
-        launches0 = gpu.launches
+        launches0 = gpu.launches + gpu_side.launches
         step(blocks, head, fused)
         torch.cuda.synchronize()
-        per_step, gflop = gpu.launches - launches0, flops[0] / 1e9
+        per_step, gflop = gpu.launches + gpu_side.launches - launches0, flops[0] / 1e9
         ms = graph_ms(torch, lambda: step(blocks, head, fused), calls=2, reps=5)
         ms = max_over_ranks(torch, dist, world, ms)
         out[label] = {"ms_per_step": round(ms, 4), "gflop_per_replica_step": round(gflop, 1), "launches_per_step": per_step + 1,

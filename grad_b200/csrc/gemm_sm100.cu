@@ -1101,10 +1101,6 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           cur_class = work.batch;
         }
         box_start(p, p.n_classes ? p.cls[work.batch].walk : p.walk, box, box_kind, box_index, work, work.m_tile * kBM, work.n_tile * p.bn, box_is_b);
-        if (!waited) {   // the first copy is this warp's first global access
-          grid_dependency_wait();
-          waited = true;
-        }
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_peeked(&hdr->empty[stage], phase ^ 1, ready, abort_flag, kStatusProducerTimeout))) break;
           uint32_t next_stage = stage + 1, next_phase = phase;
@@ -1116,6 +1112,10 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           const bool dropped = p.test_drop_kblock != 0 && blockIdx.x == 0 && issued == p.test_drop_kblock - 1;
           ++issued;
           if (lane == 0 && !dropped) mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
+          if (!waited) {   // the first copy is this warp's first global access; everything up to here ran beside the previous kernel
+            grid_dependency_wait();
+            waited = true;
+          }
           if (box.active && !dropped) box_issue<false>(box, tiles + stage * stage_bytes, &hdr->full[stage], 0);
           box_step(box);
           stage = next_stage;
@@ -1344,10 +1344,6 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
         }
         box_start(p, p.n_classes ? p.cls[work.batch].walk : p.walk, box, box_kind, box_index, work, work.m_tile * 2 * kBM + rank * kBM,
                   work.n_tile * p.bn + rank * b_lines, box_is_b);
-        if (!waited) {
-          grid_dependency_wait();
-          waited = true;
-        }
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
           if (!(ok = mbar_wait_peeked(&hdr->empty[stage], phase ^ 1, ready, abort_flag, kStatusProducerTimeout))) break;
           uint32_t next_stage = stage + 1, next_phase = phase;
@@ -1355,6 +1351,10 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
           const bool more = kb + 1 < work.kb_end || w + pairs < total_work;
           ready = more ? mbar_try_wait(&hdr->empty[next_stage], next_phase ^ 1) : 0u;
           if (lane == 0 && rank == 0) mbar_arrive_expect_tx(&hdr->full[stage], 2 * tx_bytes);
+          if (!waited) {
+            grid_dependency_wait();
+            waited = true;
+          }
           box_issue<true>(box, tiles + stage * stage_bytes, nullptr, map_to_cta(smem_u32(&hdr->full[stage]), 0));
           box_step(box);
           stage = next_stage;
