@@ -228,7 +228,10 @@ double tile_cost(uint32_t m, uint32_t n, uint32_t batch, uint32_t k_blocks, uint
   const double fill = (16384.0 + b_lines * 128.0) / 48.0, mma = 4.0 * std::max(bn / 2.0, 60.0);
   const double per_tile = k_blocks * std::max(fill, mma) + (bn > 256 ? 11000.0 : 1200.0);
   const double waves = (double)((tiles + units - 1) / units);
-  return waves * per_tile + 3000.0;
+  // A cluster launch, its two cluster-wide syncs and the cross-CTA barrier arrivals cost a pair kernel ~1.5 us more than a
+  // single-CTA one whatever the product (7.4 against 4.9 us for one K block per SM; 8.0 against 6.7 us for 8192 x 256 x 256):
+  // the pair has to earn that back with its lighter shared-memory fill per K block.
+  return waves * per_tile + 3000.0 + (pair ? 3000.0 : 0.0);
 }
 
 // K split a tile width would get: when its tiles leave SMs idle, about one work item per SM, each at least sixteen K
@@ -319,14 +322,15 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
 // operands arrive by TMA, K is not split, and a pair tile has a lower estimated time than the single-CTA
 // plan.  `encode_b(rows)` re-encodes B's map for the `rows` lines one CTA of the pair loads; false keeps
 // the single-CTA plan.
+// `mode`: 0 = by estimated time, 1 = the pair kernel whenever it can run this product, 2 = never.
 template <class EncodeB>
-bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b) {
+bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b, int mode = 0) {
   GemmParams& p = plan.p;
   if (!plan.tensor || p.a_kind == gb::kGather || p.b_kind == gb::kGather || p.m <= 128 || p.splits > 1) return false;
-  if (knobs().no_pair) return false;
+  if (knobs().no_pair || mode == 2) return false;
   const uint32_t sms = (uint32_t)h->sm_count;
   const uint32_t n_cap = std::max(min_bn, ceil_div(p.n, min_bn) * min_bn);
-  double best = tile_cost(p.m, p.n, p.batch, p.k_blocks_total, p.bn, false, sms);
+  double best = mode == 1 ? 1e300 : tile_cost(p.m, p.n, p.batch, p.k_blocks_total, p.bn, false, sms);
   uint32_t pick = 0;
   for (uint32_t cand : {512u, 256u, 128u, 64u}) {
     // a pair tile may overhang n as long as the second CTA's half still holds columns (192 columns: one 256-wide tile)
@@ -709,10 +713,11 @@ bool nhwc_view_tma(CUtensorMap* map, const void* base, bool smem_bf16, uint32_t 
 // eight lines).  One stage then serves all taps of a tap column: a third as many stages, barrier round trips
 // and producer iterations per tile for a 3x3 filter, and (box_h + 2) / (3 * box_h) of the activation bytes.
 // `encode_a(rows)` re-encodes the activation map for a box of `rows` image rows.
+// `min_fit`: stages that must fit (three by default: with two the ring holds less than a tile).
 template <class EncodeA>
-void try_column_stages(Plan& plan, EncodeA encode_a) {
+void try_column_stages(Plan& plan, EncodeA encode_a, uint32_t min_fit = 3) {
   GemmParams& p = plan.p;
-  if (knobs().no_column_stages) return;
+  if (knobs().no_column_stages || min_fit == 0) return;
   const gb::TapWalk& wk = p.walk;
   if (!plan.tensor || p.a_kind != gb::kPatchK || p.b_kind == gb::kGather || p.splits != 1 || p.box_n != 1 || p.bn > 256) return;
   if (wk.n2 < 2 || wk.n2 > 7 || wk.row_scale != 1 || wk.z_step == 0) return;
@@ -725,8 +730,8 @@ void try_column_stages(Plan& plan, EncodeA encode_a) {
   if (1 + boxes_b > 32) return;
   const uint32_t a_box = rows * p.box_w * 128, a_stage = (a_box + 1023) & ~1023u;
   const size_t stage = a_stage + (size_t)wk.n2 * b_lines * 128;
-  const size_t room = 227 * 1024 - 2048 - gb::kStoreSmemBytes;
-  if (room / stage < 3) return;
+  const size_t room = 227 * 1024 - 2048 - gb::kStoreSmemBytes - (p.stats ? 8 * gb::kStatBytesPerWarp : 0);
+  if (room / stage < min_fit) return;
   if (!encode_a(rows)) return;
   p.col_taps = wk.n2;
   p.a_stage_bytes = a_stage;
@@ -761,6 +766,18 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
   if ((g.y_step != g.c_out || g.w_step != g.c_out) && (d->w_layout != 0 || dxs || (ep && ep->bn_stats))) return GB_ERR_UNSUPPORTED;   // group slices: plain layers only
   const uint32_t pixels = g.n * g.h * g.w;
   uint32_t min_bn = 32;
+  // A pass with statistics stores the very bits of the plain pass (tests/gpu.zig:205), so it has to add up K in the same
+  // order: column-patch stages walk the taps column by column, the plain walk row by row.  The plain pass is planned first
+  // and the statistics plan (one column tile, more shared memory: possibly another tile width or CTA mode) follows its choice.
+  int want_cols = -1;
+  if ((ep && ep->bn_stats) || dxs) {
+    Plan plain;
+    gb_epilogue bare = ep ? *ep : gb_epilogue{};
+    bare.bn_stats = nullptr;
+    const int rc = plan_conv(h, pass, d, act, other, out, ep ? &bare : nullptr, plain, nullptr, affine_scale, affine_shift, y_step, w_step);
+    if (rc != GB_OK) return rc;
+    want_cols = plain.p.col_taps != 0 ? 1 : 0;
+  }
 
   if (pass == 0) {
     // y[positions, c_out] = patches(x)[positions, taps*c] * w[taps*c, c_out]
@@ -795,13 +812,24 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
                  nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, false, g.stride))
         p.a_kind = gb::kPatchK;
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? (w_rows ? gb::kDenseK : gb::kDenseMN) : gb::kGather;
-      CUtensorMap single = plan.tmap_b;
-      if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }))
-        plan.tmap_b = single;
-      if (g.stride == 1)
-        try_column_stages(plan, [&](uint32_t rows) {
-          return nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, rows, 1);
-        });
+      const Plan before = plan;   // the CTA mode and the staging are chosen below, twice for a statistics plan that has to follow the plain one
+      auto choose = [&](int pair_mode, uint32_t min_fit) {
+        plan = before;
+        CUtensorMap single = plan.tmap_b;
+        if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }, pair_mode))
+          plan.tmap_b = single;
+        if (g.stride == 1)
+          try_column_stages(plan, [&](uint32_t rows) {
+            return nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, rows, 1);
+          }, min_fit);
+      };
+      if (want_cols < 0) {
+        choose(0, 3);
+      } else {
+        choose(0, want_cols ? 2 : 0);
+        if ((p.col_taps != 0) != (want_cols != 0)) choose(p.cta_pair ? 2 : 1, want_cols ? 2 : 0);
+        if ((p.col_taps != 0) != (want_cols != 0)) return GB_ERR_UNSUPPORTED;
+      }
     }
   } else if (pass == 1) {
     // dx[pixels, c] = patchesT(dy)[pixels, taps*c_out] * wT[taps*c_out, c]
@@ -842,15 +870,26 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
         const uint64_t strides[3] = {(uint64_t)g.w_step * es, (uint64_t)g.w_step * es * g.c, (uint64_t)g.w_step * es * g.c * taps};
         const uint32_t box[4] = {epl, p.bn, 1, 1};
         if (((uint64_t)g.w_step * es) % 16 == 0 && encode_map(&plan.tmap_b, smem_bf16, other, 4, dims, strides, box)) p.b_kind = gb::kWeightK;
-        CUtensorMap single = plan.tmap_b;
-        if (!try_pair(h, plan, 32, [&](uint32_t rows) {
-              const uint32_t half_box[4] = {epl, rows, 1, 1};
-              return encode_map(&plan.tmap_b, smem_bf16, other, 4, dims, strides, half_box);
-            }))
-          plan.tmap_b = single;
-        try_column_stages(plan, [&](uint32_t rows) {
-          return nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_y, g.c_out, g.y_step, g.out_w, g.out_h, g.n, epl, p.box_w, rows, 1);
-        });
+        const Plan before = plan;
+        auto choose = [&](int pair_mode, uint32_t min_fit) {
+          plan = before;
+          CUtensorMap single = plan.tmap_b;
+          if (!try_pair(h, plan, 32, [&](uint32_t rows) {
+                const uint32_t half_box[4] = {epl, rows, 1, 1};
+                return encode_map(&plan.tmap_b, smem_bf16, other, 4, dims, strides, half_box);
+              }, pair_mode))
+            plan.tmap_b = single;
+          try_column_stages(plan, [&](uint32_t rows) {
+            return nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_y, g.c_out, g.y_step, g.out_w, g.out_h, g.n, epl, p.box_w, rows, 1);
+          }, min_fit);
+        };
+        if (want_cols < 0) {
+          choose(0, 3);
+        } else {
+          choose(0, want_cols ? 2 : 0);
+          if ((p.col_taps != 0) != (want_cols != 0)) choose(p.cta_pair ? 2 : 1, want_cols ? 2 : 0);
+          if ((p.col_taps != 0) != (want_cols != 0)) return GB_ERR_UNSUPPORTED;
+        }
       }
     }
   } else {

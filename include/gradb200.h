@@ -63,7 +63,8 @@ typedef enum { GB_ACT_NONE = 0, GB_ACT_RELU = 1 } gb_activation;
  * (v - shift[col]) and of (v - shift[col])^2 over all rows (positions), taken over the values AS STORED (rounded to bf16
  * when the result is bf16), are ADDED to sums[col] and sums[n + col]; the caller zeroes `sums` (`scratchZeroed`).  shift is
  * the running mean, a close estimate that keeps the squared sums precise.  The stored result is bit-identical to the
- * same call without statistics (tests/gpu.zig:205).  ordered = 1 is the reference's deterministic mode: every CTA writes
+ * same call without statistics (tests/gpu.zig:205): the statistics plan adds up K in the order the plain plan of the same
+ * call uses (it cannot follow a plain plan that splits K: a product of a few row tiles with K >= 2048).  ordered = 1 is the reference's deterministic mode: every CTA writes
  * its partial sums to the workspace and a second launch adds them in a fixed order, so repeated runs give identical
  * bits; ordered = 0 adds with atomics.  Needs n <= 256, n a multiple of 32 and a 16-byte aligned row-major result
  * (every ResNet training layer); otherwise the call returns GB_ERR_UNSUPPORTED and nothing is launched. */
