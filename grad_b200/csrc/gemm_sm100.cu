@@ -812,6 +812,23 @@ __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& 
   return stats;
 }
 
+// The common chunk: bf16 result = max(acc + bias, floor), nothing read from global memory (p.tma_store == 2: no old C, no
+// residual, no K split, no statistics).  Without a run-time branch per option the chunk is ~100 instructions instead
+// of several hundred: bias values are always staged (zeros when there is no bias) and `floor` is 0 or -inf.
+__device__ __forceinline__ void epilogue_chunk_fast(const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage, const float* sbias, float floor,
+                                                    uint32_t batch, uint32_t row, uint32_t col0, uint32_t lane) {
+  uint4 q[4];
+#pragma unroll
+  for (uint32_t j = 0; j < 4; ++j) {
+    const float4 b0 = *(const float4*)(sbias + 8 * j), b1 = *(const float4*)(sbias + 8 * j + 4);   // same address in every lane: broadcast reads
+    q[j] = make_uint4(pack_bf16x2(fmaxf(__uint_as_float(acc[8 * j]) + b0.x, floor), fmaxf(__uint_as_float(acc[8 * j + 1]) + b0.y, floor)),
+                      pack_bf16x2(fmaxf(__uint_as_float(acc[8 * j + 2]) + b0.z, floor), fmaxf(__uint_as_float(acc[8 * j + 3]) + b0.w, floor)),
+                      pack_bf16x2(fmaxf(__uint_as_float(acc[8 * j + 4]) + b1.x, floor), fmaxf(__uint_as_float(acc[8 * j + 5]) + b1.y, floor)),
+                      pack_bf16x2(fmaxf(__uint_as_float(acc[8 * j + 6]) + b1.z, floor), fmaxf(__uint_as_float(acc[8 * j + 7]) + b1.w, floor)));
+  }
+  stage_and_store(tmap_c, stage, q, lane, (int32_t)col0, (int32_t)(row - lane), (int32_t)batch);
+}
+
 __device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
                                                    const float* sbias, uint32_t batch, uint32_t split, uint32_t row, uint32_t col0, uint32_t lane) {
   epilogue_chunk_tma_impl<false>(p, tmap_c, acc, stage, sbias, nullptr, 0, batch, split, row, col0, lane);
@@ -849,7 +866,7 @@ __device__ __forceinline__ void epilogue_chunk_tma_stats_call(const GemmParams& 
 // chunk by chunk from global memory, each load's latency stood between two chunks.)
 __device__ __forceinline__ void stage_bias(const GemmParams& p, float* sbias, uint32_t ncols, uint32_t col_base, bool wide, uint32_t lane,
                                            uint32_t first, uint32_t step) {
-  if (p.bias == nullptr) return;
+  if (p.bias == nullptr && p.tma_store != 2) return;   // the branch-free chunk always adds: it gets zeros
   __syncwarp();
 #pragma unroll
   for (uint32_t i = 0; i < 8; ++i) {
@@ -857,7 +874,7 @@ __device__ __forceinline__ void stage_bias(const GemmParams& p, float* sbias, ui
     if (c < ncols) {
       const uint32_t tc = wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c;
       const uint32_t col = col_base + tc + lane;
-      sbias[32 * i + lane] = col < p.n ? p.bias[col] : 0.0f;
+      sbias[32 * i + lane] = (p.bias != nullptr && col < p.n) ? p.bias[col] : 0.0f;
     }
   }
   __syncwarp();
@@ -889,6 +906,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     uint32_t acc_a[32], acc_b[32];
     tmem_ld_32x32(taddr + first, acc_a);
     uint32_t i = 0;
+    const bool fast = !kStats && p.tma_store == 2;
+    const float floor = p.relu ? 0.0f : -INFINITY;
     for (uint32_t c = first; c < ncols; c += 2 * step, i += 2) {
       const bool has_b = c + step < ncols;
       tmem_ld_wait();
@@ -898,6 +917,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
         const uint32_t col0 = col_base + tile_col(c);
         if (col0 + 32 <= p.n && row - lane < p.m) {
           if constexpr (kStats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_a, store_stage, sbias + 32 * i, sstat, i, batch, row, col0, lane);
+          else if (fast) epilogue_chunk_fast(tmap_c, acc_a, store_stage, sbias + 32 * i, floor, batch, row, col0, lane);
           else epilogue_chunk_tma(p, tmap_c, acc_a, store_stage, sbias + 32 * i, batch, split, row, col0, lane);
         } else epilogue_chunk_copy(p, acc_a, batch, split, row, col0, p.bias ? sbias[32 * i + lane] : 0.0f);
       }
@@ -908,6 +928,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
         const uint32_t col0 = col_base + tile_col(c + step);
         if (col0 + 32 <= p.n && row - lane < p.m) {
           if constexpr (kStats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), sstat, i + 1, batch, row, col0, lane);
+          else if (fast) epilogue_chunk_fast(tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), floor, batch, row, col0, lane);
           else epilogue_chunk_tma(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), batch, split, row, col0, lane);
         } else epilogue_chunk_copy(p, acc_b, batch, split, row, col0, p.bias ? sbias[32 * (i + 1) + lane] : 0.0f);
       }

@@ -489,6 +489,8 @@ int prepare_plan(const gb_handle* h, Plan& plan, void* workspace, size_t workspa
     const uint64_t strides[2] = {(uint64_t)p.ldc * es, p.batch > 1 ? p.stride_c * es : (uint64_t)p.ldc * es * p.m};
     const uint32_t box[3] = {64 / es, 32, 1};
     p.tma_store = encode_map(&plan.tmap_c, p.c_is_bf16, p.c, 3, dims, strides, box, false, nullptr, true) ? 1 : 0;
+    // 2: the chunk epilogue without run-time options (bf16 result = max(acc + bias, floor), nothing read back)
+    if (p.tma_store && p.c_is_bf16 && !p.accumulate && !p.residual && !p.round_tf32 && !p.stats) p.tma_store = 2;
   }
   if (plan.tensor) {
     // The stage ring takes what the epilogue's own shared memory leaves of the 227 KB a CTA can have.
