@@ -323,31 +323,46 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
 // plan.  `encode_b(rows)` re-encodes B's map for the `rows` lines one CTA of the pair loads; false keeps
 // the single-CTA plan.
 // `mode`: 0 = by estimated time, 1 = the pair kernel whenever it can run this product, 2 = never.
+// `split_k`: the pair plan may split K like the single-CTA plan does (a weight gradient: few tiles, K = all positions; a
+// 256 x 256 pair tile moves 32 KB per K block and SM where the single-CTA 128 x 256 tile moves 48 KB for half the rows).
 template <class EncodeB>
-bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b, int mode = 0) {
+bool try_pair(const gb_handle* h, Plan& plan, uint32_t min_bn, EncodeB encode_b, int mode = 0, bool split_k = false) {
   GemmParams& p = plan.p;
-  if (!plan.tensor || p.a_kind == gb::kGather || p.b_kind == gb::kGather || p.m <= 128 || p.splits > 1) return false;
+  if (!plan.tensor || p.a_kind == gb::kGather || p.b_kind == gb::kGather || p.m <= 128 || (p.splits > 1 && !split_k)) return false;
   if (knobs().no_pair || mode == 2) return false;
   const uint32_t sms = (uint32_t)h->sm_count;
   const uint32_t n_cap = std::max(min_bn, ceil_div(p.n, min_bn) * min_bn);
-  double best = mode == 1 ? 1e300 : tile_cost(p.m, p.n, p.batch, p.k_blocks_total, p.bn, false, sms);
-  uint32_t pick = 0;
+  auto reduce_cost = [&](uint32_t parts) { return parts > 1 ? 4000.0 + (double)p.m * p.n * p.batch * parts * 4.0 / 2000.0 : 0.0; };
+  double best = mode == 1 ? 1e300
+                          : tile_cost(p.m, p.n, p.batch * p.splits, ceil_div(p.k_blocks_total, p.splits), p.bn, false, sms) + reduce_cost(p.splits);
+  uint32_t pick = 0, pick_parts = 1;
   for (uint32_t cand : {512u, 256u, 128u, 64u}) {
     // a pair tile may overhang n as long as the second CTA's half still holds columns (192 columns: one 256-wide tile)
     if (cand / 2 < min_bn || (cand > n_cap && cand / 2 >= p.n)) continue;
     if (p.stats && (cand > 256 || cand < p.n)) continue;   // statistics: one column tile of at most 256 columns
-    const double cost = tile_cost(p.m, p.n, p.batch, p.k_blocks_total, cand, true, sms);
-    if (cost <= best) { best = cost; pick = cand; }   // a tie goes to the pair: half as many MMA instructions per row
+    uint32_t parts = 1;
+    if (split_k && !p.stats) {
+      const uint32_t tiles = ceil_div(p.m, 256) * p.batch * ceil_div(p.n, cand);
+      if (tiles * 2 <= sms / 2 && p.k_blocks_total >= 32) parts = std::max(1u, std::min(sms / 2 / tiles, p.k_blocks_total / 16));
+      if (knobs().force_splits > 0) parts = std::min<uint32_t>((uint32_t)knobs().force_splits, std::max(1u, p.k_blocks_total));
+      // K parts on a pair only for the 256-wide tile: narrower ones measured slower than the single-CTA plan with its
+      // two K blocks per stage (256 x 128 pair tiles, 128 -> 128 at 16 x 16: 24.1 against 20.6 us), and the partial
+      // tiles of the two-half 512-wide tile are not laid out for the reduce
+      if (parts > 1 && cand != 256) continue;
+    }
+    const double cost = tile_cost(p.m, p.n, p.batch * parts, ceil_div(p.k_blocks_total, parts), cand, true, sms) + reduce_cost(parts);
+    // a tie goes to the pair (half as many MMA instructions per row) unless it needs a K split the single-CTA plan does without
+    if (cost < best || (cost == best && parts <= p.splits)) { best = cost; pick = cand; pick_parts = parts; }
   }
   if (pick == 0 || !encode_b(pick / 2)) return false;
   p.cta_pair = 1;
   p.bn = pick;
   p.tiles_m = ceil_div(p.m, 256);
   p.tiles_n = ceil_div(p.n, pick);
-  p.splits = 1;
-  p.k_blocks_per_split = p.k_blocks_total;
+  p.k_blocks_per_split = std::max(1u, ceil_div(p.k_blocks_total, pick_parts));
+  p.splits = std::max(1u, ceil_div(p.k_blocks_total, p.k_blocks_per_split));
   p.stages = std::min<uint32_t>(8, (227 * 1024 - 2048) / (128 * 128 + pick / 2 * 128));
-  plan.workspace = 0;
+  plan.workspace = p.splits > 1 ? (size_t)p.splits * p.batch * p.m * p.n * sizeof(float) : 0;
   return true;
 }
 
@@ -923,12 +938,17 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
                  nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, true, g.stride))
         p.a_kind = gb::kPatchMN;
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
+      {
+        CUtensorMap single = plan.tmap_b;
+        if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }, 0, true))
+          plan.tmap_b = single;
+      }
       // Both operands are MN-major (one line per position), so two K blocks per stage are simply boxes of twice
       // as many lines: half the stages, barrier round trips and producer iterations for the same MMAs.  (The K
       // loop of a weight gradient is producer-bound: ~570 cycles per stage against 256 of MMA time.)
       uint32_t bw2, bh2, bn2;
       CUtensorMap a2, b2;
-      if (p.a_kind == gb::kPatchMN && p.b_kind == gb::kDenseMN && !knobs().no_wide_stages && p.k_blocks_total >= 8 &&
+      if (!p.cta_pair && p.a_kind == gb::kPatchMN && p.b_kind == gb::kDenseMN && !knobs().no_wide_stages && p.k_blocks_total >= 8 &&
           patch_box(2 * epl, g.out_h, g.out_w, bw2, bh2, bn2) &&
           (p.patch_view ? nhwc_view_tma(&a2, other, smem_bf16, d->dtype_x, g, epl, bw2, bh2, bn2, true)
                         : nhwc_tma(&a2, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, bw2, bh2, bn2, true, g.stride)) &&
