@@ -1595,6 +1595,53 @@ __global__ void __launch_bounds__(256) splitk_reduce_vec4_kernel(const GemmParam
   (void)total;
 }
 
+// The grouped reduce (below) with four columns per lane: for the many-part weight gradients of narrow layers whose result
+// allows 16-byte accesses (f32, row-major, n % 4 == 0, nothing but `accumulate` in the epilogue).
+__global__ void __launch_bounds__(32 * kReduceGroups) splitk_reduce_grouped_vec4_kernel(const GemmParams p) {
+  __shared__ float4 group_sum[kReduceGroups][32];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const uint32_t n4 = p.n >> 2;
+  const uint64_t total4 = (uint64_t)p.m * n4;   // one batch entry: checked by the launcher
+  const float4* parts = (const float4*)p.partial;
+  const uint32_t lane = threadIdx.x & 31, group = threadIdx.x >> 5;
+  const uint32_t s_begin = (uint32_t)((uint64_t)p.splits * group / kReduceGroups), s_end = (uint32_t)((uint64_t)p.splits * (group + 1) / kReduceGroups);
+  for (uint64_t t0 = (uint64_t)blockIdx.x * 32; t0 < total4; t0 += (uint64_t)gridDim.x * 32) {
+    const uint64_t t = t0 + lane;
+    float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (t < total4) {
+      uint32_t sidx = s_begin;
+      for (; sidx + 2 <= s_end; sidx += 2) {
+        const float4 v0 = parts[(uint64_t)sidx * total4 + t], v1 = parts[(uint64_t)(sidx + 1) * total4 + t];
+        x.x += v0.x; x.y += v0.y; x.z += v0.z; x.w += v0.w;
+        x.x += v1.x; x.y += v1.y; x.z += v1.z; x.w += v1.w;
+      }
+      for (; sidx < s_end; ++sidx) {
+        const float4 v = parts[(uint64_t)sidx * total4 + t];
+        x.x += v.x; x.y += v.y; x.z += v.z; x.w += v.w;
+      }
+    }
+    __syncthreads();
+    group_sum[group][lane] = x;
+    __syncthreads();
+    if (group == 0 && t < total4) {
+      x = group_sum[0][lane];
+#pragma unroll
+      for (uint32_t gi = 1; gi < kReduceGroups; ++gi) {
+        const float4 v = group_sum[gi][lane];
+        x.x += v.x; x.y += v.y; x.z += v.z; x.w += v.w;
+      }
+      const uint32_t row = (uint32_t)t / n4, col = ((uint32_t)t - row * n4) * 4;
+      float4* dst = (float4*)((float*)p.c + (uint64_t)row * p.ldc + col);
+      if (p.accumulate) {
+        const float4 q = *dst;
+        x.x += q.x; x.y += q.y; x.z += q.z; x.w += q.w;
+      }
+      *dst = x;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(32 * kReduceGroups) splitk_reduce_grouped_kernel(const GemmParams p) {
   __shared__ float group_sum[kReduceGroups][32];
   grid_launch_dependents();
@@ -1747,6 +1794,12 @@ cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream) {
   const uint64_t total = (uint64_t)p.m * p.n * p.batch;
   if (total == 0) return cudaSuccess;
   if (p.splits >= 3 * kReduceGroups) {
+    if (p.vec_store && !p.transpose_out && !p.c_is_bf16 && p.batch == 1 && (p.n & 3) == 0 && (p.ldc & 3) == 0 && !p.bias && !p.residual && !p.relu &&
+        !p.round_tf32 && total / 4 < 0xFFFFFFFFull && ((uintptr_t)p.partial & 15) == 0) {
+      const uint64_t total4 = total / 4;
+      const uint32_t blocks4 = (uint32_t)((total4 + 31) / 32 < 148 * 16 ? (total4 + 31) / 32 : 148 * 16);
+      return launch_overlapped(splitk_reduce_grouped_vec4_kernel, dim3(blocks4), dim3(32 * kReduceGroups), 0, stream, p);
+    }
     const uint32_t blocks = (uint32_t)((total + 31) / 32 < 148 * 32 ? (total + 31) / 32 : 148 * 32);
     return launch_overlapped(splitk_reduce_grouped_kernel, dim3(blocks), dim3(32 * kReduceGroups), 0, stream, p);
   }
