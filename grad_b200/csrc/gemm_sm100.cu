@@ -992,12 +992,12 @@ __device__ __noinline__ void flush_stats(const GemmParams& p, const float* sstat
 struct MmaSetup {
   uint32_t idesc;
   uint32_t a_step16, b_step16;      // descriptor increment per K slice (bytes >> 4)
-  uint32_t stage16, b_stage16;      // descriptor increment per pipeline stage (B: 0 when its tiles are resident)
+  uint32_t stage16;                 // descriptor increment per pipeline stage
   uint64_t a_desc0, b_desc0;        // descriptors of stage 0, slice 0
 };
 
 __device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t tile_rows, uint32_t instr_n, uint32_t tiles_addr, uint32_t stage_bytes,
-                                                   uint32_t a_bytes, uint32_t resident_b_addr = 0) {
+                                                   uint32_t a_bytes) {
   const uint32_t epl = p.tf32 ? 32u : 64u;
   // K-major: the four K slices of a stage sit 32 bytes apart inside each line.  MN-major: a slice is 16
   // (bf16) or 8 (tf32) whole lines, and 64-/32-wide MN blocks follow each other every epl lines.
@@ -1013,9 +1013,8 @@ __device__ __forceinline__ MmaSetup make_mma_setup(const GemmParams& p, uint32_t
   s.a_step16 = a_step >> 4;
   s.b_step16 = b_step >> 4;
   s.stage16 = stage_bytes >> 4;
-  s.b_stage16 = resident_b_addr ? 0u : s.stage16;
   s.a_desc0 = make_smem_desc(tiles_addr, a_lbo, a_sbo, a_mode);
-  s.b_desc0 = make_smem_desc(resident_b_addr ? resident_b_addr : tiles_addr + a_bytes, b_lbo, b_sbo, b_mode);
+  s.b_desc0 = make_smem_desc(tiles_addr + a_bytes, b_lbo, b_sbo, b_mode);
   return s;
 }
 
@@ -1024,7 +1023,7 @@ template <bool kPair, bool kTf32>
 __device__ __forceinline__ void mma_stage(const MmaSetup& s, uint32_t tmem_d, uint32_t stage, uint32_t first_accumulate, uint32_t b_extra16 = 0,
                                           uint32_t a_extra16 = 0) {
   const uint64_t da = s.a_desc0 + (uint64_t)(stage * s.stage16 + a_extra16);
-  const uint64_t db = s.b_desc0 + (uint64_t)(stage * s.b_stage16 + b_extra16);
+  const uint64_t db = s.b_desc0 + (uint64_t)(stage * s.stage16 + b_extra16);
   mma_issue<kPair, kTf32>(tmem_d, da, db, s.idesc, first_accumulate);
   mma_issue<kPair, kTf32>(tmem_d, da + s.a_step16, db + s.b_step16, s.idesc, 1u);
   mma_issue<kPair, kTf32>(tmem_d, da + 2 * s.a_step16, db + 2 * s.b_step16, s.idesc, 1u);
@@ -1035,7 +1034,7 @@ template <bool kPair, bool kTf32>
 __device__ __forceinline__ void mma_stage_more(const MmaSetup& s, uint32_t tmem_d, uint32_t stage, uint32_t kmul) {
   for (uint32_t t = 1; t < kmul; ++t) {
     const uint64_t da = s.a_desc0 + (uint64_t)(stage * s.stage16 + 4 * t * s.a_step16);
-    const uint64_t db = s.b_desc0 + (uint64_t)(stage * s.b_stage16 + 4 * t * s.b_step16);
+    const uint64_t db = s.b_desc0 + (uint64_t)(stage * s.stage16 + 4 * t * s.b_step16);
 #pragma unroll
     for (uint32_t q = 0; q < 4; ++q) mma_issue<kPair, kTf32>(tmem_d, da + q * s.a_step16, db + q * s.b_step16, s.idesc, 1u);
   }
@@ -1056,12 +1055,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const uint32_t kmul = max(p.k_mul, 1u);
   const uint32_t b_tile_bytes = p.bn * kLineBytes * kmul;
   const uint32_t a_bytes = p.a_stage_bytes ? p.a_stage_bytes : kATileBytes * kmul, b_tiles = max(p.col_taps, 1u);
-  // resident B (see GemmParams::b_resident): every K block's B tiles sit in front of the ring, which then holds A boxes only
-  const uint32_t b_kb_bytes = b_tiles * b_tile_bytes;
-  const uint32_t resident_bytes = p.b_resident ? p.k_blocks_total * b_kb_bytes : 0u;
-  uint8_t* resident = tiles;
-  tiles += resident_bytes;
-  const uint32_t stage_bytes = p.b_resident ? a_bytes : a_bytes + b_kb_bytes;
+  const uint32_t stage_bytes = a_bytes + b_tiles * b_tile_bytes;
   volatile uint32_t* abort_flag = &hdr->abort_flag;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1110,8 +1104,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 
   if (warp == 0) {
     // ===== TMA producer: one lane per box =====
-    const uint32_t a_tx = p.a_kind != kGather ? (p.col_taps ? p.a_box_bytes : kATileBytes * kmul) : 0u;
-    const uint32_t b_tx = p.b_kind != kGather ? b_tiles * b_tile_bytes : 0u;
+    const uint32_t tx_bytes = (p.a_kind != kGather ? (p.col_taps ? p.a_box_bytes : kATileBytes * kmul) : 0u) + (p.b_kind != kGather ? b_tiles * b_tile_bytes : 0u);
     const uint32_t n_boxes = boxes_of(p.a_kind, kBM, epl) + b_tiles * boxes_of(p.b_kind, p.bn, epl);
     if (lane < max(n_boxes, 1u)) {
       uint32_t stage = 0, phase = 0;
@@ -1139,17 +1132,12 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           // copies, so the stage's "full" barrier never completes and the bounded waits downstream run out.
           const bool dropped = p.test_drop_kblock != 0 && blockIdx.x == 0 && issued == p.test_drop_kblock - 1;
           ++issued;
-          // resident B: its boxes travel with the first tile's stages only, to their own place in front of the ring
-          const bool with_b = !p.b_resident || w == blockIdx.x;
-          if (lane == 0 && !dropped) mbar_arrive_expect_tx(&hdr->full[stage], a_tx + (with_b ? b_tx : 0u));
+          if (lane == 0 && !dropped) mbar_arrive_expect_tx(&hdr->full[stage], tx_bytes);
           if (!waited) {   // the first copy is this warp's first global access; everything up to here ran beside the previous kernel
             grid_dependency_wait();
             waited = true;
           }
-          if (box.active && !dropped && (with_b || !box_is_b)) {
-            uint8_t* base = (p.b_resident && box_is_b) ? resident + (kb - work.kb_begin) * b_kb_bytes - a_bytes : tiles + stage * stage_bytes;
-            box_issue<false>(box, base, &hdr->full[stage], 0);
-          }
+          if (box.active && !dropped) box_issue<false>(box, tiles + stage * stage_bytes, &hdr->full[stage], 0);
           box_step(box);
           stage = next_stage;
           phase = next_phase;
@@ -1161,7 +1149,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     // The issuing thread is chosen with elect.sync, not `lane == 0`: the compiler then keeps descriptors and
     // addresses in uniform registers, and one tcgen05.mma costs ~40-48 issue cycles instead of ~92.
     if (elect_one()) {
-      const MmaSetup ms = make_mma_setup(p, kBM, p.bn, smem_u32(tiles), stage_bytes, a_bytes, p.b_resident ? smem_u32(resident) : 0u);
+      const MmaSetup ms = make_mma_setup(p, kBM, p.bn, smem_u32(tiles), stage_bytes, a_bytes);
       uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
       uint32_t ready = 0;   // the first stage is waited for in the ordinary way
@@ -1179,9 +1167,8 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           ready = more ? mbar_try_wait(&hdr->full[next_stage], next_phase) : 0u;
           tc_fence_after_sync();
           if (p.col_taps) {
-            const uint32_t b_kb16 = p.b_resident ? (kb - work.kb_begin) * (b_kb_bytes >> 4) : 0u;
             for (uint32_t t = 0; t < p.col_taps; ++t) {
-              const uint32_t a16 = (uint32_t)(p.col_a_first16 + (int32_t)t * p.col_a_step16), b16 = b_kb16 + t * (b_tile_bytes >> 4);
+              const uint32_t a16 = (uint32_t)(p.col_a_first16 + (int32_t)t * p.col_a_step16), b16 = t * (b_tile_bytes >> 4);
               if (p.tf32) mma_stage<false, true>(ms, tmem_d, stage, (kb > work.kb_begin) | (t > 0), b16, a16);
               else mma_stage<false, false>(ms, tmem_d, stage, (kb > work.kb_begin) | (t > 0), b16, a16);
             }
@@ -1714,10 +1701,10 @@ cudaError_t launch_stats_combine(const GemmParams& p, uint32_t ctas, cudaStream_
 
 size_t gemm_smem_bytes(const GemmParams& p) {
   const size_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
-  const size_t a_part = p.a_stage_bytes ? p.a_stage_bytes : kATileBytes * (p.k_mul ? p.k_mul : 1u);
-  const size_t b_part = (p.col_taps ? p.col_taps : 1u) * b_lines * kLineBytes * (p.k_mul ? p.k_mul : 1u);
-  const size_t ring = p.b_resident ? (size_t)p.stages * a_part + (size_t)p.k_blocks_total * b_part : (size_t)p.stages * (a_part + b_part);
-  return 1024 /* alignment slack */ + kHeaderBytes + ring + (p.tma_store ? kStoreSmemBytes : 0) + (p.stats ? 8 * kStatBytesPerWarp : 0);
+  return 1024 /* alignment slack */ + kHeaderBytes +
+         (size_t)p.stages * ((p.a_stage_bytes ? p.a_stage_bytes : kATileBytes * (p.k_mul ? p.k_mul : 1u)) +
+                             (p.col_taps ? p.col_taps : 1u) * b_lines * kLineBytes * (p.k_mul ? p.k_mul : 1u)) +
+         (p.tma_store ? kStoreSmemBytes : 0) + (p.stats ? 8 * kStatBytesPerWarp : 0);
 }
 
 // Co-resident 2-CTA clusters of the pair kernel for a given dynamic shared-memory size (cached per size).

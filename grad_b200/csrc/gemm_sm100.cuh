@@ -107,11 +107,6 @@ struct GemmParams {
   uint32_t col_taps;
   uint32_t a_stage_bytes;   // A part of a stage (multiple of 1024); 0 means the plain 16 KB tile
   uint32_t a_box_bytes;     // bytes the A box really delivers
-  // Column-patch plan of the single-CTA kernel whose whole B operand (every tap and channel block of the ONE column tile)
-  // fits in shared memory beside the ring: the B tiles are fetched with the first tile only and stay, the ring holds
-  // activation boxes alone.  A 64 -> 64 layer fetches 72 KB of filters per 128-position tile otherwise -- as many
-  // 128-byte lines as its activations -- and the copy engine's line rate, not the tensor core, sets its pace.
-  uint32_t b_resident;
   int32_t col_a_first16, col_a_step16;
   RowMap rowmap;            // output row placement (disabled: row m of C)
   // > 0: the batch index selects one of `n_classes` products that share operands, tile shape and C but have their

@@ -60,7 +60,6 @@ struct Knobs {
   bool no_dgrad_classes = false; // GB_NO_DGRAD_CLASSES: a strided input gradient is one gathered product
   bool no_wide_stages = false;   // GB_NO_WIDE_STAGES: weight gradients keep one K block per stage
   bool no_fused_classes = false; // GB_NO_FUSED_CLASSES: one launch per parity class of a strided input gradient
-  bool no_resident_b = false;    // GB_NO_RESIDENT_B: column-patch plans fetch their B tiles with every stage
   bool no_plan_cache = false;    // GB_NO_PLAN_CACHE: every call plans from scratch
   int force_bn = 0;              // GB_FORCE_BN=n: tile width of a dense single-CTA product (with GB_FORCE_SPLITS: its K split)
   int force_splits = 0;
@@ -82,7 +81,6 @@ const Knobs& knobs() {
     v.no_wide_stages = getenv("GB_NO_WIDE_STAGES") != nullptr;
     v.no_fused_classes = getenv("GB_NO_FUSED_CLASSES") != nullptr;
     v.no_plan_cache = getenv("GB_NO_PLAN_CACHE") != nullptr;
-    v.no_resident_b = getenv("GB_NO_RESIDENT_B") != nullptr;
     if (const char* g = getenv("GB_FORCE_BN")) v.force_bn = atoi(g);
     if (const char* g = getenv("GB_FORCE_SPLITS")) v.force_splits = atoi(g);
     if (const char* g = getenv("GB_TEST_SPIN_LIMIT")) v.test_spin_limit = (uint32_t)std::max(1, atoi(g));
@@ -513,7 +511,7 @@ int prepare_plan(const gb_handle* h, Plan& plan, void* workspace, size_t workspa
     // The stage ring takes what the epilogue's own shared memory leaves of the 227 KB a CTA can have.
     const uint32_t b_lines = p.cta_pair ? p.bn / 2 : p.bn;
     const size_t stage = (p.a_stage_bytes ? p.a_stage_bytes : 128 * 128 * std::max(p.k_mul, 1u)) +
-                         (p.b_resident ? 0 : (size_t)std::max(p.col_taps, 1u) * b_lines * 128 * std::max(p.k_mul, 1u));
+                         (size_t)std::max(p.col_taps, 1u) * b_lines * 128 * std::max(p.k_mul, 1u);
     const size_t fixed = gb::gemm_smem_bytes(p) - (size_t)p.stages * stage;
     const uint32_t fit = (uint32_t)((227 * 1024 - fixed) / stage);
     p.stages = std::max(2u, std::min(p.stages, fit));
@@ -760,13 +758,6 @@ void try_column_stages(Plan& plan, EncodeA encode_a, uint32_t min_fit = 3) {
   p.k_blocks_total = wk.n1 * wk.cblocks;
   p.k_blocks_per_split = p.k_blocks_total;
   p.stages = (uint32_t)std::min<size_t>(8, room / stage);
-  // The whole B operand beside a ring of activation boxes, when that leaves a deeper ring than stages holding both.
-  const size_t resident = (size_t)p.k_blocks_total * wk.n2 * b_lines * 128;
-  if (!knobs().no_resident_b && !p.cta_pair && p.tiles_n == 1 && p.n_classes == 0 && p.batch == 1 && resident < room &&
-      (room - resident) / a_stage >= 4 && (room - resident) / a_stage > room / stage) {
-    p.b_resident = 1;
-    p.stages = (uint32_t)std::min<size_t>(8, (room - resident) / a_stage);
-  }
 }
 
 int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* act, const void* other, void* out,
