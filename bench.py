@@ -741,7 +741,7 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
                             "includes": "`us`: one ncclAllReduce(avg) over the flat vector, back to back on the device; `us_with_host_barrier` adds the "
                                         "rendezvous-store barrier in front of it (the reference's wait(), a host round trip per step)",
                             "limiter": "NCCL latency (launch + NVLink hops), not bandwidth, while bus_gbs stays far below 770"}
-        for label in ("per_head", "fused_qkv"):
+        for label in ("per_head", "fused_qkv", "fused_qkv_two_streams"):
             total = out[label]["ms_per_step"] + us * 1e-3
             out[label]["ms_with_allreduce"] = round(total, 4)
             out[label]["tflops_with_allreduce"] = round(world * out[label]["gflop_per_replica_step"] / total, 1)
