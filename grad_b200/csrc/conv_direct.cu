@@ -26,78 +26,82 @@ __device__ __forceinline__ float round_operand(float v, uint32_t tf32) {
   return tf32 ? round_tf32(v) : bf16_to_f32((uint16_t)bf16_bits(v));
 }
 
-// Dynamic shared memory: filters as f32 [taps * c][c_out], already rounded to the operand type.  A thread
-// reads 16 bytes of them per four FMAs of ONE position; with one position per thread the kernel was bound
-// by those shared-memory reads (0.8 ms for 4096 images), so a thread keeps four positions and every filter
-// read feeds 16 FMAs.
+// Dynamic shared memory: filters as f32 [taps * c][c_out], already rounded to the operand type, and behind them the
+// patch values of the 128 positions a block works on, [taps * c][128] f32.  A block stages those once -- thread t fetches
+// the taps * c values of position t, all loads independent -- and then every thread accumulates four consecutive
+// positions x 16 channels from shared memory: per (tap, channel) one 16-byte read of patch values (the four lanes that
+// hold the channel chunks of one position group read the same address) and four of filters feed 64 FMAs.  (Reading the
+// patch values from global memory inside the FMA loop, 108 scattered 2-byte loads per thread, left the kernel waiting on
+// them: 31 us for the stem at batch 128 against ~6 us of FMA time; with one position per thread it had been bound by the
+// filter reads, 0.8 ms for 4096 images.)
+constexpr uint32_t kTilePos = 128;
+
 __global__ void __launch_bounds__(128) conv_direct_kernel(const GemmParams p) {
-  extern __shared__ float w_s[];
+  extern __shared__ __align__(16) float w_s[];
   grid_launch_dependents();   // launched with programmatic stream serialization: wait for the stream's earlier work
   grid_dependency_wait();
   const ConvGeo& g = p.geo;
   const uint32_t kk = g.k * g.k * g.c;
+  float* patch_s = w_s + ((kk * g.c_out + 3) & ~3u);
   for (uint32_t i = threadIdx.x; i < kk * g.c_out; i += blockDim.x) {
     const uint32_t row = i / g.c_out, co = i - row * g.c_out;
     const uint64_t idx = p.gbsrc.mn_major ? (uint64_t)row * p.gbsrc.ld + co : (uint64_t)co * p.gbsrc.ld + row;   // (K, c_out) or (c_out, K) rows
     const float v = p.gbsrc.src_is_bf16 ? bf16_to_f32(((const uint16_t*)p.gbsrc.base)[idx]) : ((const float*)p.gbsrc.base)[idx];
     w_s[i] = round_operand(v, p.tf32);
   }
-  __syncthreads();
   const uint32_t per_image = g.out_h * g.out_w;
-  // Work item = (group of kPos positions, chunk of kCoChunk channels), chunk fastest: neighbouring lanes hold
-  // the chunks of one position group, so together they store whole 128-byte lines of the result and share
-  // their input reads, and a small batch still yields enough threads to fill the machine.
-  const uint32_t groups = (p.m + kPos - 1) / kPos, chunks = g.c_out / kCoChunk;
-  const uint64_t items = (uint64_t)groups * chunks;
-  for (uint64_t item = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; item < items; item += (uint64_t)gridDim.x * blockDim.x) {
-    const uint32_t grp = (uint32_t)(item / chunks), co0 = (uint32_t)(item - (uint64_t)grp * chunks) * kCoChunk;
-    // top-left input pixel (before padding is subtracted) and image of each of the thread's positions
-    uint32_t base_y[kPos], base_x[kPos], image[kPos];
-#pragma unroll
-    for (uint32_t q = 0; q < kPos; ++q) {
-      const uint32_t pos = min(grp * kPos + q, p.m - 1);   // a position past the end repeats the last one and is not stored
-      const uint32_t img = pos / per_image, rem = pos - img * per_image;
-      const uint32_t oy = rem / g.out_w;
-      image[q] = img; base_y[q] = oy * g.stride; base_x[q] = (rem - oy * g.out_w) * g.stride;
-    }
+  const uint32_t chunks = g.c_out / kCoChunk, tiles = (p.m + kTilePos - 1) / kTilePos;
+  for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    __syncthreads();   // the filters are in place; the previous tile's patch values are no longer read
     {
+      // thread t stages position t of the tile (a position past the end repeats the last one and is not stored)
+      const uint32_t pos = min(tile * kTilePos + threadIdx.x, p.m - 1);
+      const uint32_t img = pos / per_image, rem = pos - img * per_image;
+      const uint32_t oy = rem / g.out_w, ox = rem - oy * g.out_w;
+      const uint32_t by = oy * g.stride, bx = ox * g.stride;
+      uint32_t r = 0;
+      for (uint32_t ky = 0; ky < g.k; ++ky)
+        for (uint32_t kx = 0; kx < g.k; ++kx) {
+          const uint32_t py = by + ky * g.dilation, px = bx + kx * g.dilation;
+          const bool inside = py >= g.pad && py - g.pad < g.h && px >= g.pad && px - g.pad < g.w;
+          const uint64_t src = inside ? ((uint64_t)(img * g.h + py - g.pad) * g.w + px - g.pad) * g.c_step : 0;
+          for (uint32_t ci = 0; ci < g.c; ++ci, ++r) {
+            float raw = 0.0f;
+            if (inside) raw = p.ga.src_is_bf16 ? bf16_to_f32(((const uint16_t*)p.ga.base)[src + ci]) : round_operand(((const float*)p.ga.base)[src + ci], p.tf32);
+            patch_s[r * kTilePos + threadIdx.x] = raw;
+          }
+        }
+    }
+    __syncthreads();
+    // Work item = (group of kPos positions, chunk of kCoChunk channels), chunk fastest: neighbouring lanes hold the chunks
+    // of one position group, so together they store whole 128-byte lines of the result and share their patch reads.
+    for (uint32_t item = threadIdx.x; item < (kTilePos / kPos) * chunks; item += blockDim.x) {
+      const uint32_t sub = item / chunks, co0 = (item - sub * chunks) * kCoChunk, grp = tile * (kTilePos / kPos) + sub;
       float acc[kPos][kCoChunk];
 #pragma unroll
       for (uint32_t q = 0; q < kPos; ++q)
 #pragma unroll
         for (uint32_t j = 0; j < kCoChunk; ++j) acc[q][j] = 0.0f;
-      for (uint32_t ky = 0; ky < g.k; ++ky)
-        for (uint32_t kx = 0; kx < g.k; ++kx) {
-          int64_t src[kPos];
+#pragma unroll 3
+      for (uint32_t r = 0; r < kk; ++r) {
+        const float4 x4 = *(const float4*)(patch_s + r * kTilePos + sub * kPos);
+        const float xv[kPos] = {x4.x, x4.y, x4.z, x4.w};
+        const float4* w4 = (const float4*)(w_s + (uint64_t)r * g.c_out + co0);
+#pragma unroll
+        for (uint32_t j = 0; j < kCoChunk / 4; ++j) {
+          const float4 wv = w4[j];
 #pragma unroll
           for (uint32_t q = 0; q < kPos; ++q) {
-            const uint32_t py = base_y[q] + ky * g.dilation, px = base_x[q] + kx * g.dilation;
-            const bool inside = py >= g.pad && py - g.pad < g.h && px >= g.pad && px - g.pad < g.w;
-            src[q] = inside ? (int64_t)(((uint64_t)(image[q] * g.h + py - g.pad) * g.w + px - g.pad) * g.c_step) : -1;
-          }
-          const float* wrow = w_s + (uint64_t)((ky * g.k + kx) * g.c) * g.c_out + co0;
-          for (uint32_t ci = 0; ci < g.c; ++ci) {
-            float xv[kPos];
-#pragma unroll
-            for (uint32_t q = 0; q < kPos; ++q) {
-              float raw = 0.0f;
-              if (src[q] >= 0) raw = p.ga.src_is_bf16 ? bf16_to_f32(((const uint16_t*)p.ga.base)[src[q] + ci]) : ((const float*)p.ga.base)[src[q] + ci];
-              xv[q] = p.ga.src_is_bf16 ? raw : round_operand(raw, p.tf32);
-            }
-            const float4* w4 = (const float4*)(wrow + (uint64_t)ci * g.c_out);
-#pragma unroll
-            for (uint32_t j = 0; j < kCoChunk / 4; ++j) {
-              const float4 wv = w4[j];
-#pragma unroll
-              for (uint32_t q = 0; q < kPos; ++q) {
-                acc[q][4 * j] = fmaf(xv[q], wv.x, acc[q][4 * j]);
-                acc[q][4 * j + 1] = fmaf(xv[q], wv.y, acc[q][4 * j + 1]);
-                acc[q][4 * j + 2] = fmaf(xv[q], wv.z, acc[q][4 * j + 2]);
-                acc[q][4 * j + 3] = fmaf(xv[q], wv.w, acc[q][4 * j + 3]);
-              }
-            }
+            acc[q][4 * j] = fmaf(xv[q], wv.x, acc[q][4 * j]);
+            acc[q][4 * j + 1] = fmaf(xv[q], wv.y, acc[q][4 * j + 1]);
+            acc[q][4 * j + 2] = fmaf(xv[q], wv.z, acc[q][4 * j + 2]);
+            acc[q][4 * j + 3] = fmaf(xv[q], wv.w, acc[q][4 * j + 3]);
           }
         }
+      }
+      float bias_r[kCoChunk];
+#pragma unroll
+      for (uint32_t j = 0; j < kCoChunk; ++j) bias_r[j] = p.bias ? p.bias[co0 + j] : 0.0f;
       // epilogue on 8 channels at a time: 16 bytes of bf16 or two 16-byte halves of f32
 #pragma unroll
       for (uint32_t q = 0; q < kPos; ++q) {
@@ -120,10 +124,8 @@ __global__ void __launch_bounds__(128) conv_direct_kernel(const GemmParams p) {
               for (uint32_t e = 0; e < 8; ++e) v[e] += ((const float*)p.c)[off + e];
             }
           }
-          if (p.bias) {
 #pragma unroll
-            for (uint32_t e = 0; e < 8; ++e) v[e] += p.bias[co0 + j + e];
-          }
+          for (uint32_t e = 0; e < 8; ++e) v[e] += bias_r[j + e];
           if (p.residual) {
             if (p.c_is_bf16) {
               const uint4 qq = *(const uint4*)((const uint16_t*)p.residual + off);
@@ -305,17 +307,16 @@ cudaError_t launch_conv_direct_wgrad(const GemmParams& p, uint32_t blocks, cudaS
 bool conv_direct_applies(const GemmParams& p) {
   const ConvGeo& g = p.geo;
   const uint64_t kk = (uint64_t)g.k * g.k * g.c;
-  return g.c <= 4 && g.c_out % kCoChunk == 0 && kk * g.c_out * 4 <= 48 * 1024 && p.vec_store && !p.transpose_out;
+  return g.c <= 4 && g.c_out % kCoChunk == 0 && (kk * g.c_out + kk * kTilePos + 4) * 4 <= 48 * 1024 && p.vec_store && !p.transpose_out;
 }
 
 cudaError_t launch_conv_direct(const GemmParams& p, int sm_count, cudaStream_t stream) {
   if (p.m == 0) return cudaSuccess;
   const ConvGeo& g = p.geo;
-  const size_t smem = (size_t)g.k * g.k * g.c * g.c_out * 4;
-  const uint64_t items = (uint64_t)((p.m + kPos - 1) / kPos) * (g.c_out / kCoChunk);
-  const uint64_t want64 = (items + 127) / 128;
-  const uint32_t cap = (uint32_t)sm_count * 16, want = (uint32_t)(want64 < cap ? want64 : cap);
-  return launch_overlapped(conv_direct_kernel, dim3(want < cap ? want : cap), dim3(128), smem, stream, p);
+  const uint32_t kk = g.k * g.k * g.c;
+  const size_t smem = (size_t)((kk * g.c_out + 3) & ~3u) * 4 + (size_t)kk * kTilePos * 4;   // filters, then one tile of patch values
+  const uint32_t tiles = (p.m + kTilePos - 1) / kTilePos, cap = (uint32_t)sm_count * 4;
+  return launch_overlapped(conv_direct_kernel, dim3(tiles < cap ? tiles : cap), dim3(128), smem, stream, p);
 }
 
 }  // namespace gb

@@ -1782,7 +1782,7 @@ cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream) {
   if (total == 0) return cudaSuccess;
   if (p.splits >= 3 * kReduceGroups) {
     if (p.vec_store && !p.transpose_out && !p.c_is_bf16 && p.batch == 1 && (p.n & 3) == 0 && (p.ldc & 3) == 0 && !p.bias && !p.residual && !p.relu &&
-        !p.round_tf32 && total / 4 < 0xFFFFFFFFull && ((uintptr_t)p.partial & 15) == 0) {
+        !p.round_tf32 && total / 4 < 0xFFFFFFFFull && total / 4 >= 148 * 32 && ((uintptr_t)p.partial & 15) == 0) {   // enough groups of four to fill the machine
       const uint64_t total4 = total / 4;
       const uint32_t blocks4 = (uint32_t)((total4 + 31) / 32 < 148 * 16 ? (total4 + 31) / 32 : 148 * 16);
       return launch_overlapped(splitk_reduce_grouped_vec4_kernel, dim3(blocks4), dim3(32 * kReduceGroups), 0, stream, p);
