@@ -464,8 +464,8 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
     its weight gradient (TN, `+=` into a slice of ONE flat f32 gradient vector).  `per_head` issues the projections
     the way the reference composes attention (one Linear per head and per Q/K/V: 12 products of 8192x256x64 and 4 of
     8192x64x256 per block, src/nn/nn.zig:421-461); `fused_qkv` issues one 8192x256x768 and one 8192x256x256 product
-    instead; `fused_qkv_two_streams` is the same list of launches captured as a graph with two branches: weight
-    gradients, dV / dK and the attention of every second head go to a side stream (a second handle with its own
+    instead and each attention product of a block as ONE launch over (sequence, head) with two batch levels; `fused_qkv_two_streams` is the same list of launches captured as a graph with two branches: weight
+    gradients and dV / dK go to a side stream (a second handle with its own
     workspace), so products that are one wave of tiles or less run beside each other instead of one after the other.  After the captured contraction step the flat gradient vector (3 228 737 floats, all parameters) is
     averaged over the replicas by ONE `gb_allreduce_mean`, outside the graph, where `averageGrads` sits in the
     reference (src/nn/trainer.zig:507-508).  Softmax, layer norm, embedding, loss and Adam are not contractions and
@@ -501,6 +501,7 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
     side_stream = torch.cuda.Stream()
     gpu_side = grad_b200.Gpu(torch.cuda.current_device())   # its own workspace: its products run beside the main handle's
     two_streams = [False]
+    side_used = [False]
 
     class on_side:
         """Runs the enclosed launches on the side stream after everything the main stream has been given so far."""
@@ -508,6 +509,7 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
         def __enter__(self):
             self.active = two_streams[0]
             if self.active:
+                side_used[0] = True
                 side_stream.wait_stream(torch.cuda.current_stream())
                 self.ctx = torch.cuda.stream(side_stream)
                 self.ctx.__enter__()
@@ -519,8 +521,9 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
             return False
 
     def join_side():
-        if two_streams[0]:
+        if two_streams[0] and side_used[0]:   # only a stream that has joined the capture can be waited for
             torch.cuda.current_stream().wait_stream(side_stream)
+            side_used[0] = False
 
     def mm(a, b, out, m, n, k, ta=False, tb=False, acc=False, batch=1, ep=None, strides=None, ld=(0, 0, 0), g=None):
         flops[0] += 2.0 * m * n * k * batch
@@ -568,30 +571,23 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
     def attention(blk, fused, backward):
         b = heads * seqs
         if fused:
-            # (rows, 3*width) activations: head h of Q sits in columns h*hd.. of the first third, row pitch 3*width;
-            # one launch per head, the 64 sequences as the batch
-            # with two streams: forward, odd heads run on the side stream; backward, dV and dK do
-            for hh in range(heads):
-                q, k_, v = (blk["qkv2"][:, part * d + hh * hd:] for part in range(3))
-                dq, dk, dv = (blk["dqkv2"][:, part * d + hh * hd:] for part in range(3))
-                p, dp = blk["p"][hh * seqs:(hh + 1) * seqs], blk["dp"][hh * seqs:(hh + 1) * seqs]
-                o, do = blk["o2"][:, hh * hd:], blk["do2"][:, hh * hd:]
-                st = seq * 3 * d
-                if not backward:
-                    if hh % 2 == 1:
-                        with on_side() as g2:
-                            batched(q, k_, p, seq, seq, hd, False, True, seqs, (st, st, seq * seq), (3 * d, 3 * d, 0), g2)
-                            batched(p, v, o, seq, hd, seq, False, False, seqs, (seq * seq, st, seq * d), (0, 3 * d, d), g2)
-                    else:
-                        batched(q, k_, p, seq, seq, hd, False, True, seqs, (st, st, seq * seq), (3 * d, 3 * d, 0))
-                        batched(p, v, o, seq, hd, seq, False, False, seqs, (seq * seq, st, seq * d), (0, 3 * d, d))
-                else:
-                    with on_side() as g2:
-                        batched(p, do, dv, seq, hd, seq, True, False, seqs, (seq * seq, seq * d, st), (0, d, 3 * d), g2)
-                    batched(do, v, dp, seq, seq, hd, False, True, seqs, (seq * d, st, seq * seq), (d, 3 * d, 0))
-                    with on_side() as g2:
-                        batched(dp, q, dk, seq, hd, seq, True, False, seqs, (seq * seq, st, st), (0, 3 * d, 3 * d), g2)
-                    batched(dp, k_, dq, seq, hd, seq, False, False, seqs, (seq * seq, st, st), (0, 3 * d, 3 * d))
+            # (rows, 3*width) activations: head h of Q sits in columns h*hd.. of the first third, row pitch 3*width.  ONE launch
+            # per product kind: the 64 sequences are the inner batch level (stride one sequence of rows), the heads the outer
+            # one (stride hd columns; seqs matrices in the contiguous score tensors).  With two streams dV and dK go to the side.
+            q, k_, v = (blk["qkv2"][:, part * d:] for part in range(3))
+            dq, dk, dv = (blk["dqkv2"][:, part * d:] for part in range(3))
+            p, dp, o, do = blk["p"], blk["dp"], blk["o2"], blk["do2"]
+            st, sp = seq * 3 * d, seqs * seq * seq
+            if not backward:
+                batched(q, k_, p, seq, seq, hd, False, True, seqs, (st, st, seq * seq), (3 * d, 3 * d, 0), (hd, hd, sp))
+                batched(p, v, o, seq, hd, seq, False, False, seqs, (seq * seq, st, seq * d), (0, 3 * d, d), (sp, hd, hd))
+            else:
+                with on_side() as g2:
+                    batched(p, do, dv, seq, hd, seq, True, False, seqs, (seq * seq, seq * d, st), (0, d, 3 * d), (sp, hd, hd), g2)
+                batched(do, v, dp, seq, seq, hd, False, True, seqs, (seq * d, st, seq * seq), (d, 3 * d, 0), (hd, hd, sp))
+                with on_side() as g2:
+                    batched(dp, q, dk, seq, hd, seq, True, False, seqs, (seq * seq, st, st), (0, 3 * d, 3 * d), (sp, hd, hd), g2)
+                batched(dp, k_, dq, seq, hd, seq, False, False, seqs, (seq * seq, st, st), (0, 3 * d, 3 * d), (sp, hd, hd))
             join_side()
             return
         q, k_, v = blk["qkv"][0:heads].view(b, seq, hd), blk["qkv"][heads:2 * heads].view(b, seq, hd), blk["qkv"][2 * heads:].view(b, seq, hd)
@@ -606,26 +602,10 @@ def transformer_step(gpu, rank, world, dist, torch, cpu_baseline):
             mm(blk["dp"], k_, dq, seq, hd, seq, batch=b)                        # dQ = dS K
             mm(blk["dp"], q, dk, seq, hd, seq, True, False, batch=b)           # dK = dS^T Q
 
-    def batched(a, b_, out, m, n, k, ta, tb, batch, strides, ld, g=None):
-        from grad_b200 import abi as _abi
-        import ctypes as C
-
-        gpu = g or gpu_main
-
-        flops[0] += 2.0 * m * n * k * batch
-        dsc = _abi.GemmDesc()
-        dsc.m, dsc.n, dsc.k, dsc.batch = m, n, k, batch
-        dsc.stride_a, dsc.stride_b, dsc.stride_c = strides
-        dsc.lda, dsc.ldb, dsc.ldc = ld
-        dsc.trans_a, dsc.trans_b = ta, tb
-        dsc.dtype_a = dsc.dtype_b = dsc.dtype_c = _abi.BF16
-        dsc.math = MATH_BF16
-        need = C.c_size_t(0)
-        _abi.check(gpu.lib.gb_gemm_workspace(gpu.handle, C.byref(dsc), C.byref(need)), "gb_gemm_workspace")
-        ws = gpu.scratch(need.value)
-        _abi.check(gpu.lib.gb_gemm(gpu.handle, gpu._stream(), C.byref(dsc), C.c_void_p(a.data_ptr()), C.c_void_p(b_.data_ptr()),
-                                   C.c_void_p(out.data_ptr()), None, None if ws is None else C.c_void_p(ws.data_ptr()), need.value), "gb_gemm")
-        gpu.launches += gpu._count()
+    def batched(a, b_, out, m, n, k, ta, tb, batch, strides, ld, outer_strides, g=None):
+        flops[0] += 2.0 * m * n * k * batch * heads
+        (g or gpu_main).matmulStrided(a, b_, out, m, n, k, MatmulOpts(ta, tb), batch=batch, strides=strides, ld=ld, outer=heads,
+                                      outer_strides=outer_strides, math=MATH_BF16)
 
     def step(blocks, head, fused):
         """Weight gradients are issued before the input gradient that reads the same dy, on the side stream when there is

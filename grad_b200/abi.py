@@ -53,7 +53,9 @@ class GemmDesc(C.Structure):
                 ("lda", C.c_uint32), ("ldb", C.c_uint32), ("ldc", C.c_uint32),
                 ("trans_a", C.c_uint8), ("trans_b", C.c_uint8), ("accumulate", C.c_uint8), ("transpose_out", C.c_uint8),
                 ("dtype_a", C.c_uint8), ("dtype_b", C.c_uint8), ("dtype_c", C.c_uint8), ("math", C.c_uint8),
-                ("deterministic", C.c_uint8), ("reserved", C.c_uint8 * 3)]
+                ("deterministic", C.c_uint8), ("reserved", C.c_uint8 * 3),
+                ("batch_outer", C.c_uint32), ("reserved2", C.c_uint32),
+                ("stride_a_outer", C.c_uint64), ("stride_b_outer", C.c_uint64), ("stride_c_outer", C.c_uint64)]
 
 
 class ConvGeometryC(C.Structure):

@@ -103,6 +103,21 @@ __device__ __forceinline__ Work decode_work(const GemmParams& p, uint32_t w) {
   return out;
 }
 
+// Two batch levels: work item b -> (inner, outer) indices, and where its C matrix starts.
+__device__ __forceinline__ void split_batch(const GemmParams& p, uint32_t batch, uint32_t& inner, uint32_t& outer) {
+  inner = batch;
+  outer = 0;
+  if (p.batch_inner) {
+    outer = fast_div(batch, p.div_batch_inner);
+    inner = batch - outer * p.batch_inner;
+  }
+}
+__device__ __forceinline__ uint64_t c_batch_offset(const GemmParams& p, uint32_t batch) {
+  uint32_t inner, outer;
+  split_batch(p, batch, inner, outer);
+  return (uint64_t)inner * p.stride_c + (uint64_t)outer * p.stride_c_outer;
+}
+
 // ---- gather sources ---------------------------------------------------------------------------------
 
 __device__ __forceinline__ float load_as_f32(const GatherDesc& d, int64_t idx) {
@@ -391,10 +406,12 @@ __device__ __forceinline__ void box_start(const GemmParams& p, const TapWalk& wa
   }
   switch (kind) {
     case kDenseK:
-      b.x = (int32_t)(k0 * epl); b.y = (int32_t)mn0; b.z = (int32_t)work.batch;
+      b.x = (int32_t)(k0 * epl); b.y = (int32_t)mn0;
+      { uint32_t bi, bo; split_batch(p, work.batch, bi, bo); b.z = (int32_t)bi; b.w = (int32_t)bo; }
       break;
     case kDenseMN:
-      b.x = (int32_t)(mn0 + index * epl); b.y = (int32_t)(k0 * epl); b.z = (int32_t)work.batch;
+      b.x = (int32_t)(mn0 + index * epl); b.y = (int32_t)(k0 * epl);
+      { uint32_t bi, bo; split_batch(p, work.batch, bi, bo); b.z = (int32_t)bi; b.w = (int32_t)bo; }
       break;
     case kPatchK: {
       uint32_t cb = 0, tx = 0, ty = 0;
@@ -504,7 +521,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
     }
     return;
   }
-  const uint64_t cbase = (uint64_t)batch * p.stride_c;
+  const uint64_t cbase = c_batch_offset(p, batch);
   float v[32];
 #pragma unroll
   for (uint32_t i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
@@ -617,7 +634,7 @@ __device__ __forceinline__ void epilogue_chunk_copy(const GemmParams& p, const u
 // quarter-warp hit eight different 16-byte bank groups) and lane 0 hands it to the TMA unit, which writes whole
 // rows and clips the box at the edges of C.  The block is reused as soon as the previous store has read it.
 __device__ __forceinline__ void stage_and_store(const CUtensorMap* tmap_c, uint8_t* stage, const uint4 (&q)[4], uint32_t lane, int32_t x,
-                                                int32_t y, int32_t z) {
+                                                int32_t y, int32_t z, int32_t w = -1) {   // w >= 0: a map with two batch levels
   if (lane == 0) bulk_wait_read_all();
   __syncwarp();
   const uint32_t sw = (lane >> 1) & 3;
@@ -627,7 +644,8 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* tmap_c, uint8
   fence_proxy_async_smem();
   __syncwarp();
   if (lane == 0) {
-    tma_store_3d(tmap_c, stage, x, y, z);
+    if (w >= 0) tma_store_4d(tmap_c, stage, x, y, z, w);
+    else tma_store_3d(tmap_c, stage, x, y, z);
     bulk_commit_group();
   }
 }
@@ -721,7 +739,7 @@ __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& 
     return stats;
   }
   const bool live = row < p.m;
-  const uint64_t off = (uint64_t)batch * p.stride_c + (uint64_t)row * p.ldc + col0;
+  const uint64_t off = c_batch_offset(p, batch) + (uint64_t)row * p.ldc + col0;
   float v[32];
 #pragma unroll
   for (uint32_t i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
@@ -781,6 +799,8 @@ __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& 
     for (uint32_t i = 0; i < 32; ++i) v[i] = round_tf32(v[i]);
   }
   const int32_t y = (int32_t)(row - lane);
+  int32_t bz = (int32_t)batch, bw = -1;
+  if (p.batch_inner) { uint32_t bi, bo; split_batch(p, batch, bi, bo); bz = (int32_t)bi; bw = (int32_t)bo; }
   if (p.c_is_bf16) {
     uint4 q[4];
 #pragma unroll
@@ -796,7 +816,7 @@ __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& 
       }
       stats = p.stats == 2 ? chunk_dx_stats(p, v, sstat, slot, off, live, lane) : chunk_stats(v, sstat + 32 * slot, live, lane);
     }
-    stage_and_store(tmap_c, stage, q, lane, (int32_t)col0, y, (int32_t)batch);
+    stage_and_store(tmap_c, stage, q, lane, (int32_t)col0, y, bz, bw);
   } else {
     if constexpr (kStats) stats = chunk_stats(v, sstat + 32 * slot, live, lane);   // the backward sums exist for bf16 maps only
 #pragma unroll
@@ -806,7 +826,7 @@ __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& 
       for (uint32_t j = 0; j < 4; ++j)
         q[j] = make_uint4(__float_as_uint(v[16 * half + 4 * j]), __float_as_uint(v[16 * half + 4 * j + 1]), __float_as_uint(v[16 * half + 4 * j + 2]),
                           __float_as_uint(v[16 * half + 4 * j + 3]));
-      stage_and_store(tmap_c, stage, q, lane, (int32_t)(col0 + 16 * half), y, (int32_t)batch);
+      stage_and_store(tmap_c, stage, q, lane, (int32_t)(col0 + 16 * half), y, bz, bw);
     }
   }
   return stats;
@@ -816,7 +836,7 @@ __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& 
 // residual, no K split, no statistics).  Without a run-time branch per option the chunk is ~100 instructions instead
 // of several hundred: bias values are always staged (zeros when there is no bias) and `floor` is 0 or -inf.
 __device__ __forceinline__ void epilogue_chunk_fast(const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage, const float* sbias, float floor,
-                                                    uint32_t batch, uint32_t row, uint32_t col0, uint32_t lane) {
+                                                    int32_t bz, int32_t bw, uint32_t row, uint32_t col0, uint32_t lane) {
   uint4 q[4];
 #pragma unroll
   for (uint32_t j = 0; j < 4; ++j) {
@@ -826,7 +846,7 @@ __device__ __forceinline__ void epilogue_chunk_fast(const CUtensorMap* tmap_c, c
                       pack_bf16x2(fmaxf(__uint_as_float(acc[8 * j + 4]) + b1.x, floor), fmaxf(__uint_as_float(acc[8 * j + 5]) + b1.y, floor)),
                       pack_bf16x2(fmaxf(__uint_as_float(acc[8 * j + 6]) + b1.z, floor), fmaxf(__uint_as_float(acc[8 * j + 7]) + b1.w, floor)));
   }
-  stage_and_store(tmap_c, stage, q, lane, (int32_t)col0, (int32_t)(row - lane), (int32_t)batch);
+  stage_and_store(tmap_c, stage, q, lane, (int32_t)col0, (int32_t)(row - lane), bz, bw);
 }
 
 __device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
@@ -908,6 +928,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     uint32_t i = 0;
     const bool fast = !kStats && p.tma_store == 2;
     const float floor = p.relu ? 0.0f : -INFINITY;
+    int32_t bz = (int32_t)batch, bw = -1;
+    if (p.batch_inner) { uint32_t bi, bo; split_batch(p, batch, bi, bo); bz = (int32_t)bi; bw = (int32_t)bo; }
     for (uint32_t c = first; c < ncols; c += 2 * step, i += 2) {
       const bool has_b = c + step < ncols;
       tmem_ld_wait();
@@ -917,7 +939,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
         const uint32_t col0 = col_base + tile_col(c);
         if (col0 + 32 <= p.n && row - lane < p.m) {
           if constexpr (kStats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_a, store_stage, sbias + 32 * i, sstat, i, batch, row, col0, lane);
-          else if (fast) epilogue_chunk_fast(tmap_c, acc_a, store_stage, sbias + 32 * i, floor, batch, row, col0, lane);
+          else if (fast) epilogue_chunk_fast(tmap_c, acc_a, store_stage, sbias + 32 * i, floor, bz, bw, row, col0, lane);
           else epilogue_chunk_tma(p, tmap_c, acc_a, store_stage, sbias + 32 * i, batch, split, row, col0, lane);
         } else epilogue_chunk_copy(p, acc_a, batch, split, row, col0, p.bias ? sbias[32 * i + lane] : 0.0f);
       }
@@ -928,7 +950,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
         const uint32_t col0 = col_base + tile_col(c + step);
         if (col0 + 32 <= p.n && row - lane < p.m) {
           if constexpr (kStats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), sstat, i + 1, batch, row, col0, lane);
-          else if (fast) epilogue_chunk_fast(tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), floor, batch, row, col0, lane);
+          else if (fast) epilogue_chunk_fast(tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), floor, bz, bw, row, col0, lane);
           else epilogue_chunk_tma(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), batch, split, row, col0, lane);
         } else epilogue_chunk_copy(p, acc_b, batch, split, row, col0, p.bias ? sbias[32 * (i + 1) + lane] : 0.0f);
       }
@@ -1503,7 +1525,7 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
     const uint32_t row = (uint32_t)(r / p.n), col = (uint32_t)(r - (uint64_t)row * p.n);
     float x = 0.0f;
     for (uint32_t s = 0; s < p.splits; ++s) x += p.partial[(uint64_t)s * total + t];
-    const uint64_t idx = (uint64_t)batch * p.stride_c + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
+    const uint64_t idx = c_batch_offset(p, batch) + (p.transpose_out ? (uint64_t)col * p.ldc + row : (uint64_t)row * p.ldc + col);
     if (p.accumulate) x += load_out(p.c, p.c_is_bf16, idx);
     if (p.bias) x += p.bias[col];
     if (p.residual) x += load_out(p.residual, p.c_is_bf16, idx);
@@ -1791,7 +1813,7 @@ cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream) {
     return launch_overlapped(splitk_reduce_grouped_kernel, dim3(blocks), dim3(32 * kReduceGroups), 0, stream, p);
   }
   // 16-byte path: row-major result, every pointer and pitch 16-byte aligned (vec_store), whole groups of four columns
-  if (p.splits >= 1 && p.vec_store && !p.transpose_out && (p.n & 3) == 0 && (p.ldc & 3) == 0 && (p.stride_c & 3) == 0 &&
+  if (p.splits >= 1 && p.batch_inner == 0 && p.vec_store && !p.transpose_out && (p.n & 3) == 0 && (p.ldc & 3) == 0 && (p.stride_c & 3) == 0 &&
       (uint64_t)p.m * p.n / 4 < 0xFFFFFFFFull && ((uintptr_t)p.partial & 15) == 0) {
     const uint64_t total4 = total / 4;
     const uint32_t blocks4 = (uint32_t)((total4 + 255) / 256 < 148 * 8 ? (total4 + 255) / 256 : 148 * 8);

@@ -125,6 +125,11 @@ struct GemmParams {
   const void* residual;
   float* partial;           // split-K partials: [split][batch][m][n] f32, dense
   uint64_t stride_c;        // batch stride of C in elements
+  // Two batch levels (batch_inner != 0): work item b is product (b / batch_inner, b % batch_inner); operand maps carry the
+  // outer level as their fourth dimension, C as its fourth dimension or through stride_c_outer.
+  uint64_t stride_c_outer;
+  uint32_t batch_inner;
+  FastDiv div_batch_inner;
   uint32_t ldc;
   uint32_t c_is_bf16, transpose_out, accumulate, relu, vec_store;
   uint32_t epi_groups;      // epilogue warps = 4 * epi_groups; group g drains column chunks g, g + groups, ...

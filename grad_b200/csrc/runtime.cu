@@ -179,6 +179,8 @@ struct DenseOperand {
   uint32_t dtype, lines, inner, ld;
   uint64_t batch_stride;
   bool mn_major;            // the contiguous (inner) index is the MN index
+  uint32_t outer = 1;       // second batch level: count and stride in elements
+  uint64_t outer_stride = 0;
 };
 
 void fill_dense_gather(gb::GatherDesc& g, const DenseOperand& o) {
@@ -198,10 +200,12 @@ bool dense_tma(CUtensorMap* map, const DenseOperand& o, bool smem_bf16, uint32_t
   if ((o.dtype == GB_BF16) != smem_bf16) return false;
   if (!aligned16(o.base) || ((uint64_t)o.ld * es) % 16 != 0) return false;
   if (batch > 1 && (o.batch_stride == 0 || (o.batch_stride * es) % 16 != 0)) return false;
-  // Every operand map has four dimensions (the kernel issues one form of copy); a dense one ends in an extent of 1.
-  const uint64_t dims[4] = {o.inner, o.lines, batch, 1};
+  if (o.outer > 1 && (o.outer_stride == 0 || (o.outer_stride * es) % 16 != 0)) return false;
+  // Every operand map has four dimensions (the kernel issues one form of copy); a dense one ends in the outer batch
+  // level, an extent of 1 when there is none.
+  const uint64_t dims[4] = {o.inner, o.lines, batch, o.outer};
   const uint64_t batch_bytes = batch > 1 ? o.batch_stride * es : (uint64_t)o.ld * es * std::max<uint64_t>(o.lines, 1);
-  const uint64_t strides[3] = {(uint64_t)o.ld * es, batch_bytes, batch_bytes * batch};
+  const uint64_t strides[3] = {(uint64_t)o.ld * es, batch_bytes, o.outer > 1 ? o.outer_stride * es : batch_bytes * batch};
   // K-major: box = 128 bytes of K x tile_mn lines.  MN-major: box = 128 bytes of MN x epl K lines.
   const uint32_t box[4] = {epl, o.mn_major ? epl * k_mul : tile_mn, 1, 1};
   if (box[1] > 256) return false;
@@ -392,7 +396,14 @@ int plan_gemm(const gb_handle* h, const gb_gemm_desc* d, const void* a, const vo
   std::memset(&plan.p, 0, sizeof(plan.p));
   GemmParams& p = plan.p;
   const uint32_t batch = std::max<uint32_t>(d->batch, 1);
-  p.m = d->m; p.n = d->n; p.k = d->k; p.batch = batch;
+  const uint32_t outer = std::max<uint32_t>(d->batch_outer, 1);
+  p.m = d->m; p.n = d->n; p.k = d->k; p.batch = batch * outer;
+  if (outer > 1) {
+    if (d->transpose_out || d->k == 0) return GB_ERR_UNSUPPORTED;
+    p.batch_inner = batch;
+    p.div_batch_inner = gb::make_fastdiv_host(batch);
+    p.stride_c_outer = d->stride_c_outer;
+  }
   // The bf16 path is taken whenever an operand or the result is bf16, like `Gpu.matmul` (gpu.zig:644-647).
   uint32_t math = d->math;
   if (math == GB_MATH_F32 && (d->dtype_a == GB_BF16 || d->dtype_b == GB_BF16)) math = GB_MATH_BF16;
@@ -412,6 +423,9 @@ int plan_gemm(const gb_handle* h, const gb_gemm_desc* d, const void* a, const vo
   ob.lines = d->trans_b ? d->n : d->k;
   ob.inner = d->trans_b ? d->k : d->n;
   ob.ld = d->ldb ? d->ldb : ob.inner;
+  oa.outer = ob.outer = outer;
+  oa.outer_stride = d->stride_a_outer;
+  ob.outer_stride = d->stride_b_outer;
   if (oa.ld < oa.inner || ob.ld < ob.inner) return GB_ERR_INVALID;
   fill_dense_gather(p.ga, oa);
   fill_dense_gather(p.gbsrc, ob);
@@ -424,11 +438,14 @@ int plan_gemm(const gb_handle* h, const gb_gemm_desc* d, const void* a, const vo
   set_output(p, c, d->dtype_c, ldc, batch > 1 ? d->stride_c : 0, d->transpose_out, d->accumulate, ep);
 
   const uint32_t min_bn = (plan.tensor && ob.mn_major) ? epl : 32;
-  int rc = finish_plan(h, plan, true, min_bn, ep);
+  if (outer > 1 && !plan.tensor) return GB_ERR_UNSUPPORTED;
+  if (outer > 1 && (d->stride_c_outer * elem_size(d->dtype_c)) % 16 != 0) p.vec_store = 0;   // per-lane stores reach any offset
+  int rc = finish_plan(h, plan, outer == 1, min_bn, ep);   // no K split across two batch levels
   if (rc != GB_OK) return rc;
   if (plan.tensor) {
     p.a_kind = dense_tma(&plan.tmap_a, oa, smem_bf16, batch, 128, epl) ? (oa.mn_major ? gb::kDenseMN : gb::kDenseK) : gb::kGather;
     p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, batch, p.bn, epl) ? (ob.mn_major ? gb::kDenseMN : gb::kDenseK) : gb::kGather;
+    if (outer > 1 && (p.a_kind == gb::kGather || p.b_kind == gb::kGather)) return GB_ERR_UNSUPPORTED;   // the gather warps know one batch stride
     CUtensorMap single = plan.tmap_b;
     if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, batch, rows, epl); }))
       plan.tmap_b = single;
@@ -500,10 +517,17 @@ int prepare_plan(const gb_handle* h, Plan& plan, void* workspace, size_t workspa
   } else if (plan.tensor && p.k != 0 && p.splits == 1 && p.vec_store && !p.transpose_out && !p.rowmap.enabled && p.epi_groups == 2 &&
       !knobs().no_tma_store) {
     const uint32_t es = p.c_is_bf16 ? 2 : 4;
-    const uint64_t dims[3] = {p.n, p.m, p.batch};
-    const uint64_t strides[2] = {(uint64_t)p.ldc * es, p.batch > 1 ? p.stride_c * es : (uint64_t)p.ldc * es * p.m};
-    const uint32_t box[3] = {64 / es, 32, 1};
-    p.tma_store = encode_map(&plan.tmap_c, p.c_is_bf16, p.c, 3, dims, strides, box, false, nullptr, true) ? 1 : 0;
+    if (p.batch_inner) {   // two batch levels: a four-dimensional map of C
+      const uint64_t dims[4] = {p.n, p.m, p.batch_inner, p.batch / p.batch_inner};
+      const uint64_t strides[3] = {(uint64_t)p.ldc * es, p.batch_inner > 1 ? p.stride_c * es : (uint64_t)p.ldc * es * p.m, p.stride_c_outer * es};
+      const uint32_t box[4] = {64 / es, 32, 1, 1};
+      p.tma_store = encode_map(&plan.tmap_c, p.c_is_bf16, p.c, 4, dims, strides, box, false, nullptr, true) ? 1 : 0;
+    } else {
+      const uint64_t dims[3] = {p.n, p.m, p.batch};
+      const uint64_t strides[2] = {(uint64_t)p.ldc * es, p.batch > 1 ? p.stride_c * es : (uint64_t)p.ldc * es * p.m};
+      const uint32_t box[3] = {64 / es, 32, 1};
+      p.tma_store = encode_map(&plan.tmap_c, p.c_is_bf16, p.c, 3, dims, strides, box, false, nullptr, true) ? 1 : 0;
+    }
     // 2: the chunk epilogue without run-time options (bf16 result = max(acc + bias, floor), nothing read back)
     if (p.tma_store && p.c_is_bf16 && !p.accumulate && !p.residual && !p.round_tf32 && !p.stats) p.tma_store = 2;
   }

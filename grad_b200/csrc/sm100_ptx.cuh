@@ -134,6 +134,11 @@ __device__ __forceinline__ void tma_store_3d(const void* tmap, const void* src, 
                ::"l"((uint64_t)tmap), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_4d(const void* tmap, const void* src, int32_t x, int32_t y, int32_t z, int32_t w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"((uint64_t)tmap), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Returns once every committed store of this thread has finished READING its shared-memory source.
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

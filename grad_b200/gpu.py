@@ -252,6 +252,35 @@ class Gpu:
         abi.check(rc, "gb_gemm")
         self.launches += self._count()
 
+    def matmulStrided(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, m: int, n: int, k: int, opts: MatmulOpts = MatmulOpts(),
+                      batch: int = 1, strides=(0, 0, 0), ld=(0, 0, 0), outer: int = 1, outer_strides=(0, 0, 0),
+                      epilogue: Optional[Epilogue] = None, math: Optional[int] = None):
+        """The batched entry with explicit element strides (`GemmShape`, src/gpu/args.zig:1-12) and, with `outer` > 1, a second
+        batch level: product (o, i) starts at i * strides[x] + o * outer_strides[x] in a, b and out.  The pointers may be
+        views into larger tensors (a head's columns of a (rows, heads * width) activation)."""
+        assert not (opts.trans_a and opts.trans_b)
+        d = abi.GemmDesc()
+        d.m, d.n, d.k, d.batch = m, n, k, batch
+        d.stride_a, d.stride_b, d.stride_c = strides
+        d.lda, d.ldb, d.ldc = ld
+        d.batch_outer = outer
+        d.stride_a_outer, d.stride_b_outer, d.stride_c_outer = outer_strides
+        d.trans_a, d.trans_b, d.accumulate = opts.trans_a, opts.trans_b, opts.accumulate
+        d.dtype_a, d.dtype_b, d.dtype_c = _dtype_code(a), _dtype_code(b), _dtype_code(out)
+        d.math = self._gemm_math(a, b, out, MatmulShape(m, n, k, batch * outer), math)
+        d.deterministic = self.deterministic
+        key = bytes(d)
+        need = self._needs.get(key)
+        if need is None:
+            size = C.c_size_t(0)
+            abi.check(self.lib.gb_gemm_workspace(self.handle, C.byref(d), C.byref(size)), "gb_gemm_workspace")
+            need = self._needs[key] = size.value
+        ws = self.scratch(need)
+        rc = self.lib.gb_gemm(self.handle, self._stream(), C.byref(d), _ptr(a), _ptr(b), _ptr(out), self._epilogue(epilogue),
+                              _ptr(ws), need)
+        abi.check(rc, "gb_gemm")
+        self.launches += self._count()
+
     # ---- convolution ------------------------------------------------------------------------------
     def _conv_desc(self, geo: ConvGeometry, x_like, w_like, y_like, math: Optional[int], accumulate: bool, w_layout: int = 0) -> abi.ConvDesc:
         d = abi.ConvDesc()

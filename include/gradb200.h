@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define GB_ABI_VERSION 2
+#define GB_ABI_VERSION 3
 
 typedef struct gb_handle gb_handle;   /* per-device state; one per host thread, like one `Gpu` per thread */
 typedef struct gb_comm gb_comm;       /* one rank of a gradient-averaging group */
@@ -108,6 +108,11 @@ typedef struct {
  *   lda/ldb/ldc: row pitch in elements of the STORED matrices; 0 = dense (the stored row length).
  *   batch > 1: that many consecutive products, operands stride_* elements apart (args.zig:1-12);
  *              a stride of 0 broadcasts that operand.
+ *   batch_outer > 1: a second batch level: product (o, i), i < batch, o < batch_outer, reads and writes at
+ *              i * stride_x + o * stride_x_outer.  For operands whose batch entries are not equally spaced: the heads
+ *              of a (rows, heads * width) activation, one product per (sequence, head) of an attention layer in one
+ *              launch.  Tensor-core path with both operands reachable by TMA only (16-byte aligned strides), no K
+ *              split; otherwise GB_ERR_UNSUPPORTED.
  *   transpose_out: C is written as (n, m) with pitch ldc (args.zig `transpose_out`).
  *   deterministic: split-K partials are combined in a fixed order (gpu.zig:1024-1034); this
  *              library's split-K is always ordered, so the flag only documents the caller's intent. */
@@ -118,6 +123,8 @@ typedef struct {
   uint8_t trans_a, trans_b, accumulate, transpose_out;
   uint8_t dtype_a, dtype_b, dtype_c, math;   /* gb_dtype x3, gb_math */
   uint8_t deterministic, reserved[3];
+  uint32_t batch_outer, reserved2;            /* 0 or 1: a single batch level */
+  uint64_t stride_a_outer, stride_b_outer, stride_c_outer;
 } gb_gemm_desc;
 
 /* Field-for-field copy of `ConvGeometry` (src/gpu/args.zig:78) so a Zig `extern struct` passes by

@@ -218,3 +218,70 @@ def test_rejects_both_transposes(gpu):
         t = torch.zeros(8, 8, device="cuda")
         gpu.matmul(t, t, t, MatmulShape(8, 8, 8), MatmulOpts(True, True))
     assert issubclass(GbError, RuntimeError)
+
+
+@pytest.mark.parametrize("heads,seqs,seq,hd", [(4, 6, 128, 64), (2, 3, 64, 32), (3, 5, 96, 64)])
+def test_two_batch_levels_match_one_launch_per_head(gpu, heads, seqs, seq, hd):
+    """The attention products of a fused-QKV layout -- activations (rows, 3 * heads * hd), one product per (sequence, head)
+    -- as ONE launch with two batch levels (sequence inside, head outside) against one launch per head with a single batch
+    level (src/gpu/args.zig:1-12 strides) and against the oracle: scores = Q K^T (NT), mix = P V (NN), dV = P^T dO (TN)."""
+    import torch
+    from grad_b200 import MatmulOpts
+    from oracle import binding as orc
+
+    d = heads * hd
+    rows = seqs * seq
+    rng = np.random.default_rng(77 + heads)
+    qkv = orc.bf16_round(rng.standard_normal((rows, 3 * d), dtype=np.float32))
+    do_ = orc.bf16_round(rng.standard_normal((rows, d), dtype=np.float32))
+    tq, tdo = to_dev(qkv, True), to_dev(do_, True)
+    st = seq * 3 * d
+
+    def run(two_levels, a, b, out, m, n, k, opts, strides, ld, outer_strides):
+        if two_levels:
+            gpu.matmulStrided(a(0), b(0), out(0), m, n, k, opts, batch=seqs, strides=strides, ld=ld, outer=heads, outer_strides=outer_strides)
+        else:
+            for h in range(heads):
+                gpu.matmulStrided(a(h), b(h), out(h), m, n, k, opts, batch=seqs, strides=strides, ld=ld)
+
+    results = []
+    for two_levels in (True, False):
+        p = torch.full((heads * seqs, seq, seq), -7.0, dtype=torch.bfloat16, device="cuda")
+        o = torch.full((rows, d), -7.0, dtype=torch.bfloat16, device="cuda")
+        dv = torch.full((rows, 3 * d), -7.0, dtype=torch.bfloat16, device="cuda")
+        q = lambda h: tq[:, h * hd:]
+        k_ = lambda h: tq[:, d + h * hd:]
+        v = lambda h: tq[:, 2 * d + h * hd:]
+        run(two_levels, q, k_, lambda h: p[h * seqs:], seq, seq, hd, MatmulOpts(False, True), (st, st, seq * seq), (3 * d, 3 * d, 0),
+            (hd, hd, seqs * seq * seq))
+        run(two_levels, lambda h: p[h * seqs:], v, lambda h: o[:, h * hd:], seq, hd, seq, MatmulOpts(), (seq * seq, st, seq * d), (0, 3 * d, d),
+            (seqs * seq * seq, hd, hd))
+        run(two_levels, lambda h: p[h * seqs:], lambda h: tdo[:, h * hd:], lambda h: dv[:, 2 * d + h * hd:], seq, hd, seq, MatmulOpts(True, False),
+            (seq * seq, seq * d, st), (0, d, 3 * d), (seqs * seq * seq, hd, hd))
+        torch.cuda.synchronize()
+        results.append((p.clone(), o.clone(), dv.clone()))
+    for one, per_head in zip(results[0], results[1]):
+        assert torch.equal(one, per_head)
+    # and against the oracle: head 1 of the second sequence
+    h, s_ = 1 % heads, 1 % seqs
+    r0 = s_ * seq
+    qh, kh, vh = (qkv[r0:r0 + seq, part * d + h * hd:part * d + (h + 1) * hd] for part in range(3))
+    want_p = orc.matmul_tiled(np.ascontiguousarray(qh), np.ascontiguousarray(kh), seq, hd, seq, False, True)
+    got_p = to_host(results[0][0][h * seqs + s_])
+    assert rel_fro(got_p, want_p) <= TOL_BF16
+    want_o = orc.matmul_tiled(orc.bf16_round(got_p), np.ascontiguousarray(vh), seq, seq, hd, False, False)
+    assert rel_fro(to_host(results[0][1][r0:r0 + seq, h * hd:(h + 1) * hd]), want_o) <= TOL_BF16
+    # untouched columns of dv stay as they were (the launch writes the V third only)
+    assert (to_host(results[0][2][:, :2 * d]) == -7.0).all()
+
+
+def test_two_batch_levels_reject_what_they_cannot_do(gpu):
+    """Strict f32 and operands that TMA cannot reach have no second batch level: GB_ERR_UNSUPPORTED, nothing launched."""
+    import torch
+    from grad_b200 import MatmulOpts
+    from grad_b200.abi import GbError
+
+    a = torch.zeros((4, 64, 64), device="cuda")
+    out = torch.zeros((4, 64, 64), device="cuda")
+    with pytest.raises(GbError):
+        gpu.matmulStrided(a, a, out, 64, 64, 64, MatmulOpts(), batch=2, strides=(4096, 4096, 4096), outer=2, outer_strides=(8192, 8192, 8192), math=0)
