@@ -19,8 +19,9 @@
 //               loads: any pitch, f32 -> bf16 conversion on the fly, implicit im2col of NHWC activations
 //               for any stride / dilation / padding / channel count.
 //
-// The prologue (barriers, TMEM, cluster sync) touches no global memory and is followed by griddepcontrol.wait:
-// launched with programmatic stream serialization it overlaps the tail of the previous kernel in the stream.
+// The prologue (barriers by warp 2, TMEM by warp 1, the producer's box set-up by warp 0, cluster sync) touches no global
+// memory; launched with programmatic stream serialization it overlaps the tail of the previous kernel in the stream, and
+// each role executes griddepcontrol.wait only right before its first global access.
 //
 // The same kernel serves the dense matmul family (NN / NT / TN through K-major or MN-major shared-memory
 // descriptors, no packed or transposed copies) and the implicit-GEMM convolutions (forward, input
