@@ -285,3 +285,34 @@ def test_two_batch_levels_reject_what_they_cannot_do(gpu):
     out = torch.zeros((4, 64, 64), device="cuda")
     with pytest.raises(GbError):
         gpu.matmulStrided(a, a, out, 64, 64, 64, MatmulOpts(), batch=2, strides=(4096, 4096, 4096), outer=2, outer_strides=(8192, 8192, 8192), math=0)
+
+
+@pytest.mark.parametrize("math,tol", [(1, TOL_TF32), (2, TOL_BF16)])
+@pytest.mark.parametrize("m,n,k", [(96, 40, 72), (200, 136, 64)])
+def test_two_batch_levels_with_ragged_tiles_against_the_oracle(gpu, math, tol, m, n, k):
+    """Two batch levels on shapes whose tiles overhang (rows past m, a last chunk narrower than 32 columns: the per-lane
+    store path) and with padded pitches, every product against the oracle; accumulate adds to the old C."""
+    import torch
+    from grad_b200 import MatmulOpts
+    from oracle import binding as orc
+
+    inner, outer = 3, 2
+    lda, ldb, ldc = k + 8, n + 8, n + 8
+    rng = np.random.default_rng(5 + m + math)
+    a = rng.standard_normal((outer, inner, m, lda), dtype=np.float32)
+    b = rng.standard_normal((outer, inner, k, ldb), dtype=np.float32)
+    c0 = rng.standard_normal((outer, inner, m, ldc), dtype=np.float32)
+    half = math == 2
+    if half:
+        a, b, c0 = orc.bf16_round(a), orc.bf16_round(b), orc.bf16_round(c0)
+    ta, tb, tc = to_dev(a, half), to_dev(b, half), to_dev(c0, half)
+    gpu.matmulStrided(ta, tb, tc, m, n, k, MatmulOpts(False, False, True), batch=inner, strides=(m * lda, k * ldb, m * ldc), ld=(lda, ldb, ldc),
+                      outer=outer, outer_strides=(inner * m * lda, inner * k * ldb, inner * m * ldc), math=math)
+    torch.cuda.synchronize()
+    got = to_host(tc)
+    for o in range(outer):
+        for i in range(inner):
+            want = orc.matmul_tiled(np.ascontiguousarray(a[o, i, :, :k]), np.ascontiguousarray(b[o, i, :, :n]), m, k, n, False, False,
+                                    out=np.ascontiguousarray(c0[o, i, :, :n]))
+            assert rel_fro(got[o, i, :, :n], want) <= tol, (o, i, rel_fro(got[o, i, :, :n], want))
+            assert np.array_equal(got[o, i, :, n:], c0[o, i, :, n:])   # the padding columns are not written
