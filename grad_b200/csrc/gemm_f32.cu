@@ -146,6 +146,21 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmParams p) {
 // the MLP's one-tile products).  Each thread keeps pointers to its elements of the next K step and bumps them;
 // the next step's elements are fetched into registers while the current step is multiplied out of shared
 // memory.  TM x TN tile, 256 threads, (TM/16) x (TN/16) accumulators per thread.
+// Two IEEE fused multiply-adds in one instruction (sm_100: fma.rn.f32x2 on register pairs): the same bits as two scalar
+// FMAs at half the issue slots, which is what bounds these kernels (64 FMAs against four 16-byte shared-memory reads per K
+// value and thread).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
 template <int TM, int TN>
 __global__ void __launch_bounds__(256) gemm_f32_dense_kernel(const GemmParams p) {
   constexpr int RM = TM / 16, RN = TN / 16, EA = TM * 16 / 256, EB = TN * 16 / 256;
@@ -197,11 +212,11 @@ __global__ void __launch_bounds__(256) gemm_f32_dense_kernel(const GemmParams p)
     }
   };
   const uint32_t tr = tid / 16, tc = tid % 16;
-  float acc[RM][RN];
+  uint64_t acc2[RM][RN / 2];   // pairs of neighbouring columns
 #pragma unroll
   for (int i = 0; i < RM; ++i)
 #pragma unroll
-    for (int j = 0; j < RN; ++j) acc[i][j] = 0.0f;
+    for (int j = 0; j < RN / 2; ++j) acc2[i][j] = 0ull;
   if (k_begin < k_end) load_step(k_begin);
   for (uint32_t k0 = k_begin; k0 < k_end; k0 += kTK) {
 #pragma unroll
@@ -212,7 +227,8 @@ __global__ void __launch_bounds__(256) gemm_f32_dense_kernel(const GemmParams p)
     if (k0 + kTK < k_end) load_step(k0 + kTK);
 #pragma unroll
     for (uint32_t kk = 0; kk < kTK; ++kk) {
-      float a[RM], b[RN];
+      float a[RM];
+      uint64_t b2[RN / 2];
 #pragma unroll
       for (int i = 0; i < RM; i += 4) {
         const float4 v = *(const float4*)&As[kk][tr * RM + i];
@@ -221,15 +237,23 @@ __global__ void __launch_bounds__(256) gemm_f32_dense_kernel(const GemmParams p)
 #pragma unroll
       for (int j = 0; j < RN; j += 4) {
         const float4 v = *(const float4*)&Bs[kk][tc * RN + j];
-        b[j] = v.x; b[j + 1] = v.y; b[j + 2] = v.z; b[j + 3] = v.w;
+        b2[j / 2] = pack_f32x2(v.x, v.y);
+        b2[j / 2 + 1] = pack_f32x2(v.z, v.w);
       }
 #pragma unroll
-      for (int i = 0; i < RM; ++i)
+      for (int i = 0; i < RM; ++i) {
+        const uint64_t aa = pack_f32x2(a[i], a[i]);
 #pragma unroll
-        for (int j = 0; j < RN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < RN / 2; ++j) acc2[i][j] = fma_f32x2(aa, b2[j], acc2[i][j]);
+      }
     }
     __syncthreads();
   }
+  float acc[RM][RN];
+#pragma unroll
+  for (int i = 0; i < RM; ++i)
+#pragma unroll
+    for (int j = 0; j < RN / 2; ++j) unpack_f32x2(acc2[i][j], acc[i][2 * j], acc[i][2 * j + 1]);
 #pragma unroll
   for (int i = 0; i < RM; ++i) {
     const uint32_t row = m0 + tr * RM + i;
