@@ -146,21 +146,6 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmParams p) {
 // the MLP's one-tile products).  Each thread keeps pointers to its elements of the next K step and bumps them;
 // the next step's elements are fetched into registers while the current step is multiplied out of shared
 // memory.  TM x TN tile, 256 threads, (TM/16) x (TN/16) accumulators per thread.
-// Two IEEE fused multiply-adds in one instruction (sm_100: fma.rn.f32x2 on register pairs): the same bits as two scalar
-// FMAs at half the issue slots, which is what bounds these kernels (64 FMAs against four 16-byte shared-memory reads per K
-// value and thread).
-__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-
 template <int TM, int TN>
 __global__ void __launch_bounds__(256) gemm_f32_dense_kernel(const GemmParams p) {
   constexpr int RM = TM / 16, RN = TN / 16, EA = TM * 16 / 256, EB = TN * 16 / 256;

@@ -99,6 +99,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// Two IEEE fused multiply-adds in one instruction (sm_100: fma.rn.f32x2 on register pairs): the same bits as two scalar
+// FMAs at half the issue slots, which is what bounds the CUDA-core kernels (64 FMAs against four or five 16-byte shared-memory
+// reads per K value and thread).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------------------
 // A kernel launched with the programmatic-serialization attribute may start while its predecessor in the stream
 // is still running; `grid_dependency_wait` returns once every predecessor has completed and its memory is
