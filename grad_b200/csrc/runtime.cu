@@ -309,8 +309,11 @@ int finish_plan(const gb_handle* h, Plan& plan, bool allow_split, uint32_t min_b
     p.k_blocks_total = ceil_div(p.k, 16);
     const uint32_t tiles = ceil_div(p.m, 64) * ceil_div(p.n, 64) * p.batch;
     uint32_t splits = 1;
-    if (allow_split && tiles > 0 && tiles < 2u * h->sm_count && p.k_blocks_total >= 32)
-      splits = std::max(1u, std::min(ceil_div(2u * h->sm_count, tiles), p.k_blocks_total / 16));
+    // A 16-deep K step of the CUDA-core kernel is one global-load round trip (~1 us) whatever the tile count, so a
+    // product of a few tiles is as slow as its K is deep (64 x 128 x 784: 17 us in three parts): parts of two steps each,
+    // as many as fill the machine, and the reduce launch (~3 us) costs less than the steps it removes.
+    if (allow_split && tiles > 0 && tiles < 2u * h->sm_count && p.k_blocks_total >= 4)
+      splits = std::max(1u, std::min(ceil_div(2u * h->sm_count, tiles), p.k_blocks_total / 2));
     p.k_blocks_per_split = std::max(1u, ceil_div(p.k_blocks_total, splits));
     p.splits = std::max(1u, ceil_div(p.k_blocks_total, p.k_blocks_per_split));
     p.tiles_m = ceil_div(p.m, 64);
