@@ -48,6 +48,7 @@ constexpr uint32_t kHeaderBytes = 1024;  // barriers + TMEM base + abort flag, a
 struct SmemHeader {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
+  uint64_t xfull[kMaxStages];   // transformed-operand plans: the stage's A tile has been rewritten in place
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -1083,7 +1084,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t epi_threads = 128 * p.epi_groups;
-  const bool has_gather = blockDim.x > 64 + epi_threads;
+  const bool has_gather = p.a_kind == kGather || p.b_kind == kGather;   // the extra warps gather (else, with p.xform, they transform)
   const uint32_t total_work = p.tiles_m * p.tiles_n * p.batch * p.splits;
   const uint32_t tmem_cols = p.bn * 2 <= 32 ? 32u : (p.bn * 2 <= 64 ? 64u : (p.bn * 2 <= 128 ? 128u : (p.bn * 2 <= 256 ? 256u : 512u)));
 
@@ -1099,6 +1100,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     for (uint32_t s = 0; s < p.stages; ++s) {
       mbar_init(&hdr->full[s], full_count);
       mbar_init(&hdr->empty[s], 1);
+      mbar_init(&hdr->xfull[s], kGatherThreads / 32);
     }
     for (uint32_t b = 0; b < 2; ++b) {
       mbar_init(&hdr->acc_full[b], 1);
@@ -1173,6 +1175,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     // addresses in uniform registers, and one tcgen05.mma costs ~40-48 issue cycles instead of ~92.
     if (elect_one()) {
       const MmaSetup ms = make_mma_setup(p, kBM, p.bn, smem_u32(tiles), stage_bytes, a_bytes);
+      uint64_t* const stage_ready = p.xform ? hdr->xfull : hdr->full;   // a transformed operand is ready one hand-off later
       uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
       bool ok = true;
       uint32_t ready = 0;   // the first stage is waited for in the ordinary way
@@ -1183,11 +1186,11 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * p.bn;
         for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
-          if (!(ok = mbar_wait_peeked(&hdr->full[stage], phase, ready, abort_flag, kStatusMmaTimeout))) break;
+          if (!(ok = mbar_wait_peeked(&stage_ready[stage], phase, ready, abort_flag, kStatusMmaTimeout))) break;
           uint32_t next_stage = stage + 1, next_phase = phase;
           if (next_stage == p.stages) { next_stage = 0; next_phase ^= 1; }
           const bool more = kb + 1 < work.kb_end || w + gridDim.x < total_work;
-          ready = more ? mbar_try_wait(&hdr->full[next_stage], next_phase) : 0u;
+          ready = more ? mbar_try_wait(&stage_ready[next_stage], next_phase) : 0u;
           tc_fence_after_sync();
           if (p.col_taps) {
             for (uint32_t t = 0; t < p.col_taps; ++t) {
@@ -1262,7 +1265,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     }
     if constexpr (kStats) if (ok) flush_stats(p, sstat, warp - 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
     if (tma_out && lane == 0) bulk_wait_all();   // the staging block must outlive its last store
-  } else {
+  } else if (has_gather) {
     // ===== gather warps =====
     grid_dependency_wait();
     const uint32_t tid = threadIdx.x - 64 - epi_threads;
@@ -1282,6 +1285,45 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&hdr->full[stage]);
         if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (p.xform) {
+    // ===== transform warps: relu(scale * x + shift) over each landed A tile, in place =====
+    // The copy filled whatever lies outside the image with NaN; fma keeps it NaN and max(NaN, 0) is 0, so padding ends up
+    // exactly zero and in-bounds values become what the normalised-and-rectified map would have held (src/gpu/device.zig:
+    // 77-86, 1604-1612).  A line is 64 channels of one pixel (the channel block of this K block: blocks are innermost in
+    // every K walk); its 16-byte chunk j sits at chunk j ^ (line % 8).
+    grid_dependency_wait();
+    const uint32_t tid = threadIdx.x - 64 - epi_threads;
+    const uint32_t a_lines = (p.col_taps ? p.a_box_bytes : kATileBytes) / kLineBytes;
+    const uint32_t cblocks = max(p.walk.cblocks, 1u);
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+      const Work work = decode_work(p, w);
+      if (work.empty) continue;
+      uint32_t cb = work.kb_begin % cblocks;
+      for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
+        ok = mbar_wait(&hdr->full[stage], phase, abort_flag, kStatusProducerTimeout);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        uint8_t* a_tile = tiles + stage * stage_bytes;
+        const uint16_t* scale = p.affine_scale + cb * 64;
+        const uint16_t* shift = p.affine_shift + cb * 64;
+        for (uint32_t e = tid; e < a_lines * 8; e += kGatherThreads) {
+          const uint32_t l = e >> 3, pc = e & 7, j = pc ^ (l & 7);
+          uint4* at = (uint4*)(a_tile + l * kLineBytes + pc * 16);
+          uint4 v = *at;
+          const uint4 sc = *(const uint4*)(scale + j * 8), sh = *(const uint4*)(shift + j * 8);
+          v = make_uint4(affine_relu_bf16x2(v.x, sc.x, sh.x), affine_relu_bf16x2(v.y, sc.y, sh.y), affine_relu_bf16x2(v.z, sc.z, sh.z),
+                         affine_relu_bf16x2(v.w, sc.w, sh.w));
+          *at = v;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&hdr->xfull[stage]);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        if (++cb == cblocks) cb = 0;
       }
     }
   }
@@ -1797,7 +1839,9 @@ cudaError_t launch_gemm_sm100(const GemmParams& p, const CUtensorMap& tmap_a, co
   const bool gather = p.a_kind == kGather || p.b_kind == kGather;
   const uint32_t grid = total_work < (uint32_t)sm_count ? total_work : (uint32_t)sm_count;
   auto kernel = p.stats ? gemm_sm100_kernel<true> : gemm_sm100_kernel<false>;
-  return launch_overlapped(kernel, dim3(grid), dim3(64 + 128 * p.epi_groups + (gather ? kGatherThreads : 0)), gemm_smem_bytes(p), stream, p, tmap_a, tmap_b, tmap_c);
+  // the extra warps gather operands TMA cannot fetch, or rewrite landed tiles of a transformed operand
+  return launch_overlapped(kernel, dim3(grid), dim3(64 + 128 * p.epi_groups + ((gather || p.xform) ? kGatherThreads : 0)), gemm_smem_bytes(p), stream, p, tmap_a,
+                           tmap_b, tmap_c);
 }
 
 cudaError_t launch_splitk_reduce(const GemmParams& p, cudaStream_t stream) {

@@ -119,6 +119,10 @@ struct GemmParams {
   // that were never written out); bf16[c] each, applied by the gather warps to in-bounds taps only (padding stays zero)
   const uint16_t* affine_scale;
   const uint16_t* affine_shift;
+  // 1: the A operand stands for relu(scale * x + shift) and arrives by TMA with out-of-bounds elements filled with NaN;
+  // the two extra warps rewrite each landed A tile in place (NaN -> 0: padding stays zero) and only then hand the stage to
+  // the MMA issuer.  0 with affine_scale set: the gather warps apply the transform while they build the tile.
+  uint32_t xform;
   // output
   void* c;
   const float* bias;

@@ -100,8 +100,11 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 // Encodes a tiled map with 128-byte swizzle.  dims/strides/box follow the driver's convention: dims[0] is
 // the contiguous one, strides (bytes) start at dims[1].
+// `oob_nan`: elements outside the tensor arrive as NaN instead of zero (for an operand that is transformed after it lands and
+// whose padding must come out as exactly zero: see GemmParams::xform).
 bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                const uint32_t* box, bool swizzle_32b_chunks = false, const uint32_t* elem_strides = nullptr, bool swizzle_64b = false) {
+                const uint32_t* box, bool swizzle_32b_chunks = false, const uint32_t* elem_strides = nullptr, bool swizzle_64b = false,
+                bool oob_nan = false) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t gdims[5];
@@ -117,7 +120,8 @@ bool encode_map(CUtensorMap* map, bool bf16, const void* base, uint32_t rank, co
                         gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         swizzle_64b ? CU_TENSOR_MAP_SWIZZLE_64B
                                     : (swizzle_32b_chunks ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B),
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        oob_nan ? CU_TENSOR_MAP_FLOAT_OOB_FILL_NAN_REQUEST_ZERO_FMA : CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
@@ -699,7 +703,7 @@ bool patch_box(uint32_t count, uint32_t grid_h, uint32_t grid_w, uint32_t& bw, u
 // 4-D map over an NHWC tensor {channels, width, height, images} with a box of `epl` channels x (bw, bh, bn).
 bool nhwc_tma(CUtensorMap* map, const void* base, bool smem_bf16, uint32_t dtype, uint32_t channels, uint32_t c_step, uint32_t width,
               uint32_t height, uint32_t images, uint32_t epl, uint32_t bw, uint32_t bh, uint32_t bn, bool mn_major = false,
-              uint32_t conv_stride = 1) {
+              uint32_t conv_stride = 1, bool oob_nan = false) {
   const uint32_t es = smem_bf16 ? 2 : 4;
   if ((dtype == GB_BF16) != smem_bf16) return false;
   if (channels % epl != 0 || !aligned16(base) || ((uint64_t)c_step * es) % 16 != 0) return false;
@@ -710,7 +714,7 @@ bool nhwc_tma(CUtensorMap* map, const void* base, bool smem_bf16, uint32_t dtype
   const uint32_t box[4] = {epl, bw * conv_stride, bh * conv_stride, bn};
   const uint32_t estr[4] = {1, conv_stride, conv_stride, 1};
   if (box[1] > 256 || box[2] > 256) return false;
-  return encode_map(map, smem_bf16, base, 4, dims, strides, box, !smem_bf16 && mn_major, estr);
+  return encode_map(map, smem_bf16, base, 4, dims, strides, box, !smem_bf16 && mn_major, estr, false, oob_nan);
 }
 
 // K walk of the patch boxes of a forward pass (taps in storage order, patch origin at -pad).
@@ -847,7 +851,13 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       walk_forward(p.walk, g, epl);
       const bool view = g.k == 1 && g.pad == 0 && g.stride > 1 && !knobs().no_strided_tma;
       if (affine) {
-        // stays gathered
+        // The virtual normalised input: fetched by TMA with NaN outside the image and rewritten in place by the transform
+        // warps; where no TMA map fits it stays with the gather warps, which transform while they build the tile.
+        if (smem_bf16 && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+            nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, false, g.stride, true)) {
+          p.a_kind = gb::kPatchK;
+          p.xform = 1;
+        }
       } else if (view && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
           nhwc_view_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g, epl, p.box_w, p.box_h, p.box_n, false)) {
         p.a_kind = gb::kPatchK;
@@ -860,11 +870,12 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       auto choose = [&](int pair_mode, uint32_t min_fit) {
         plan = before;
         CUtensorMap single = plan.tmap_b;
-        if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }, pair_mode))
+        // (the transform warps exist in the single-CTA kernel only)
+        if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }, p.xform ? 2 : pair_mode))
           plan.tmap_b = single;
         if (g.stride == 1)
           try_column_stages(plan, [&](uint32_t rows) {
-            return nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, rows, 1);
+            return nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, rows, 1, false, 1, p.xform != 0);
           }, min_fit);
       };
       if (want_cols < 0) {

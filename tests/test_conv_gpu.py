@@ -561,7 +561,9 @@ def test_forward_and_weight_gradient_over_a_virtual_normalised_input(gpu, case):
     sums = torch.zeros(2 * d.c_out, device="cuda")
     shift = to_dev(np.zeros(d.c_out, np.float32))
     gpu.convForwardAffine(tx, tw, y, geo, *norm, epilogue=Epilogue(stats_shift=shift, stats_sums=sums))
-    assert gpu.last_plan()["a_kind"] == 5                          # gathered: the transform happens while the tile is built
+    # 64-channel blocks of a stride-1 layer arrive by TMA (NaN outside the image) and are rewritten in place before the MMAs read
+    # them; anything TMA cannot fetch is transformed by the gather warps while they build the tile
+    assert gpu.last_plan()["a_kind"] == (2 if case[6] == 1 else 5), gpu.last_plan()
     y_written = torch.empty_like(y)
     gpu.convForward(to_dev(z, True), tw, y_written, geo)           # the same layer on the written-out map
     gw = torch.zeros((d.taps, d.c_out), device="cuda")
