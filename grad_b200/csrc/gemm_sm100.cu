@@ -1293,31 +1293,46 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     // exactly zero and in-bounds values become what the normalised-and-rectified map would have held (src/gpu/device.zig:
     // 77-86, 1604-1612).  A line is 64 channels of one pixel (the channel block of this K block: blocks are innermost in
     // every K walk); its 16-byte chunk j sits at chunk j ^ (line % 8).
+    // In a weight gradient the patch operand is MN-major: a line is still 64 channels of one pixel, but the channel block
+    // belongs to the BOX (64 of the tile's (tap, channel) rows), not to the K block.
     grid_dependency_wait();
     const uint32_t tid = threadIdx.x - 64 - epi_threads;
-    const uint32_t a_lines = (p.col_taps ? p.a_box_bytes : kATileBytes) / kLineBytes;
-    const uint32_t cblocks = max(p.walk.cblocks, 1u);
+    const uint32_t a_lines = (p.col_taps ? p.a_box_bytes : kATileBytes * kmul) / kLineBytes;
+    const uint32_t cblocks = max(p.walk.cblocks, 1u), box_lines = 64 * kmul;
     uint32_t stage = 0, phase = 0;
     bool ok = true;
     for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
       const Work work = decode_work(p, w);
       if (work.empty) continue;
       uint32_t cb = work.kb_begin % cblocks;
+      const uint32_t row_base = (work.m_tile * kBM) % p.geo.c;   // MN-major: first channel of the tile's first box
       for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
         ok = mbar_wait(&hdr->full[stage], phase, abort_flag, kStatusProducerTimeout);
         ok = __all_sync(0xFFFFFFFFu, ok);
         if (!ok) break;
         uint8_t* a_tile = tiles + stage * stage_bytes;
-        const uint16_t* scale = p.affine_scale + cb * 64;
-        const uint16_t* shift = p.affine_shift + cb * 64;
-        for (uint32_t e = tid; e < a_lines * 8; e += kGatherThreads) {
-          const uint32_t l = e >> 3, pc = e & 7, j = pc ^ (l & 7);
-          uint4* at = (uint4*)(a_tile + l * kLineBytes + pc * 16);
-          uint4 v = *at;
-          const uint4 sc = *(const uint4*)(scale + j * 8), sh = *(const uint4*)(shift + j * 8);
-          v = make_uint4(affine_relu_bf16x2(v.x, sc.x, sh.x), affine_relu_bf16x2(v.y, sc.y, sh.y), affine_relu_bf16x2(v.z, sc.z, sh.z),
-                         affine_relu_bf16x2(v.w, sc.w, sh.w));
-          *at = v;
+        // Thread t owns physical chunk t % 8 of lines t / 8, t / 8 + 8, ...: line % 8 is the same for all of them, so the
+        // thread's logical chunk (its eight channels within the block) is fixed and its scale / shift values are loaded
+        // once per stage (per box of an MN-major operand), not once per chunk.
+        const uint32_t pc = tid & 7, l0 = tid >> 3, jch = pc ^ (l0 & 7);
+        const uint32_t n_boxes = p.a_mn_major ? a_lines / box_lines : 1u, lines_per_box = p.a_mn_major ? box_lines : a_lines;
+        for (uint32_t box = 0; box < n_boxes; ++box) {
+          uint32_t c0 = cb * 64;
+          if (p.a_mn_major) {
+            c0 = row_base + box * 64;
+            if (c0 >= p.geo.c) c0 -= p.geo.c;
+          }
+          const uint4 sc = *(const uint4*)(p.affine_scale + c0 + jch * 8), sh = *(const uint4*)(p.affine_shift + c0 + jch * 8);
+          uint8_t* base = a_tile + (box * lines_per_box + l0) * kLineBytes + pc * 16;
+          const uint32_t rounds = (lines_per_box - l0 + 7) / 8;   // lines l0, l0 + 8, ... of this box
+#pragma unroll 4
+          for (uint32_t r = 0; r < rounds; ++r) {
+            uint4* at = (uint4*)(base + r * 8 * kLineBytes);
+            uint4 v = *at;
+            v = make_uint4(affine_relu_bf16x2(v.x, sc.x, sh.x), affine_relu_bf16x2(v.y, sc.y, sh.y), affine_relu_bf16x2(v.z, sc.z, sh.z),
+                           affine_relu_bf16x2(v.w, sc.w, sh.w));
+            *at = v;
+          }
         }
         fence_proxy_async_smem();
         __syncwarp();

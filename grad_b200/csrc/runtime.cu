@@ -967,7 +967,12 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       p.a_kind = gb::kGather;
       const bool view = g.k == 1 && g.pad == 0 && g.stride > 1 && !knobs().no_strided_tma;
       if (affine) {
-        // stays gathered
+        // as in the forward pass: TMA with NaN outside the image + the transform warps, else the gather warps
+        if (smem_bf16 && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+            nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, true, g.stride, true)) {
+          p.a_kind = gb::kPatchMN;
+          p.xform = 1;
+        }
       } else if (view && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
           nhwc_view_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g, epl, p.box_w, p.box_h, p.box_n, true)) {
         p.a_kind = gb::kPatchMN;
@@ -978,7 +983,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       p.b_kind = dense_tma(&plan.tmap_b, ob, smem_bf16, 1, p.bn, epl) ? gb::kDenseMN : gb::kGather;
       {
         CUtensorMap single = plan.tmap_b;
-        if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }, 0, true))
+        if (!try_pair(h, plan, min_bn, [&](uint32_t rows) { return dense_tma(&plan.tmap_b, ob, smem_bf16, 1, rows, epl); }, p.xform ? 2 : 0, true))
           plan.tmap_b = single;
       }
       // Both operands are MN-major (one line per position), so two K blocks per stage are simply boxes of twice
@@ -989,7 +994,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       if (!p.cta_pair && p.a_kind == gb::kPatchMN && p.b_kind == gb::kDenseMN && !knobs().no_wide_stages && p.k_blocks_total >= 8 &&
           patch_box(2 * epl, g.out_h, g.out_w, bw2, bh2, bn2) &&
           (p.patch_view ? nhwc_view_tma(&a2, other, smem_bf16, d->dtype_x, g, epl, bw2, bh2, bn2, true)
-                        : nhwc_tma(&a2, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, bw2, bh2, bn2, true, g.stride)) &&
+                        : nhwc_tma(&a2, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, bw2, bh2, bn2, true, g.stride, p.xform != 0)) &&
           (227 * 1024 - 2048 - gb::kStoreSmemBytes) / (2 * (128 * 128 + p.bn * 128)) >= 3 &&   // two-block stages only while three of them fit
           dense_tma(&b2, ob, smem_bf16, 1, p.bn, epl, 2)) {
         plan.tmap_a = a2; plan.tmap_b = b2;
