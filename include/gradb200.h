@@ -219,10 +219,11 @@ int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
  * every in-bounds tap reads relu(s * x + t) with s = gamma * inv_std and t = beta - mean * s per input channel, both
  * rounded to bf16 and applied as one bf16 fused multiply-add (`affineExpand` / `affinePair`, src/gpu/device.zig:1774-1805,
  * 1604-1612); padding taps stay exactly zero.  Replaces `Gpu.convImplicitForwardAffineStats` (src/gpu/gpu.zig:951-959;
- * the statistics part is `epilogue->bn_stats`).  bf16 activations and bf16 math only.  The transform is applied by the
- * gather warps while they build the operand tile -- a TMA copy zero-fills padding, and relu(s * 0 + t) is not zero -- so
- * this path runs at the gathered rate, several times slower than gb_conv_fprop; the first 4 * c bytes of the workspace
- * (rounded up to 256) hold the expanded s and t. */
+ * the statistics part is `epilogue->bn_stats`).  bf16 activations and bf16 math only.  Where TMA can fetch the map (channel
+ * counts in multiples of 64) it arrives with NaN outside the image and two warps rewrite each landed tile in shared memory
+ * before the tensor core reads it (NaN -> 0: the reference's marker trick, device.zig:77-86), 2-3 times the time of
+ * gb_conv_fprop; otherwise the gather warps transform while they build the tile, far slower.  The first 4 * c bytes of the
+ * workspace (rounded up to 256) hold the expanded s and t. */
 typedef struct {
   const float *mean, *inv_std, *gamma, *beta;   /* f32[c] each: the norm that the input stands for */
 } gb_affine_input;
