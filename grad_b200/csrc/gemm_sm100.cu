@@ -855,33 +855,9 @@ __device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CU
                                                    const float* sbias, uint32_t batch, uint32_t split, uint32_t row, uint32_t col0, uint32_t lane) {
   epilogue_chunk_tma_impl<false>(p, tmap_c, acc, stage, sbias, nullptr, 0, batch, split, row, col0, lane);
 }
-// The chunk epilogue of a statistics plan.  Kept out of line on its own copy of the chunk: inlined, its 64 temporaries
-// raised the register pressure (and the spills) of every plan's epilogue, with or without statistics.
-// `sstat` is the warp's statistics block in shared memory (floats): [0, 128) the shift (or mean) values of its four
+// `sstat`, an epilogue warp's statistics block in shared memory (floats): [0, 128) the shift (or mean) values of its four
 // column chunks, [128, 384) per chunk and lane the running (sum, sum of squares) of that lane's column over every row the
 // warp has drained, and for the backward sums [384, 512) inv_std, [512, 640) gamma, [640, 768) beta.
-__device__ __noinline__ void epilogue_chunk_tma_stats(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t* vals, uint8_t* stage,
-                                                      const float* sbias, float* sstat, uint32_t slot, uint32_t batch, uint32_t row, uint32_t col0,
-                                                      uint32_t lane) {
-  uint32_t copy[32];
-#pragma unroll
-  for (uint32_t i = 0; i < 32; ++i) copy[i] = vals[i];
-  const ChunkStats c = epilogue_chunk_tma_impl<true>(p, tmap_c, copy, stage, sbias, sstat, slot, batch, 0, row, col0, lane);
-  float2* cell = (float2*)(sstat + 128) + slot * 32 + lane;   // only this lane ever touches its cell
-  float2 v = *cell;
-  v.x += c.sum;
-  v.y += c.squares;
-  *cell = v;
-}
-__device__ __forceinline__ void epilogue_chunk_tma_stats_call(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
-                                                           const float* sbias, float* sstat, uint32_t slot, uint32_t batch, uint32_t row, uint32_t col0,
-                                                           uint32_t lane) {
-  uint32_t spill[32];
-#pragma unroll
-  for (uint32_t i = 0; i < 32; ++i) spill[i] = acc[i];
-  epilogue_chunk_tma_stats(p, tmap_c, spill, stage, sbias, sstat, slot, batch, row, col0, lane);
-}
-
 
 // The bias values of every chunk this warp will drain from the next accumulator, fetched into the warp's own
 // shared memory before it waits for that accumulator: chunk i's 32 values sit at sbias[32 * i].  (Fetched
@@ -925,10 +901,31 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     // Chunks that lie wholly inside C and rows that begin inside it go through the TMA store; a ragged last
     // chunk takes the guarded scalar path with its bias read back from the staged values.
     auto tile_col = [&](uint32_t c) { return wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c; };
+    if constexpr (kStats) {
+      // One register buffer and the chunk routine inline: with two buffers, or with the routine out of line and its
+      // accumulators handed over through local memory, the statistics pass took twice the plain pass.
+      uint32_t i = 0;
+      for (uint32_t c = first; c < ncols; c += step, ++i) {
+        uint32_t acc[32];
+        tmem_ld_32x32(taddr + c, acc);
+        tmem_ld_wait();
+        if (c + step >= ncols) release();
+        const uint32_t col0 = col_base + tile_col(c);
+        if (col0 + 32 <= p.n && row - lane < p.m) {
+          const ChunkStats s = epilogue_chunk_tma_impl<true>(p, tmap_c, acc, store_stage, sbias + 32 * i, sstat, i, batch, 0, row, col0, lane);
+          float2* cell = (float2*)(sstat + 128) + i * 32 + lane;   // only this lane ever touches its cell
+          float2 v = *cell;
+          v.x += s.sum;
+          v.y += s.squares;
+          *cell = v;
+        } else epilogue_chunk_copy(p, acc, batch, split, row, col0, p.bias ? sbias[32 * i + lane] : 0.0f);
+      }
+      return;
+    }
     uint32_t acc_a[32], acc_b[32];
     tmem_ld_32x32(taddr + first, acc_a);
     uint32_t i = 0;
-    const bool fast = !kStats && p.tma_store == 2;
+    const bool fast = p.tma_store == 2;
     const float floor = p.relu ? 0.0f : -INFINITY;
     int32_t bz = (int32_t)batch, bw = -1;
     if (p.batch_inner) { uint32_t bi, bo; split_batch(p, batch, bi, bo); bz = (int32_t)bi; bw = (int32_t)bo; }
@@ -940,8 +937,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
       {
         const uint32_t col0 = col_base + tile_col(c);
         if (col0 + 32 <= p.n && row - lane < p.m) {
-          if constexpr (kStats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_a, store_stage, sbias + 32 * i, sstat, i, batch, row, col0, lane);
-          else if (fast) epilogue_chunk_fast(tmap_c, acc_a, store_stage, sbias + 32 * i, floor, bz, bw, row, col0, lane);
+          if (fast) epilogue_chunk_fast(tmap_c, acc_a, store_stage, sbias + 32 * i, floor, bz, bw, row, col0, lane);
           else epilogue_chunk_tma(p, tmap_c, acc_a, store_stage, sbias + 32 * i, batch, split, row, col0, lane);
         } else epilogue_chunk_copy(p, acc_a, batch, split, row, col0, p.bias ? sbias[32 * i + lane] : 0.0f);
       }
@@ -951,8 +947,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
         else release();
         const uint32_t col0 = col_base + tile_col(c + step);
         if (col0 + 32 <= p.n && row - lane < p.m) {
-          if constexpr (kStats) epilogue_chunk_tma_stats_call(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), sstat, i + 1, batch, row, col0, lane);
-          else if (fast) epilogue_chunk_fast(tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), floor, bz, bw, row, col0, lane);
+          if (fast) epilogue_chunk_fast(tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), floor, bz, bw, row, col0, lane);
           else epilogue_chunk_tma(p, tmap_c, acc_b, store_stage, sbias + 32 * (i + 1), batch, split, row, col0, lane);
         } else epilogue_chunk_copy(p, acc_b, batch, split, row, col0, p.bias ? sbias[32 * (i + 1) + lane] : 0.0f);
       }
