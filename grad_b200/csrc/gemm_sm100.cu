@@ -1746,21 +1746,44 @@ __global__ void __launch_bounds__(32 * kReduceGroups) splitk_reduce_grouped_kern
   }
 }
 
-// Ordered combine of the statistics partials (the role of `columnCombine`, src/gpu/device.zig:672-678): one thread per
-// column adds the slots of every CTA and of the four row quarters in a fixed order, then adds the total into sums.
-__global__ void stats_combine_kernel(const float* partial, float* sums, uint32_t ctas, uint32_t n, uint32_t epi_groups) {
+// Ordered combine of the statistics partials (the role of `columnCombine`, src/gpu/device.zig:672-678).  One block per
+// 32-column chunk; warp w adds, for its lane's column, the slots of the CTAs [w * per, (w + 1) * per) and of their four
+// row quarters in ascending order, then warp 0 adds the warps' subtotals in warp order and the total into sums.  The
+// order depends on the CTA count alone, never on timing.  (One thread per column walking every CTA took ~25 us for 148
+// CTAs: its 592 dependent additions each waited for a load.)
+constexpr uint32_t kCombineWarps = 16;
+__global__ void __launch_bounds__(32 * kCombineWarps) stats_combine_kernel(const float* partial, float* sums, uint32_t ctas, uint32_t n, uint32_t epi_groups) {
+  __shared__ float2 sub[kCombineWarps][32];
   grid_launch_dependents();
   grid_dependency_wait();
-  const uint32_t col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= n) return;
-  const uint32_t chunk = col >> 5, lane = col & 31, group = chunk % epi_groups, slot = chunk / epi_groups;
+  const uint32_t chunk = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t group = chunk % epi_groups, slot = chunk / epi_groups;
+  const uint32_t per = (ctas + kCombineWarps - 1) / kCombineWarps;
+  const uint32_t begin = min(warp * per, ctas), end = min(begin + per, ctas);
   float s = 0.0f, q = 0.0f;
-  for (uint32_t cta = 0; cta < ctas; ++cta)
+#pragma unroll 4
+  for (uint32_t cta = begin; cta < end; ++cta) {
+    float2 v[4];
+#pragma unroll
+    for (uint32_t quarter = 0; quarter < 4; ++quarter)
+      v[quarter] = *(const float2*)(partial + (((uint64_t)cta * 8 + group * 4 + quarter) * 4 + slot) * 64 + lane * 2);
+#pragma unroll
     for (uint32_t quarter = 0; quarter < 4; ++quarter) {
-      const float* src = partial + (((uint64_t)cta * 8 + group * 4 + quarter) * 4 + slot) * 64 + lane * 2;
-      s += src[0];
-      q += src[1];
+      s += v[quarter].x;
+      q += v[quarter].y;
     }
+  }
+  sub[warp][lane] = make_float2(s, q);
+  __syncthreads();
+  const uint32_t col = chunk * 32 + lane;
+  if (warp != 0 || col >= n) return;
+  s = 0.0f;
+  q = 0.0f;
+#pragma unroll
+  for (uint32_t w = 0; w < kCombineWarps; ++w) {
+    s += sub[w][lane].x;
+    q += sub[w][lane].y;
+  }
   sums[col] += s;
   sums[n + col] += q;
 }
@@ -1770,8 +1793,8 @@ __global__ void stats_combine_kernel(const float* partial, float* sums, uint32_t
 uint32_t gemm_grid_ctas(const GemmParams& p, int sm_count);
 
 cudaError_t launch_stats_combine(const GemmParams& p, uint32_t ctas, cudaStream_t stream) {
-  return launch_overlapped(stats_combine_kernel, dim3((p.n + 127) / 128), dim3(128), 0, stream, (const float*)p.stat_partial, p.stat_sums, ctas, p.n,
-                           p.epi_groups);
+  return launch_overlapped(stats_combine_kernel, dim3((p.n + 31) / 32), dim3(32 * kCombineWarps), 0, stream, (const float*)p.stat_partial, p.stat_sums,
+                           ctas, p.n, p.epi_groups);
 }
 
 size_t gemm_smem_bytes(const GemmParams& p) {
