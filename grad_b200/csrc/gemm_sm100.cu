@@ -258,7 +258,7 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
       out = make_uint4(affine_relu_bf16x2(out.x, sc.x, sh.x), affine_relu_bf16x2(out.y, sc.y, sh.y), affine_relu_bf16x2(out.z, sc.z, sh.z),
                        affine_relu_bf16x2(out.w, sc.w, sh.w));
     }
-    *(uint4*)(line + ((chunk ^ sw) << 4)) = out;
+    sts128(smem_u32(line) + ((chunk ^ sw) << 4), out);
   }
 }
 __device__ __forceinline__ void gather_tile(const GemmParams& p, const GatherDesc& d, uint8_t* tile, uint32_t lines_in_tile,
@@ -640,9 +640,9 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* tmap_c, uint8
   if (lane == 0) bulk_wait_read_all();
   __syncwarp();
   const uint32_t sw = (lane >> 1) & 3;
-  uint8_t* line = stage + lane * 64;
+  const uint32_t line = smem_u32(stage) + lane * 64;
 #pragma unroll
-  for (uint32_t j = 0; j < 4; ++j) *(uint4*)(line + ((j ^ sw) << 4)) = q[j];
+  for (uint32_t j = 0; j < 4; ++j) sts128(line + ((j ^ sw) << 4), q[j]);
   fence_proxy_async_smem();
   __syncwarp();
   if (lane == 0) {
@@ -1301,33 +1301,46 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       if (work.empty) continue;
       uint32_t cb = work.kb_begin % cblocks;
       const uint32_t row_base = (work.m_tile * kBM) % p.geo.c;   // MN-major: first channel of the tile's first box
+      // Thread t owns physical chunk t % 8 of lines t / 8, t / 8 + 8, ...: line % 8 is the same for all of them, so the
+      // thread's logical chunk (its eight channels within the block) is fixed and its scale / shift values are loaded
+      // once per stage (per box of an MN-major operand), not once per chunk -- and before the wait for the stage, one
+      // box ahead, so that their latency never stands between a landed tile and its rewrite.
+      const uint32_t pc = tid & 7, l0 = tid >> 3, jch = pc ^ (l0 & 7);
+      const uint32_t n_boxes = p.a_mn_major ? a_lines / box_lines : 1u, lines_per_box = p.a_mn_major ? box_lines : a_lines;
+      auto channel0 = [&](uint32_t box) {
+        if (!p.a_mn_major) return cb * 64;
+        const uint32_t c0 = row_base + box * 64;
+        return c0 >= p.geo.c ? c0 - p.geo.c : c0;
+      };
       for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
+        uint32_t c0 = channel0(0);
+        uint4 sc = *(const uint4*)(p.affine_scale + c0 + jch * 8), sh = *(const uint4*)(p.affine_shift + c0 + jch * 8);
         ok = mbar_wait(&hdr->full[stage], phase, abort_flag, kStatusProducerTimeout);
         ok = __all_sync(0xFFFFFFFFu, ok);
         if (!ok) break;
         uint8_t* a_tile = tiles + stage * stage_bytes;
-        // Thread t owns physical chunk t % 8 of lines t / 8, t / 8 + 8, ...: line % 8 is the same for all of them, so the
-        // thread's logical chunk (its eight channels within the block) is fixed and its scale / shift values are loaded
-        // once per stage (per box of an MN-major operand), not once per chunk.
-        const uint32_t pc = tid & 7, l0 = tid >> 3, jch = pc ^ (l0 & 7);
-        const uint32_t n_boxes = p.a_mn_major ? a_lines / box_lines : 1u, lines_per_box = p.a_mn_major ? box_lines : a_lines;
         for (uint32_t box = 0; box < n_boxes; ++box) {
-          uint32_t c0 = cb * 64;
-          if (p.a_mn_major) {
-            c0 = row_base + box * 64;
-            if (c0 >= p.geo.c) c0 -= p.geo.c;
+          const uint4 sc_box = sc, sh_box = sh;
+          if (box + 1 < n_boxes) {
+            c0 = channel0(box + 1);
+            sc = *(const uint4*)(p.affine_scale + c0 + jch * 8);
+            sh = *(const uint4*)(p.affine_shift + c0 + jch * 8);
           }
-          const uint4 sc = *(const uint4*)(p.affine_scale + c0 + jch * 8), sh = *(const uint4*)(p.affine_shift + c0 + jch * 8);
-          uint8_t* base = a_tile + (box * lines_per_box + l0) * kLineBytes + pc * 16;
+          const uint32_t base = smem_u32(a_tile + (box * lines_per_box + l0) * kLineBytes + pc * 16);
           const uint32_t rounds = (lines_per_box - l0 + 7) / 8;   // lines l0, l0 + 8, ... of this box
-#pragma unroll 4
-          for (uint32_t r = 0; r < rounds; ++r) {
-            uint4* at = (uint4*)(base + r * 8 * kLineBytes);
-            uint4 v = *at;
-            v = make_uint4(affine_relu_bf16x2(v.x, sc.x, sh.x), affine_relu_bf16x2(v.y, sc.y, sh.y), affine_relu_bf16x2(v.z, sc.z, sh.z),
-                           affine_relu_bf16x2(v.w, sc.w, sh.w));
-            *at = v;
+          auto rewrite = [&](const uint4& v) {
+            return make_uint4(affine_relu_bf16x2(v.x, sc_box.x, sh_box.x), affine_relu_bf16x2(v.y, sc_box.y, sh_box.y),
+                              affine_relu_bf16x2(v.z, sc_box.z, sh_box.z), affine_relu_bf16x2(v.w, sc_box.w, sh_box.w));
+          };
+          uint32_t r = 0;
+          for (; r + 8 <= rounds; r += 8) {   // eight loads in flight, then eight rewrites
+            uint4 v[8];
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j) v[j] = lds128(base + (r + j) * 8 * kLineBytes);
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j) sts128(base + (r + j) * 8 * kLineBytes, rewrite(v[j]));
           }
+          for (; r < rounds; ++r) sts128(base + r * 8 * kLineBytes, rewrite(lds128(base + r * 8 * kLineBytes)));
         }
         fence_proxy_async_smem();
         __syncwarp();
