@@ -1068,7 +1068,7 @@ __global__ void __launch_bounds__(64 + 256 + kGatherThreads, 1)
 gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic, no integer round trip: every pointer derived from it stays known as shared memory
   SmemHeader* hdr = (SmemHeader*)smem;
   uint8_t* tiles = smem + kHeaderBytes;
   const uint32_t kmul = max(p.k_mul, 1u);
@@ -1378,7 +1378,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic, no integer round trip: every pointer derived from it stays known as shared memory
   SmemHeader* hdr = (SmemHeader*)smem;
   uint8_t* tiles = smem + kHeaderBytes;
   // A tile wider than 256 columns is two 256-column halves accumulated side by side in TMEM by two MMAs per

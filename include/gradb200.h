@@ -221,7 +221,7 @@ int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
  * 1604-1612); padding taps stay exactly zero.  Replaces `Gpu.convImplicitForwardAffineStats` (src/gpu/gpu.zig:951-959;
  * the statistics part is `epilogue->bn_stats`).  bf16 activations and bf16 math only.  Where TMA can fetch the map (channel
  * counts in multiples of 64) it arrives with NaN outside the image and two warps rewrite each landed tile in shared memory
- * before the tensor core reads it (NaN -> 0: the reference's marker trick, device.zig:77-86), 2-3 times the time of
+ * before the tensor core reads it (NaN -> 0: the reference's marker trick, device.zig:77-86), 1.5-2.5 times the time of
  * gb_conv_fprop; otherwise the gather warps transform while they build the tile, far slower.  The first 4 * c bytes of the
  * workspace (rounded up to 256) hold the expanded s and t. */
 typedef struct {
