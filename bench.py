@@ -62,7 +62,7 @@ def parse_args():
     ap.add_argument("--profile-resnet", type=int, default=0, metavar="BATCH",
                     help="run only three eager ResNet-14 inference passes at this batch and exit (launch lists under a profiler)")
     ap.add_argument("--profile-conv", default="", metavar="N,H,W,C,K,COUT,STRIDE,PAD[,PASS]",
-                    help="run only six launches of this bf16 convolution layer (PASS fprop|dgrad|wgrad, default fprop) and exit")
+                    help="run only six launches of this bf16 convolution layer (PASS fprop|dgrad|wgrad|stats|affine|wgrad_affine, default fprop) and exit")
     ap.add_argument("--profile-gemm", default="", metavar="M,N,K,LAYOUT,MATH", help="run only six launches of this product and exit")
     return ap.parse_args()
 
@@ -356,6 +356,8 @@ def conv_layers(gpu, torch, cpu_baseline, peaks):
                     totals[key] += count * ms
             if count:
                 totals["gflop"] += count * flop / 1e9
+            if name in cpu_for:
+                row["batch_norm_pieces_us"] = batch_norm_pieces(gpu, torch, gen, geo, x, w, y, dy, dx, dw)
             if cpu_baseline and name in cpu_for:
                 row["cpu_baseline"] = conv_cpu(n, hw, c, k, co, stride, flop)
             rows.append(row)
@@ -364,6 +366,29 @@ def conv_layers(gpu, torch, cpu_baseline, peaks):
         summary[key] = {"ms": round(totals[key], 4), "tflops": round(totals["gflop"] / totals[key], 1),
                         "frac_of_nominal_2250": round(totals["gflop"] / totals[key] / NOMINAL_BF16, 3)}
     return {"layers": rows, "network_sum": summary}
+
+
+def batch_norm_pieces(gpu, torch, gen, geo, x, w, y, dy, dx, dw):
+    """The fused batch-norm pieces of the bf16 training path on one layer (src/gpu/gpu.zig:915-1022), each beside the plain
+    pass it extends: forward with the statistics of its result in the epilogue (atomics, and the ordered mode with its
+    combine launch), forward and weight gradient over a normalised-and-rectified input that is never written out, input
+    gradient with the masked batch-norm gradient sums.  Microseconds from CUDA-graph replays."""
+    from grad_b200 import Epilogue
+
+    c, co = x.shape[-1], y.shape[-1]
+    mean = torch.randn(c, generator=gen, device="cuda") * 0.1
+    inv_std, gamma = torch.rand(c, generator=gen, device="cuda") + 0.5, torch.rand(c, generator=gen, device="cuda") + 0.5
+    beta = torch.randn(c, generator=gen, device="cuda") * 0.1
+    shift, sums, dx_sums = torch.zeros(co, device="cuda"), torch.zeros(2 * co, device="cuda"), torch.zeros(2 * c, device="cuda")
+    cases = (("fprop", lambda: gpu.convForward(x, w, y, geo)),
+             ("fprop_stats", lambda: gpu.convForward(x, w, y, geo, epilogue=Epilogue(stats_shift=shift, stats_sums=sums))),
+             ("fprop_stats_ordered", lambda: gpu.convForward(x, w, y, geo, epilogue=Epilogue(stats_shift=shift, stats_sums=sums, stats_ordered=True))),
+             ("fprop_affine_input", lambda: gpu.convForwardAffine(x, w, y, geo, mean, inv_std, gamma, beta)),
+             ("wgrad", lambda: gpu.convWeightGrad(dy, x, dw, geo)),
+             ("wgrad_affine_input", lambda: gpu.convWeightGradAffine(dy, x, dw, geo, mean, inv_std, gamma, beta)),
+             ("dgrad", lambda: gpu.convInputGrad(dy, w, dx, geo, accumulate=False)),
+             ("dgrad_dx_stats", lambda: gpu.convInputGradDxStats(dy, w, dx, geo, x, mean, inv_std, gamma, beta, dx_sums)))
+    return {key: round(graph_ms(torch, fn) * 1e3, 1) for key, fn in cases}
 
 
 def conv_cpu(n, hw, c, k, co, stride, flop):
@@ -811,11 +836,19 @@ def profile_only(args, gpu, torch):
         dx = torch.empty_like(x)
         dw = torch.zeros((k * k * c, co), device="cuda")
         bias = torch.randn(co, device="cuda")
+        shift, sums = torch.zeros(co, device="cuda"), torch.zeros(2 * co, device="cuda")
+        norm = [torch.rand(c, device="cuda") + 0.5 for _ in range(4)]   # mean, inv_std, gamma, beta of a virtual normalised input
         for _ in range(6):
             if which == "fprop":
                 gpu.convForward(x, w, y, geo, epilogue=Epilogue(bias, None, True))
             elif which == "dgrad":
                 gpu.convInputGrad(y, w, dx, geo, accumulate=False)
+            elif which == "stats":
+                gpu.convForward(x, w, y, geo, epilogue=Epilogue(stats_shift=shift, stats_sums=sums))
+            elif which == "affine":
+                gpu.convForwardAffine(x, w, y, geo, *norm)
+            elif which == "wgrad_affine":
+                gpu.convWeightGradAffine(y, x, dw, geo, *norm)
             else:
                 gpu.convWeightGrad(y, x, dw, geo)
     torch.cuda.synchronize()
