@@ -696,14 +696,21 @@ __device__ __forceinline__ ChunkStats chunk_stats(const float* v, const float* s
 // that was never written, x = the raw map the norm ran on.  x_hat = (x - mean) * inv_std rebuilds the normalised value,
 // gamma * x_hat + beta > 0 the ReLU mask; the masked gradient g and g * x_hat are summed per column.  The products and
 // sums are rounded one by one (no fused multiply-add), like the reference's separate operations.
-__device__ __forceinline__ ChunkStats chunk_dx_stats(const GemmParams& p, const float* v, const float* sstat, uint32_t slot, uint64_t off, bool live,
-                                                     uint32_t lane) {
+// This lane's 32 bf16 values of the batch-norm input (its row, the chunk's columns) for the masked gradient sums, fetched
+// ahead of the accumulator they will be combined with: read inside the chunk routine, each chunk waited for them (a lane
+// owns a row, so nothing else was in flight) and the pass took twice the plain input gradient.
+__device__ __forceinline__ void dx_stats_fetch(const GemmParams& p, uint32_t batch, uint32_t row, uint32_t col0, uint4 (&raw)[4]) {
+  const bool take = p.stats == 2 && row < p.m && col0 + 32 <= p.n;
+  const uint16_t* src = (const uint16_t*)p.stat_x + c_batch_offset(p, batch) + (uint64_t)row * p.ldc + col0;
+#pragma unroll
+  for (uint32_t j = 0; j < 4; ++j) raw[j] = take ? *(const uint4*)(src + 8 * j) : make_uint4(0u, 0u, 0u, 0u);
+}
+__device__ __forceinline__ ChunkStats chunk_dx_stats(const float* v, const float* sstat, uint32_t slot, const uint4 (&xraw)[4], bool live, uint32_t lane) {
   const float *mean = sstat + 32 * slot, *inv_std = sstat + 384 + 32 * slot, *gamma = sstat + 512 + 32 * slot, *beta = sstat + 640 + 32 * slot;
   float t[32], q[32];
 #pragma unroll
   for (uint32_t i = 0; i < 32; i += 8) {
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (live) raw = *(const uint4*)((const uint16_t*)p.stat_x + off + i);
+    const uint4 raw = xraw[i / 8];
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (uint32_t j = 0; j < 8; ++j) {
@@ -723,8 +730,8 @@ __device__ __forceinline__ ChunkStats chunk_dx_stats(const GemmParams& p, const 
 
 template <bool kStats>
 __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
-                                                              const float* sbias, const float* sstat, uint32_t slot, uint32_t batch, uint32_t split,
-                                                              uint32_t row, uint32_t col0, uint32_t lane) {
+                                                              const float* sbias, const float* sstat, uint32_t slot, const uint4 (&xraw)[4], uint32_t batch,
+                                                              uint32_t split, uint32_t row, uint32_t col0, uint32_t lane) {
   ChunkStats stats = {0.0f, 0.0f};
   if (p.splits > 1) {
     // A K part's partial tile: the raw f32 accumulators, into the map of the partial buffer {n, m, split * batch}.
@@ -816,7 +823,7 @@ __device__ __forceinline__ ChunkStats epilogue_chunk_tma_impl(const GemmParams& 
         v[2 * j] = __uint_as_float(w[j] << 16);
         v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
       }
-      stats = p.stats == 2 ? chunk_dx_stats(p, v, sstat, slot, off, live, lane) : chunk_stats(v, sstat + 32 * slot, live, lane);
+      stats = p.stats == 2 ? chunk_dx_stats(v, sstat, slot, xraw, live, lane) : chunk_stats(v, sstat + 32 * slot, live, lane);
     }
     stage_and_store(tmap_c, stage, q, lane, (int32_t)col0, y, bz, bw);
   } else {
@@ -853,7 +860,8 @@ __device__ __forceinline__ void epilogue_chunk_fast(const CUtensorMap* tmap_c, c
 
 __device__ __forceinline__ void epilogue_chunk_tma(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t (&acc)[32], uint8_t* stage,
                                                    const float* sbias, uint32_t batch, uint32_t split, uint32_t row, uint32_t col0, uint32_t lane) {
-  epilogue_chunk_tma_impl<false>(p, tmap_c, acc, stage, sbias, nullptr, 0, batch, split, row, col0, lane);
+  const uint4 none[4] = {};
+  epilogue_chunk_tma_impl<false>(p, tmap_c, acc, stage, sbias, nullptr, 0, none, batch, split, row, col0, lane);
 }
 // `sstat`, an epilogue warp's statistics block in shared memory (floats): [0, 128) the shift (or mean) values of its four
 // column chunks, [128, 384) per chunk and lane the running (sum, sum of squares) of that lane's column over every row the
@@ -888,7 +896,7 @@ template <bool kStats, class Release>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, uint32_t ncols, uint32_t batch, uint32_t split,
                                               uint32_t row, uint32_t col_base, bool wide, uint32_t lane,
                                               uint32_t first, uint32_t step, const CUtensorMap* tmap_c, uint8_t* store_stage, const float* sbias,
-                                              float* sstat, Release release) {
+                                              float* sstat, uint4 (&xraw)[4], Release release) {
   // a fused class product places its rows by its own map and ends at its own row count
   const RowMap& rowmap = p.n_classes ? p.cls[batch].rowmap : p.rowmap;
   const uint32_t m_limit = p.n_classes ? p.cls[batch].m : p.m;
@@ -903,22 +911,28 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
     auto tile_col = [&](uint32_t c) { return wide ? ((c & 255) >> 7) * (ncols / 2) + (c >> 8) * 128 + (c & 127) : c; };
     if constexpr (kStats) {
       // One register buffer and the chunk routine inline: with two buffers, or with the routine out of line and its
-      // accumulators handed over through local memory, the statistics pass took twice the plain pass.
+      // accumulators handed over through local memory, the statistics pass took twice the plain pass.  `xraw` holds the
+      // batch-norm input of the current chunk (mode 2; the caller fetched the first chunk's before it waited for the
+      // accumulator), the next chunk's is requested before this chunk's accumulator values are waited for.
       uint32_t i = 0;
       for (uint32_t c = first; c < ncols; c += step, ++i) {
         uint32_t acc[32];
         tmem_ld_32x32(taddr + c, acc);
+        uint4 xnext[4];
+        dx_stats_fetch(p, batch, row, c + step < ncols ? col_base + tile_col(c + step) : p.n, xnext);
         tmem_ld_wait();
         if (c + step >= ncols) release();
         const uint32_t col0 = col_base + tile_col(c);
         if (col0 + 32 <= p.n && row - lane < p.m) {
-          const ChunkStats s = epilogue_chunk_tma_impl<true>(p, tmap_c, acc, store_stage, sbias + 32 * i, sstat, i, batch, 0, row, col0, lane);
+          const ChunkStats s = epilogue_chunk_tma_impl<true>(p, tmap_c, acc, store_stage, sbias + 32 * i, sstat, i, xraw, batch, 0, row, col0, lane);
           float2* cell = (float2*)(sstat + 128) + i * 32 + lane;   // only this lane ever touches its cell
           float2 v = *cell;
           v.x += s.sum;
           v.y += s.squares;
           *cell = v;
         } else epilogue_chunk_copy(p, acc, batch, split, row, col0, p.bias ? sbias[32 * i + lane] : 0.0f);
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) xraw[j] = xnext[j];
       }
       return;
     }
@@ -1244,14 +1258,16 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         stage_bias(p, sbias, p.bn, work.n_tile * p.bn, false, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
         bias_tile = work.n_tile;
       }
+      const uint32_t row = work.m_tile * kBM + quarter * 32 + lane;
+      uint4 xraw[4] = {};
+      if constexpr (kStats) dx_stats_fetch(p, work.batch, row, work.n_tile * p.bn + ((warp - 2) >> 2) * 32, xraw);
       ok = mbar_wait(&hdr->acc_full[buf], buf_phase, abort_flag, kStatusEpilogueTimeout);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t row = work.m_tile * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * p.bn;
       epilogue_tile<kStats>(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, false, lane,
-                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, sstat, [&] {
+                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, sstat, xraw, [&] {
                                                  tc_fence_before_sync();
                                                  __syncwarp();
                                                  if (lane == 0) mbar_arrive(&hdr->acc_empty[buf]);
@@ -1547,14 +1563,16 @@ gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p, const __grid_consta
         stage_bias(p, sbias, p.bn, work.n_tile * p.bn, halves == 2, lane, ((warp - 2) >> 2) * 32, 32 * p.epi_groups);
         bias_tile = work.n_tile;
       }
+      const uint32_t row = work.m_tile * 2 * kBM + rank * kBM + quarter * 32 + lane;
+      uint4 xraw[4] = {};
+      if constexpr (kStats) dx_stats_fetch(p, work.batch, row, work.n_tile * p.bn + ((warp - 2) >> 2) * 32, xraw);   // statistics plans have no wide tiles
       ok = mbar_wait(&hdr->acc_full[buf], buf_phase, abort_flag, kStatusEpilogueTimeout);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t row = work.m_tile * 2 * kBM + rank * kBM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32) << 16) + buf * (p.bn / halves);
       epilogue_tile<kStats>(p, taddr, p.bn, work.batch, work.split, row, work.n_tile * p.bn, halves == 2, lane,
-                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, sstat, [&] {
+                                               ((warp - 2) >> 2) * 32, 32 * p.epi_groups, &tmap_c, store_stage, sbias, sstat, xraw, [&] {
                                                  tc_fence_before_sync();
                                                  __syncwarp();
                                                  if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->acc_empty[buf]), 0));
