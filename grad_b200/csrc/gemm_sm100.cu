@@ -709,15 +709,19 @@ __device__ __forceinline__ ChunkStats chunk_dx_stats(const float* v, const float
   const float *mean = sstat + 32 * slot, *inv_std = sstat + 384 + 32 * slot, *gamma = sstat + 512 + 32 * slot, *beta = sstat + 640 + 32 * slot;
   float t[32], q[32];
 #pragma unroll
-  for (uint32_t i = 0; i < 32; i += 8) {
+  for (uint32_t i = 0; i < 32; i += 4) {
+    // four columns' parameters per 16-byte broadcast read (read one by one, the 128 shared-memory loads of a chunk
+    // were the larger part of what this epilogue adds to the plain input gradient)
+    const float4 m4 = *(const float4*)(mean + i), s4 = *(const float4*)(inv_std + i), g4 = *(const float4*)(gamma + i), b4 = *(const float4*)(beta + i);
+    const float m[4] = {m4.x, m4.y, m4.z, m4.w}, is[4] = {s4.x, s4.y, s4.z, s4.w}, ga[4] = {g4.x, g4.y, g4.z, g4.w}, be[4] = {b4.x, b4.y, b4.z, b4.w};
     const uint4 raw = xraw[i / 8];
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    const uint32_t w[2] = {(i & 4) ? raw.z : raw.x, (i & 4) ? raw.w : raw.y};
 #pragma unroll
-    for (uint32_t j = 0; j < 8; ++j) {
+    for (uint32_t j = 0; j < 4; ++j) {
       const uint32_t c = i + j;
       const float x = __uint_as_float((j & 1) ? (w[j >> 1] & 0xFFFF0000u) : (w[j >> 1] << 16));
-      const float xh = __fmul_rn(__fsub_rn(x, mean[c]), inv_std[c]);
-      const bool on = live && __fadd_rn(__fmul_rn(gamma[c], xh), beta[c]) > 0.0f;
+      const float xh = __fmul_rn(__fsub_rn(x, m[j]), is[j]);
+      const bool on = live && __fadd_rn(__fmul_rn(ga[j], xh), be[j]) > 0.0f;
       t[c] = on ? v[c] : 0.0f;
       q[c] = on ? __fmul_rn(v[c], xh) : 0.0f;
     }
