@@ -62,7 +62,7 @@ def parse_args():
     ap.add_argument("--profile-resnet", type=int, default=0, metavar="BATCH",
                     help="run only three eager ResNet-14 inference passes at this batch and exit (launch lists under a profiler)")
     ap.add_argument("--profile-conv", default="", metavar="N,H,W,C,K,COUT,STRIDE,PAD[,PASS]",
-                    help="run only six launches of this bf16 convolution layer (PASS fprop|dgrad|wgrad|stats|affine|wgrad_affine, default fprop) and exit")
+                    help="run only six launches of this bf16 convolution layer (PASS fprop|dgrad|wgrad|stats|affine|wgrad_affine|dx_stats, default fprop) and exit")
     ap.add_argument("--profile-gemm", default="", metavar="M,N,K,LAYOUT,MATH", help="run only six launches of this product and exit")
     return ap.parse_args()
 
@@ -836,7 +836,7 @@ def profile_only(args, gpu, torch):
         dx = torch.empty_like(x)
         dw = torch.zeros((k * k * c, co), device="cuda")
         bias = torch.randn(co, device="cuda")
-        shift, sums = torch.zeros(co, device="cuda"), torch.zeros(2 * co, device="cuda")
+        shift, sums, dx_sums = torch.zeros(co, device="cuda"), torch.zeros(2 * co, device="cuda"), torch.zeros(2 * c, device="cuda")
         norm = [torch.rand(c, device="cuda") + 0.5 for _ in range(4)]   # mean, inv_std, gamma, beta of a virtual normalised input
         for _ in range(6):
             if which == "fprop":
@@ -849,6 +849,8 @@ def profile_only(args, gpu, torch):
                 gpu.convForwardAffine(x, w, y, geo, *norm)
             elif which == "wgrad_affine":
                 gpu.convWeightGradAffine(y, x, dw, geo, *norm)
+            elif which == "dx_stats":
+                gpu.convInputGradDxStats(y, w, dx, geo, x, *norm, dx_sums)
             else:
                 gpu.convWeightGrad(y, x, dw, geo)
     torch.cuda.synchronize()
