@@ -1312,6 +1312,28 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     // belongs to the BOX (64 of the tile's (tap, channel) rows), not to the K block.
     grid_dependency_wait();
     const uint32_t tid = threadIdx.x - 64 - epi_threads;
+    // The norm expanded into bf16 scale / shift tables behind the epilogue's shared memory, once per CTA.
+    const uint32_t cpad = (p.geo.c + 7) & ~7u;
+    uint16_t* table = (uint16_t*)(tiles + p.stages * stage_bytes + (p.tma_store ? kStoreSmemBytes : 0) + (p.stats ? 8 * kStatBytesPerWarp : 0));
+    const bool own_table = p.aff_mean != nullptr;
+    if (own_table) {
+      for (uint32_t ch = tid; ch < p.geo.c; ch += kGatherThreads) {
+        const float sc = __fmul_rn(p.aff_gamma[ch], p.aff_inv_std[ch]);
+        table[ch] = (uint16_t)bf16_bits(sc);
+        table[cpad + ch] = (uint16_t)bf16_bits(__fsub_rn(p.aff_beta[ch], __fmul_rn(p.aff_mean[ch], sc)));
+      }
+      asm volatile("bar.sync 1, %0;" ::"r"(kGatherThreads) : "memory");   // the transform warps only
+    }
+    const uint32_t table_scale = smem_u32(table), table_shift = smem_u32(table + cpad);
+    auto norm_of = [&](uint32_t ch, uint4& sc, uint4& sh) {   // scale and shift of channels ch .. ch + 7
+      if (own_table) {
+        sc = lds128(table_scale + 2 * ch);
+        sh = lds128(table_shift + 2 * ch);
+      } else {
+        sc = *(const uint4*)(p.affine_scale + ch);
+        sh = *(const uint4*)(p.affine_shift + ch);
+      }
+    };
     const uint32_t a_lines = (p.col_taps ? p.a_box_bytes : kATileBytes * kmul) / kLineBytes;
     const uint32_t cblocks = max(p.walk.cblocks, 1u), box_lines = 64 * kmul;
     uint32_t stage = 0, phase = 0;
@@ -1334,7 +1356,8 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       };
       for (uint32_t kb = work.kb_begin; kb < work.kb_end; ++kb) {
         uint32_t c0 = channel0(0);
-        uint4 sc = *(const uint4*)(p.affine_scale + c0 + jch * 8), sh = *(const uint4*)(p.affine_shift + c0 + jch * 8);
+        uint4 sc, sh;
+        norm_of(c0 + jch * 8, sc, sh);
         ok = mbar_wait(&hdr->full[stage], phase, abort_flag, kStatusProducerTimeout);
         ok = __all_sync(0xFFFFFFFFu, ok);
         if (!ok) break;
@@ -1343,8 +1366,7 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           const uint4 sc_box = sc, sh_box = sh;
           if (box + 1 < n_boxes) {
             c0 = channel0(box + 1);
-            sc = *(const uint4*)(p.affine_scale + c0 + jch * 8);
-            sh = *(const uint4*)(p.affine_shift + c0 + jch * 8);
+            norm_of(c0 + jch * 8, sc, sh);
           }
           const uint32_t base = smem_u32(a_tile + (box * lines_per_box + l0) * kLineBytes + pc * 16);
           const uint32_t rounds = (lines_per_box - l0 + 7) / 8;   // lines l0, l0 + 8, ... of this box
@@ -1837,7 +1859,8 @@ size_t gemm_smem_bytes(const GemmParams& p) {
   return 1024 /* alignment slack */ + kHeaderBytes +
          (size_t)p.stages * ((p.a_stage_bytes ? p.a_stage_bytes : kATileBytes * (p.k_mul ? p.k_mul : 1u)) +
                              (p.col_taps ? p.col_taps : 1u) * b_lines * kLineBytes * (p.k_mul ? p.k_mul : 1u)) +
-         (p.tma_store ? kStoreSmemBytes : 0) + (p.stats ? 8 * kStatBytesPerWarp : 0);
+         (p.tma_store ? kStoreSmemBytes : 0) + (p.stats ? 8 * kStatBytesPerWarp : 0) +
+         (p.xform && p.aff_mean ? (size_t)4 * ((p.geo.c + 7) & ~7u) : 0);
 }
 
 // Co-resident 2-CTA clusters of the pair kernel for a given dynamic shared-memory size (cached per size).

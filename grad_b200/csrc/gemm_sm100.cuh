@@ -123,6 +123,13 @@ struct GemmParams {
   // the two extra warps rewrite each landed A tile in place (NaN -> 0: padding stays zero) and only then hand the stage to
   // the MMA issuer.  0 with affine_scale set: the gather warps apply the transform while they build the tile.
   uint32_t xform;
+  // with xform: the four per-channel vectors of the norm (f32[c]).  The transform warps expand them into a table in
+  // shared memory at kernel start (s = gamma * inv_std, t = beta - mean * s, each rounded to bf16: `affineExpand`,
+  // src/gpu/device.zig:1774-1783), which saves the expansion launch; affine_scale / affine_shift are not read then.
+  const float* aff_mean;
+  const float* aff_inv_std;
+  const float* aff_gamma;
+  const float* aff_beta;
   // output
   void* c;
   const float* bias;
@@ -162,6 +169,7 @@ constexpr uint32_t kStoreBiasBytesPerWarp = 1024;
 constexpr uint32_t kStoreSmemBytes = 8 * (kStoreStageBytesPerWarp + kStoreBiasBytesPerWarp);
 // statistics plans: per epilogue warp the per-column values of its four column chunks (4 x 512 B) and its running sums (1 KB), behind the block above
 constexpr uint32_t kStatBytesPerWarp = 4 * 512 + 1024;
+constexpr uint32_t kMaxXformTableChannels = 2048;   // 8 KB of shared memory for the scale and shift tables
 // Launch with programmatic stream serialization (the kernel must execute griddepcontrol.wait before its first
 // global access).  GB_NO_OVERLAPPED_LAUNCH=1 falls back to plain stream order.
 template <class... KernelArgs, class... Args>

@@ -1431,21 +1431,38 @@ int gb_conv_dgrad(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
 }
 
 namespace {
-// Expands the norm into bf16 scale / shift vectors at the head of the workspace; returns what is left of it.
-int expand_affine(gb_handle* h, cudaStream_t stream, const gb_affine_input* affine, uint32_t c, void*& workspace, size_t& workspace_bytes,
-                  const uint16_t*& scale, const uint16_t*& shift) {
+// Carves the bf16 scale / shift vectors of the expanded norm out of the head of the workspace; returns what is left of it.
+int carve_affine(const gb_affine_input* affine, uint32_t c, void*& workspace, size_t& workspace_bytes, uint16_t*& scale, uint16_t*& shift) {
   if (!affine || !affine->mean || !affine->inv_std || !affine->gamma || !affine->beta) return GB_ERR_INVALID;
   const size_t need = ((size_t)c * 4 + 255) & ~(size_t)255;
   if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace)) return GB_ERR_WORKSPACE;
-  uint16_t* s = (uint16_t*)workspace;
-  uint16_t* t = s + ((c + 7) & ~7u);
-  const cudaError_t e = gb::launch_affine_expand(affine->mean, affine->inv_std, affine->gamma, affine->beta, s, t, c, stream);
-  if (e != cudaSuccess) return cuda_fail(h, e);
-  scale = s;
-  shift = t;
+  scale = (uint16_t*)workspace;
+  shift = scale + ((c + 7) & ~7u);
   workspace = (char*)workspace + need;
   workspace_bytes -= need;
   return GB_OK;
+}
+
+// Plans, prepares and launches a pass over a virtual normalised input.  Where the transform warps take the operand they
+// expand the norm themselves (a table in shared memory); otherwise the expansion kernel fills the workspace vectors first.
+int run_affine(gb_handle* h, cudaStream_t stream, int pass, const gb_conv_desc* desc, const void* act, const void* other, void* out,
+               const gb_epilogue* epilogue, const gb_affine_input* affine, uint16_t* scale, uint16_t* shift, void* workspace, size_t workspace_bytes) {
+  Plan plan;
+  int rc = plan_conv(h, pass, desc, act, other, out, epilogue, plan, nullptr, scale, shift);
+  if (rc != GB_OK) return rc;
+  const bool own_table = plan.p.xform && desc->geo.c <= gb::kMaxXformTableChannels;
+  if (own_table) {
+    plan.p.aff_mean = affine->mean; plan.p.aff_inv_std = affine->inv_std; plan.p.aff_gamma = affine->gamma; plan.p.aff_beta = affine->beta;
+  }
+  rc = prepare_plan(h, plan, workspace, workspace_bytes);
+  if (rc != GB_OK) return rc;
+  if (!own_table) {
+    const cudaError_t e = gb::launch_affine_expand(affine->mean, affine->inv_std, affine->gamma, affine->beta, scale, shift, desc->geo.c, stream);
+    if (e != cudaSuccess) return cuda_fail(h, e);
+  }
+  rc = launch_plan(h, stream, plan);
+  h->last_plan.kernel_launches += own_table ? 0 : 1;
+  return rc;
 }
 }  // namespace
 
@@ -1455,18 +1472,15 @@ int gb_conv_fprop_affine(gb_handle* h, void* stream, const gb_conv_desc* desc, c
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
   if (desc->groups > 1) return GB_ERR_UNSUPPORTED;
-  const uint16_t *scale = nullptr, *shift = nullptr;
-  rc = expand_affine(h, (cudaStream_t)stream, affine, desc->geo.c, workspace, workspace_bytes, scale, shift);
+  uint16_t *scale = nullptr, *shift = nullptr;
+  rc = carve_affine(affine, desc->geo.c, workspace, workspace_bytes, scale, shift);
   if (rc != GB_OK) return rc;
   gb_conv_desc shadow;
   rc = make_filter_shadow(h, (cudaStream_t)stream, desc, shadow, w, workspace, workspace_bytes);
   if (rc != GB_OK) return rc;
-  Plan plan;
-  rc = plan_conv(h, 0, desc, x, w, y, epilogue, plan, nullptr, scale, shift);
-  if (rc == GB_OK) rc = prepare_plan(h, plan, workspace, workspace_bytes);
-  if (rc != GB_OK) return rc;
-  rc = launch_plan(h, (cudaStream_t)stream, plan);
-  h->last_plan.kernel_launches += 1 + (desc == &shadow ? 1 : 0);
+  const bool cast = desc == &shadow;
+  rc = run_affine(h, (cudaStream_t)stream, 0, desc, x, w, y, epilogue, affine, scale, shift, workspace, workspace_bytes);
+  if (rc == GB_OK && cast) h->last_plan.kernel_launches += 1;
   return rc;
 }
 
@@ -1476,16 +1490,10 @@ int gb_conv_wgrad_affine(gb_handle* h, void* stream, const gb_conv_desc* desc, c
   int rc = validate_conv(desc);
   if (rc != GB_OK) return rc;
   if (desc->dtype_w != GB_F32 || desc->w_layout != 0 || desc->groups > 1) return GB_ERR_UNSUPPORTED;
-  const uint16_t *scale = nullptr, *shift = nullptr;
-  rc = expand_affine(h, (cudaStream_t)stream, affine, desc->geo.c, workspace, workspace_bytes, scale, shift);
+  uint16_t *scale = nullptr, *shift = nullptr;
+  rc = carve_affine(affine, desc->geo.c, workspace, workspace_bytes, scale, shift);
   if (rc != GB_OK) return rc;
-  Plan plan;
-  rc = plan_conv(h, 2, desc, dy, x, dw, nullptr, plan, nullptr, scale, shift);
-  if (rc == GB_OK) rc = prepare_plan(h, plan, workspace, workspace_bytes);
-  if (rc != GB_OK) return rc;
-  rc = launch_plan(h, (cudaStream_t)stream, plan);
-  h->last_plan.kernel_launches += 1;
-  return rc;
+  return run_affine(h, (cudaStream_t)stream, 2, desc, dy, x, dw, nullptr, affine, scale, shift, workspace, workspace_bytes);
 }
 
 int gb_conv_dgrad_stats(gb_handle* h, void* stream, const gb_conv_desc* desc, const void* dy, const void* w, void* dx,

@@ -223,7 +223,8 @@ int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
  * counts in multiples of 64) it arrives with NaN outside the image and two warps rewrite each landed tile in shared memory
  * before the tensor core reads it (NaN -> 0: the reference's marker trick, device.zig:77-86), 1.5-2.5 times the time of
  * gb_conv_fprop; otherwise the gather warps transform while they build the tile, far slower.  The first 4 * c bytes of the
- * workspace (rounded up to 256) hold the expanded s and t. */
+ * workspace (rounded up to 256) are reserved for the expanded s and t: the gather path fills them with one extra launch,
+ * the TMA path expands the norm inside the kernel (a table in shared memory) and leaves them untouched. */
 typedef struct {
   const float *mean, *inv_std, *gamma, *beta;   /* f32[c] each: the norm that the input stands for */
 } gb_affine_input;
