@@ -2,7 +2,7 @@
 """Benchmark of the dense-contraction path: bf16 GEMM TFLOP/s at M = N = K = 8192 (fused bias + ReLU).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--size S] [--layout NN|NT|TN]
-                    [--legs gemm,sustained,e2e,resnet,conv,mlp,transformer]
+                    [--legs gemm,sustained,e2e,sweep,resnet,conv,mlp,transformer]
 
 One step is one pass of the hot path over one batch of synthetic input: one 8192 x 8192 x 8192 product
 with N(0,1) bf16 operands, f32 accumulation, y = relu(A*B + bias) stored as bf16.  With --gpus N every rank
@@ -20,6 +20,8 @@ ranks.  Rank 0 prints ONE JSON line.
   --impl reference  times that CPU path alone (the reference is Zig and cannot be built here)
 
 Further keys carry the other benchmark configurations, each figure beside the CPU path timed in the same run:
+  gemm_sweep          M = N = K in {1024, 2048, 4096, 8192} and the skinny 128 x 4096 x 4096, NN / NT / TN, in bf16, TF32
+                      and strict f32, fused bias + ReLU: microseconds and TFLOP/s per product from CUDA-graph replays
   resnet14_inference  ONNX-executor inference of ResNet-14 64-192-384, batch 4096 and 100, sharded over the ranks
   conv_layers         every convolution layer of the ResNet-14 64-128-256 stack (and the 64-192-384 widths) at batch
                       128, forward / input gradient / weight gradient, with roofline fractions and HBM GB/s
@@ -43,7 +45,7 @@ sys.path.insert(0, ROOT)
 METRIC = "bf16 GEMM TFLOP/s (M=N=K=8192, fused bias+ReLU)"
 UNIT = "TFLOP/s"
 NOMINAL_BF16, NOMINAL_TF32, NOMINAL_HBM = 2250.0, 1125.0, 8000.0
-ALL_LEGS = ("gemm", "sustained", "e2e", "resnet", "conv", "mlp", "transformer")
+ALL_LEGS = ("gemm", "sustained", "e2e", "sweep", "resnet", "conv", "mlp", "transformer")
 
 
 def parse_args():
@@ -412,6 +414,46 @@ def conv_cpu(n, hw, c, k, co, stride, flop):
             best = min(best, time.perf_counter() - t0)
         out[key] = {"ms": round(best * 1e3, 1), "tflops": round(flop / best / 1e12, 4)}
     return out
+
+
+# ---- config 2: the GEMM sweep ---------------------------------------------------------------------------------
+def gemm_sweep(gpu, torch, peaks):
+    """The standalone GEMM sweep (src/bench.zig:177-273 runs the same shapes on the CPU): square products of 1024..8192 and
+    the skinny 128 x 4096 x 4096 in the three layouts autograd uses (NN forward, NT for dX, TN for dW), with bf16 operands,
+    with f32 operands under TF32 math, and in strict f32 (up to 4096: 8192^3 on the FMA path is 27 ms a launch), each
+    with the fused bias + ReLU epilogue.  Device time per launch from the replay of a CUDA graph."""
+    from grad_b200 import Epilogue, MatmulOpts, MatmulShape
+    from grad_b200.abi import MATH_BF16, MATH_F32, MATH_TF32
+
+    gen = torch.Generator(device="cuda").manual_seed(1234 + 1)
+    rows = []
+    shapes = [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (128, 4096, 4096)]
+    for math, name, dt, nominal in ((MATH_BF16, "bf16", torch.bfloat16, NOMINAL_BF16), (MATH_TF32, "tf32", torch.float32, NOMINAL_TF32),
+                                    (MATH_F32, "f32", torch.float32, None)):
+        for m, n, k in shapes:
+            if math == MATH_F32 and m * n * k > 4096 ** 3:
+                continue
+            for layout in ("NN", "NT", "TN"):
+                ta, tb = layout == "TN", layout == "NT"
+                a = torch.randn((k, m) if ta else (m, k), generator=gen, device="cuda").to(dt)
+                b = torch.randn((n, k) if tb else (k, n), generator=gen, device="cuda").to(dt)
+                bias = torch.randn(n, generator=gen, device="cuda")
+                out = torch.empty((m, n), dtype=dt, device="cuda")
+                shape, opts, ep = MatmulShape(m, n, k), MatmulOpts(ta, tb), Epilogue(bias, None, True)
+                flop = 2.0 * m * n * k
+                calls = 3 if flop > 2e11 else (10 if flop > 1e10 else 20)
+                ms = graph_ms(torch, lambda: gpu.matmul(a, b, out, shape, opts, epilogue=ep, math=math), calls=calls, reps=3)
+                plan = gpu.last_plan()
+                row = {"m": m, "n": n, "k": k, "layout": layout, "math": name, "us": round(ms * 1e3, 1), "tflops": round(flop / ms / 1e9, 1),
+                       "tile": f"{plan['tile_m']}x{plan['tile_n']}", "splits": plan["splits"], "launches": plan["kernel_launches"]}
+                if nominal:
+                    row["frac_of_nominal"] = round(flop / ms / 1e9 / nominal, 3)
+                if math == MATH_BF16:
+                    row["frac_of_measured"] = round(flop / ms / 1e9 / peaks["bf16_tflops"], 3)
+                rows.append(row)
+                del a, b, out
+    torch.cuda.empty_cache()
+    return {"epilogue": "bias + ReLU", "nominal_tflops": {"bf16": NOMINAL_BF16, "tf32": NOMINAL_TF32}, "products": rows}
 
 
 # ---- config 1: the MLP step ------------------------------------------------------------------------------------
@@ -883,7 +925,7 @@ def run_ours(args):
     legs = set(args.legs.split(",")) & set(ALL_LEGS)
     legs.add("gemm")
     if args.no_resnet:
-        legs -= {"resnet", "conv", "mlp", "transformer", "sustained"}
+        legs -= {"resnet", "conv", "mlp", "transformer", "sustained", "sweep"}
     cpu_ok = not args.no_cpu_baseline
     size = args.size
     m = n = k = size
@@ -1032,6 +1074,7 @@ def run_ours(args):
 
     resnet = resnet_inference(gpu, rank, world, dist, torch, cpu_ok and world == 1) if "resnet" in legs else None
     transformer = transformer_step(gpu, rank, world, dist, torch, cpu_ok and world == 1) if "transformer" in legs else None
+    sweep = gemm_sweep(gpu, torch, peaks) if (rank == 0 and "sweep" in legs) else None
     convs = conv_layers(gpu, torch, cpu_ok and world == 1, peaks) if (rank == 0 and "conv" in legs) else None
     mlp = mlp_step(gpu, torch, cpu_ok and world == 1) if (rank == 0 and "mlp" in legs) else None
     gpu.check_status()
@@ -1070,6 +1113,8 @@ def run_ours(args):
         line["parity"] = parity
     if sustained is not None:
         line["sustained"] = sustained
+    if sweep is not None:
+        line["gemm_sweep"] = sweep
     if resnet is not None:
         line["resnet14_inference"] = resnet
     if convs is not None:
