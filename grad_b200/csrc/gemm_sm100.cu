@@ -1312,27 +1312,20 @@ gemm_sm100_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     // belongs to the BOX (64 of the tile's (tap, channel) rows), not to the K block.
     grid_dependency_wait();
     const uint32_t tid = threadIdx.x - 64 - epi_threads;
-    // The norm expanded into bf16 scale / shift tables behind the epilogue's shared memory, once per CTA.
+    // The norm expanded into bf16 scale / shift tables behind the epilogue's shared memory, once per CTA (a plan with
+    // p.xform always carries the four vectors).
     const uint32_t cpad = (p.geo.c + 7) & ~7u;
     uint16_t* table = (uint16_t*)(tiles + p.stages * stage_bytes + (p.tma_store ? kStoreSmemBytes : 0) + (p.stats ? 8 * kStatBytesPerWarp : 0));
-    const bool own_table = p.aff_mean != nullptr;
-    if (own_table) {
-      for (uint32_t ch = tid; ch < p.geo.c; ch += kGatherThreads) {
-        const float sc = __fmul_rn(p.aff_gamma[ch], p.aff_inv_std[ch]);
-        table[ch] = (uint16_t)bf16_bits(sc);
-        table[cpad + ch] = (uint16_t)bf16_bits(__fsub_rn(p.aff_beta[ch], __fmul_rn(p.aff_mean[ch], sc)));
-      }
-      asm volatile("bar.sync 1, %0;" ::"r"(kGatherThreads) : "memory");   // the transform warps only
+    for (uint32_t ch = tid; ch < p.geo.c; ch += kGatherThreads) {
+      const float sc = __fmul_rn(p.aff_gamma[ch], p.aff_inv_std[ch]);
+      table[ch] = (uint16_t)bf16_bits(sc);
+      table[cpad + ch] = (uint16_t)bf16_bits(__fsub_rn(p.aff_beta[ch], __fmul_rn(p.aff_mean[ch], sc)));
     }
+    asm volatile("bar.sync 1, %0;" ::"r"(kGatherThreads) : "memory");   // the transform warps only
     const uint32_t table_scale = smem_u32(table), table_shift = smem_u32(table + cpad);
     auto norm_of = [&](uint32_t ch, uint4& sc, uint4& sh) {   // scale and shift of channels ch .. ch + 7
-      if (own_table) {
-        sc = lds128(table_scale + 2 * ch);
-        sh = lds128(table_shift + 2 * ch);
-      } else {
-        sc = *(const uint4*)(p.affine_scale + ch);
-        sh = *(const uint4*)(p.affine_shift + ch);
-      }
+      sc = lds128(table_scale + 2 * ch);
+      sh = lds128(table_shift + 2 * ch);
     };
     const uint32_t a_lines = (p.col_taps ? p.a_box_bytes : kATileBytes * kmul) / kLineBytes;
     const uint32_t cblocks = max(p.walk.cblocks, 1u), box_lines = 64 * kmul;

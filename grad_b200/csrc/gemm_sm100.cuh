@@ -123,9 +123,10 @@ struct GemmParams {
   // the two extra warps rewrite each landed A tile in place (NaN -> 0: padding stays zero) and only then hand the stage to
   // the MMA issuer.  0 with affine_scale set: the gather warps apply the transform while they build the tile.
   uint32_t xform;
-  // with xform: the four per-channel vectors of the norm (f32[c]).  The transform warps expand them into a table in
-  // shared memory at kernel start (s = gamma * inv_std, t = beta - mean * s, each rounded to bf16: `affineExpand`,
-  // src/gpu/device.zig:1774-1783), which saves the expansion launch; affine_scale / affine_shift are not read then.
+  // with xform (always set then): the four per-channel vectors of the norm (f32[c], c <= kMaxXformTableChannels).  The
+  // transform warps expand them into a table in shared memory at kernel start (s = gamma * inv_std, t = beta - mean * s,
+  // each rounded to bf16: `affineExpand`, src/gpu/device.zig:1774-1783), which saves the expansion launch;
+  // affine_scale / affine_shift are not read then.
   const float* aff_mean;
   const float* aff_inv_std;
   const float* aff_gamma;

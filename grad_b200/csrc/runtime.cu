@@ -853,7 +853,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       if (affine) {
         // The virtual normalised input: fetched by TMA with NaN outside the image and rewritten in place by the transform
         // warps; where no TMA map fits it stays with the gather warps, which transform while they build the tile.
-        if (smem_bf16 && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+        if (smem_bf16 && g.c <= gb::kMaxXformTableChannels && patch_box(128, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
             nhwc_tma(&plan.tmap_a, act, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, false, g.stride, true)) {
           p.a_kind = gb::kPatchK;
           p.xform = 1;
@@ -968,7 +968,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
       const bool view = g.k == 1 && g.pad == 0 && g.stride > 1 && !knobs().no_strided_tma;
       if (affine) {
         // as in the forward pass: TMA with NaN outside the image + the transform warps, else the gather warps
-        if (smem_bf16 && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
+        if (smem_bf16 && g.c <= gb::kMaxXformTableChannels && patch_box(epl, g.out_h, g.out_w, p.box_w, p.box_h, p.box_n) &&
             nhwc_tma(&plan.tmap_a, other, smem_bf16, d->dtype_x, g.c, g.c_step, g.w, g.h, g.n, epl, p.box_w, p.box_h, p.box_n, true, g.stride, true)) {
           p.a_kind = gb::kPatchMN;
           p.xform = 1;
@@ -1450,7 +1450,7 @@ int run_affine(gb_handle* h, cudaStream_t stream, int pass, const gb_conv_desc* 
   Plan plan;
   int rc = plan_conv(h, pass, desc, act, other, out, epilogue, plan, nullptr, scale, shift);
   if (rc != GB_OK) return rc;
-  const bool own_table = plan.p.xform && desc->geo.c <= gb::kMaxXformTableChannels;
+  const bool own_table = plan.p.xform != 0;
   if (own_table) {
     plan.p.aff_mean = affine->mean; plan.p.aff_inv_std = affine->inv_std; plan.p.aff_gamma = affine->gamma; plan.p.aff_beta = affine->beta;
   }

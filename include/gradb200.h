@@ -220,8 +220,8 @@ int gb_conv_fprop(gb_handle* h, void* stream, const gb_conv_desc* desc, const vo
  * rounded to bf16 and applied as one bf16 fused multiply-add (`affineExpand` / `affinePair`, src/gpu/device.zig:1774-1805,
  * 1604-1612); padding taps stay exactly zero.  Replaces `Gpu.convImplicitForwardAffineStats` (src/gpu/gpu.zig:951-959;
  * the statistics part is `epilogue->bn_stats`).  bf16 activations and bf16 math only.  Where TMA can fetch the map (channel
- * counts in multiples of 64) it arrives with NaN outside the image and two warps rewrite each landed tile in shared memory
- * before the tensor core reads it (NaN -> 0: the reference's marker trick, device.zig:77-86), 1.5-2.5 times the time of
+ * counts in multiples of 64, up to 2048) it arrives with NaN outside the image and two warps rewrite each landed tile in shared memory
+ * before the tensor core reads it (NaN -> 0: the reference's marker trick, device.zig:77-86), 1.4-2 times the time of
  * gb_conv_fprop; otherwise the gather warps transform while they build the tile, far slower.  The first 4 * c bytes of the
  * workspace (rounded up to 256) are reserved for the expanded s and t: the gather path fills them with one extra launch,
  * the TMA path expands the norm inside the kernel (a table in shared memory) and leaves them untouched. */
