@@ -592,6 +592,21 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
 #pragma unroll
       for (uint32_t i = 0; i < 32; i += 4) *(float4*)((float*)p.c + off + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
     }
+    if (p.zero_fill > 1) {
+      // the pixels (y + dy, x + dx), 0 <= dy, dx < s, beside this row's pixel belong to classes without taps: zero
+      const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+      for (uint32_t dy = 0; dy < p.zero_fill; ++dy)
+        for (uint32_t dx = dy == 0 ? 1u : 0u; dx < p.zero_fill; ++dx) {
+          const uint64_t at = off + ((uint64_t)dy * p.rowmap.w + dx) * p.ldc;
+          if (p.c_is_bf16) {
+#pragma unroll
+            for (uint32_t i = 0; i < 32; i += 8) *(uint4*)((uint16_t*)p.c + at + i) = zero;
+          } else {
+#pragma unroll
+            for (uint32_t i = 0; i < 32; i += 4) *(uint4*)((float*)p.c + at + i) = zero;
+          }
+        }
+    }
     return;
   }
   if (!live) return;

@@ -98,6 +98,9 @@ struct GemmParams {
   uint32_t box_w, box_h, box_n;
   ConvGeo geo;
   uint32_t dgrad;           // 1: patches are taken from dy with flipped taps (input gradient)
+  // s > 1: the only parity class of a strided input gradient that has taps (a 1x1 layer of stride s); its epilogue also
+  // writes the zeros of the s*s - 1 pixels beside each of its pixels, which saves clearing dx in front of the launch
+  uint32_t zero_fill;
   uint32_t patch_view;      // 1: the activation map is already a strided view of x (1x1 strided layer): MN-major patch boxes step rows by 1
   TapWalk walk;             // K walk of patch / filter-tap boxes
   // Column-patch stages (col_taps > 0): one stage holds, for one (tap column, channel block), the activation

@@ -1121,7 +1121,16 @@ int run_dgrad_classes(gb_handle* h, cudaStream_t stream, const gb_conv_desc* d, 
       rm.per_image = wk.div_image; rm.grid_w = wk.div_w;
       rm.h = g.h; rm.w = g.w; rm.scale = s; rm.off_y = py; rm.off_x = px;
     }
-  if (any_empty && !d->accumulate) {
+  // A 1x1 layer has ONE class with taps; where the image is whole blocks of s x s pixels its epilogue writes the other
+  // pixels' zeros itself (each of its rows owns the block at its pixel), else dx is cleared in front.
+  bool fill_in_kernel = false;
+  if (any_empty && !d->accumulate && plans.size() == 1) {
+    GemmParams& p = plans[0].p;
+    fill_in_kernel = g.h % s == 0 && g.w % s == 0 && p.rowmap.off_y == 0 && p.rowmap.off_x == 0 && p.vec_store && p.n % 32 == 0 &&
+                     !p.transpose_out && p.splits <= 1;
+    if (fill_in_kernel) p.zero_fill = s;
+  }
+  if (any_empty && !d->accumulate && !fill_in_kernel) {
     // Pixels of a class without taps get no product; they are zero.  Only a dense dx can be cleared as a block.
     if (g.c_step != g.c) return GB_ERR_UNSUPPORTED;
     const cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)g.n * g.h * g.w * g.c * elem_size(d->dtype_x), stream);
