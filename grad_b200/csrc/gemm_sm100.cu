@@ -261,10 +261,67 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
     sts128(smem_u32(line) + ((chunk ^ sw) << 4), out);
   }
 }
+// A line of the patch operand of a 3-channel 3x3 stride-1 layer over a bf16 map (the network's stem): the 27 values of a
+// window are three runs of nine consecutive bf16 (the pixels x - 1 .. x + 1 of a row, three channels each), so the line
+// is 27 two-byte loads issued together, packed and stored as four 16-byte chunks, the other four chunks zero.  (Through
+// the general routine every chunk of such a line straddles taps and goes element by element through the index arithmetic.)
+__device__ __forceinline__ bool stem_line_applies(const GemmParams& p, const GatherDesc& d) {
+  const ConvGeo& g = p.geo;
+  return d.source == kSrcPatch && !d.mn_major && d.src_is_bf16 && !p.tf32 && g.c == 3 && g.c_step == 3 && g.k == 3 && g.stride == 1 &&
+         g.dilation == 1 && p.affine_scale == nullptr;
+}
+// The loads of one line: 27 values (v[27] = 0 pads the last pair).  One pointer per window row, constant offsets within
+// it (the pixel pitch is 3), nine predicates; the position is split with the walk's precomputed divisors.
+__device__ __forceinline__ void stem_line_load(const GemmParams& p, const GatherDesc& d, uint32_t position, uint16_t (&v)[28]) {
+  const ConvGeo& g = p.geo;
+  const uint32_t img = fast_div(position, p.walk.div_image), rem = position - img * p.walk.div_image.d;
+  const uint32_t oy = fast_div(rem, p.walk.div_w), ox = rem - oy * p.walk.div_w.d;
+  const int32_t y0 = (int32_t)oy - (int32_t)g.pad, x0 = (int32_t)ox - (int32_t)g.pad;
+  const bool valid = position < d.lines_total;
+  const int32_t row_pitch = (int32_t)(g.w * 3);
+  const uint16_t* corner = (const uint16_t*)d.base + (int64_t)img * g.h * row_pitch + (int64_t)y0 * row_pitch + (int64_t)x0 * 3;   // may lie outside: read under predicates only
+  bool col_in[3];
+#pragma unroll
+  for (uint32_t kx = 0; kx < 3; ++kx) col_in[kx] = x0 + (int32_t)kx >= 0 && x0 + (int32_t)kx < (int32_t)g.w;
+#pragma unroll
+  for (uint32_t ky = 0; ky < 3; ++ky) {
+    const bool row_in = valid && y0 + (int32_t)ky >= 0 && y0 + (int32_t)ky < (int32_t)g.h;
+    const uint16_t* row = corner + (int32_t)ky * row_pitch;
+#pragma unroll
+    for (uint32_t e = 0; e < 9; ++e) v[ky * 9 + e] = (row_in && col_in[e / 3]) ? row[e] : (uint16_t)0;
+  }
+  v[27] = 0;
+}
+__device__ __forceinline__ void stem_line_store(uint8_t* tile, uint32_t l, const uint16_t (&v)[28]) {
+  const uint32_t line = smem_u32(tile + l * kLineBytes), sw = l & 7;
+#pragma unroll
+  for (uint32_t chunk = 0; chunk < 8; ++chunk) {
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (chunk < 4) {
+      uint32_t w[4];
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) {
+        const uint32_t e = chunk * 8 + 2 * j;
+        w[j] = (e < 28 ? (uint32_t)v[e] : 0u) | ((e + 1 < 28 ? (uint32_t)v[e + 1] : 0u) << 16);
+      }
+      out = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    sts128(line + ((chunk ^ sw) << 4), out);
+  }
+}
+
 __device__ __forceinline__ void gather_tile(const GemmParams& p, const GatherDesc& d, uint8_t* tile, uint32_t lines_in_tile,
                                             uint32_t mn0, uint32_t k0, uint32_t batch, uint32_t tid) {
   const uint32_t epl = p.tf32 ? 32u : 64u;
   const uint64_t batch_off = (uint64_t)batch * d.batch_stride;
+  if (k0 == 0 && batch_off == 0 && stem_line_applies(p, d)) {   // K = 27: the one K block of the stem
+    for (uint32_t l = tid; l < lines_in_tile; l += kGatherThreads) {
+      uint16_t v[28];
+      stem_line_load(p, d, mn0 + l, v);
+      stem_line_store(tile, l, v);
+    }
+    return;
+  }
   for (uint32_t l = tid; l < lines_in_tile; l += kGatherThreads) {
     if (d.mn_major) {
       const uint32_t block = l / epl, kline = l - block * epl;

@@ -60,6 +60,7 @@ struct Knobs {
   bool no_dgrad_classes = false; // GB_NO_DGRAD_CLASSES: a strided input gradient is one gathered product
   bool no_wide_stages = false;   // GB_NO_WIDE_STAGES: weight gradients keep one K block per stage
   bool no_fused_classes = false; // GB_NO_FUSED_CLASSES: one launch per parity class of a strided input gradient
+  bool no_stem_lines = false;    // GB_NO_STEM_LINES: the 3-channel stem keeps the FMA kernel for its forward pass
   bool no_plan_cache = false;    // GB_NO_PLAN_CACHE: every call plans from scratch
   int force_bn = 0;              // GB_FORCE_BN=n: tile width of a dense single-CTA product (with GB_FORCE_SPLITS: its K split)
   int force_splits = 0;
@@ -80,6 +81,7 @@ const Knobs& knobs() {
     v.no_dgrad_classes = getenv("GB_NO_DGRAD_CLASSES") != nullptr;
     v.no_wide_stages = getenv("GB_NO_WIDE_STAGES") != nullptr;
     v.no_fused_classes = getenv("GB_NO_FUSED_CLASSES") != nullptr;
+    v.no_stem_lines = getenv("GB_NO_STEM_LINES") != nullptr;
     v.no_plan_cache = getenv("GB_NO_PLAN_CACHE") != nullptr;
     if (const char* g = getenv("GB_FORCE_BN")) v.force_bn = atoi(g);
     if (const char* g = getenv("GB_FORCE_SPLITS")) v.force_splits = atoi(g);
@@ -841,7 +843,11 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     set_output(p, out, d->dtype_y, g.y_step, 0, false, d->accumulate, ep);
     int rc = finish_plan(h, plan, true, min_bn, ep);
     if (rc != GB_OK) return rc;
-    if (plan.tensor && gb::conv_direct_applies(p) && !knobs().no_direct_conv && !p.stats && !affine) {
+    // A 3-channel 3x3 stride-1 layer over a bf16 map goes through the tensor kernel: its gather warps have a line builder
+    // for exactly that window (14.8 against 29.9 us at batch 128, 449 against 605 us at batch 4096 for the FMA kernel).
+    const bool stem_lines = smem_bf16 && d->dtype_x == GB_BF16 && g.c == 3 && g.c_step == 3 && g.k == 3 && g.stride == 1 && g.dilation == 1 &&
+                            !w_rows && !knobs().no_stem_lines;   // (a prepared filter row of 27 values is no TMA operand)
+    if (plan.tensor && gb::conv_direct_applies(p) && !knobs().no_direct_conv && !p.stats && !affine && !stem_lines) {
       plan.direct = true;
       plan.workspace = 0;
       return GB_OK;

@@ -96,18 +96,22 @@ class Executor:
             self.stats.uploads += 1
         return self.constants[name]
 
-    def _conv_weights(self, name: str) -> torch.Tensor:
+    def _conv_weights(self, name: str):
         key = name + "/taps"
         if key not in self.derived:
             w = self._constant(name)
             m, c, kh, kw = w.shape
             if self.mode == "tf32":   # filters are rounded to TF32 once (nearest), not truncated at every use
                 w = (w.view(torch.int32) + 0x1000).bitwise_and(-8192).view(torch.float32)
-            # filters are kept as (c_out, kh*kw*c): K contiguous per output channel (gb_conv_desc.w_layout = 1)
-            out = torch.empty((m, kh * kw * c), dtype=self.act_dtype, device=self.gpu.device)
-            abi.check(self.gpu.lib.gb_reorder_oihw_rows(self._stream(), self._code(out), C.c_void_p(w.data_ptr()), C.c_void_p(out.data_ptr()),
-                                                        m, c, kh, kw), "gb_reorder_oihw_rows")
-            self.derived[key] = out
+            # filters are kept as (c_out, kh*kw*c): K contiguous per output channel (gb_conv_desc.w_layout = 1) -- unless such a
+            # row is not a whole number of 16-byte units (the 3-channel stem: 27 values), which TMA cannot fetch: those stay
+            # (kh*kw*c, c_out), whose rows of c_out values it can
+            rows = (kh * kw * c * torch.empty((), dtype=self.act_dtype).element_size()) % 16 == 0
+            out = torch.empty((m, kh * kw * c) if rows else (kh * kw * c, m), dtype=self.act_dtype, device=self.gpu.device)
+            fn = self.gpu.lib.gb_reorder_oihw_rows if rows else self.gpu.lib.gb_reorder_oihw
+            abi.check(fn(self._stream(), self._code(out), C.c_void_p(w.data_ptr()), C.c_void_p(out.data_ptr()), m, c, kh, kw),
+                      "gb_reorder_oihw_rows" if rows else "gb_reorder_oihw")
+            self.derived[key] = (out, rows)
             self.stats.launches += 1
         return self.derived[key]
 
@@ -174,10 +178,10 @@ class Executor:
         Returns how many nodes after the window were consumed."""
         if int(node.attrs.get("group", 1)) != 1:
             raise NotImplementedError("grouped convolution takes the NCHW host path in the reference (runtime.zig:871)")
-        w = self._conv_weights(node.inputs[1])
-        m = w.shape[0]
+        w, w_rows = self._conv_weights(node.inputs[1])
+        m, taps_c = (w.shape[0], w.shape[1]) if w_rows else (w.shape[1], w.shape[0])
         n, h, width, c = x.shape
-        k = int(round((w.shape[1] // c) ** 0.5))
+        k = int(round((taps_c // c) ** 0.5))
         stride, pad, dil = _pair(node.attrs, "strides", 1), _pair(node.attrs, "pads", 0), _pair(node.attrs, "dilations", 1)
         geo = conv_geometry(n, h, width, c, k, m, stride, pad, dil)
         bias = self._constant(node.inputs[2]) if len(node.inputs) > 2 else None
@@ -194,7 +198,7 @@ class Executor:
                 relu, result, consumed = True, nxt.outputs[0], consumed + 1
         y = torch.empty((n, geo.out_h, geo.out_w, m), dtype=self.act_dtype, device=self.gpu.device)
         before = self.gpu.launches
-        self.gpu.convForward(x.contiguous(), w, y, geo, epilogue=Epilogue(bias, residual, relu, self.mode == "tf32"), math=self.math, w_rows=True)
+        self.gpu.convForward(x.contiguous(), w, y, geo, epilogue=Epilogue(bias, residual, relu, self.mode == "tf32"), math=self.math, w_rows=w_rows)
         self.stats.launches += self.gpu.launches - before
         values[result] = y
         self.stats.device_nodes += 3 + consumed
