@@ -292,6 +292,34 @@ __device__ __forceinline__ void stem_line_load(const GemmParams& p, const Gather
   }
   v[27] = 0;
 }
+// Two neighbouring positions of one output row share eight of their twelve window columns' values: one set of 36
+// loads (three rows of four pixels) serves both lines.
+__device__ __forceinline__ void stem_line_pair_load(const GemmParams& p, const GatherDesc& d, uint32_t position, uint32_t img, uint32_t oy,
+                                                    uint32_t ox, uint16_t (&va)[28], uint16_t (&vb)[28]) {
+  const ConvGeo& g = p.geo;
+  const int32_t y0 = (int32_t)oy - (int32_t)g.pad, x0 = (int32_t)ox - (int32_t)g.pad;
+  const bool valid_a = position < d.lines_total, valid_b = position + 1 < d.lines_total;
+  const int32_t row_pitch = (int32_t)(g.w * 3);
+  const uint16_t* corner = (const uint16_t*)d.base + (int64_t)img * g.h * row_pitch + (int64_t)y0 * row_pitch + (int64_t)x0 * 3;
+  bool col_in[4];
+#pragma unroll
+  for (uint32_t kx = 0; kx < 4; ++kx) col_in[kx] = x0 + (int32_t)kx >= 0 && x0 + (int32_t)kx < (int32_t)g.w;
+#pragma unroll
+  for (uint32_t ky = 0; ky < 3; ++ky) {
+    const bool row_in = valid_a && y0 + (int32_t)ky >= 0 && y0 + (int32_t)ky < (int32_t)g.h;
+    const uint16_t* row = corner + (int32_t)ky * row_pitch;
+    uint16_t w[12];
+#pragma unroll
+    for (uint32_t e = 0; e < 12; ++e) w[e] = (row_in && col_in[e / 3]) ? row[e] : (uint16_t)0;
+#pragma unroll
+    for (uint32_t e = 0; e < 9; ++e) {
+      va[ky * 9 + e] = w[e];
+      vb[ky * 9 + e] = valid_b ? w[e + 3] : (uint16_t)0;
+    }
+  }
+  va[27] = 0;
+  vb[27] = 0;
+}
 __device__ __forceinline__ void stem_line_store(uint8_t* tile, uint32_t l, const uint16_t (&v)[28]) {
   const uint32_t line = smem_u32(tile + l * kLineBytes), sw = l & 7;
 #pragma unroll
@@ -315,10 +343,19 @@ __device__ __forceinline__ void gather_tile(const GemmParams& p, const GatherDes
   const uint32_t epl = p.tf32 ? 32u : 64u;
   const uint64_t batch_off = (uint64_t)batch * d.batch_stride;
   if (k0 == 0 && batch_off == 0 && stem_line_applies(p, d)) {   // K = 27: the one K block of the stem
-    for (uint32_t l = tid; l < lines_in_tile; l += kGatherThreads) {
-      uint16_t v[28];
-      stem_line_load(p, d, mn0 + l, v);
-      stem_line_store(tile, l, v);
+    for (uint32_t l = 2 * tid; l < lines_in_tile; l += 2 * kGatherThreads) {   // lines l and l + 1
+      const uint32_t position = mn0 + l;
+      const uint32_t img = fast_div(position, p.walk.div_image), rem = position - img * p.walk.div_image.d;
+      const uint32_t oy = fast_div(rem, p.walk.div_w), ox = rem - oy * p.walk.div_w.d;
+      uint16_t va[28], vb[28];
+      if (ox + 1 < p.geo.out_w) {
+        stem_line_pair_load(p, d, position, img, oy, ox, va, vb);
+      } else {   // the second position starts the next row (or image): two windows of their own
+        stem_line_load(p, d, position, va);
+        stem_line_load(p, d, position + 1, vb);
+      }
+      stem_line_store(tile, l, va);
+      if (l + 1 < lines_in_tile) stem_line_store(tile, l + 1, vb);
     }
     return;
   }

@@ -844,7 +844,7 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     int rc = finish_plan(h, plan, true, min_bn, ep);
     if (rc != GB_OK) return rc;
     // A 3-channel 3x3 stride-1 layer over a bf16 map goes through the tensor kernel: its gather warps have a line builder
-    // for exactly that window (14.8 against 29.9 us at batch 128, 449 against 605 us at batch 4096 for the FMA kernel).
+    // for exactly that window (13.6 against 29.9 us at batch 128, 378 against 605 us at batch 4096 for the FMA kernel).
     const bool stem_lines = smem_bf16 && d->dtype_x == GB_BF16 && g.c == 3 && g.c_step == 3 && g.k == 3 && g.stride == 1 && g.dilation == 1 &&
                             !w_rows && !knobs().no_stem_lines;   // (a prepared filter row of 27 values is no TMA operand)
     if (plan.tensor && gb::conv_direct_applies(p) && !knobs().no_direct_conv && !p.stats && !affine && !stem_lines) {
