@@ -267,8 +267,8 @@ __device__ __forceinline__ void gather_line(const GemmParams& p, const GatherDes
 // the general routine every chunk of such a line straddles taps and goes element by element through the index arithmetic.)
 __device__ __forceinline__ bool stem_line_applies(const GemmParams& p, const GatherDesc& d) {
   const ConvGeo& g = p.geo;
-  return d.source == kSrcPatch && !d.mn_major && d.src_is_bf16 && !p.tf32 && g.c == 3 && g.c_step == 3 && g.k == 3 && g.stride == 1 &&
-         g.dilation == 1 && p.affine_scale == nullptr;
+  return d.source == kSrcPatch && d.src_is_bf16 && !p.tf32 && g.c == 3 && g.c_step == 3 && g.k == 3 && g.stride == 1 && g.dilation == 1 &&
+         p.affine_scale == nullptr;
 }
 // The loads of one line: 27 values (v[27] = 0 pads the last pair).  One pointer per window row, constant offsets within
 // it (the pixel pitch is 3), nine predicates; the position is split with the walk's precomputed divisors.
@@ -342,9 +342,19 @@ __device__ __forceinline__ void gather_tile(const GemmParams& p, const GatherDes
                                             uint32_t mn0, uint32_t k0, uint32_t batch, uint32_t tid) {
   const uint32_t epl = p.tf32 ? 32u : 64u;
   const uint64_t batch_off = (uint64_t)batch * d.batch_stride;
-  if (k0 == 0 && batch_off == 0 && stem_line_applies(p, d)) {   // K = 27: the one K block of the stem
-    for (uint32_t l = 2 * tid; l < lines_in_tile; l += 2 * kGatherThreads) {   // lines l and l + 1
-      const uint32_t position = mn0 + l;
+  // The stem: K-major (forward) its 27 values are the one K block of a position's line; MN-major (weight gradient) they
+  // are the first 27 of the tile's 128 rows, one line per position of the K block, and the lines of rows 64.. are zero.
+  if (batch_off == 0 && (d.mn_major ? mn0 == 0 : k0 == 0) && stem_line_applies(p, d)) {
+    const uint32_t first = d.mn_major ? k0 : mn0, windows = d.mn_major ? min(lines_in_tile, epl) : lines_in_tile;
+    if (windows <= kGatherThreads) {   // a line for every thread: sharing loads between neighbours would idle half of them
+      if (tid < windows) {
+        uint16_t v[28];
+        stem_line_load(p, d, first + tid, v);
+        stem_line_store(tile, tid, v);
+      }
+    } else
+    for (uint32_t l = 2 * tid; l < windows; l += 2 * kGatherThreads) {   // lines l and l + 1
+      const uint32_t position = first + l;
       const uint32_t img = fast_div(position, p.walk.div_image), rem = position - img * p.walk.div_image.d;
       const uint32_t oy = fast_div(rem, p.walk.div_w), ox = rem - oy * p.walk.div_w.d;
       uint16_t va[28], vb[28];
@@ -355,7 +365,12 @@ __device__ __forceinline__ void gather_tile(const GemmParams& p, const GatherDes
         stem_line_load(p, d, position + 1, vb);
       }
       stem_line_store(tile, l, va);
-      if (l + 1 < lines_in_tile) stem_line_store(tile, l + 1, vb);
+      if (l + 1 < windows) stem_line_store(tile, l + 1, vb);
+    }
+    for (uint32_t l = windows + tid; l < lines_in_tile; l += kGatherThreads) {
+      const uint32_t line = smem_u32(tile + l * kLineBytes);
+#pragma unroll
+      for (uint32_t chunk = 0; chunk < 8; ++chunk) sts128(line + (chunk << 4), make_uint4(0u, 0u, 0u, 0u));
     }
     return;
   }

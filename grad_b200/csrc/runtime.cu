@@ -965,12 +965,17 @@ int plan_conv(const gb_handle* h, int pass, const gb_conv_desc* d, const void* a
     set_output(p, out, d->dtype_w, g.w_step, 0, false, d->accumulate, nullptr);
     int rc = finish_plan(h, plan, true, min_bn, nullptr);
     if (rc != GB_OK) return rc;
-    if (plan.tensor && gb::conv_direct_wgrad_applies(p) && !knobs().no_direct_conv && !affine) {
+    // (the 3-channel bf16 stem: the tensor kernel's gather warps build its window lines, see the forward pass)
+    const bool stem_lines = smem_bf16 && d->dtype_x == GB_BF16 && g.c == 3 && g.c_step == 3 && g.k == 3 && g.stride == 1 && g.dilation == 1 &&
+                            !affine && !knobs().no_stem_lines;
+    if (plan.tensor && gb::conv_direct_wgrad_applies(p) && !knobs().no_direct_conv && !affine && !stem_lines) {
       plan.direct_wgrad_blocks = gb::conv_direct_wgrad_blocks(p, h->sm_count);
       plan.direct_wgrad_bytes = (size_t)plan.direct_wgrad_blocks * p.m * p.n * sizeof(float);
     }
     if (plan.tensor) {
       p.a_kind = gb::kGather;
+      p.walk.div_image = gb::make_fastdiv_host(g.out_h * g.out_w);   // the stem lines split a position with these
+      p.walk.div_w = gb::make_fastdiv_host(g.out_w);
       const bool view = g.k == 1 && g.pad == 0 && g.stride > 1 && !knobs().no_strided_tma;
       if (affine) {
         // as in the forward pass: TMA with NaN outside the image + the transform warps, else the gather warps
