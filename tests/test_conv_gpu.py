@@ -121,6 +121,19 @@ def test_resnet_layer_shapes(gpu, case, math, tol, half):
     _run_all(gpu, case, math, tol, bf16_storage=half, seed=200)
 
 
+# 3-channel 3x3 stride-1 layers over a bf16 map: the tensor kernel's gather warps build their window lines with a routine of
+# their own.  Odd widths make neighbouring positions straddle rows and images, the position count is no multiple of a
+# tile, padding 0 and 2 move the window's corner off the default.
+STEM_LIKE = [(3, 31, 29, 3, 3, 64, 1, 1, 1), (2, 9, 7, 3, 3, 32, 1, 0, 1), (1, 6, 6, 3, 3, 64, 1, 2, 1), (5, 8, 33, 3, 3, 128, 1, 1, 1)]
+
+
+@pytest.mark.parametrize("case", STEM_LIKE)
+def test_three_channel_window_lines_against_the_oracle(gpu, case):
+    _run_all(gpu, case, 2, TOL_BF16, bf16_storage=True, seed=300)
+    plan = gpu.last_plan()   # of the weight gradient, the last of the three passes
+    assert plan["tensor_path"] == 1 and plan["a_kind"] == 5, plan   # 5: the gathered operand of the tensor kernel
+
+
 def test_bf16_conv_agrees_with_f32_conv_within_reference_bounds(gpu):
     """tests/autograd.zig:1309-1359: 2x8x8x64 -> 32, pad 1; y, dX, dW element-wise bounds."""
     import torch
